@@ -1,0 +1,295 @@
+#!/usr/bin/env python
+"""Q8 decode throughput of the Llama-7B-shaped configuration on B200.
+
+One "step" = one greedy decode step (one new token per sequence) of the Q8 decoder
+through `deepj_cuda_flush_ops`, with the KV cache already holding the prompt.
+
+  value      tokens/s with the token fed back on the device (inputs resident in HBM),
+             timed with CUDA events on the library's stream.
+  e2e        tokens/s through the host-buffer call: every step uploads the token ids
+             from host memory, flushes synchronously and downloads the picked ids.
+  roofline   the Q8 GEMV kernel: algorithmic bytes of every GEMV launch of one step ÷
+             their summed device time (op-by-op CUDA-event profile of the same step).
+  cpu_baseline / --impl reference: the CPU oracle's KV-cached decode of the same
+             configuration on the host cores, on a bounded sample (see `sample`).
+
+Synthetic data: random-init weights of the named architecture (device-side
+counter-based generator, N(0,0.02)-like), uniform random prompt ids.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE configs[4]: Llama-7B shape, 2048-token prompts, 128 generated tokens
+    "llama7b_q8_decode_b1": dict(kind="llama", vocab=32000, d=4096, heads=32, layers=32, d_ff=11008, max_seq=2176,
+                                 prompt=2048, batch=1, seed=9, std=0.02),
+    "llama7b_q8_decode_b16": dict(kind="llama", vocab=32000, d=4096, heads=32, layers=32, d_ff=11008, max_seq=2176,
+                                  prompt=2048, batch=16, seed=9, std=0.02),
+    # BASELINE configs[2]: Llama-1B shape
+    "llama1b_q8_decode_b1": dict(kind="llama", vocab=32000, d=2048, heads=32, layers=22, d_ff=5632, max_seq=768,
+                                 prompt=512, batch=1, seed=3, std=0.02),
+    # BASELINE configs[3]: DeepSeek shape (qRank = dModel/2 assumed)
+    "deepseek_q8_decode_b1": dict(kind="deepseek", vocab=32000, d=2048, heads=16, layers=16, d_ff=5632, max_seq=1280,
+                                  prompt=1024, batch=1, seed=5, std=0.02, q_rank=1024, kv_rank=512),
+    # BASELINE configs[0]: tiny Llama (latency-bound; no roofline claim)
+    "tiny_llama_q8_decode_b1": dict(kind="llama", vocab=256, d=256, heads=8, layers=4, d_ff=688, max_seq=256,
+                                    prompt=32, batch=1, seed=42, std=0.1),
+}
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        sm, smax, reasons = [], [], set()
+        for line in self.tmp.read().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.tmp.name)
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(smax)), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_decode_sample(w, threads: int):
+    """CPU oracle, KV-cached decode of workload `w`: time one block + the LM head at a
+    short context and extrapolate to the full depth.  Returns (tok/s, description)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle
+    oracle.lib().oracle_set_threads(threads)
+    used = oracle.lib().oracle_get_threads()
+    built = 1
+    om = oracle.OracleModel(w["kind"], w["vocab"], 8, w["d"], w["heads"], w["layers"], w["d_ff"],
+                            w.get("q_rank", 0), w.get("kv_rank", 0), seed=w["seed"], init_mode=1, std=w["std"],
+                            layers_built=built)
+    rng = np.random.default_rng(w["seed"] + 1000)
+    toks = rng.integers(0, w["vocab"], size=8)
+    om.reset_cache()
+    om.decode_step(int(toks[0]))                     # warm the pages
+    t0 = time.perf_counter()
+    n = 3
+    for i in range(n):
+        om.decode_step(int(toks[1 + i]))
+    t_layer_head = (time.perf_counter() - t0) / n
+    x = rng.standard_normal((1, w["d"])).astype(np.float32)
+    Wlm = om.weight("Wlm").reshape(w["d"], w["vocab"])
+    oracle.matmul(x, Wlm)
+    t0 = time.perf_counter()
+    for i in range(n):
+        oracle.matmul(x, Wlm)
+    t_head = (time.perf_counter() - t0) / n
+    t_layer = max(t_layer_head - t_head, 1e-9)
+    t_token = t_layer * w["layers"] + t_head
+    sample = (f"C++ restatement of CpuBackend, KV-cached decode, fp32 weights: {n} steps of {built} of {w['layers']} blocks "
+              f"+ LM head at context <= 4, extrapolated x{w['layers']} blocks (block {t_layer * 1e3:.1f} ms, head {t_head * 1e3:.1f} ms); "
+              f"batch 1; the reference itself re-forwards the whole context per token and is slower still")
+    return 1.0 / t_token, used, sample
+
+
+def run_reference(args, w, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = max(1, (os.cpu_count() or 2) - 1)      # DeepJExecutor default: cores - 1
+    t0 = time.perf_counter()
+    vals = []
+    used, sample = threads, ""
+    for _ in range(max(1, min(args.steps, 2))):
+        v, used, sample = cpu_decode_sample(w, threads)
+        vals.append(v)
+    v = float(np.median(vals)) * w["batch"] / w["batch"]
+    line = {
+        "impl": "reference", "metric": "q8_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "parallelism": "cpu"},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": used, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama7b_q8_decode_b1", choices=sorted(WORKLOADS))
+    ap.add_argument("--prompt-len", type=int, default=0, help="override the prompt length (debugging)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+    if args.prompt_len > 0:
+        w["prompt"] = args.prompt_len
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args, w, args.workload)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if args.gpus == 1 and world == 1:
+            pass
+        else:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    if world > 1:
+        raise SystemExit("tensor-parallel decode is not wired into bench.py yet")
+
+    from deepj_b200.decoder import DecoderConfig, Q8Decoder
+
+    cfg = DecoderConfig(w["kind"], w["vocab"], w["max_seq"], w["d"], w["heads"], w["layers"], w["d_ff"],
+                        w.get("q_rank", 0), w.get("kv_rank", 0))
+    B = w["batch"]
+    if w["prompt"] + args.warmup + 2 * args.steps + 2 > w["max_seq"]:
+        raise SystemExit("steps + warmup do not fit the context window of this workload")
+    dec = Q8Decoder(cfg, batch=B, device=local_rank)
+    t_load = time.perf_counter()
+    dec.load_synthetic(w["seed"], w["std"])
+    rng = np.random.default_rng(w["seed"] + 1000)
+    prompts = rng.integers(0, w["vocab"], size=(B, w["prompt"]))
+    dec.reset()
+    nxt = dec.prefill(prompts)
+    t_load = time.perf_counter() - t_load
+
+    lib = dec.lib
+    from deepj_b200 import _lib
+    import ctypes
+
+    # ── device-resident loop (value) ──
+    dec.set_tokens(nxt)
+    dec.step_device(args.warmup)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    _lib.check(lib.deepj_cuda_synchronize())
+    st0 = dec.stats()
+    _lib.check(lib.deepj_cuda_timer_begin())
+    dec.step_device(args.steps, sync=False)
+    ms = ctypes.c_float(0)
+    _lib.check(lib.deepj_cuda_timer_end(ctypes.byref(ms)))
+    _lib.check(lib.deepj_cuda_synchronize())
+    clocks = sampler.stop()
+    st1 = dec.stats()
+    ms_per_step = ms.value / args.steps
+    value = B * 1e3 / ms_per_step
+    launches = (st1["graph_replays"] - st0["graph_replays"]) * st1["kernels_per_replay"] + (st1["eager_launches"] - st0["eager_launches"])
+
+    # ── host-buffer loop (e2e) ──
+    tok = dec.next_tokens()
+    for _ in range(3):
+        tok = dec.step(tok)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok = dec.step(tok)
+    e2e_s = time.perf_counter() - t0
+    e2e = B * args.steps / e2e_s
+
+    # ── the GEMV kernel against the HBM roofline ──
+    peak, peak_kind = measured_peak_gbs()
+    prof = dec.profile_step()
+    prof = dec.profile_step()
+    shapes = {n: (k, n_) for n, k, n_ in cfg.matmul_shapes()}
+
+    def q8b(k, n):
+        return k * n + ((k + 31) // 32) * n * 4
+    d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
+    op_bytes = {"qkv": q8b(d, 3 * d) + 4 * B * (d + 3 * d), "wo": q8b(d, d) + 4 * B * 3 * d,
+                "swiglu": 2 * q8b(d, F) + 4 * B * (d + F), "down": q8b(F, d) + 4 * B * (F + 2 * d),
+                "lm_head": q8b(d, V) + 4 * B * (d + V)}
+    if cfg.kind == "deepseek":
+        r = cfg.q_rank + cfg.kv_rank
+        op_bytes.update({"mla_down": q8b(d, r) + 4 * B * (d + r), "mla_up_q": q8b(cfg.q_rank, d) + 4 * B * (cfg.q_rank + d),
+                         "mla_up_kv": q8b(cfg.kv_rank, 2 * d) + 4 * B * (cfg.kv_rank + 2 * d)})
+    gemv_ms = sum(t for lbl, t in prof if lbl in op_bytes)
+    gemv_bytes = sum(op_bytes[lbl] for lbl, _ in prof if lbl in op_bytes)
+    n_gemv = sum(1 for lbl, _ in prof if lbl in op_bytes)
+    attn_ms = sum(t for lbl, t in prof if lbl == "attn")
+    total_prof_ms = sum(t for _, t in prof)
+    achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9
+    ctx = dec.position
+    step_bytes = cfg.q8_weight_bytes() + B * ctx * cfg.kv_bytes_per_position()
+    step_achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    line = {
+        "metric": "q8_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "q8 weights, f32 activations/accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "batch": B, "prompt_len": w["prompt"], "context_at_timing": ctx,
+                   "parallelism": "tp1", "kv_cache": "f32", "l2": "weights+KV per step exceed L2 (inputs larger than L2)"},
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "k_q8_gemv", "launches_per_step": n_gemv,
+                     "bytes_per_step": gemv_bytes, "ms_per_step_op_by_op": gemv_ms},
+        "roofline_step": {"bytes_per_token": step_bytes, "achieved": step_achieved, "frac": step_achieved / peak,
+                          "roofline_tokens_per_s": B * peak * 1e9 / step_bytes},
+        "profile_ms": {"gemv": gemv_ms, "attention": attn_ms, "all_ops": total_prof_ms},
+        "setup_s": t_load,
+    }
+    if not args.no_cpu_baseline and rank == 0:
+        v, used, sample = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))
+        line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": used, "kind": "port", "sample": sample}
+    print(json.dumps(line), flush=True)
+    dec.close()
+
+
+if __name__ == "__main__":
+    main()

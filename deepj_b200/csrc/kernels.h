@@ -1,0 +1,111 @@
+// Launcher declarations shared by the runtime (runtime.cu) and the kernel files.
+// Every launcher enqueues on the given stream and never synchronises.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#define DJ_CUDA_CHECK(expr)                                                                  \
+    do {                                                                                     \
+        cudaError_t _e = (expr);                                                             \
+        if (_e != cudaSuccess)                                                               \
+            throw std::runtime_error(std::string("CUDA error: ") + cudaGetErrorString(_e) + \
+                                     " at " + __FILE__ + ":" + std::to_string(__LINE__));   \
+    } while (0)
+
+namespace dj {
+
+// Counts kernel launches issued by this library (eager path and capture).
+extern long long g_launches;
+extern int g_num_sms;
+// When true, launchers attach the programmatic-dependent-launch attribute so that
+// a kernel's weight prefetch overlaps the tail of its predecessor.
+extern bool g_use_pdl;
+
+// A Q8 weight as laid out in HBM: codes[N][Kp] int8 (Kp = K rounded up to 16, zero
+// padded) followed by scales[N][nb] fp32, nb = ceil(K/32).
+struct Q8View {
+    const int8_t* codes;
+    const float* scales;
+    int K, N, Kp, nb;
+};
+
+// ── base ops (ComputeGraph op codes 1-42) ──
+void launch_binary(int op, const float* a, const float* b, float* out, int n, cudaStream_t s);
+void launch_unary(int op, const float* in, float* out, int n, cudaStream_t s);
+void launch_scalar(int op, const float* in, float* out, float v, int n, cudaStream_t s);
+void launch_clamp(const float* in, float* out, float lo, float hi, int n, cudaStream_t s);
+void launch_matmul_f32(const float* a, const float* b, float* out, int m, int n, int k, cudaStream_t s);
+void launch_transpose(const float* in, float* out, int rows, int cols, cudaStream_t s);
+void launch_row_broadcast(int op, const float* a, const float* v, float* out, int rows, int cols, cudaStream_t s);
+void launch_col_broadcast(int op, const float* a, const float* v, float* out, int rows, int cols, cudaStream_t s);
+void launch_row_reduce(int op, const float* in, float* out, int rows, int cols, cudaStream_t s);
+void launch_sum_rows(const float* in, float* out, int rows, int cols, cudaStream_t s);
+void launch_sum_scalar(const float* in, float* out, long long n, cudaStream_t s);
+void launch_softmax_rows(const float* in, float* out, int rows, int cols, cudaStream_t s);
+void launch_softmax_backward(const float* g, const float* sm, float* out, int rows, int cols, cudaStream_t s);
+void launch_layernorm_backward(const float* dxh, const float* xh, const float* sd, float* out, int rows, int cols, cudaStream_t s);
+void launch_adamw(float* w, const float* g, float* mt, float* vt, float lr, float b1, float b2, float eps,
+                  float wd, float bc1, float bc2, int n, cudaStream_t s);
+void launch_scatter_add_rows(float* target, const float* idx, const float* grad, int tRows, int tCols, int nIdx, cudaStream_t s);
+void launch_ce_loss(const float* logits, const float* targets, float* out, int rows, int cols, cudaStream_t s);
+void launch_ce_grad(const float* logits, const float* targets, float* out, int rows, int cols, cudaStream_t s);
+
+// ── Q8 ──
+void launch_q8_quantize(const float* src, int src_ld, int K, int n_cols, int8_t* codes, float* scales,
+                        int Kp, int nb, cudaStream_t s);
+struct Q8LinearArgs {
+    const float* x; int ldx;            // activations [M × K], row stride ldx
+    const float* gamma; float eps;      // RMSNorm fused into the activation load when gamma != nullptr
+    Q8View w;                           // plain linear / SwiGLU gate
+    const float* bias;
+    Q8View w2;                          // SwiGLU up projection (codes == nullptr → plain linear)
+    const float* bias2;
+    const float* residual; int ldr;
+    float* out; int ldo;
+    int M;
+};
+void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s);
+
+// ── decode attention ──
+struct AttnDecodeArgs {
+    float* qkv; int q_off, k_off, v_off, ld;   // current token's projections, one row per sequence
+    float* kcache; float* vcache;              // this layer's planes [B][H][maxSeq][hd]
+    int maxSeq;
+    const float* pos;                          // [B] floats holding the write position
+    const float* cosT; const float* sinT;      // [maxSeq × hd/2]
+    float* out; int ldo;                       // merged heads [B × H·hd]
+    int B, H, hd;
+    float scale;
+    float* ws;                                 // split partials: [B][H][splits][hd + 2]
+    int splits;
+};
+size_t attn_decode_ws_floats(int B, int H, int hd, int splits);
+int attn_decode_splits(int B, int H, int maxSeq);
+void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s);
+
+// ── misc ──
+void launch_embed_gather(const float* table, const float* ids, float* out, int rows, int d, int vocab, cudaStream_t s);
+void launch_argmax_rows(const float* in, float* out, int rows, int cols, cudaStream_t s);
+void launch_add_scalar_inplace(float* buf, float v, int n, cudaStream_t s);
+void launch_copy(const float* src, float* dst, long long n, cudaStream_t s);
+void launch_synth_fill(float* out, unsigned long long seed, unsigned long long ordinal, float std_dev,
+                       long long first, long long n, cudaStream_t s);
+
+// Launch helper: plain <<<>>> or cudaLaunchKernelEx with the PDL attribute.
+template <typename... KArgs, typename... Args>
+inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, Args... args) {
+    g_launches++;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    if (pdl && g_use_pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    DJ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+}
+
+}  // namespace dj

@@ -1,0 +1,136 @@
+// Small decode-path kernels: embedding row gather, greedy argmax, position advance,
+// device copy, and the counter-based synthetic weight generator.
+#include "kernels.h"
+
+namespace dj {
+
+namespace {
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Embedding.forward → Tensor.sliceRows (transformer/embeddings/Embedding.java:28-34):
+// out[r] = table[ids[r]].  The reference throws on an out-of-range id before any
+// work; the runtime cannot see device-resident ids, so such a row is filled with NaN.
+__global__ void k_embed_gather(const float* __restrict__ table, const float* __restrict__ ids, float* __restrict__ out,
+                               int rows, int d, int vocab) {
+    pdl_wait();
+    pdl_launch_dependents();
+    int r = blockIdx.x;
+    int id = (int)ids[r];
+    bool ok = id >= 0 && id < vocab;
+    for (int c = threadIdx.x; c < d; c += blockDim.x)
+        out[(size_t)r * d + c] = ok ? table[(size_t)id * d + c] : NAN;
+}
+
+// Total order of Float.compare (models/TextGenerator.java:163-170): -0.0 < +0.0,
+// NaN above +inf.  Map the bits to a signed key with the same order.
+__device__ __forceinline__ int order_key(float v) {
+    int b = (v != v) ? 0x7fc00000 : __float_as_int(v);
+    return b ^ ((b >> 31) & 0x7fffffff);
+}
+
+// Greedy pick: the first index of the largest value (a stable descending sort
+// keeps the lowest index among equals).  One CTA per row.
+__global__ void k_argmax_rows(const float* __restrict__ in, float* __restrict__ out, int rows, int cols) {
+    __shared__ int s_key[32];
+    __shared__ int s_idx[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    int r = blockIdx.x;
+    const float* d = in + (size_t)r * cols;
+    int bestKey = INT_MIN, bestIdx = INT_MAX;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        int k = order_key(d[c]);
+        if (k > bestKey || (k == bestKey && c < bestIdx)) { bestKey = k; bestIdx = c; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        int k2 = __shfl_xor_sync(0xffffffffu, bestKey, o), i2 = __shfl_xor_sync(0xffffffffu, bestIdx, o);
+        if (k2 > bestKey || (k2 == bestKey && i2 < bestIdx)) { bestKey = k2; bestIdx = i2; }
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) { s_key[warp] = bestKey; s_idx[warp] = bestIdx; }
+    __syncthreads();
+    if (warp == 0) {
+        bestKey = lane < nw ? s_key[lane] : INT_MIN;
+        bestIdx = lane < nw ? s_idx[lane] : INT_MAX;
+        for (int o = 16; o > 0; o >>= 1) {
+            int k2 = __shfl_xor_sync(0xffffffffu, bestKey, o), i2 = __shfl_xor_sync(0xffffffffu, bestIdx, o);
+            if (k2 > bestKey || (k2 == bestKey && i2 < bestIdx)) { bestKey = k2; bestIdx = i2; }
+        }
+        if (lane == 0) out[r] = (float)bestIdx;
+    }
+}
+
+__global__ void k_add_scalar_inplace(float* __restrict__ buf, float v, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) buf[i] = buf[i] + v;
+}
+
+__global__ void k_copy(const float* __restrict__ src, float* __restrict__ dst, long long n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+// Integer-exact generator: two splitmix64 outputs give eight 16-bit uniform fields;
+// their centred sum (Irwin–Hall) times one float constant.  Same bits on any device.
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ULL;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+    return z ^ (z >> 31);
+}
+__global__ void k_synth_fill(float* __restrict__ out, unsigned long long key, float scale, long long first, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        unsigned long long idx = (unsigned long long)(first + i);
+        unsigned long long a = splitmix64(key + 2 * idx), b = splitmix64(key + 2 * idx + 1);
+        int s = 0;
+#pragma unroll
+        for (int f = 0; f < 4; f++) { s += (int)((a >> (16 * f)) & 0xFFFF); s += (int)((b >> (16 * f)) & 0xFFFF); }
+        int centred = 2 * s - 8 * 65535;
+        out[i] = __fmul_rn((float)centred, scale);
+    }
+}
+
+unsigned long long h_splitmix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ULL;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+    return z ^ (z >> 31);
+}
+
+}  // namespace
+
+void launch_embed_gather(const float* table, const float* ids, float* out, int rows, int d, int vocab, cudaStream_t s) {
+    if (rows <= 0) return;
+    launch_k(k_embed_gather, dim3(rows), dim3(256), 0, s, true, table, ids, out, rows, d, vocab);
+}
+void launch_argmax_rows(const float* in, float* out, int rows, int cols, cudaStream_t s) {
+    if (rows <= 0) return;
+    launch_k(k_argmax_rows, dim3(rows), dim3(1024), 0, s, true, in, out, rows, cols);
+}
+void launch_add_scalar_inplace(float* buf, float v, int n, cudaStream_t s) {
+    if (n <= 0) return;
+    launch_k(k_add_scalar_inplace, dim3((n + 127) / 128), dim3(128), 0, s, true, buf, v, n);
+}
+void launch_copy(const float* src, float* dst, long long n, cudaStream_t s) {
+    if (n <= 0) return;
+    long long g = (n + 255) / 256;
+    if (g > (long long)g_num_sms * 8) g = (long long)g_num_sms * 8;
+    launch_k(k_copy, dim3((unsigned)g), dim3(256), 0, s, true, src, dst, n);
+}
+void launch_synth_fill(float* out, unsigned long long seed, unsigned long long ordinal, float std_dev,
+                       long long first, long long n, cudaStream_t s) {
+    if (n <= 0) return;
+    unsigned long long key = h_splitmix64(seed ^ (ordinal * 0xD1342543DE82EF95ULL));
+    double sd = 2.0 * sqrt(8.0 * (65536.0 * 65536.0 - 1.0) / 12.0);
+    float scale = (float)((double)std_dev / sd);
+    long long g = (n + 255) / 256;
+    if (g > (long long)g_num_sms * 16) g = (long long)g_num_sms * 16;
+    launch_k(k_synth_fill, dim3((unsigned)g), dim3(256), 0, s, false, out, key, scale, first, n);
+}
+
+}  // namespace dj

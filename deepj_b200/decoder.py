@@ -1,0 +1,420 @@
+"""Q8 decoder runner: DeepJ's LlamaModel / DeepSeekModel forward for ONE new token per
+sequence, recorded as a ComputeGraph command stream of fused decode ops and replayed
+through `deepj_cuda_flush_ops` (one flush per token; the library turns the repeated
+stream into a CUDA graph).
+
+What the stream computes, per token, is the last row of the reference's
+`DecoderOnlyModel.forward` (models/DecoderOnlyModel.java:58-64): embedding row →
+per block `x2 = x + attn(rmsnorm(x)); x = x2 + swiglu(rmsnorm(x2))`
+(layers/transformer/blocks/LlamaTransformerBlock.java:50-53,
+DeepSeekTransformerBlock.java:54-57) → final RMSNorm → LM head, then the greedy pick
+of models/TextGenerator.java (topK = 1).  K and V of earlier positions come from a
+cache in HBM instead of being recomputed.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional
+
+import numpy as np
+
+from . import _lib
+from .compute_graph import (OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_COPY, OP_EMBED_GATHER,
+                            OP_Q8_LINEAR, OP_Q8_SWIGLU, float_bits)
+
+RMS_EPS = 1e-6      # layers/transformer/norm/RMSNorm1D.java:30
+
+
+@dataclass(frozen=True)
+class DecoderConfig:
+    """Field-for-field the reference's LlamaConfig / DeepSeekConfig records
+    (models/llama/LlamaConfig.java:10-22, models/deepseek/DeepSeekConfig.java)."""
+    kind: str            # "llama" | "deepseek"
+    vocab_size: int
+    max_seq_len: int
+    d_model: int
+    n_heads: int
+    n_layers: int
+    d_ff: int
+    q_rank: int = 0
+    kv_rank: int = 0
+
+    def __post_init__(self):
+        # models/TransformerConfig.java:19-31
+        if self.kind not in ("llama", "deepseek"):
+            raise ValueError("kind must be 'llama' or 'deepseek'")
+        for name in ("vocab_size", "max_seq_len", "d_model", "n_heads", "n_layers", "d_ff"):
+            if getattr(self, name) <= 0:
+                raise ValueError(f"{name} must be > 0")
+        if self.d_model % self.n_heads != 0:
+            raise ValueError("dModel must be divisible by nHeads")
+        if (self.d_model // self.n_heads) % 2 != 0:
+            raise ValueError("headDim must be a positive even number")
+        if self.kind == "deepseek" and (self.q_rank <= 0 or self.kv_rank <= 0):
+            raise ValueError("qRank and kvRank must be > 0")
+
+    @property
+    def head_dim(self) -> int:
+        return self.d_model // self.n_heads
+
+    def matmul_shapes(self) -> List[tuple]:
+        """(name, K, N) of the matmul weights of one block, in the reference's
+        construction order (MultiHeadSelfAttention.java:47-50,
+        MultiHeadLatentAttention.java:82-87, SwiGLULayer.java:56-58)."""
+        d, f = self.d_model, self.d_ff
+        if self.kind == "llama":
+            attn = [("Wq", d, d), ("Wk", d, d), ("Wv", d, d), ("Wo", d, d)]
+        else:
+            attn = [("Wdq", d, self.q_rank), ("Wuq", self.q_rank, d), ("Wdkv", d, self.kv_rank),
+                    ("Wuk", self.kv_rank, d), ("Wuv", self.kv_rank, d), ("Wo", d, d)]
+        return attn + [("Wg", d, f), ("Wu", d, f), ("Wd", f, d)]
+
+    def q8_weight_bytes(self) -> int:
+        """Q8 bytes of every matmul weight streamed for one token (codes + scales)."""
+        def q8(k, n):
+            return k * n + ((k + 31) // 32) * n * 4
+        per_layer = sum(q8(k, n) for _, k, n in self.matmul_shapes())
+        return per_layer * self.n_layers + q8(self.d_model, self.vocab_size)
+
+    def kv_bytes_per_position(self) -> int:
+        """fp32 K and V rows of one cached position, all layers."""
+        return 2 * self.n_layers * self.d_model * 4
+
+
+def rope_tables(head_dim: int, max_seq: int):
+    """cos/sin tables with the reference's exact expression order
+    (transformer/embeddings/RotaryEmbedding.java:52-71): float exponent, double pow,
+    float theta, double cos/sin rounded to float."""
+    if head_dim <= 0 or head_dim % 2 != 0:
+        raise ValueError(f"headDim must be a positive even number, got {head_dim}")
+    if max_seq <= 0:
+        raise ValueError("maxSeqLen must be > 0")
+    half = head_dim // 2
+    f32 = np.float32
+    inv = [math.pow(float(f32(10000.0)), float(f32(f32(2.0) * f32(i)) / f32(head_dim))) for i in range(half)]
+    cos = np.empty((max_seq, half), dtype=np.float32)
+    sin = np.empty((max_seq, half), dtype=np.float32)
+    for pos in range(max_seq):
+        for i in range(half):
+            theta = float(f32(pos / inv[i]))
+            cos[pos, i] = math.cos(theta)
+            sin[pos, i] = math.sin(theta)
+    return cos, sin
+
+
+class Q8Decoder:
+    """Owns the device-side weights, KV cache and the per-token command stream.
+
+    Buffer ids are taken from `id_base` upwards so they never collide with the ids a
+    `ComputeGraph` hands out (those start at 0).
+    """
+
+    def __init__(self, cfg: DecoderConfig, batch: int = 1, device: int = 0, id_base: int = 1 << 24):
+        self.cfg = cfg
+        self.B = int(batch)
+        self.lib = _lib.load()
+        _lib.check(self.lib.deepj_cuda_init(device))
+        self._next_id = id_base
+        self._owned: List[int] = []
+        self.ids: Dict[str, int] = {}
+        self.loaded = False
+        self._stream_host: Optional[np.ndarray] = None
+        self._stream_dev: Optional[np.ndarray] = None
+        self._op_labels: List[str] = []
+        self.position = 0
+        self._alloc_state()
+
+    # ── id / buffer helpers ──
+    def _new_id(self) -> int:
+        i = self._next_id
+        self._next_id += 1
+        self._owned.append(i)
+        return i
+
+    def _f32(self, name: str, n: int, data: Optional[np.ndarray] = None) -> int:
+        i = self._new_id()
+        ids = (ctypes.c_int32 * 1)(i)
+        sizes = (ctypes.c_int32 * 1)(n)
+        _lib.check(self.lib.deepj_cuda_alloc_buffers(ids, sizes, 1))
+        if data is not None:
+            self._upload(i, data)
+        if name:
+            self.ids[name] = i
+        return i
+
+    def _upload(self, buf_id: int, data: np.ndarray) -> None:
+        data = np.ascontiguousarray(data, dtype=np.float32)
+        _lib.check(self.lib.deepj_cuda_upload_buffer(buf_id, data.ctypes.data, data.size))
+
+    def _download(self, buf_id: int, n: int) -> np.ndarray:
+        out = np.empty(n, dtype=np.float32)
+        _lib.check(self.lib.deepj_cuda_download_buffer(buf_id, out.ctypes.data, n))
+        return out
+
+    def _release(self, ids: List[int]) -> None:
+        arr = (ctypes.c_int32 * len(ids))(*ids)
+        _lib.check(self.lib.deepj_cuda_release_buffers(arr, len(ids)))
+        for i in ids:
+            if i in self._owned:
+                self._owned.remove(i)
+
+    def _alloc_state(self) -> None:
+        c, B = self.cfg, self.B
+        d = c.d_model
+        cos, sin = rope_tables(c.head_dim, c.max_seq_len)
+        self._f32("cos", cos.size, cos)
+        self._f32("sin", sin.size, sin)
+        self._f32("tok", B)              # current token ids (floats holding ints)
+        self._f32("pos", B)              # write position of every sequence
+        self._f32("x", B * d)
+        self._f32("x2", B * d)
+        self._f32("qkv", B * 3 * d)
+        self._f32("att", B * d)
+        self._f32("h", B * c.d_ff)
+        self._f32("logits", B * c.vocab_size)
+        self._f32("next", B)
+        if c.kind == "deepseek":
+            self._f32("lat", B * (c.q_rank + c.kv_rank))
+        kv = self._new_id()
+        _lib.check(self.lib.deepj_cuda_kv_alloc(kv, c.n_layers, B, c.n_heads, c.max_seq_len, c.head_dim))
+        self.ids["kv"] = kv
+
+    # ── weights ──
+    def _q8_from_parts(self, name: str, K: int, parts: List[Callable[[int], None]], widths: List[int]) -> None:
+        """Allocate a Q8 object [K × ΣN] and quantize each part into its column range.
+        `parts[i](tmp_id)` must fill the float buffer tmp_id with the [K × widths[i]] matrix."""
+        q = self._new_id()
+        _lib.check(self.lib.deepj_cuda_q8_alloc(q, K, sum(widths)))
+        col = 0
+        for fill, n in zip(parts, widths):
+            tmp = self._f32("", K * n)
+            fill(tmp)
+            _lib.check(self.lib.deepj_cuda_q8_quantize_into(q, col, tmp, 0, 0, n, n))
+            self._release([tmp])
+            col += n
+        self.ids[name] = q
+
+    def _layer_plan(self) -> List[tuple]:
+        """(device object name, K, [reference weight names concatenated along N])."""
+        c = self.cfg
+        d = c.d_model
+        if c.kind == "llama":
+            plan = [("Wqkv", d, ["Wq", "Wk", "Wv"]), ("Wo", d, ["Wo"])]
+        else:
+            plan = [("Wdqkv", d, ["Wdq", "Wdkv"]), ("Wuq", c.q_rank, ["Wuq"]), ("Wukv", c.kv_rank, ["Wuk", "Wuv"]),
+                    ("Wo", d, ["Wo"])]
+        return plan + [("Wg", d, ["Wg"]), ("Wu", d, ["Wu"]), ("Wd", c.d_ff, ["Wd"])]
+
+    def load_weights(self, get: Callable[[str, int], np.ndarray]) -> None:
+        """Upload fp32 weights and quantize them on the device.
+
+        `get(name, layer)` returns the reference tensor as a numpy array: matmul
+        weights as [dIn × dOut] (layers/Linear.java:26), vectors 1-D.  Names: "emb",
+        per layer "g1","g2", the block's matmul names (`DecoderConfig.matmul_shapes`),
+        "bg","bu","bd"; then "gF","Wlm","blm" (layer = -1 for model-level tensors).
+        """
+        c = self.cfg
+        shapes = {n: (k, w) for n, k, w in c.matmul_shapes()}
+        self._f32("emb", c.vocab_size * c.d_model, get("emb", -1))
+        for l in range(c.n_layers):
+            self._f32(f"g1.{l}", c.d_model, get("g1", l))
+            self._f32(f"g2.{l}", c.d_model, get("g2", l))
+            for obj, K, names in self._layer_plan():
+                fills = [(lambda tmp, nm=nm: self._upload(tmp, get(nm, l))) for nm in names]
+                self._q8_from_parts(f"{obj}.{l}", K, fills, [shapes[nm][1] for nm in names])
+            self._f32(f"bg.{l}", c.d_ff, get("bg", l))
+            self._f32(f"bu.{l}", c.d_ff, get("bu", l))
+            self._f32(f"bd.{l}", c.d_model, get("bd", l))
+        self._f32("gF", c.d_model, get("gF", -1))
+        self._q8_from_parts("Wlm", c.d_model, [lambda tmp: self._upload(tmp, get("Wlm", -1))], [c.vocab_size])
+        self._f32("blm", c.vocab_size, get("blm", -1))
+        self.loaded = True
+
+    def load_synthetic(self, seed: int, std: float) -> None:
+        """Random-init weights of this architecture generated on the device with the
+        library's counter-based generator; one ordinal per matrix in the reference's
+        construction order (embedding, then every block's matrices, then the LM
+        head).  Norm gains are ones and biases zeros, as the reference initialises them."""
+        c = self.cfg
+        per_layer = c.matmul_shapes()
+        ordinal_of = {}
+        for l in range(c.n_layers):
+            for j, (nm, _, _) in enumerate(per_layer):
+                ordinal_of[(nm, l)] = 1 + l * len(per_layer) + j
+        lm_ordinal = 1 + c.n_layers * len(per_layer)
+        shapes = {n: (k, w) for n, k, w in per_layer}
+
+        def synth(ordinal, n):
+            def fill(tmp):
+                _lib.check(self.lib.deepj_cuda_synth_fill(tmp, seed, ordinal, std, 0, n))
+            return fill
+
+        emb = self._f32("emb", c.vocab_size * c.d_model)
+        _lib.check(self.lib.deepj_cuda_synth_fill(emb, seed, 0, std, 0, c.vocab_size * c.d_model))
+        ones = np.ones(c.d_model, dtype=np.float32)
+        for l in range(c.n_layers):
+            self._f32(f"g1.{l}", c.d_model, ones)
+            self._f32(f"g2.{l}", c.d_model, ones)
+            for obj, K, names in self._layer_plan():
+                fills = [synth(ordinal_of[(nm, l)], K * shapes[nm][1]) for nm in names]
+                self._q8_from_parts(f"{obj}.{l}", K, fills, [shapes[nm][1] for nm in names])
+            self._f32(f"bg.{l}", c.d_ff)
+            self._f32(f"bu.{l}", c.d_ff)
+            self._f32(f"bd.{l}", c.d_model)
+        self._f32("gF", c.d_model, ones)
+        self._q8_from_parts("Wlm", c.d_model, [synth(lm_ordinal, c.d_model * c.vocab_size)], [c.vocab_size])
+        self._f32("blm", c.vocab_size)
+        self.loaded = True
+
+    def q8_arrays(self, name: str):
+        """Canonical (codes[N][K] int8, scales[N][ceil(K/32)] fp32) of a device Q8 object."""
+        c = self.cfg
+        K = {o: k for o, k, _ in self._layer_plan()}.get(name.split(".")[0], c.d_model)
+        shapes = {n: w for n, _, w in c.matmul_shapes()}
+        widths = {o: sum(shapes[n] for n in names) for o, _, names in self._layer_plan()}
+        N = widths.get(name.split(".")[0], c.vocab_size)
+        codes = np.empty((N, K), dtype=np.int8)
+        scales = np.empty((N, (K + 31) // 32), dtype=np.float32)
+        _lib.check(self.lib.deepj_cuda_q8_download(self.ids[name], codes.ctypes.data, scales.ctypes.data))
+        return codes, scales
+
+    # ── the per-token stream ──
+    def _build(self, feed_back: bool) -> np.ndarray:
+        c, B, I = self.cfg, self.B, self.ids
+        d, F, V = c.d_model, c.d_ff, c.vocab_size
+        eps = float_bits(RMS_EPS)
+        s: List[int] = []
+        labels: List[str] = []
+
+        def op(label, *ints):
+            s.extend(int(v) for v in ints)
+            labels.append(label)
+
+        def linear(label, x, x_off, ldx, gamma, w, bias, res, res_off, ldr, out, out_off, ldo):
+            op(label, OP_Q8_LINEAR, x, x_off, ldx, gamma, eps, w, bias, res, res_off, ldr, out, out_off, ldo, B)
+
+        op("embed", OP_EMBED_GATHER, I["emb"], I["tok"], I["x"], B, d, V)
+        for l in range(c.n_layers):
+            if c.kind == "llama":
+                linear("qkv", I["x"], 0, d, I[f"g1.{l}"], I[f"Wqkv.{l}"], -1, -1, 0, 0, I["qkv"], 0, 3 * d)
+            else:
+                r = c.q_rank + c.kv_rank
+                linear("mla_down", I["x"], 0, d, I[f"g1.{l}"], I[f"Wdqkv.{l}"], -1, -1, 0, 0, I["lat"], 0, r)
+                linear("mla_up_q", I["lat"], 0, r, -1, I[f"Wuq.{l}"], -1, -1, 0, 0, I["qkv"], 0, 3 * d)
+                linear("mla_up_kv", I["lat"], c.q_rank, r, -1, I[f"Wukv.{l}"], -1, -1, 0, 0, I["qkv"], d, 3 * d)
+            op("attn", OP_ATTN_DECODE, I["qkv"], 0, d, 2 * d, 3 * d, I["kv"], l, I["pos"], I["cos"], I["sin"],
+               I["att"], 0, d, B, c.n_heads, c.head_dim)
+            linear("wo", I["att"], 0, d, -1, I[f"Wo.{l}"], -1, I["x"], 0, d, I["x2"], 0, d)
+            op("swiglu", OP_Q8_SWIGLU, I["x2"], 0, d, I[f"g2.{l}"], eps, I[f"Wg.{l}"], I[f"bg.{l}"], I[f"Wu.{l}"],
+               I[f"bu.{l}"], I["h"], 0, F, B)
+            linear("down", I["h"], 0, F, -1, I[f"Wd.{l}"], I[f"bd.{l}"], I["x2"], 0, d, I["x"], 0, d)
+        linear("lm_head", I["x"], 0, d, I["gF"], I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0, V)
+        op("argmax", OP_ARGMAX_ROWS, I["logits"], I["next"], B, V)
+        op("advance", OP_ADD_SCALAR_INPLACE, I["pos"], float_bits(1.0), B)
+        if feed_back:
+            op("feed_back", OP_COPY, I["next"], 0, I["tok"], 0, B)
+        self._op_labels = labels
+        return np.asarray(s, dtype=np.int32)
+
+    def _streams(self):
+        if not self.loaded:
+            raise RuntimeError("weights are not loaded")
+        if self._stream_host is None:
+            self._stream_dev = self._build(feed_back=True)
+            self._stream_host = self._build(feed_back=False)
+        return self._stream_host, self._stream_dev
+
+    # ── stepping ──
+    def reset(self) -> None:
+        """Start every sequence at position 0 (cache contents are overwritten as it refills)."""
+        self._upload(self.ids["pos"], np.zeros(self.B, dtype=np.float32))
+        self.position = 0
+
+    def set_tokens(self, tokens) -> None:
+        t = np.asarray(tokens, dtype=np.int64).reshape(-1)
+        if t.size != self.B:
+            raise ValueError(f"expected {self.B} token ids, got {t.size}")
+        # Embedding.forward range check (transformer/embeddings/Embedding.java:30-32)
+        for v in t:
+            if v < 0 or v >= self.cfg.vocab_size:
+                raise ValueError(f"Token id out of range: {int(v)}")
+        self._upload(self.ids["tok"], t.astype(np.float32))
+
+    def step(self, tokens) -> np.ndarray:
+        """One token per sequence through host buffers: upload the ids, flush the
+        stream (synchronous), download the greedy picks."""
+        if self.position >= self.cfg.max_seq_len:
+            raise ValueError(f"seqLen {self.position + 1} exceeds maxSeqLen {self.cfg.max_seq_len}")
+        host, _ = self._streams()
+        self.set_tokens(tokens)
+        _lib.check(self.lib.deepj_cuda_flush_ops(host.ctypes.data, host.size))
+        self.position += 1
+        return self._download(self.ids["next"], self.B).astype(np.int64)
+
+    def step_device(self, n_steps: int = 1, sync: bool = True) -> None:
+        """n greedy steps with the picked token fed back on the device (no host copies)."""
+        if self.position + n_steps > self.cfg.max_seq_len:
+            raise ValueError(f"seqLen {self.position + n_steps} exceeds maxSeqLen {self.cfg.max_seq_len}")
+        _, dev = self._streams()
+        for _ in range(n_steps):
+            _lib.check(self.lib.deepj_cuda_flush_ops_async(dev.ctypes.data, dev.size))
+        self.position += n_steps
+        if sync:
+            _lib.check(self.lib.deepj_cuda_synchronize())
+
+    def logits(self) -> np.ndarray:
+        return self._download(self.ids["logits"], self.B * self.cfg.vocab_size).reshape(self.B, self.cfg.vocab_size)
+
+    def next_tokens(self) -> np.ndarray:
+        return self._download(self.ids["next"], self.B).astype(np.int64)
+
+    def prefill(self, prompts) -> np.ndarray:
+        """Feed the prompt one position at a time (every sequence the same length);
+        returns the greedy pick after the last prompt token."""
+        p = np.asarray(prompts, dtype=np.int64).reshape(self.B, -1)
+        nxt = None
+        for t in range(p.shape[1]):
+            nxt = self.step(p[:, t])
+        return nxt
+
+    def generate_greedy(self, prompt, max_new_tokens: int, keep_logits: bool = False):
+        """TextGenerator.generate with topK = 1 (models/TextGenerator.java:66-100)
+        for batch 1: returns the new token ids (and the logits row behind each)."""
+        if max_new_tokens < 0:
+            raise ValueError("maxNewTokens must be >= 0")
+        if self.B != 1:
+            raise ValueError("generate_greedy drives one sequence")
+        self.reset()
+        nxt = self.prefill(np.asarray(prompt).reshape(1, -1))
+        out, rows = [], []
+        for i in range(max_new_tokens):
+            if keep_logits:
+                rows.append(self.logits()[0].copy())
+            tok = int(nxt[0])
+            out.append(tok)
+            if i + 1 < max_new_tokens:
+                nxt = self.step([tok])
+        return (np.asarray(out, dtype=np.int64), np.stack(rows) if rows else None) if keep_logits else np.asarray(out, dtype=np.int64)
+
+    def profile_step(self):
+        """Device time of every op of one token step, run op by op: [(label, ms)]."""
+        host, _ = self._streams()
+        n = len(self._op_labels) + 1
+        ms = np.zeros(n, dtype=np.float32)
+        cnt = ctypes.c_int32(0)
+        self._build(feed_back=False)
+        _lib.check(self.lib.deepj_cuda_profile_ops(host.ctypes.data, host.size, ms.ctypes.data, n, ctypes.byref(cnt)))
+        self.position += 1
+        return list(zip(self._op_labels, ms[: cnt.value].tolist()))
+
+    def stats(self) -> Dict[str, int]:
+        v = (ctypes.c_int64 * 6)()
+        _lib.check(self.lib.deepj_cuda_stats(v, 6))
+        return {"eager_launches": v[0], "graph_replays": v[1], "graphs_captured": v[2],
+                "kernels_per_replay": v[3], "workspace_bytes": v[4], "device_error": v[5]}
+
+    def close(self) -> None:
+        if self._owned:
+            self._release(list(self._owned))

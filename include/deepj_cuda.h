@@ -1,0 +1,133 @@
+/*
+ * deepj_cuda.h — C ABI of libdeepj_cuda_jni, a CUDA (sm_100a) GpuRuntime for
+ * DeepJ's lazy ComputeGraph command stream.
+ *
+ * The first five entry points are one-to-one twins of the five `static native`
+ * methods DeepJ binds for its Metal runtime; a JNI shim (or any other FFI) forwards
+ * to them with plain pointers and lengths.  Everything returns 0 on success and a
+ * non-zero status on failure; the message is available from deepj_cuda_last_error()
+ * (the JNI shim turns it into java.lang.RuntimeException, as the Metal library does
+ * in native/deepj_metal_jni.mm:888-893).
+ *
+ * Threading: one caller thread per process, like the reference runtime
+ * (unsynchronised singletons, native/deepj_metal_jni.mm:63,1358).
+ */
+#ifndef DEEPJ_CUDA_H
+#define DEEPJ_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ───────────── the reference's five natives ───────────── */
+
+/* Replaces MetalNative.nativeAllocBuffers (tensor/metal/MetalNative.java:41,
+ * native/deepj_metal_jni.mm:1480-1507).  ids[i] gets sizes[i] floats; an id that
+ * already exists is left untouched.  New buffers are zero-filled. */
+int deepj_cuda_alloc_buffers(const int32_t* ids, const int32_t* sizes_in_floats, int32_t count);
+
+/* Replaces MetalNative.nativeUploadBuffer (MetalNative.java:44,
+ * native/deepj_metal_jni.mm:1509-1523).  Copies len floats from host memory;
+ * unknown id → error "Buffer not found for upload". */
+int deepj_cuda_upload_buffer(int32_t id, const float* data, int32_t len);
+
+/* Replaces MetalNative.nativeDownloadBuffer (MetalNative.java:47,
+ * native/deepj_metal_jni.mm:1525-1539).  Waits for all queued work, then copies
+ * len floats to host memory. */
+int deepj_cuda_download_buffer(int32_t id, float* out, int32_t len);
+
+/* Replaces MetalNative.nativeReleaseBuffers (MetalNative.java:50,
+ * native/deepj_metal_jni.mm:1541-1550).  Unknown ids are ignored. */
+int deepj_cuda_release_buffers(const int32_t* ids, int32_t count);
+
+/* Replaces MetalNative.nativeFlushOps (MetalNative.java:57,
+ * native/deepj_metal_jni.mm:1554-2140).  Executes a ComputeGraph command stream
+ * (op codes 1-42 of tensor/ComputeGraph.java:19-60 plus the fused decode op codes
+ * listed below) and returns when the results are readable.  The whole stream is
+ * validated before the first launch.  A stream seen for the second time is
+ * captured as a CUDA graph and replayed from then on. */
+int deepj_cuda_flush_ops(const int32_t* cmd, int32_t len);
+
+/* Message of the last failed call on this thread (never NULL). */
+const char* deepj_cuda_last_error(void);
+
+/* ───────────── additions (no counterpart in the reference) ───────────── */
+
+/* Bind the library to a CUDA device (default: device 0 at first use). */
+int deepj_cuda_init(int32_t device);
+/* Free every buffer, graph and workspace. */
+int deepj_cuda_shutdown(void);
+
+/* Same as deepj_cuda_flush_ops but returns after enqueueing. */
+int deepj_cuda_flush_ops_async(const int32_t* cmd, int32_t len);
+int deepj_cuda_synchronize(void);
+
+/* Device-time measurement on the library's stream (CUDA events). */
+int deepj_cuda_timer_begin(void);
+int deepj_cuda_timer_end(float* elapsed_ms);
+
+/* Run a stream op by op (no graph) and report the device time of every op, in
+ * stream order; n_ops receives the number of ops. */
+int deepj_cuda_profile_ops(const int32_t* cmd, int32_t len, float* ms_per_op, int32_t max_ops, int32_t* n_ops);
+
+/* counters[0]=kernel launches issued eagerly, [1]=graph replays, [2]=graphs
+ * captured, [3]=kernel nodes in the last replayed graph, [4]=workspace bytes,
+ * [5]=device-side error flag of bounded waits (0 = none). */
+int deepj_cuda_stats(int64_t* counters, int32_t n);
+
+/* Q8 weights.  Format (defined by this library; DeepJ has no quantization): for a
+ * weight W[K×N] (row-major, K = reduction dimension), every output column n is cut
+ * into blocks of 32 consecutive k (the last block is shorter when K % 32 != 0);
+ * scale = max|w| / 127.0f, code = clamp(round-half-even(w / scale), -127, 127),
+ * scale == 0 → code 0.  Canonical arrays: codes[N][K] int8, scales[N][ceil(K/32)]
+ * float.  A Q8 object lives in the same id space as float buffers. */
+int deepj_cuda_q8_alloc(int32_t q8_id, int32_t K, int32_t N);
+/* Quantize columns [src_col0, src_col0+n_cols) and rows [src_row0, src_row0+K) of
+ * the float buffer src_id (a row-major matrix with src_ld columns) into columns
+ * [dst_col0, dst_col0+n_cols) of the Q8 object. */
+int deepj_cuda_q8_quantize_into(int32_t q8_id, int32_t dst_col0, int32_t src_id,
+                                int32_t src_row0, int32_t src_col0, int32_t src_ld, int32_t n_cols);
+int deepj_cuda_q8_upload(int32_t q8_id, const int8_t* codes, const float* scales);
+int deepj_cuda_q8_download(int32_t q8_id, int8_t* codes, float* scales);
+
+/* Fill a float buffer with the library's counter-based synthetic weights (the same
+ * integer-exact generator the CPU oracle restates): element i of the buffer gets
+ * generator index first_index + i. */
+int deepj_cuda_synth_fill(int32_t id, uint64_t seed, uint64_t ordinal, float std_dev,
+                          int64_t first_index, int64_t n);
+
+/* KV cache object: K and V planes of [layers][batch][heads][max_seq][head_dim]
+ * floats, zero-filled. */
+int deepj_cuda_kv_alloc(int32_t kv_id, int32_t layers, int32_t batch, int32_t heads,
+                        int32_t max_seq, int32_t head_dim);
+
+/* ───────────── fused decode op codes (extend ComputeGraph.java:19-60) ─────────────
+ * Buffer-id slots may hold -1 where an operand is optional.  Integers that the
+ * reference would keep in an int[] (token ids, positions) travel as floats holding
+ * integers, like its index tensors (tensor/metal/MetalBackend.java:43-54).
+ *
+ *  64 EMBED_GATHER      [op, table, ids, out, rows, d, vocab]
+ *  65 Q8_LINEAR         [op, x, x_off, ldx, gamma, epsBits, w, bias, residual, res_off, ldr, out, out_off, ldo, M]
+ *                        out = (gamma>=0 ? rmsnorm(x) : x) · W (+bias) (+residual)
+ *  66 Q8_SWIGLU         [op, x, x_off, ldx, gamma, epsBits, w_gate, b_gate, w_up, b_up, out, out_off, ldo, M]
+ *                        out = silu(xn·Wg + bg) ⊙ (xn·Wu + bu)
+ *  67 ATTN_DECODE       [op, qkv, q_off, k_off, v_off, ld, kv, layer, pos, cos, sin, out, out_off, ldo, B, H, hd]
+ *                        RoPE(q,k) at pos[b]; append k,v; causal softmax attention over 0..pos[b]
+ *  68 ARGMAX_ROWS       [op, in, out, rows, cols]      lowest index among equal maxima
+ *  69 ADD_SCALAR_INPLACE[op, buf, valueBits, n]         buf[i] += value (advances positions)
+ *  70 COPY              [op, src, src_off, dst, dst_off, n]
+ */
+#define DEEPJ_OP_EMBED_GATHER        64
+#define DEEPJ_OP_Q8_LINEAR           65
+#define DEEPJ_OP_Q8_SWIGLU           66
+#define DEEPJ_OP_ATTN_DECODE         67
+#define DEEPJ_OP_ARGMAX_ROWS         68
+#define DEEPJ_OP_ADD_SCALAR_INPLACE  69
+#define DEEPJ_OP_COPY                70
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEEPJ_CUDA_H */

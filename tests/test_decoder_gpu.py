@@ -1,0 +1,175 @@
+"""End-to-end parity of the Q8 decode path against the CPU oracle: bit-exact weight
+quantization, identical greedy tokens, logits within 2e-3 of the logit range."""
+import numpy as np
+import pytest
+
+import oracle
+from deepj_b200.decoder import DecoderConfig, Q8Decoder
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_TOL = 2e-3      # max-abs-err relative to the logit range
+
+
+def weight_getter(om, cfg):
+    shapes = {n: (k, w) for n, k, w in cfg.matmul_shapes()}
+
+    def get(name, layer):
+        w = om.weight(name, layer)
+        if name in shapes:
+            return w.reshape(shapes[name])
+        if name == "emb":
+            return w.reshape(cfg.vocab_size, cfg.d_model)
+        if name == "Wlm":
+            return w.reshape(cfg.d_model, cfg.vocab_size)
+        return w
+    return get
+
+
+def check_q8_bit_exact(dec, om, cfg, layer):
+    shapes = {n: (k, w) for n, k, w in cfg.matmul_shapes()}
+    for obj, K, names in dec._layer_plan():
+        codes, scales = dec.q8_arrays(f"{obj}.{layer}")
+        col = 0
+        for nm in names:
+            k, n = shapes[nm]
+            co, so = oracle.q8_quantize(om.weight(nm, layer).reshape(k, n))
+            assert np.array_equal(codes[col:col + n], co), f"{nm} codes differ"
+            assert np.array_equal(scales[col:col + n].view(np.uint32), so.view(np.uint32)), f"{nm} scales differ"
+            col += n
+
+
+def run_parity(cfg, seed, prompt, n_new, std=0.1):
+    om = oracle.OracleModel(cfg.kind, cfg.vocab_size, cfg.max_seq_len, cfg.d_model, cfg.n_heads, cfg.n_layers,
+                            cfg.d_ff, cfg.q_rank, cfg.kv_rank, seed=seed, init_mode=0, std=std)
+    dec = Q8Decoder(cfg, batch=1)
+    try:
+        dec.load_weights(weight_getter(om, cfg))
+        check_q8_bit_exact(dec, om, cfg, 0)
+        check_q8_bit_exact(dec, om, cfg, cfg.n_layers - 1)
+        codes, scales = dec.q8_arrays("Wlm")
+        co, so = oracle.q8_quantize(om.weight("Wlm").reshape(cfg.d_model, cfg.vocab_size))
+        assert np.array_equal(codes, co) and np.array_equal(scales, so)
+        om.apply_q8()                                  # oracle B: same arithmetic, dequantized weights
+        toks_o, logits_o = om.generate_greedy(prompt, n_new, use_cache=True)
+        toks_g, logits_g = dec.generate_greedy(prompt, n_new, keep_logits=True)
+        rng_ = float(logits_o.max() - logits_o.min())
+        err = float(np.abs(logits_o - logits_g).max())
+        assert err <= LOGIT_TOL * rng_, f"logit err {err} vs range {rng_}"
+        assert np.array_equal(toks_o, toks_g), f"greedy tokens differ: {toks_o} vs {toks_g}"
+        st = dec.stats()
+        assert st["graph_replays"] > 0 and st["kernels_per_replay"] > 0, st
+        return err / rng_
+    finally:
+        dec.close()
+
+
+def test_tiny_llama_greedy_matches_oracle():
+    """The tiny reference configuration: vocab 256, dModel 256, 8 heads, 4 blocks, dFF 688,
+    context 256, java.util.Random(42) weights x0.1, 32 random byte tokens (Random(7)), 64 new tokens."""
+    cfg = DecoderConfig("llama", 256, 256, 256, 8, 4, 688)
+    r = oracle.JRandom(7)
+    prompt = [r.next_int(256) for _ in range(32)]
+    run_parity(cfg, 42, prompt, 64)
+
+
+def test_tiny_deepseek_greedy_matches_oracle():
+    cfg = DecoderConfig("deepseek", 256, 128, 256, 8, 2, 688, q_rank=128, kv_rank=64)
+    r = oracle.JRandom(11)
+    prompt = [r.next_int(256) for _ in range(24)]
+    run_parity(cfg, 5, prompt, 32)
+
+
+def test_oracle_b_equals_reference_full_reforward_on_tiny():
+    """The oracle's cached decode is the reference's full re-forward of the context, bit for bit."""
+    om = oracle.OracleModel("llama", 256, 64, 64, 4, 2, 176, seed=3)
+    r = oracle.JRandom(9)
+    prompt = [r.next_int(256) for _ in range(12)]
+    t1, l1 = om.generate_greedy(prompt, 6, use_cache=True)
+    t2, l2 = om.generate_greedy(prompt, 6, use_cache=False)
+    assert np.array_equal(t1, t2) and np.array_equal(l1.view(np.uint32), l2.view(np.uint32))
+
+
+def test_batched_sequences_are_independent():
+    """B concurrent sequences: every row equals the same sequence run alone."""
+    cfg = DecoderConfig("llama", 256, 64, 128, 4, 2, 352)
+    om = oracle.OracleModel("llama", 256, 64, 128, 4, 2, 352, seed=8)
+    get = weight_getter(om, cfg)
+    rng = np.random.default_rng(0)
+    prompts = rng.integers(0, 256, size=(3, 10))
+    single = []
+    for b in range(3):
+        dec = Q8Decoder(cfg, batch=1)
+        dec.load_weights(get)
+        dec.reset()
+        dec.prefill(prompts[b:b + 1])
+        single.append(dec.logits()[0].copy())
+        dec.close()
+    dec = Q8Decoder(cfg, batch=3)
+    dec.load_weights(get)
+    dec.reset()
+    dec.prefill(prompts)
+    got = dec.logits()
+    dec.close()
+    for b in range(3):
+        assert np.array_equal(got[b].view(np.uint32), single[b].view(np.uint32))
+
+
+def test_synthetic_weights_match_oracle_generator_and_decode():
+    """Device-generated synthetic weights are the oracle's generator bit for bit, and a
+    mid-sized model decodes to the oracle's logits."""
+    cfg = DecoderConfig("llama", 512, 48, 512, 8, 2, 1408)
+    om = oracle.OracleModel("llama", 512, 48, 512, 8, 2, 1408, seed=3, init_mode=1, std=0.02)
+    dec = Q8Decoder(cfg, batch=1)
+    try:
+        dec.load_synthetic(3, 0.02)
+        emb = dec._download(dec.ids["emb"], 512 * 512)
+        assert np.array_equal(emb.view(np.uint32), om.weight("emb").view(np.uint32))
+        check_q8_bit_exact(dec, om, cfg, 1)
+        om.apply_q8()
+        prompt = list(np.random.default_rng(1).integers(0, 512, size=16))
+        toks_o, logits_o = om.generate_greedy(prompt, 8, use_cache=True)
+        toks_g, logits_g = dec.generate_greedy(prompt, 8, keep_logits=True)
+        rng_ = float(logits_o.max() - logits_o.min())
+        assert float(np.abs(logits_o - logits_g).max()) <= LOGIT_TOL * rng_
+        assert np.array_equal(toks_o, toks_g)
+    finally:
+        dec.close()
+
+
+def test_device_feedback_loop_equals_host_loop():
+    """step_device (token fed back on the GPU) produces the same tokens as the host loop."""
+    cfg = DecoderConfig("llama", 256, 64, 128, 4, 2, 352)
+    om = oracle.OracleModel("llama", 256, 64, 128, 4, 2, 352, seed=8)
+    dec = Q8Decoder(cfg, batch=1)
+    try:
+        dec.load_weights(weight_getter(om, cfg))
+        prompt = [5, 17, 200, 31]
+        host = dec.generate_greedy(prompt, 10)
+        dec.reset()
+        nxt = dec.prefill(np.asarray(prompt).reshape(1, -1))
+        dec.set_tokens(nxt)
+        got = [int(nxt[0])]
+        for _ in range(9):
+            dec.step_device(1)
+            got.append(int(dec.next_tokens()[0]))
+        assert list(host) == got
+    finally:
+        dec.close()
+
+
+def test_token_out_of_range_and_context_overflow_raise():
+    cfg = DecoderConfig("llama", 256, 4, 64, 4, 1, 176)
+    om = oracle.OracleModel("llama", 256, 4, 64, 4, 1, 176, seed=1)
+    dec = Q8Decoder(cfg, batch=1)
+    try:
+        dec.load_weights(weight_getter(om, cfg))
+        dec.reset()
+        with pytest.raises(ValueError):
+            dec.step([256])
+        for t in range(4):
+            dec.step([t])
+        with pytest.raises(ValueError):       # RotaryEmbedding.validateSeqLen
+            dec.step([1])
+    finally:
+        dec.close()
