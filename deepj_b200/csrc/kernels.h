@@ -22,6 +22,11 @@ extern int g_num_sms;
 // When true, launchers attach the programmatic-dependent-launch attribute so that
 // a kernel's weight prefetch overlaps the tail of its predecessor.
 extern bool g_use_pdl;
+// Q8 GEMV kernel choice (environment DEEPJ_CUDA_GEMV = tma | mma | fma); shapes outside a
+// kernel's domain fall through to the next one.
+extern int g_gemv_mode;
+// Device int set non-zero when a bounded wait inside a kernel expired.
+extern int* g_dev_error;
 
 // A Q8 weight as laid out in HBM: codes[N][Kp] int8 (Kp = K rounded up to 16, zero
 // padded) followed by scales[N][nb] fp32, nb = ceil(K/32).
@@ -67,6 +72,7 @@ struct Q8LinearArgs {
     int M;
 };
 void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s);
+bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s);
 
 // ── decode attention ──
 struct AttnDecodeArgs {

@@ -77,6 +77,11 @@ void ensure_init() {
     if (e && e[0] == '1') R.graphs_enabled = false;
     e = getenv("DEEPJ_CUDA_NO_PDL");
     if (e && e[0] == '1') g_use_pdl = false;
+    e = getenv("DEEPJ_CUDA_GEMV");
+    if (e && std::string(e) == "fma") g_gemv_mode = 0;
+    if (e && std::string(e) == "mma") g_gemv_mode = 1;
+    DJ_CUDA_CHECK(cudaMalloc((void**)&g_dev_error, sizeof(int)));
+    DJ_CUDA_CHECK(cudaMemset(g_dev_error, 0, sizeof(int)));
     R.inited = true;
 }
 
@@ -583,7 +588,12 @@ int deepj_cuda_profile_ops(const int32_t* cmd, int32_t len, float* ms_per_op, in
 
 int deepj_cuda_stats(int64_t* counters, int32_t n) {
     DJ_TRY
-    int64_t v[6] = {g_launches, R.replays, R.captured, R.last_nodes, (int64_t)(R.ws_floats * 4), 0};
+    int dev_err = 0;
+    if (R.inited && g_dev_error) {
+        DJ_CUDA_CHECK(cudaStreamSynchronize(R.stream));
+        DJ_CUDA_CHECK(cudaMemcpy(&dev_err, g_dev_error, sizeof(int), cudaMemcpyDeviceToHost));
+    }
+    int64_t v[6] = {g_launches, R.replays, R.captured, R.last_nodes, (int64_t)(R.ws_floats * 4), dev_err};
     for (int i = 0; i < n && i < 6; i++) counters[i] = v[i];
     DJ_CATCH
 }

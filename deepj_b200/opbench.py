@@ -1,0 +1,97 @@
+"""Q8 matmul operator benchmark: `python -m deepj_b200.opbench --m 1 --k 4096 --n 11008`.
+
+Times the fused Q8 linear op (y = x·W, W quantized to Q8) through the C ABI.  The
+weights of one GEMV (19-51 MB) fit in the B200's L2, so the stream cycles through
+`--copies` distinct weight objects (≥ 8, more than L2 in total) and every launch
+streams its weights from HBM.  Prints one JSON line with the algorithmic GB/s
+(K·N·1.125 + 4·M·(K+N) bytes per launch) and TFLOP/s (2·M·K·N).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+
+import numpy as np
+
+from . import _lib
+from .compute_graph import OP_Q8_LINEAR, OP_Q8_SWIGLU, float_bits
+
+
+def run(m: int, k: int, n: int, copies: int, iters: int, warmup: int, swiglu: bool = False, norm: bool = False,
+        device: int = 0, seed: int = 1):
+    lib = _lib.load()
+    _lib.check(lib.deepj_cuda_init(device))
+    base = 1 << 26
+    nid = [base]
+
+    def new_id():
+        nid[0] += 1
+        return nid[0]
+
+    def f32(count, data=None):
+        i = new_id()
+        _lib.check(lib.deepj_cuda_alloc_buffers((ctypes.c_int32 * 1)(i), (ctypes.c_int32 * 1)(count), 1))
+        if data is not None:
+            d = np.ascontiguousarray(data, dtype=np.float32)
+            _lib.check(lib.deepj_cuda_upload_buffer(i, d.ctypes.data, d.size))
+        return i
+
+    rng = np.random.default_rng(seed)
+    x = f32(m * k, rng.standard_normal((m, k)).astype(np.float32))
+    out = f32(m * n)
+    gamma = f32(k, np.ones(k, dtype=np.float32)) if norm else -1
+    tmp = f32(k * n)
+    per_op = 2 if swiglu else 1
+    ws = []
+    for c in range(copies * per_op):
+        q = new_id()
+        _lib.check(lib.deepj_cuda_synth_fill(tmp, seed, c, 0.02, 0, k * n))
+        _lib.check(lib.deepj_cuda_q8_alloc(q, k, n))
+        _lib.check(lib.deepj_cuda_q8_quantize_into(q, 0, tmp, 0, 0, n, n))
+        ws.append(q)
+    _lib.check(lib.deepj_cuda_release_buffers((ctypes.c_int32 * 1)(tmp), 1))
+    eps = float_bits(1e-6)
+    s = []
+    for c in range(copies):
+        if swiglu:
+            s += [OP_Q8_SWIGLU, x, 0, k, gamma, eps, ws[2 * c], -1, ws[2 * c + 1], -1, out, 0, n, m]
+        else:
+            s += [OP_Q8_LINEAR, x, 0, k, gamma, eps, ws[c], -1, -1, 0, 0, out, 0, n, m]
+    cmd = np.asarray(s, dtype=np.int32)
+    for _ in range(max(warmup, 3)):
+        _lib.check(lib.deepj_cuda_flush_ops(cmd.ctypes.data, cmd.size))
+    _lib.check(lib.deepj_cuda_timer_begin())
+    for _ in range(iters):
+        _lib.check(lib.deepj_cuda_flush_ops_async(cmd.ctypes.data, cmd.size))
+    ms = ctypes.c_float(0)
+    _lib.check(lib.deepj_cuda_timer_end(ctypes.byref(ms)))
+    launches = iters * copies
+    us = ms.value * 1e3 / launches
+    nb = (k + 31) // 32
+    bytes_per = per_op * (k * n + nb * n * 4) + 4 * m * (k + n)
+    flops = 2.0 * m * k * n * per_op
+    res = {"op": "q8_swiglu" if swiglu else "q8_linear", "m": m, "k": k, "n": n, "copies": copies, "launches": launches,
+           "us_per_launch": us, "algorithmic_bytes": bytes_per, "gb_per_s": bytes_per / (us * 1e-6) / 1e9,
+           "tflop_per_s": flops / (us * 1e-6) / 1e12, "rmsnorm_fused": norm}
+    ids = list(range(base + 1, nid[0] + 1))
+    _lib.check(lib.deepj_cuda_release_buffers((ctypes.c_int32 * len(ids))(*ids), len(ids)))
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--copies", type=int, default=8)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--norm", action="store_true")
+    a = ap.parse_args()
+    print(json.dumps(run(a.m, a.k, a.n, a.copies, a.iters, a.warmup, a.swiglu, a.norm)))
+
+
+if __name__ == "__main__":
+    main()
