@@ -31,6 +31,7 @@ SIGNATURES = {
     "deepj_cuda_timer_begin": (ctypes.c_int, []),
     "deepj_cuda_timer_end": (ctypes.c_int, [_f32p]),
     "deepj_cuda_profile_ops": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int32, _i32p]),
+    "deepj_cuda_trace_read": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, _i32p]),
     "deepj_cuda_stats": (ctypes.c_int, [_i64p, ctypes.c_int32]),
     "deepj_cuda_q8_alloc": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]),
     "deepj_cuda_q8_quantize_into": (ctypes.c_int, [ctypes.c_int32] * 7),

@@ -27,6 +27,11 @@ extern bool g_use_pdl;
 extern int g_gemv_mode;
 // Device int set non-zero when a bounded wait inside a kernel expired.
 extern int* g_dev_error;
+// Phase-trace ring (null unless tracing is on) and the number of traced launches so far.
+constexpr int kTraceSlots = 4096;
+extern unsigned long long* g_trace;
+extern long long g_trace_launches;
+unsigned long long* trace_slot();
 
 // A Q8 weight as laid out in HBM: codes[N][Kp] int8 (Kp = K rounded up to 16, zero
 // padded) followed by scales[N][nb] fp32, nb = ceil(K/32).

@@ -80,6 +80,12 @@ void ensure_init() {
     e = getenv("DEEPJ_CUDA_GEMV");
     if (e && std::string(e) == "fma") g_gemv_mode = 0;
     if (e && std::string(e) == "mma") g_gemv_mode = 1;
+    e = getenv("DEEPJ_CUDA_TRACE");
+    if (e && e[0] == '1') {
+        DJ_CUDA_CHECK(cudaMalloc((void**)&g_trace, (size_t)kTraceSlots * 8 * sizeof(unsigned long long)));
+        DJ_CUDA_CHECK(cudaMemset(g_trace, 0, (size_t)kTraceSlots * 8 * sizeof(unsigned long long)));
+        R.graphs_enabled = false;      // slots are handed out per launch, which a replayed graph would not do
+    }
     DJ_CUDA_CHECK(cudaMalloc((void**)&g_dev_error, sizeof(int)));
     DJ_CUDA_CHECK(cudaMemset(g_dev_error, 0, sizeof(int)));
     R.inited = true;
@@ -595,6 +601,18 @@ int deepj_cuda_stats(int64_t* counters, int32_t n) {
     }
     int64_t v[6] = {g_launches, R.replays, R.captured, R.last_nodes, (int64_t)(R.ws_floats * 4), dev_err};
     for (int i = 0; i < n && i < 6; i++) counters[i] = v[i];
+    DJ_CATCH
+}
+
+int deepj_cuda_trace_read(uint64_t* out, int32_t max_launches, int32_t* n_launches) {
+    DJ_TRY
+    ensure_init();
+    if (!g_trace) throw std::runtime_error("tracing is off (set DEEPJ_CUDA_TRACE=1 before the first call)");
+    DJ_CUDA_CHECK(cudaStreamSynchronize(R.stream));
+    long long n = g_trace_launches < kTraceSlots ? g_trace_launches : kTraceSlots;
+    if (n > max_launches) n = max_launches;
+    if (n_launches) *n_launches = (int32_t)n;
+    if (n > 0) DJ_CUDA_CHECK(cudaMemcpy(out, g_trace, (size_t)n * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     DJ_CATCH
 }
 

@@ -74,6 +74,19 @@ def run(m: int, k: int, n: int, copies: int, iters: int, warmup: int, swiglu: bo
     res = {"op": "q8_swiglu" if swiglu else "q8_linear", "m": m, "k": k, "n": n, "copies": copies, "launches": launches,
            "us_per_launch": us, "algorithmic_bytes": bytes_per, "gb_per_s": bytes_per / (us * 1e-6) / 1e9,
            "tflop_per_s": flops / (us * 1e-6) / 1e12, "rmsnorm_fused": norm}
+    import os
+    if os.environ.get("DEEPJ_CUDA_TRACE") == "1":
+        tr = np.zeros((4096, 8), dtype=np.uint64)
+        cnt = ctypes.c_int32(0)
+        _lib.check(lib.deepj_cuda_trace_read(tr.ctypes.data, 4096, ctypes.byref(cnt)))
+        t = tr[cnt.value // 2: cnt.value].astype(np.int64)
+        if len(t) > 1:
+            d = np.diff(t[:, :6], axis=1)
+            gap = t[1:, 0] - t[:-1, 5]
+            res["trace_ns_median"] = {"prefetch_issue": float(np.median(d[:, 0])), "wait_prev": float(np.median(d[:, 1])),
+                                      "stage_x": float(np.median(d[:, 2])), "first_tile": float(np.median(d[:, 3])),
+                                      "rest": float(np.median(d[:, 4])), "start_minus_prev_end": float(np.median(gap)),
+                                      "start_to_start": float(np.median(np.diff(t[:, 0])))}
     ids = list(range(base + 1, nid[0] + 1))
     _lib.check(lib.deepj_cuda_release_buffers((ctypes.c_int32 * len(ids))(*ids), len(ids)))
     return res

@@ -72,6 +72,12 @@ int deepj_cuda_timer_end(float* elapsed_ms);
  * stream order; n_ops receives the number of ops. */
 int deepj_cuda_profile_ops(const int32_t* cmd, int32_t len, float* ms_per_op, int32_t max_ops, int32_t* n_ops);
 
+/* Phase tracing of the Q8 GEMV kernel.  With DEEPJ_CUDA_TRACE=1 in the environment at
+ * the first call, graphs are off and every GEMV launch records six device timestamps
+ * (ns): start, weights prefetch issued, previous kernel finished, activations staged,
+ * first tile reduced, end.  Reads up to max_launches records of eight uint64 each. */
+int deepj_cuda_trace_read(uint64_t* out, int32_t max_launches, int32_t* n_launches);
+
 /* counters[0]=kernel launches issued eagerly, [1]=graph replays, [2]=graphs
  * captured, [3]=kernel nodes in the last replayed graph, [4]=workspace bytes,
  * [5]=device-side error flag of bounded waits (0 = none). */
