@@ -1,17 +1,18 @@
-// Single-token causal attention over a K/V cache resident in HBM.
+// Single-token causal attention over a K/V cache resident in HBM — one kernel.
 //
 // Replaces, for one new token per sequence, the reference's split-heads / RoPE /
 // per-head QKᵀ / mask / softmax / PV / merge chain (HeadOps.java:33-140,
 // RotaryEmbedding.java:81-122).  Masked positions contribute exactly +0 to the
 // reference's softmax, so attending over 0..pos only is the same function.
 //
-//  k_rope_append : rotate q and k at the sequence's position (interleaved pairs,
-//                  x0·c − x1·s, x0·s + x1·c), write k and v into the cache.
-//  k_attn_split  : flash-decoding.  grid (splits, heads, batch); a CTA streams its
-//                  slice of the cache once, hd/16 lanes per position with 128-bit
-//                  loads, online softmax in fp32, and leaves (acc[hd], m, l).
-//  k_attn_combine: merges the split partials into the merged-heads row.
-// HBM-bound: the algorithmic traffic is the K and V rows of 0..pos, read once.
+// grid (splits, heads, batch), flash-decoding: a CTA rotates its head's q in
+// registers (interleaved pairs, x0·c − x1·s, x0·s + x1·c), streams its slice of the
+// cache once — hd/16 lanes per position, 128-bit loads, online softmax in fp32 — and
+// leaves (acc[hd], m, l) in a workspace.  The lane group that meets the newest
+// position takes k and v from the projection buffer instead, rotates k and appends
+// both to the cache.  The last CTA of a head to finish (a ticket counter that it
+// resets) merges the split partials into the merged-heads row, so no second launch
+// is needed.  HBM-bound: the algorithmic traffic is the K and V rows of 0..pos.
 #include "kernels.h"
 
 namespace dj {
@@ -21,43 +22,20 @@ namespace {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-__global__ void k_rope_append(float* __restrict__ qkv, int q_off, int k_off, int v_off, int ld,
-                              float* __restrict__ kcache, float* __restrict__ vcache, int maxSeq,
-                              const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
-                              int H, int hd) {
-    pdl_wait();
-    pdl_launch_dependents();
-    int h = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = hd >> 1;
-    int pos = (int)posbuf[b];
-    if (pos < 0 || pos >= maxSeq || i >= half) return;
-    float c = cosT[(size_t)pos * half + i], s = sinT[(size_t)pos * half + i];
-    float* row = qkv + (size_t)b * ld;
-    float* q = row + q_off + h * hd;
-    float q0 = q[2 * i], q1 = q[2 * i + 1];
-    q[2 * i] = q0 * c - q1 * s;
-    q[2 * i + 1] = q0 * s + q1 * c;
-    const float* k = row + k_off + h * hd;
-    float k0 = k[2 * i], k1 = k[2 * i + 1];
-    size_t dst = (((size_t)b * H + h) * maxSeq + pos) * hd;
-    kcache[dst + 2 * i] = k0 * c - k1 * s;
-    kcache[dst + 2 * i + 1] = k0 * s + k1 * c;
-    const float* v = row + v_off + h * hd;
-    vcache[dst + 2 * i] = v[2 * i];
-    vcache[dst + 2 * i + 1] = v[2 * i + 1];
-}
-
 constexpr int kAttnWarps = 4;
 
 template <int LPP>   // lanes per position = hd / 16
-__global__ void __launch_bounds__(kAttnWarps * 32) k_attn_split(
-        const float* __restrict__ qkv, int q_off, int ld,
-        const float* __restrict__ kcache, const float* __restrict__ vcache, int maxSeq,
-        const float* __restrict__ posbuf, float* __restrict__ ws, int H, float scale) {
+__global__ void __launch_bounds__(kAttnWarps * 32) k_attn_decode(
+        const float* __restrict__ qkv, int q_off, int k_off, int v_off, int ld,
+        float* __restrict__ kcache, float* __restrict__ vcache, int maxSeq,
+        const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
+        float* __restrict__ ws, int* __restrict__ tickets, float* __restrict__ out, int ldo, int H, float scale) {
     constexpr int HD = LPP * 16;
     constexpr int PPW = 32 / LPP;                 // positions per warp iteration
     constexpr int G = kAttnWarps * PPW;           // position groups per CTA
     __shared__ float s_acc[G][HD];
     __shared__ float s_m[G], s_l[G];
+    __shared__ int s_last;
 
     pdl_wait();
     pdl_launch_dependents();
@@ -65,59 +43,99 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_split(
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int group = lane / LPP, gl = lane % LPP;
     int pos = (int)posbuf[b];
+    if (pos < 0) pos = 0;
     if (pos >= maxSeq) pos = maxSeq - 1;
     const int seq = pos + 1;
     const int chunk = (seq + splits - 1) / splits;
     const int start = split * chunk;
     const int end = min(seq, start + chunk);
+    const int half = HD >> 1;
 
+    // this lane's 8 rotation pairs at the current position
+    float cs[8], sn[8];
+    {
+        const float4* cp = reinterpret_cast<const float4*>(cosT + (size_t)pos * half + gl * 8);
+        const float4* sp = reinterpret_cast<const float4*>(sinT + (size_t)pos * half + gl * 8);
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            float4 c4 = cp[j], s4 = sp[j];
+            cs[4 * j] = c4.x; cs[4 * j + 1] = c4.y; cs[4 * j + 2] = c4.z; cs[4 * j + 3] = c4.w;
+            sn[4 * j] = s4.x; sn[4 * j + 1] = s4.y; sn[4 * j + 2] = s4.z; sn[4 * j + 3] = s4.w;
+        }
+    }
+    const float* rowp = qkv + (size_t)b * ld;
     float q[16];
     {
-        const float4* qp = reinterpret_cast<const float4*>(qkv + (size_t)b * ld + q_off + h * HD + gl * 16);
+        const float4* qp = reinterpret_cast<const float4*>(rowp + q_off + h * HD + gl * 16);
 #pragma unroll
         for (int j = 0; j < 4; j++) { float4 v = qp[j]; q[4 * j] = v.x; q[4 * j + 1] = v.y; q[4 * j + 2] = v.z; q[4 * j + 3] = v.w; }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float x0 = q[2 * i], x1 = q[2 * i + 1];
+            q[2 * i] = x0 * cs[i] - x1 * sn[i];
+            q[2 * i + 1] = x0 * sn[i] + x1 * cs[i];
+        }
     }
-    const float* kbase = kcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
-    const float* vbase = vcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
+    float* kbase = kcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
+    float* vbase = vcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
 
     float m = -INFINITY, l = 0.0f, acc[16];
 #pragma unroll
     for (int j = 0; j < 16; j++) acc[j] = 0.0f;
 
     for (int base = start + warp * PPW; base < end; base += G) {
-        int p = base + group;
-        bool valid = p < end;
-        float4 kf[4], vf[4];
-        if (valid) {
+        const int p = base + group;
+        const bool valid = p < end;
+        float kf[16], vf[16];
+        if (valid && p == pos) {
+            // the new token: k and v come from the projections; rotate k, append both to the cache
+            const float4* kp = reinterpret_cast<const float4*>(rowp + k_off + h * HD + gl * 16);
+            const float4* vp = reinterpret_cast<const float4*>(rowp + v_off + h * HD + gl * 16);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float4 a = kp[j], c = vp[j];
+                kf[4 * j] = a.x; kf[4 * j + 1] = a.y; kf[4 * j + 2] = a.z; kf[4 * j + 3] = a.w;
+                vf[4 * j] = c.x; vf[4 * j + 1] = c.y; vf[4 * j + 2] = c.z; vf[4 * j + 3] = c.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float x0 = kf[2 * i], x1 = kf[2 * i + 1];
+                kf[2 * i] = x0 * cs[i] - x1 * sn[i];
+                kf[2 * i + 1] = x0 * sn[i] + x1 * cs[i];
+            }
+            float4* kd = reinterpret_cast<float4*>(kbase + (size_t)p * HD);
+            float4* vd = reinterpret_cast<float4*>(vbase + (size_t)p * HD);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                kd[j] = make_float4(kf[4 * j], kf[4 * j + 1], kf[4 * j + 2], kf[4 * j + 3]);
+                vd[j] = make_float4(vf[4 * j], vf[4 * j + 1], vf[4 * j + 2], vf[4 * j + 3]);
+            }
+        } else if (valid) {
             const float4* kp = reinterpret_cast<const float4*>(kbase + (size_t)p * HD);
             const float4* vp = reinterpret_cast<const float4*>(vbase + (size_t)p * HD);
 #pragma unroll
-            for (int j = 0; j < 4; j++) { kf[j] = __ldcs(kp + j); vf[j] = __ldcs(vp + j); }
+            for (int j = 0; j < 4; j++) {
+                float4 a = __ldcs(kp + j), c = __ldcs(vp + j);
+                kf[4 * j] = a.x; kf[4 * j + 1] = a.y; kf[4 * j + 2] = a.z; kf[4 * j + 3] = a.w;
+                vf[4 * j] = c.x; vf[4 * j + 1] = c.y; vf[4 * j + 2] = c.z; vf[4 * j + 3] = c.w;
+            }
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; j++) { kf[j] = make_float4(0.f, 0.f, 0.f, 0.f); vf[j] = kf[j]; }
+            for (int j = 0; j < 16; j++) { kf[j] = 0.0f; vf[j] = 0.0f; }
         }
         float dot = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            dot = fmaf(q[4 * j], kf[j].x, dot); dot = fmaf(q[4 * j + 1], kf[j].y, dot);
-            dot = fmaf(q[4 * j + 2], kf[j].z, dot); dot = fmaf(q[4 * j + 3], kf[j].w, dot);
-        }
+        for (int j = 0; j < 16; j++) dot = fmaf(q[j], kf[j], dot);
 #pragma unroll
         for (int o = LPP / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         if (valid) {
-            float s = dot * scale;
-            float mn = fmaxf(m, s);
-            float corr = expf(m - mn);
-            float pe = expf(s - mn);
+            const float s = dot * scale;
+            const float mn = fmaxf(m, s);
+            const float corr = expf(m - mn);
+            const float pe = expf(s - mn);
             l = l * corr + pe;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                acc[4 * j] = fmaf(pe, vf[j].x, acc[4 * j] * corr);
-                acc[4 * j + 1] = fmaf(pe, vf[j].y, acc[4 * j + 1] * corr);
-                acc[4 * j + 2] = fmaf(pe, vf[j].z, acc[4 * j + 2] * corr);
-                acc[4 * j + 3] = fmaf(pe, vf[j].w, acc[4 * j + 3] * corr);
-            }
+            for (int j = 0; j < 16; j++) acc[j] = fmaf(pe, vf[j], acc[j] * corr);
             m = mn;
         }
     }
@@ -126,40 +144,50 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_split(
     for (int j = 0; j < 16; j++) s_acc[g][gl * 16 + j] = acc[j];
     if (gl == 0) { s_m[g] = m; s_l[g] = l; }
     __syncthreads();
-    float* out = ws + (((size_t)b * H + h) * splits + split) * (HD + 2);
+    float* mine = ws + (((size_t)b * H + h) * splits + split) * (HD + 2);
     for (int j = threadIdx.x; j < HD; j += blockDim.x) {
         float M = -INFINITY;
-#pragma unroll 4
         for (int gg = 0; gg < G; gg++) M = fmaxf(M, s_m[gg]);
         float a = 0.0f, L = 0.0f;
         if (M > -INFINITY) {
             for (int gg = 0; gg < G; gg++) {
-                float e = expf(s_m[gg] - M);
+                const float e = expf(s_m[gg] - M);
                 a = fmaf(s_acc[gg][j], e, a);
                 L = fmaf(s_l[gg], e, L);
             }
         }
-        out[j] = a;
-        if (j == 0) { out[HD] = M; out[HD + 1] = L; }
+        mine[j] = a;
+        if (j == 0) { mine[HD] = M; mine[HD + 1] = L; }
     }
-}
-
-__global__ void k_attn_combine(const float* __restrict__ ws, float* __restrict__ out, int ldo, int H, int hd, int splits) {
-    pdl_wait();
-    pdl_launch_dependents();
-    int h = blockIdx.x, b = blockIdx.y;
-    const float* base = ws + ((size_t)b * H + h) * splits * (hd + 2);
+    if (splits == 1) {
+        // nothing to merge
+        __syncthreads();
+        for (int j = threadIdx.x; j < HD; j += blockDim.x) out[(size_t)b * ldo + h * HD + j] = mine[j] / mine[HD + 1];
+        return;
+    }
+    // ── the last CTA of this head merges the split partials ──
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(&tickets[b * H + h], 1);
+        s_last = ticket == splits - 1;
+        if (s_last) tickets[b * H + h] = 0;          // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* pbase = ws + ((size_t)b * H + h) * splits * (HD + 2);
     float M = -INFINITY;
-    for (int s = 0; s < splits; s++) M = fmaxf(M, base[(size_t)s * (hd + 2) + hd]);
-    for (int j = threadIdx.x; j < hd; j += blockDim.x) {
+    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, __ldcg(pbase + (size_t)sp * (HD + 2) + HD));
+    for (int j = threadIdx.x; j < HD; j += blockDim.x) {
         float a = 0.0f, L = 0.0f;
-        for (int s = 0; s < splits; s++) {
-            const float* p = base + (size_t)s * (hd + 2);
-            float e = expf(p[hd] - M);
-            a = fmaf(p[j], e, a);
-            L = fmaf(p[hd + 1], e, L);
+        for (int sp = 0; sp < splits; sp++) {
+            const float* pp = pbase + (size_t)sp * (HD + 2);
+            const float e = expf(__ldcg(pp + HD) - M);
+            a = fmaf(__ldcg(pp + j), e, a);
+            L = fmaf(__ldcg(pp + HD + 1), e, L);
         }
-        out[(size_t)b * ldo + h * hd + j] = a / L;
+        out[(size_t)b * ldo + h * HD + j] = a / L;
     }
 }
 
@@ -179,18 +207,16 @@ void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s) {
     int lpp = a.hd / 16;
     if (a.hd % 16 != 0 || (lpp != 1 && lpp != 2 && lpp != 4 && lpp != 8 && lpp != 16 && lpp != 32))
         throw std::runtime_error("attention: head dim " + std::to_string(a.hd) + " is not one of 16,32,64,128,256,512");
-    launch_k(k_rope_append, dim3(a.H, a.B), dim3(a.hd / 2 < 32 ? 32 : a.hd / 2), 0, s, true,
-             a.qkv, a.q_off, a.k_off, a.v_off, a.ld, a.kcache, a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.H, a.hd);
     dim3 grid(a.splits, a.H, a.B), block(kAttnWarps * 32);
-#define DJ_ATTN_CASE(L)                                                                                   \
-    case L: launch_k(k_attn_split<L>, grid, block, 0, s, true, (const float*)a.qkv, a.q_off, a.ld,      \
-                     (const float*)a.kcache, (const float*)a.vcache, a.maxSeq, a.pos, a.ws, a.H, a.scale); break;
+    if (a.B * a.H > kAttnTickets) throw std::runtime_error("attention: batch × heads exceeds " + std::to_string(kAttnTickets));
+    int* tickets = a.tickets;
+#define DJ_ATTN_CASE(L)                                                                                              \
+    case L: launch_k(k_attn_decode<L>, grid, block, 0, s, true, (const float*)a.qkv, a.q_off, a.k_off, a.v_off, a.ld, \
+                     a.kcache, a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.ws, tickets, a.out, a.ldo, a.H, a.scale); break;
     switch (lpp) {
         DJ_ATTN_CASE(1) DJ_ATTN_CASE(2) DJ_ATTN_CASE(4) DJ_ATTN_CASE(8) DJ_ATTN_CASE(16) DJ_ATTN_CASE(32)
     }
 #undef DJ_ATTN_CASE
-    launch_k(k_attn_combine, dim3(a.H, a.B), dim3(a.hd < 32 ? 32 : (a.hd > 256 ? 256 : a.hd)), 0, s, true,
-             (const float*)a.ws, a.out, a.ldo, a.H, a.hd, a.splits);
 }
 
 }  // namespace dj

@@ -90,8 +90,10 @@ struct AttnDecodeArgs {
     int B, H, hd;
     float scale;
     float* ws;                                 // split partials: [B][H][splits][hd + 2]
+    int* tickets;                              // [B·H] zero-initialised, self-resetting counters
     int splits;
 };
+constexpr int kAttnTickets = 1 << 16;
 size_t attn_decode_ws_floats(int B, int H, int hd, int splits);
 int attn_decode_splits(int B, int H, int maxSeq);
 void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s);

@@ -56,6 +56,7 @@ struct Runtime {
     unsigned long long epoch = 1;          // bumped whenever a pointer baked into a graph may have died
     float* ws = nullptr;
     size_t ws_floats = 0;
+    int* tickets = nullptr;
     std::unordered_map<unsigned long long, GraphEntry> graphs;
     cudaEvent_t t0 = nullptr, t1 = nullptr;
     long long replays = 0, captured = 0, last_nodes = 0;
@@ -86,6 +87,8 @@ void ensure_init() {
         DJ_CUDA_CHECK(cudaMemset(g_trace, 0, (size_t)kTraceSlots * 8 * sizeof(unsigned long long)));
         R.graphs_enabled = false;      // slots are handed out per launch, which a replayed graph would not do
     }
+    DJ_CUDA_CHECK(cudaMalloc((void**)&R.tickets, kAttnTickets * sizeof(int)));
+    DJ_CUDA_CHECK(cudaMemset(R.tickets, 0, kAttnTickets * sizeof(int)));
     DJ_CUDA_CHECK(cudaMalloc((void**)&g_dev_error, sizeof(int)));
     DJ_CUDA_CHECK(cudaMemset(g_dev_error, 0, sizeof(int)));
     R.inited = true;
@@ -338,6 +341,7 @@ void do_op(Ctx& ctx, const int32_t* c) {
             size_t need = attn_decode_ws_floats(B, H, hd, a.splits);
             if (need > ctx.ws_need) ctx.ws_need = need;
             a.ws = R.ws;
+            a.tickets = R.tickets;
             if (go) launch_attn_decode(a, s);
             break;
         }

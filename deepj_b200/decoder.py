@@ -332,6 +332,14 @@ class Q8Decoder:
         self._upload(self.ids["pos"], np.zeros(self.B, dtype=np.float32))
         self.position = 0
 
+    def set_position(self, position: int) -> None:
+        """Rewind (or advance) every sequence to `position`; cache rows at and beyond it are
+        overwritten by the following steps."""
+        if position < 0 or position > self.cfg.max_seq_len:
+            raise ValueError(f"position {position} outside 0..{self.cfg.max_seq_len}")
+        self._upload(self.ids["pos"], np.full(self.B, float(position), dtype=np.float32))
+        self.position = int(position)
+
     def set_tokens(self, tokens) -> None:
         t = np.asarray(tokens, dtype=np.int64).reshape(-1)
         if t.size != self.B:
