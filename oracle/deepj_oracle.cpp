@@ -673,7 +673,7 @@ void fillSynth(uint64_t seed, uint64_t& ordinal, std::vector<float>& w, size_t n
 // values are (float)(nextGaussian()*mult), mult = 0.1 in the reference.
 // initMode 1: counter-based generator above, one ordinal per matrix in the same order.
 Model* buildModel(int kind, int V, int maxSeq, int d, int H, int L, int F, int qRank, int kvRank,
-                  int64_t seed, int initMode, float std_, int nLayersBuilt) {
+                  int64_t seed, int initMode, double std_, int nLayersBuilt) {
     if (kind == GPT) throw std::runtime_error("GPT family is not built in the oracle yet");
     auto* m = new Model();
     m->kind = kind; m->V = V; m->maxSeq = maxSeq; m->d = d; m->H = H; m->L = L; m->F = F; m->qRank = qRank; m->kvRank = kvRank;
@@ -681,7 +681,7 @@ Model* buildModel(int kind, int V, int maxSeq, int d, int H, int L, int F, int q
     uint64_t ord = 0;
     JRandom rEmb(seed), rStack(seed), rHead(seed + 1);
     auto fill = [&](JRandom& r, std::vector<float>& w, size_t n) {
-        if (initMode == 0) fillJava(r, w, n, (double)std_); else fillSynth((uint64_t)seed, ord, w, n, std_);
+        if (initMode == 0) fillJava(r, w, n, std_); else fillSynth((uint64_t)seed, ord, w, n, (float)std_);
     };
     fill(rEmb, m->emb, (size_t)V * d);
     m->blocks.resize(built);
@@ -1004,7 +1004,7 @@ int oracle_rope_tables(int32_t headDim, int32_t maxSeq, float* cosT, float* sinT
 
 // ── models ──
 void* oracle_model_new(int32_t kind, int32_t V, int32_t maxSeq, int32_t d, int32_t H, int32_t L, int32_t F,
-                       int32_t qRank, int32_t kvRank, int64_t seed, int32_t initMode, float std_, int32_t nLayersBuilt) {
+                       int32_t qRank, int32_t kvRank, int64_t seed, int32_t initMode, double std_, int32_t nLayersBuilt) {
     try { return buildModel(kind, V, maxSeq, d, H, L, F, qRank, kvRank, seed, initMode, std_, nLayersBuilt); }
     catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }

@@ -47,7 +47,7 @@ def lib() -> ctypes.CDLL:
     L.oracle_matmul.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32]
     L.oracle_rope_tables.argtypes = [_i32, _i32, _vp, _vp]
     L.oracle_model_new.restype = _vp
-    L.oracle_model_new.argtypes = [_i32] * 9 + [_i64, _i32, ctypes.c_float, _i32]
+    L.oracle_model_new.argtypes = [_i32] * 9 + [_i64, _i32, ctypes.c_double, _i32]
     L.oracle_model_free.argtypes = [_vp]
     L.oracle_model_weight_size.restype = _i64
     L.oracle_model_weight_size.argtypes = [_vp, ctypes.c_char_p, _i32]
