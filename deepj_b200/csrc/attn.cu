@@ -13,7 +13,9 @@
 // both to the cache.  The last CTA of a head to finish (a ticket counter that it
 // resets) merges the split partials into the merged-heads row, so no second launch
 // is needed.  HBM-bound: the algorithmic traffic is the K and V rows of 0..pos.
+#include "../../include/deepj_cuda.h"
 #include "kernels.h"
+#include <cmath>
 
 namespace dj {
 
@@ -220,3 +222,80 @@ void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s) {
 }
 
 }  // namespace dj
+
+// ───────────── attention without any allocation ─────────────
+// Scratch for deepj_cuda_attn_decode_static: the split partials and the ticket counters
+// live in this fixed array instead of the runtime's growable workspace.  Every GPU that
+// loads the library holds these 2 MiB + 16 KiB until the process exits.
+namespace {
+constexpr size_t kStaticPartialFloats = 512 * 1024;     // 2 MiB of (acc[hd], m, l) records
+constexpr size_t kStaticTickets = 4096;                 // batch × heads
+static __device__ __align__(256) float g_attn_static_scratch[kStaticPartialFloats + kStaticTickets];
+
+// The array's name is only a host-side handle; the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+float* g_static_scratch_addr[64] = {};
+}  // namespace
+
+extern "C" int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int32_t v_off, int32_t ld,
+                                             int32_t kv, int32_t layer, int32_t pos, int32_t cos_table, int32_t sin_table,
+                                             int32_t out, int32_t out_off, int32_t ldo, int32_t B, int32_t H, int32_t hd) {
+    using namespace dj;
+    try {
+        cudaStream_t stream = runtime_stream();
+        if (stream == nullptr) throw std::runtime_error("attn_decode_static: the library holds no buffers yet (nothing was allocated through it)");
+        const int dev = runtime_device();
+        if (dev < 0 || dev >= 64) throw std::runtime_error("attn_decode_static: device index out of range");
+        int cur = -1;
+        DJ_CUDA_CHECK(cudaGetDevice(&cur));
+        if (cur != dev) DJ_CUDA_CHECK(cudaSetDevice(dev));
+        if (g_static_scratch_addr[dev] == nullptr) {
+            // first call on this device: resolve the scratch array's device address
+            float* p = nullptr;
+            DJ_CUDA_CHECK(cudaGetSymbolAddress((void**)&p, g_attn_static_scratch));
+            if (p == nullptr) throw std::runtime_error("attn_decode_static: scratch address is null");
+            g_static_scratch_addr[dev] = p;
+        }
+        float* scratch = g_static_scratch_addr[dev];
+
+        PoolKV kvb; PoolF32 bq, bp, bc, bs, bo;
+        if (!pool_kv(kv, &kvb)) throw std::runtime_error("attn_decode_static: missing KV cache id=" + std::to_string(kv));
+        if (!pool_f32(qkv, &bq) || !pool_f32(pos, &bp) || !pool_f32(cos_table, &bc) || !pool_f32(sin_table, &bs) || !pool_f32(out, &bo))
+            throw std::runtime_error("attn_decode_static: missing GPU buffer");
+        if (B < 1 || H < 1 || hd < 2 || B > kvb.B || H != kvb.H || hd != kvb.hd) throw std::runtime_error("attn_decode_static: shape does not match the KV cache");
+        if (layer < 0 || layer >= kvb.layers) throw std::runtime_error("attn_decode_static: layer out of range");
+        if (q_off < 0 || k_off < 0 || v_off < 0 || out_off < 0 || ld % 4 || q_off % 4 || k_off % 4 || v_off % 4)
+            throw std::runtime_error("attn_decode_static: offsets and stride must be non-negative multiples of 4 floats");
+        const int d = H * hd;
+        const int maxOff = std::max(q_off, std::max(k_off, v_off));
+        if (ld < maxOff + d || ldo < d) throw std::runtime_error("attn_decode_static: row stride smaller than the row");
+        if (bq.floats < (size_t)(B - 1) * ld + maxOff + d || bp.floats < (size_t)B || bo.floats < (size_t)out_off + (size_t)(B - 1) * ldo + d ||
+            bc.floats < (size_t)kvb.maxSeq * (hd / 2) || bs.floats < (size_t)kvb.maxSeq * (hd / 2))
+            throw std::runtime_error("attn_decode_static: a buffer is smaller than the op needs");
+        const int splits = attn_decode_splits(B, H, kvb.maxSeq);
+        const size_t need = attn_decode_ws_floats(B, H, hd, splits);
+        if (need > kStaticPartialFloats || (size_t)B * H > kStaticTickets)
+            throw std::runtime_error("attn_decode_static: needs " + std::to_string(need) + " scratch floats and " + std::to_string((size_t)B * H) +
+                                     " counters; the static scratch holds " + std::to_string(kStaticPartialFloats) + " and " +
+                                     std::to_string(kStaticTickets) + " (use op 67 through deepj_cuda_flush_ops for larger shapes)");
+        int* tickets = reinterpret_cast<int*>(scratch + kStaticPartialFloats);
+        // the array keeps whatever the last call left: the counters must start at zero
+        DJ_CUDA_CHECK(cudaMemsetAsync(tickets, 0, (size_t)B * H * sizeof(int), stream));
+        AttnDecodeArgs a = {};
+        a.qkv = bq.ptr; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.ld = ld;
+        const size_t plane = (size_t)kvb.layers * kvb.B * kvb.H * kvb.maxSeq * kvb.hd;
+        const size_t layerOff = (size_t)layer * kvb.B * kvb.H * kvb.maxSeq * kvb.hd;
+        a.kcache = kvb.ptr + layerOff; a.vcache = kvb.ptr + plane + layerOff; a.maxSeq = kvb.maxSeq;
+        a.pos = bp.ptr; a.cosT = bc.ptr; a.sinT = bs.ptr;
+        a.out = bo.ptr + out_off; a.ldo = ldo; a.B = B; a.H = H; a.hd = hd;
+        a.scale = (float)(1.0 / std::sqrt((double)hd));
+        a.splits = splits; a.ws = scratch; a.tickets = tickets;
+        launch_attn_decode(a, stream);
+        DJ_CUDA_CHECK(cudaStreamSynchronize(stream));
+        return 0;
+    } catch (const std::exception& e) {
+        set_last_error(e.what());
+        return 1;
+    }
+}
+

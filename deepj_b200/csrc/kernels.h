@@ -106,6 +106,16 @@ void launch_copy(const float* src, float* dst, long long n, cudaStream_t s);
 void launch_synth_fill(float* out, unsigned long long seed, unsigned long long ordinal, float std_dev,
                        long long first, long long n, cudaStream_t s);
 
+// Read-only views of the runtime's buffer pool for entry points that live beside their kernels.
+struct PoolF32 { float* ptr; size_t floats; };
+struct PoolKV { float* ptr; int layers, B, H, maxSeq, hd; };
+bool pool_f32(int id, PoolF32* out);
+bool pool_kv(int id, PoolKV* out);
+// The library's stream and device; the stream is null until the library has been initialised.
+cudaStream_t runtime_stream();
+int runtime_device();
+void set_last_error(const std::string& msg);
+
 // Launch helper: plain <<<>>> or cudaLaunchKernelEx with the PDL attribute.
 template <typename... KArgs, typename... Args>
 inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, Args... args) {

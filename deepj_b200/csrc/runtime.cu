@@ -478,6 +478,25 @@ void flush(const int32_t* cmd, int len, bool sync) {
 
 }  // namespace
 
+namespace dj {
+bool pool_f32(int id, PoolF32* out) {
+    auto it = R.pool.find(id);
+    if (it == R.pool.end() || it->second.kind != kF32 || it->second.ptr == nullptr) return false;
+    out->ptr = (float*)it->second.ptr; out->floats = it->second.floats;
+    return true;
+}
+bool pool_kv(int id, PoolKV* out) {
+    auto it = R.pool.find(id);
+    if (it == R.pool.end() || it->second.kind != kKV || it->second.ptr == nullptr) return false;
+    const Buf& b = it->second;
+    out->ptr = (float*)b.ptr; out->layers = b.layers; out->B = b.B; out->H = b.H; out->maxSeq = b.maxSeq; out->hd = b.hd;
+    return true;
+}
+cudaStream_t runtime_stream() { return R.inited ? R.stream : nullptr; }
+int runtime_device() { return R.device; }
+void set_last_error(const std::string& msg) { g_err = msg; }
+}  // namespace dj
+
 #define DJ_TRY try {
 #define DJ_CATCH } catch (const std::exception& e) { g_err = e.what(); return 1; } catch (...) { g_err = "unknown error"; return 1; } return 0;
 

@@ -109,6 +109,27 @@ int deepj_cuda_synth_fill(int32_t id, uint64_t seed, uint64_t ordinal, float std
 int deepj_cuda_kv_alloc(int32_t kv_id, int32_t layers, int32_t batch, int32_t heads,
                         int32_t max_seq, int32_t head_dim);
 
+/* Decode attention for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Some hosts of this library cannot let a call reach cudaMalloc: a JVM thread inside a
+ * latency-critical section, a serving loop that has handed all device memory to its own
+ * arena, a process whose memory budget was fixed at start-up.  The stream form of this op
+ * (code 67) takes its split-partial scratch from a workspace that the library grows on
+ * demand, so its first use, or a larger shape, allocates.  This entry point runs the same
+ * kernel with the scratch in a fixed 2 MiB + 16 KiB array inside the library image (held
+ * by every GPU that loads the library until the process exits) and calls no allocating
+ * routine.  Arguments are those of op 67: buffer ids of objects that already exist, float
+ * offsets, strides and shapes; it returns when `out` is readable.
+ * Limits: batch·heads·splits·(head_dim+2) <= 524288 floats and batch·heads <= 4096;
+ * anything larger is rejected with a message naming both numbers.
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress);
+ * make that first call before any stream capture begins.  Every call shares the one
+ * array: calls that overlap on the GPU race on it, so keep them on one thread, one after
+ * the other (the call is synchronous, which does that for a single caller). */
+int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int32_t v_off, int32_t ld,
+                                  int32_t kv, int32_t layer, int32_t pos, int32_t cos_table, int32_t sin_table,
+                                  int32_t out, int32_t out_off, int32_t ldo, int32_t batch, int32_t heads, int32_t head_dim);
+
 /* ───────────── fused decode op codes (extend ComputeGraph.java:19-60) ─────────────
  * Buffer-id slots may hold -1 where an operand is optional.  Integers that the
  * reference would keep in an int[] (token ids, positions) travel as floats holding
