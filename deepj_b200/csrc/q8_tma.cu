@@ -102,33 +102,39 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     const bool tracing = p.trace != nullptr && blockIdx.x == 0 && tid == 0;
     if (tracing) p.trace[0] = gtime();
 
-    // issue the copies of one (tile, pair) item into a ring slot
-    auto issue = [&](int tile, int pi, int slot) {
-        unsigned char* dst = myring + (size_t)slot * kSlotBytes;
+    // ── copy issue: per-lane constants are hoisted; rows past N are clamped to the last row
+    // (their results are never written), so the copy path carries no predicates ──
+    const uint32_t ring_s = smem_u32(myring);
+    uint32_t dstoff[2]; int rloc[2]; const int8_t* cbase[2];
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int q = lane + 32 * j, r = q >> 2, piece = q & 3;
-            int row; const int8_t* cbase;
-            if (SWIGLU) { row = tile * 8 + (r & 7); cbase = r < 8 ? p.codes : p.codes2; }
-            else { row = tile * 16 + r; cbase = p.codes; }
-            if (row < p.N) cp_async16(dst + r * kRowStride + ((piece ^ (((r >> 1) & 1) << 1)) * 16), cbase + (size_t)row * p.Kp + pi * 64 + piece * 16);
-        }
-        {
-            const int r = lane >> 1, which = lane & 1;
-            int row; const float* sbase;
-            if (SWIGLU) { row = tile * 8 + (r & 7); sbase = r < 8 ? p.scales : p.scales2; }
-            else { row = tile * 16 + r; sbase = p.scales; }
-            if (row < p.N) cp_async4(dst + kRows * kRowStride + lane * 4, sbase + (size_t)row * p.nb + pi * 2 + which);
-        }
-    };
+    for (int j = 0; j < 2; j++) {
+        const int q = lane + 32 * j, r = q >> 2, piece = q & 3;
+        dstoff[j] = (uint32_t)(r * kRowStride + ((piece ^ (((r >> 1) & 1) << 1)) * 16));
+        rloc[j] = SWIGLU ? (r & 7) : r;
+        cbase[j] = ((SWIGLU && r >= 8) ? p.codes2 : p.codes) + piece * 16;
+    }
+    const int srow = lane >> 1;
+    const int sloc = SWIGLU ? (srow & 7) : srow;
+    const float* sbase = ((SWIGLU && srow >= 8) ? p.scales2 : p.scales) + (lane & 1);
+    const uint32_t sdst = (uint32_t)(kRows * kRowStride + lane * 4);
 
     // flat (tile, pair) sequence of this warp, with a cursor running DEPTH-1 items ahead
     int itile = blockIdx.x, ipi = warp, islot = 0;
+    const int8_t* csrc[2]; const float* ssrc;
+    auto set_issue_tile = [&]() {
+#pragma unroll
+        for (int j = 0; j < 2; j++) csrc[j] = cbase[j] + (size_t)min(itile * rowsPerTile + rloc[j], p.N - 1) * p.Kp;
+        ssrc = sbase + (size_t)min(itile * rowsPerTile + sloc, p.N - 1) * p.nb;
+    };
+    set_issue_tile();
     auto issue_next = [&]() {
         if (itile < nTiles && ipi < nPairs) {
-            issue(itile, ipi, islot);
+            const uint32_t dst = ring_s + (uint32_t)islot * kSlotBytes;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + dstoff[0]), "l"(csrc[0] + ipi * 64) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + dstoff[1]), "l"(csrc[1] + ipi * 64) : "memory");
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + sdst), "l"(ssrc + ipi * 2) : "memory");
             ipi += kWarps;
-            if (ipi >= nPairs) { ipi = warp; itile += gridDim.x; }
+            if (ipi >= nPairs) { ipi = warp; itile += gridDim.x; set_issue_tile(); }
         }
         cp_async_commit();
         islot = islot + 1 == DEPTH ? 0 : islot + 1;
@@ -254,9 +260,11 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     const float* myxsc = xsc + (size_t)((t >> 1) < p.M ? (t >> 1) : 0) * nBlocks;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     int cslot = 0, buf = 0;
+    int aoff[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) aoff[h] = g * kRowStride + (h ^ ((g >> 1) & 1)) * 32 + t * 8;
+    const int soff = kRows * kRowStride + g * 8;      // scales of row g: two floats; row g+8 is 64 bytes on
     for (int tile = blockIdx.x; tile < nTiles; tile += gridDim.x) {
-        const int row0 = tile * rowsPerTile + g;
-        const bool v0ok = row0 < p.N, v1ok = SWIGLU ? v0ok : (row0 + 8 < p.N);   // absent rows leave stale slot bytes
         // epilogue operands are fetched now so that their latency hides behind the tile
         const int er = tid % rowsPerTile, em = tid / rowsPerTile, en = tile * rowsPerTile + er;
         float ebias = 0.0f, ebias2 = 0.0f, eres = 0.0f;
@@ -270,15 +278,12 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
             cp_async_wait<DEPTH - 1>();
             __syncwarp();
             const unsigned char* slot = myring + (size_t)cslot * kSlotBytes;
-            const float* sc = reinterpret_cast<const float*>(slot + kRows * kRowStride);
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                const int hs = (h ^ ((g >> 1) & 1)) * 32 + t * 8;      // rows g and g+8 share the swizzle bit
-                uint2 a = *reinterpret_cast<const uint2*>(slot + g * kRowStride + hs);
-                uint2 d = *reinterpret_cast<const uint2*>(slot + (g + 8) * kRowStride + hs);
-                float s0 = sc[g * 2 + h], s1 = sc[(g + 8) * 2 + h];
-                if (!v0ok) { a = make_uint2(0u, 0u); s0 = 0.0f; }
-                if (!v1ok) { d = make_uint2(0u, 0u); s1 = 0.0f; }
+                const uint2 a = *reinterpret_cast<const uint2*>(slot + aoff[h]);
+                const uint2 d = *reinterpret_cast<const uint2*>(slot + aoff[h] + 8 * kRowStride);   // row g+8: same swizzle bit
+                const float s0 = *reinterpret_cast<const float*>(slot + soff + h * 4);
+                const float s1 = *reinterpret_cast<const float*>(slot + soff + 64 + h * 4);
                 const int blk = pi * 2 + h;
                 uint2 xb = make_uint2(0u, 0u);
                 if (hasCol) xb = *reinterpret_cast<const uint2*>(xcol + blk * 32);
