@@ -27,7 +27,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 constexpr int kAttnWarps = 4;
 
 template <int LPP>   // lanes per position = hd / 16
-__global__ void __launch_bounds__(kAttnWarps * 32) k_attn_decode(
+__global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
         const float* __restrict__ qkv, int q_off, int k_off, int v_off, int ld,
         float* __restrict__ kcache, float* __restrict__ vcache, int maxSeq,
         const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
@@ -53,42 +53,35 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_decode(
     const int end = min(seq, start + chunk);
     const int half = HD >> 1;
 
-    // this lane's 8 rotation pairs at the current position
-    float cs[8], sn[8];
-    {
+    // rotate 8 interleaved pairs held in v[16] by the table row of the current position
+    auto rotate = [&](float (&v)[16]) {
         const float4* cp = reinterpret_cast<const float4*>(cosT + (size_t)pos * half + gl * 8);
         const float4* sp = reinterpret_cast<const float4*>(sinT + (size_t)pos * half + gl * 8);
 #pragma unroll
         for (int j = 0; j < 2; j++) {
-            float4 c4 = cp[j], s4 = sp[j];
-            cs[4 * j] = c4.x; cs[4 * j + 1] = c4.y; cs[4 * j + 2] = c4.z; cs[4 * j + 3] = c4.w;
-            sn[4 * j] = s4.x; sn[4 * j + 1] = s4.y; sn[4 * j + 2] = s4.z; sn[4 * j + 3] = s4.w;
+            const float4 c4 = cp[j], s4 = sp[j];
+            const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float x0 = v[8 * j + 2 * i], x1 = v[8 * j + 2 * i + 1];
+                v[8 * j + 2 * i] = x0 * cs[i] - x1 * sn[i];
+                v[8 * j + 2 * i + 1] = x0 * sn[i] + x1 * cs[i];
+            }
         }
-    }
+    };
     const float* rowp = qkv + (size_t)b * ld;
     float q[16];
     {
         const float4* qp = reinterpret_cast<const float4*>(rowp + q_off + h * HD + gl * 16);
 #pragma unroll
         for (int j = 0; j < 4; j++) { float4 v = qp[j]; q[4 * j] = v.x; q[4 * j + 1] = v.y; q[4 * j + 2] = v.z; q[4 * j + 3] = v.w; }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            float x0 = q[2 * i], x1 = q[2 * i + 1];
-            q[2 * i] = x0 * cs[i] - x1 * sn[i];
-            q[2 * i + 1] = x0 * sn[i] + x1 * cs[i];
-        }
+        rotate(q);
     }
     float* kbase = kcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
     float* vbase = vcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
 
-    float m = -INFINITY, l = 0.0f, acc[16];
-#pragma unroll
-    for (int j = 0; j < 16; j++) acc[j] = 0.0f;
-
-    for (int base = start + warp * PPW; base < end; base += G) {
-        const int p = base + group;
-        const bool valid = p < end;
-        float kf[16], vf[16];
+    // K and V slices of position p for this lane (zeros when the lane has no position)
+    auto fetch = [&](int p, bool valid, float (&kf)[16], float (&vf)[16]) {
         if (valid && p == pos) {
             // the new token: k and v come from the projections; rotate k, append both to the cache
             const float4* kp = reinterpret_cast<const float4*>(rowp + k_off + h * HD + gl * 16);
@@ -99,12 +92,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_decode(
                 kf[4 * j] = a.x; kf[4 * j + 1] = a.y; kf[4 * j + 2] = a.z; kf[4 * j + 3] = a.w;
                 vf[4 * j] = c.x; vf[4 * j + 1] = c.y; vf[4 * j + 2] = c.z; vf[4 * j + 3] = c.w;
             }
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                float x0 = kf[2 * i], x1 = kf[2 * i + 1];
-                kf[2 * i] = x0 * cs[i] - x1 * sn[i];
-                kf[2 * i + 1] = x0 * sn[i] + x1 * cs[i];
-            }
+            rotate(kf);
             float4* kd = reinterpret_cast<float4*>(kbase + (size_t)p * HD);
             float4* vd = reinterpret_cast<float4*>(vbase + (size_t)p * HD);
 #pragma unroll
@@ -125,6 +113,20 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_decode(
 #pragma unroll
             for (int j = 0; j < 16; j++) { kf[j] = 0.0f; vf[j] = 0.0f; }
         }
+    };
+
+    float m = -INFINITY, l = 0.0f, acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) acc[j] = 0.0f;
+
+    // the loads of the next group of positions are in flight while this one is folded in
+    float kf[16], vf[16], kn[16], vn[16];
+    int base = start + warp * PPW;
+    if (base < end) fetch(base + group, base + group < end, kf, vf);
+    for (; base < end; base += G) {
+        const bool valid = base + group < end;
+        const int nbase = base + G;
+        if (nbase < end) fetch(nbase + group, nbase + group < end, kn, vn);
         float dot = 0.0f;
 #pragma unroll
         for (int j = 0; j < 16; j++) dot = fmaf(q[j], kf[j], dot);
@@ -140,6 +142,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_decode(
             for (int j = 0; j < 16; j++) acc[j] = fmaf(pe, vf[j], acc[j] * corr);
             m = mn;
         }
+#pragma unroll
+        for (int j = 0; j < 16; j++) { kf[j] = kn[j]; vf[j] = vn[j]; }
     }
     const int g = warp * PPW + group;
 #pragma unroll
