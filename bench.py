@@ -190,10 +190,10 @@ def main():
             pass
         else:
             raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
-    if world > 1:
-        raise SystemExit("tensor-parallel decode is not wired into bench.py yet")
-
     from deepj_b200.decoder import DecoderConfig, Q8Decoder
+    from deepj_b200 import tp
+    if world > 1:
+        tp.init_process_group()
 
     cfg = DecoderConfig(w["kind"], w["vocab"], w["max_seq"], w["d"], w["heads"], w["layers"], w["d_ff"],
                         w.get("q_rank", 0), w.get("kv_rank", 0))
@@ -201,7 +201,11 @@ def main():
     room = w["max_seq"] - w["prompt"] - 1          # decode steps that fit behind the prompt
     if room < 8:
         raise SystemExit("the context window of this workload leaves no room to decode")
-    dec = Q8Decoder(cfg, batch=B, device=local_rank)
+    dec = Q8Decoder(cfg, batch=B, device=local_rank, tp_rank=rank, tp_world=world)
+    if world > 1:
+        # weights are split by rows/columns over the ranks; [B x d] partial sums and the logits
+        # shards cross NVLink through the library's own peer-memory exchange kernel
+        tp.connect(rank, world, max(B * cfg.d_model, B * cfg.vocab_size // world))
     t_load = time.perf_counter()
     dec.load_synthetic(w["seed"], w["std"])
     rng = np.random.default_rng(w["seed"] + 1000)
@@ -233,15 +237,20 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     _lib.check(lib.deepj_cuda_synchronize())
+    if world > 1:
+        tp.barrier()
     st0 = dec.stats()
     _lib.check(lib.deepj_cuda_timer_begin())
     run_device(args.steps)
     ms = ctypes.c_float(0)
     _lib.check(lib.deepj_cuda_timer_end(ctypes.byref(ms)))
     _lib.check(lib.deepj_cuda_synchronize())
+    if world > 1:
+        tp.barrier()
     clocks = sampler.stop()
     st1 = dec.stats()
-    ms_per_step = ms.value / args.steps
+    elapsed_ms = tp.max_over_ranks(ms.value) if world > 1 else ms.value      # device time, max over ranks
+    ms_per_step = elapsed_ms / args.steps
     value = B * 1e3 / ms_per_step
     launches = (st1["graph_replays"] - st0["graph_replays"]) * st1["kernels_per_replay"] + (st1["eager_launches"] - st0["eager_launches"])
 
@@ -257,6 +266,8 @@ def main():
             dec.set_position(w["prompt"])
         tok = dec.step(tok)
     e2e_s = time.perf_counter() - t0
+    if world > 1:
+        e2e_s = tp.max_over_ranks(e2e_s)
     e2e = B * args.steps / e2e_s
     dec.set_position(min(ctx0 + min(args.steps, room) // 2, w["max_seq"] - 3))
 
@@ -268,46 +279,51 @@ def main():
 
     def q8b(k, n):
         return k * n + ((k + 31) // 32) * n * 4
-    d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
-    op_bytes = {"qkv": q8b(d, 3 * d) + 4 * B * (d + 3 * d), "wo": q8b(d, d) + 4 * B * 3 * d,
-                "swiglu": 2 * q8b(d, F) + 4 * B * (d + F), "down": q8b(F, d) + 4 * B * (F + 2 * d),
-                "lm_head": q8b(d, V) + 4 * B * (d + V)}
+    d = cfg.d_model
+    dl, Fl, Vl = d // world, cfg.d_ff // world, cfg.vocab_size // world      # this rank's shard
+    op_bytes = {"qkv": q8b(d, 3 * dl) + 4 * B * (d + 3 * dl), "wo": q8b(dl, d) + 4 * B * (dl + 2 * d),
+                "swiglu": 2 * q8b(d, Fl) + 4 * B * (d + Fl), "down": q8b(Fl, d) + 4 * B * (Fl + 2 * d),
+                "lm_head": q8b(d, Vl) + 4 * B * (d + Vl)}
     if cfg.kind == "deepseek":
         r = cfg.q_rank + cfg.kv_rank
-        op_bytes.update({"mla_down": q8b(d, r) + 4 * B * (d + r), "mla_up_q": q8b(cfg.q_rank, d) + 4 * B * (cfg.q_rank + d),
-                         "mla_up_kv": q8b(cfg.kv_rank, 2 * d) + 4 * B * (cfg.kv_rank + 2 * d)})
+        op_bytes.update({"mla_down": q8b(d, r) + 4 * B * (d + r), "mla_up_q": q8b(cfg.q_rank, dl) + 4 * B * (cfg.q_rank + dl),
+                         "mla_up_kv": q8b(cfg.kv_rank, 2 * dl) + 4 * B * (cfg.kv_rank + 2 * dl)})
     gemv_ms = sum(t for lbl, t in prof if lbl in op_bytes)
     gemv_bytes = sum(op_bytes[lbl] for lbl, _ in prof if lbl in op_bytes)
     n_gemv = sum(1 for lbl, _ in prof if lbl in op_bytes)
     attn_ms = sum(t for lbl, t in prof if lbl == "attn")
+    exch_ms = sum(t for lbl, t in prof if lbl in ("allreduce", "allgather"))
     total_prof_ms = sum(t for _, t in prof)
     achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9
     ctx = min(ctx0 + min(args.steps, room) // 2, w["max_seq"] - 3)
-    step_bytes = cfg.q8_weight_bytes() + B * ctx * cfg.kv_bytes_per_position()
-    step_achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    step_bytes = cfg.q8_weight_bytes() + B * ctx * cfg.kv_bytes_per_position()      # whole job, all ranks
+    step_achieved = step_bytes / world / (ms_per_step * 1e-3) / 1e9                  # per GPU
 
     line = {
         "metric": "q8_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "q8 weights, f32 activations/accumulate", "data": "synthetic",
         "config": {"workload": args.workload, "batch": B, "prompt_len": w["prompt"], "context_at_timing": ctx,
-                   "parallelism": "tp1", "kv_cache": "f32", "l2": "weights+KV per step exceed L2 (inputs larger than L2)"},
+                   "parallelism": f"tp{world}", "kv_cache": "f32", "l2": "weights+KV per step exceed L2 (inputs larger than L2)"},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind, "kernel": "k_q8_gemv", "launches_per_step": n_gemv,
                      "bytes_per_step": gemv_bytes, "ms_per_step_op_by_op": gemv_ms},
-        "roofline_step": {"bytes_per_token": step_bytes, "achieved": step_achieved, "frac": step_achieved / peak,
-                          "roofline_tokens_per_s": B * peak * 1e9 / step_bytes},
-        "profile_ms": {"gemv": gemv_ms, "attention": attn_ms, "all_ops": total_prof_ms},
+        "roofline_step": {"bytes_per_token": step_bytes, "achieved_per_gpu": step_achieved, "frac": step_achieved / peak,
+                          "roofline_tokens_per_s": B * world * peak * 1e9 / step_bytes},
+        "profile_ms": {"gemv": gemv_ms, "attention": attn_ms, "exchange": exch_ms, "all_ops": total_prof_ms},
         "setup_s": t_load,
     }
     if not args.no_cpu_baseline and rank == 0:
         v, used, sample = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": used, "kind": "port", "sample": sample}
-    print(json.dumps(line), flush=True)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     dec.close()
+    if world > 1:
+        tp.disconnect()
 
 
 if __name__ == "__main__":

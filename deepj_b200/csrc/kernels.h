@@ -106,6 +106,13 @@ void launch_copy(const float* src, float* dst, long long n, cudaStream_t s);
 void launch_synth_fill(float* out, unsigned long long seed, unsigned long long ordinal, float std_dev,
                        long long first, long long n, cudaStream_t s);
 
+// ── tensor-parallel exchange over peer memory (tp.cu) ──
+bool tp_ready();
+int tp_world();
+// mode 0: out = residual + bias + Σ_ranks in (all-reduce); mode 1: out[m][r·n_local + j] = in_r[m][j] (all-gather)
+void launch_tp_exchange(const float* in, const float* bias, const float* residual, float* out, int M, int n_local, int mode,
+                        cudaStream_t s);
+
 // Read-only views of the runtime's buffer pool for entry points that live beside their kernels.
 struct PoolF32 { float* ptr; size_t floats; };
 struct PoolKV { float* ptr; int layers, B, H, maxSeq, hd; };

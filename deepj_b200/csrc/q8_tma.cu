@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     const int rowsPerTile = SWIGLU ? 8 : 16;
     const int nTiles = (p.N + rowsPerTile - 1) / rowsPerTile;
     const int nBlocks = p.K >> 5;
-    const int nPairs = p.K >> 6;
+    const int nPairs = (nBlocks + 1) >> 1;      // an odd block count leaves the last pair half empty
     unsigned char* myring = smem + (size_t)warp * DEPTH * kSlotBytes;
     const bool tracing = p.trace != nullptr && blockIdx.x == 0 && tid == 0;
     if (tracing) p.trace[0] = gtime();
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
             const uint32_t dst = ring_s + (uint32_t)islot * kSlotBytes;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + dstoff[0]), "l"(csrc[0] + ipi * 64) : "memory");
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + dstoff[1]), "l"(csrc[1] + ipi * 64) : "memory");
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + sdst), "l"(ssrc + ipi * 2) : "memory");
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + sdst), "l"(ssrc + min(ipi * 2, nBlocks - 1 - (lane & 1))) : "memory");
             ipi += kWarps;
             if (ipi >= nPairs) { ipi = warp; itile += gridDim.x; set_issue_tile(); }
         }
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
                 if (hasCol) xb = *reinterpret_cast<const uint2*>(xcol + blk * 32);
                 int cc[4] = {0, 0, 0, 0};
                 mma_s8_16832(cc, a.x, d.x, a.y, d.y, xb.x, xb.y);
-                const float xs_ = myxsc[blk];
+                const float xs_ = blk < nBlocks ? myxsc[blk] : 0.0f;     // the empty half of an odd last pair adds nothing
                 const float f0 = s0 * xs_, f1 = s1 * xs_;
                 acc[0] = fmaf(f0, (float)cc[0], acc[0]);
                 acc[1] = fmaf(f0, (float)cc[1], acc[1]);
@@ -373,7 +373,7 @@ void launch_i8_depth(const TmaParams& p, int depth, cudaStream_t s) {
 // shared memory: the ring takes what the activation digits leave.
 bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s) {
     const int K = a.w.K;
-    if (K % 256 != 0 || a.w.Kp != K) return false;
+    if (K % 32 != 0 || a.w.Kp != K) return false;
     const bool swiglu = a.w2.codes != nullptr;
     const size_t budget = 111 * 1024;
     if (i8_smem_bytes(K, 1, 3) > budget) return false;

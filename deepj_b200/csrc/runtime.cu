@@ -160,6 +160,8 @@ int op_stride(int op) {
         case DEEPJ_OP_ARGMAX_ROWS: return 5;
         case DEEPJ_OP_ADD_SCALAR_INPLACE: return 4;
         case DEEPJ_OP_COPY: return 6;
+        case DEEPJ_OP_TP_ALLREDUCE: return 7;
+        case DEEPJ_OP_TP_ALLGATHER: return 5;
         default: return -1;
     }
 }
@@ -361,6 +363,24 @@ void do_op(Ctx& ctx, const int32_t* c) {
             int so = c[2], dof = c[4], n = c[5]; require(so >= 0 && dof >= 0 && n >= 0, "copy", "bad offset or count");
             const float* src = f32(ctx, c[1], (size_t)so + n, "copy") + so; float* dst = f32(ctx, c[3], (size_t)dof + n, "copy") + dof;
             if (go) launch_copy(src, dst, n, s);
+            break;
+        }
+        case DEEPJ_OP_TP_ALLREDUCE: {   // [op, in, bias, residual, out, M, N]
+            int M = c[5], N = c[6]; require(M >= 1 && N >= 1, "tpAllReduce", "bad dimension");
+            require(tp_ready(), "tpAllReduce", "deepj_cuda_tp_connect has not been called");
+            const float* in = f32(ctx, c[1], sz(M, N), "tpAllReduce");
+            const float* bias = f32_opt(ctx, c[2], N, "tpAllReduce");
+            const float* res = f32_opt(ctx, c[3], sz(M, N), "tpAllReduce");
+            float* o = f32(ctx, c[4], sz(M, N), "tpAllReduce");
+            if (go) launch_tp_exchange(in, bias, res, o, M, N, 0, s);
+            break;
+        }
+        case DEEPJ_OP_TP_ALLGATHER: {   // [op, in, out, M, n_local]
+            int M = c[3], nl = c[4]; require(M >= 1 && nl >= 1, "tpAllGather", "bad dimension");
+            require(tp_ready(), "tpAllGather", "deepj_cuda_tp_connect has not been called");
+            const float* in = f32(ctx, c[1], sz(M, nl), "tpAllGather");
+            float* o = f32(ctx, c[2], sz(M, nl) * tp_world(), "tpAllGather");
+            if (go) launch_tp_exchange(in, nullptr, nullptr, o, M, nl, 1, s);
             break;
         }
         default:

@@ -22,7 +22,7 @@ import numpy as np
 
 from . import _lib
 from .compute_graph import (OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_COPY, OP_EMBED_GATHER,
-                            OP_Q8_LINEAR, OP_Q8_SWIGLU, float_bits)
+                            OP_Q8_LINEAR, OP_Q8_SWIGLU, OP_TP_ALLGATHER, OP_TP_ALLREDUCE, float_bits)
 
 RMS_EPS = 1e-6      # layers/transformer/norm/RMSNorm1D.java:30
 
@@ -104,6 +104,23 @@ def rope_tables(head_dim: int, max_seq: int):
     return cos, sin
 
 
+def shard_plan(cfg: DecoderConfig, rank: int, world: int) -> List[tuple]:
+    """(device object, K_local, [(reference name, first row, first column, columns)]) of one block for
+    one tensor-parallel rank.  Megatron-style split: Wq/Wk/Wv (or MLA's up-projections), gate and up
+    by output columns (whole heads per rank); Wo and down by reduction rows — every split lands on a
+    32-element Q8 block boundary.  MLA's low-rank down-projections are replicated."""
+    c, r = cfg, rank
+    d, dl, Fl = c.d_model, c.d_model // world, c.d_ff // world
+    if c.kind == "llama":
+        plan = [("Wqkv", d, [("Wq", 0, r * dl, dl), ("Wk", 0, r * dl, dl), ("Wv", 0, r * dl, dl)])]
+    else:
+        plan = [("Wdqkv", d, [("Wdq", 0, 0, c.q_rank), ("Wdkv", 0, 0, c.kv_rank)]),
+                ("Wuq", c.q_rank, [("Wuq", 0, r * dl, dl)]),
+                ("Wukv", c.kv_rank, [("Wuk", 0, r * dl, dl), ("Wuv", 0, r * dl, dl)])]
+    return plan + [("Wo", dl, [("Wo", r * dl, 0, d)]), ("Wg", d, [("Wg", 0, r * Fl, Fl)]),
+                   ("Wu", d, [("Wu", 0, r * Fl, Fl)]), ("Wd", Fl, [("Wd", r * Fl, 0, d)])]
+
+
 class Q8Decoder:
     """Owns the device-side weights, KV cache and the per-token command stream.
 
@@ -111,9 +128,22 @@ class Q8Decoder:
     `ComputeGraph` hands out (those start at 0).
     """
 
-    def __init__(self, cfg: DecoderConfig, batch: int = 1, device: int = 0, id_base: int = 1 << 24):
+    def __init__(self, cfg: DecoderConfig, batch: int = 1, device: int = 0, id_base: int = 1 << 24,
+                 tp_rank: int = 0, tp_world: int = 1):
         self.cfg = cfg
         self.B = int(batch)
+        if tp_world < 1 or not (0 <= tp_rank < tp_world):
+            raise ValueError("bad tensor-parallel rank / world size")
+        if cfg.n_heads % tp_world or cfg.d_ff % tp_world or cfg.vocab_size % tp_world or (cfg.d_ff // tp_world) % 32 or \
+                (cfg.d_model // tp_world) % 32:
+            raise ValueError("heads, dFF and vocab must divide by the tensor-parallel size, on 32-element block boundaries")
+        self.tp_rank, self.tp_world = int(tp_rank), int(tp_world)
+        self.h_local = cfg.n_heads // tp_world
+        self.d_local = cfg.d_model // tp_world
+        self.f_local = cfg.d_ff // tp_world
+        self.v_local = cfg.vocab_size // tp_world
+        self._ref_shapes = {n: (k, w) for n, k, w in cfg.matmul_shapes()}
+        self._ref_shapes["Wlm"] = (cfg.d_model, cfg.vocab_size)
         self.lib = _lib.load()
         _lib.check(self.lib.deepj_cuda_init(device))
         self._next_id = id_base
@@ -170,34 +200,24 @@ class Q8Decoder:
         self._f32("pos", B)              # write position of every sequence
         self._f32("x", B * d)
         self._f32("x2", B * d)
-        self._f32("qkv", B * 3 * d)
-        self._f32("att", B * d)
-        self._f32("h", B * c.d_ff)
+        self._f32("qkv", B * 3 * self.d_local)
+        self._f32("att", B * self.d_local)
+        self._f32("h", B * self.f_local)
         self._f32("logits", B * c.vocab_size)
+        if self.tp_world > 1:
+            self._f32("part", B * d)
+            self._f32("logits_local", B * self.v_local)
         self._f32("next", B)
         if c.kind == "deepseek":
             self._f32("lat", B * (c.q_rank + c.kv_rank))
         kv = self._new_id()
-        _lib.check(self.lib.deepj_cuda_kv_alloc(kv, c.n_layers, B, c.n_heads, c.max_seq_len, c.head_dim))
+        _lib.check(self.lib.deepj_cuda_kv_alloc(kv, c.n_layers, B, self.h_local, c.max_seq_len, c.head_dim))
         self.ids["kv"] = kv
 
     # ── weights ──
-    def _q8_from_parts(self, name: str, K: int, parts: List[Callable[[int], None]], widths: List[int]) -> None:
-        """Allocate a Q8 object [K × ΣN] and quantize each part into its column range.
-        `parts[i](tmp_id)` must fill the float buffer tmp_id with the [K × widths[i]] matrix."""
-        q = self._new_id()
-        _lib.check(self.lib.deepj_cuda_q8_alloc(q, K, sum(widths)))
-        col = 0
-        for fill, n in zip(parts, widths):
-            tmp = self._f32("", K * n)
-            fill(tmp)
-            _lib.check(self.lib.deepj_cuda_q8_quantize_into(q, col, tmp, 0, 0, n, n))
-            self._release([tmp])
-            col += n
-        self.ids[name] = q
-
     def _layer_plan(self) -> List[tuple]:
-        """(device object name, K, [reference weight names concatenated along N])."""
+        """(device object name, K, [reference weight names concatenated along N]) of the
+        unsharded model."""
         c = self.cfg
         d = c.d_model
         if c.kind == "llama":
@@ -207,6 +227,41 @@ class Q8Decoder:
                     ("Wo", d, ["Wo"])]
         return plan + [("Wg", d, ["Wg"]), ("Wu", d, ["Wu"]), ("Wd", c.d_ff, ["Wd"])]
 
+    def _shard_plan(self) -> List[tuple]:
+        return shard_plan(self.cfg, self.tp_rank, self.tp_world)
+
+    def _q8_from_parts(self, name: str, K: int, parts: List[tuple], fill: Callable[[str, int], None]) -> None:
+        """Allocate a Q8 object [K × ΣN] and quantize each window into its column range.
+        `fill(ref_name, tmp_id)` must fill the float buffer tmp_id with the whole reference matrix."""
+        shapes = self._ref_shapes
+        q = self._new_id()
+        _lib.check(self.lib.deepj_cuda_q8_alloc(q, K, sum(p[3] for p in parts)))
+        col = 0
+        for ref, k0, n0, n in parts:
+            rows, cols = shapes[ref]
+            tmp = self._f32("", rows * cols)
+            fill(ref, tmp)
+            _lib.check(self.lib.deepj_cuda_q8_quantize_into(q, col, tmp, k0, n0, cols, n))
+            self._release([tmp])
+            col += n
+        self.ids[name] = q
+
+    def _load(self, fill_layer: Callable[[int], Callable[[str, int], None]], vec: Callable[[str, int, int], np.ndarray]) -> None:
+        c, r = self.cfg, self.tp_rank
+        Fl, Vl = self.f_local, self.v_local
+        for l in range(c.n_layers):
+            self._f32(f"g1.{l}", c.d_model, vec("g1", l, c.d_model))
+            self._f32(f"g2.{l}", c.d_model, vec("g2", l, c.d_model))
+            for obj, K, parts in self._shard_plan():
+                self._q8_from_parts(f"{obj}.{l}", K, parts, fill_layer(l))
+            self._f32(f"bg.{l}", Fl, vec("bg", l, c.d_ff)[r * Fl:(r + 1) * Fl])
+            self._f32(f"bu.{l}", Fl, vec("bu", l, c.d_ff)[r * Fl:(r + 1) * Fl])
+            self._f32(f"bd.{l}", c.d_model, vec("bd", l, c.d_model))
+        self._f32("gF", c.d_model, vec("gF", -1, c.d_model))
+        self._q8_from_parts("Wlm", c.d_model, [("Wlm", 0, r * Vl, Vl)], fill_layer(-1))
+        self._f32("blm", Vl, vec("blm", -1, c.vocab_size)[r * Vl:(r + 1) * Vl])
+        self.loaded = True
+
     def load_weights(self, get: Callable[[str, int], np.ndarray]) -> None:
         """Upload fp32 weights and quantize them on the device.
 
@@ -214,23 +269,12 @@ class Q8Decoder:
         weights as [dIn × dOut] (layers/Linear.java:26), vectors 1-D.  Names: "emb",
         per layer "g1","g2", the block's matmul names (`DecoderConfig.matmul_shapes`),
         "bg","bu","bd"; then "gF","Wlm","blm" (layer = -1 for model-level tensors).
+        Under tensor parallelism every rank is given the full tensors and keeps its shard.
         """
         c = self.cfg
-        shapes = {n: (k, w) for n, k, w in c.matmul_shapes()}
         self._f32("emb", c.vocab_size * c.d_model, get("emb", -1))
-        for l in range(c.n_layers):
-            self._f32(f"g1.{l}", c.d_model, get("g1", l))
-            self._f32(f"g2.{l}", c.d_model, get("g2", l))
-            for obj, K, names in self._layer_plan():
-                fills = [(lambda tmp, nm=nm: self._upload(tmp, get(nm, l))) for nm in names]
-                self._q8_from_parts(f"{obj}.{l}", K, fills, [shapes[nm][1] for nm in names])
-            self._f32(f"bg.{l}", c.d_ff, get("bg", l))
-            self._f32(f"bu.{l}", c.d_ff, get("bu", l))
-            self._f32(f"bd.{l}", c.d_model, get("bd", l))
-        self._f32("gF", c.d_model, get("gF", -1))
-        self._q8_from_parts("Wlm", c.d_model, [lambda tmp: self._upload(tmp, get("Wlm", -1))], [c.vocab_size])
-        self._f32("blm", c.vocab_size, get("blm", -1))
-        self.loaded = True
+        self._load(lambda l: (lambda ref, tmp: self._upload(tmp, get(ref, l))),
+                   lambda name, l, n: np.asarray(get(name, l), dtype=np.float32).reshape(-1))
 
     def load_synthetic(self, seed: int, std: float) -> None:
         """Random-init weights of this architecture generated on the device with the
@@ -239,42 +283,25 @@ class Q8Decoder:
         head).  Norm gains are ones and biases zeros, as the reference initialises them."""
         c = self.cfg
         per_layer = c.matmul_shapes()
-        ordinal_of = {}
-        for l in range(c.n_layers):
-            for j, (nm, _, _) in enumerate(per_layer):
-                ordinal_of[(nm, l)] = 1 + l * len(per_layer) + j
-        lm_ordinal = 1 + c.n_layers * len(per_layer)
-        shapes = {n: (k, w) for n, k, w in per_layer}
+        shapes = self._ref_shapes
 
-        def synth(ordinal, n):
-            def fill(tmp):
-                _lib.check(self.lib.deepj_cuda_synth_fill(tmp, seed, ordinal, std, 0, n))
+        def fill_layer(l):
+            def fill(ref, tmp):
+                ordinal = 1 + c.n_layers * len(per_layer) if ref == "Wlm" else \
+                    1 + l * len(per_layer) + [n for n, _, _ in per_layer].index(ref)
+                _lib.check(self.lib.deepj_cuda_synth_fill(tmp, seed, ordinal, std, 0, shapes[ref][0] * shapes[ref][1]))
             return fill
 
         emb = self._f32("emb", c.vocab_size * c.d_model)
         _lib.check(self.lib.deepj_cuda_synth_fill(emb, seed, 0, std, 0, c.vocab_size * c.d_model))
-        ones = np.ones(c.d_model, dtype=np.float32)
-        for l in range(c.n_layers):
-            self._f32(f"g1.{l}", c.d_model, ones)
-            self._f32(f"g2.{l}", c.d_model, ones)
-            for obj, K, names in self._layer_plan():
-                fills = [synth(ordinal_of[(nm, l)], K * shapes[nm][1]) for nm in names]
-                self._q8_from_parts(f"{obj}.{l}", K, fills, [shapes[nm][1] for nm in names])
-            self._f32(f"bg.{l}", c.d_ff)
-            self._f32(f"bu.{l}", c.d_ff)
-            self._f32(f"bd.{l}", c.d_model)
-        self._f32("gF", c.d_model, ones)
-        self._q8_from_parts("Wlm", c.d_model, [synth(lm_ordinal, c.d_model * c.vocab_size)], [c.vocab_size])
-        self._f32("blm", c.vocab_size)
-        self.loaded = True
+        self._load(fill_layer, lambda name, l, n: (np.ones(n, dtype=np.float32) if name.startswith("g") else np.zeros(n, dtype=np.float32)))
 
     def q8_arrays(self, name: str):
         """Canonical (codes[N][K] int8, scales[N][ceil(K/32)] fp32) of a device Q8 object."""
         c = self.cfg
-        K = {o: k for o, k, _ in self._layer_plan()}.get(name.split(".")[0], c.d_model)
-        shapes = {n: w for n, _, w in c.matmul_shapes()}
-        widths = {o: sum(shapes[n] for n in names) for o, _, names in self._layer_plan()}
-        N = widths.get(name.split(".")[0], c.vocab_size)
+        base = name.split(".")[0]
+        plan = {o: (k, sum(p[3] for p in parts)) for o, k, parts in self._shard_plan()}
+        K, N = plan.get(base, (c.d_model, self.v_local))
         codes = np.empty((N, K), dtype=np.int8)
         scales = np.empty((N, (K + 31) // 32), dtype=np.float32)
         _lib.check(self.lib.deepj_cuda_q8_download(self.ids[name], codes.ctypes.data, scales.ctypes.data))
@@ -283,7 +310,9 @@ class Q8Decoder:
     # ── the per-token stream ──
     def _build(self, feed_back: bool) -> np.ndarray:
         c, B, I = self.cfg, self.B, self.ids
-        d, F, V = c.d_model, c.d_ff, c.vocab_size
+        d, V = c.d_model, c.vocab_size
+        dl, Fl, Vl, Hl = self.d_local, self.f_local, self.v_local, self.h_local
+        tp = self.tp_world > 1
         eps = float_bits(RMS_EPS)
         s: List[int] = []
         labels: List[str] = []
@@ -298,19 +327,32 @@ class Q8Decoder:
         op("embed", OP_EMBED_GATHER, I["emb"], I["tok"], I["x"], B, d, V)
         for l in range(c.n_layers):
             if c.kind == "llama":
-                linear("qkv", I["x"], 0, d, I[f"g1.{l}"], I[f"Wqkv.{l}"], -1, -1, 0, 0, I["qkv"], 0, 3 * d)
+                linear("qkv", I["x"], 0, d, I[f"g1.{l}"], I[f"Wqkv.{l}"], -1, -1, 0, 0, I["qkv"], 0, 3 * dl)
             else:
                 r = c.q_rank + c.kv_rank
                 linear("mla_down", I["x"], 0, d, I[f"g1.{l}"], I[f"Wdqkv.{l}"], -1, -1, 0, 0, I["lat"], 0, r)
-                linear("mla_up_q", I["lat"], 0, r, -1, I[f"Wuq.{l}"], -1, -1, 0, 0, I["qkv"], 0, 3 * d)
-                linear("mla_up_kv", I["lat"], c.q_rank, r, -1, I[f"Wukv.{l}"], -1, -1, 0, 0, I["qkv"], d, 3 * d)
-            op("attn", OP_ATTN_DECODE, I["qkv"], 0, d, 2 * d, 3 * d, I["kv"], l, I["pos"], I["cos"], I["sin"],
-               I["att"], 0, d, B, c.n_heads, c.head_dim)
-            linear("wo", I["att"], 0, d, -1, I[f"Wo.{l}"], -1, I["x"], 0, d, I["x2"], 0, d)
+                linear("mla_up_q", I["lat"], 0, r, -1, I[f"Wuq.{l}"], -1, -1, 0, 0, I["qkv"], 0, 3 * dl)
+                linear("mla_up_kv", I["lat"], c.q_rank, r, -1, I[f"Wukv.{l}"], -1, -1, 0, 0, I["qkv"], dl, 3 * dl)
+            op("attn", OP_ATTN_DECODE, I["qkv"], 0, dl, 2 * dl, 3 * dl, I["kv"], l, I["pos"], I["cos"], I["sin"],
+               I["att"], 0, dl, B, Hl, c.head_dim)
+            if tp:
+                # row-parallel: every rank holds a partial sum; the exchange adds them (+ residual, + bias)
+                linear("wo", I["att"], 0, dl, -1, I[f"Wo.{l}"], -1, -1, 0, 0, I["part"], 0, d)
+                op("allreduce", OP_TP_ALLREDUCE, I["part"], -1, I["x"], I["x2"], B, d)
+            else:
+                linear("wo", I["att"], 0, dl, -1, I[f"Wo.{l}"], -1, I["x"], 0, d, I["x2"], 0, d)
             op("swiglu", OP_Q8_SWIGLU, I["x2"], 0, d, I[f"g2.{l}"], eps, I[f"Wg.{l}"], I[f"bg.{l}"], I[f"Wu.{l}"],
-               I[f"bu.{l}"], I["h"], 0, F, B)
-            linear("down", I["h"], 0, F, -1, I[f"Wd.{l}"], I[f"bd.{l}"], I["x2"], 0, d, I["x"], 0, d)
-        linear("lm_head", I["x"], 0, d, I["gF"], I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0, V)
+               I[f"bu.{l}"], I["h"], 0, Fl, B)
+            if tp:
+                linear("down", I["h"], 0, Fl, -1, I[f"Wd.{l}"], -1, -1, 0, 0, I["part"], 0, d)
+                op("allreduce", OP_TP_ALLREDUCE, I["part"], I[f"bd.{l}"], I["x2"], I["x"], B, d)
+            else:
+                linear("down", I["h"], 0, Fl, -1, I[f"Wd.{l}"], I[f"bd.{l}"], I["x2"], 0, d, I["x"], 0, d)
+        if tp:
+            linear("lm_head", I["x"], 0, d, I["gF"], I["Wlm"], I["blm"], -1, 0, 0, I["logits_local"], 0, Vl)
+            op("allgather", OP_TP_ALLGATHER, I["logits_local"], I["logits"], B, Vl)
+        else:
+            linear("lm_head", I["x"], 0, d, I["gF"], I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0, V)
         op("argmax", OP_ARGMAX_ROWS, I["logits"], I["next"], B, V)
         op("advance", OP_ADD_SCALAR_INPLACE, I["pos"], float_bits(1.0), B)
         if feed_back:

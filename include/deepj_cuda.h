@@ -109,6 +109,17 @@ int deepj_cuda_synth_fill(int32_t id, uint64_t seed, uint64_t ordinal, float std
 int deepj_cuda_kv_alloc(int32_t kv_id, int32_t layers, int32_t batch, int32_t heads,
                         int32_t max_seq, int32_t head_dim);
 
+/* Tensor parallelism, one process per GPU of one node.  No counterpart in the reference
+ * (DeepJ is single-device).  Every rank calls tp_create (allocates its exchange buffer:
+ * 2 x world slots of slot_floats floats plus flags, returns a 64-byte CUDA IPC handle),
+ * the host exchanges the handles by any means (the Python runner uses torch.distributed),
+ * then every rank calls tp_connect with all handles in rank order.  After that op codes 71
+ * and 72 may appear in streams; every rank must flush the same sequence of them.  Waits
+ * inside the exchange kernel are bounded; an expired wait sets stats counter [5]. */
+int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void* handle_out64);
+int deepj_cuda_tp_connect(const void* handles, int32_t world);
+int deepj_cuda_tp_destroy(void);
+
 /* Decode attention for callers that must not allocate.  No counterpart in the reference.
  *
  * Some hosts of this library cannot let a call reach cudaMalloc: a JVM thread inside a
@@ -145,6 +156,8 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
  *  68 ARGMAX_ROWS       [op, in, out, rows, cols]      lowest index among equal maxima
  *  69 ADD_SCALAR_INPLACE[op, buf, valueBits, n]         buf[i] += value (advances positions)
  *  70 COPY              [op, src, src_off, dst, dst_off, n]
+ *  71 TP_ALLREDUCE      [op, in, bias, residual, out, M, N]   out = residual + bias + sum over ranks of in (rank order)
+ *  72 TP_ALLGATHER      [op, in, out, M, n_local]             out[m][r*n_local + j] = in of rank r
  */
 #define DEEPJ_OP_EMBED_GATHER        64
 #define DEEPJ_OP_Q8_LINEAR           65
@@ -153,6 +166,8 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
 #define DEEPJ_OP_ARGMAX_ROWS         68
 #define DEEPJ_OP_ADD_SCALAR_INPLACE  69
 #define DEEPJ_OP_COPY                70
+#define DEEPJ_OP_TP_ALLREDUCE        71
+#define DEEPJ_OP_TP_ALLGATHER        72
 
 #ifdef __cplusplus
 }

@@ -124,7 +124,7 @@ def oracle_rmsnorm(x, gamma):
 
 
 @pytest.mark.parametrize("M,K,N", [(1, 256, 256), (1, 688, 256), (3, 256, 688), (1, 4096, 512), (2, 2048, 100),
-                                   (1, 11008, 64), (1, 100, 33), (1, 512, 2048), (1, 5632, 128), (6, 512, 40), (4, 4096, 24)])
+                                   (1, 11008, 64), (1, 100, 33), (1, 512, 2048), (1, 5632, 128), (6, 512, 40), (4, 4096, 24), (1, 1376, 64), (2, 96, 20), (1, 2752, 33)])
 @pytest.mark.parametrize("fused", ["plain", "norm_bias_res"])
 def test_q8_linear_matches_oracle(dev, M, K, N, fused):
     rng = np.random.default_rng(K * 7 + N + M)
