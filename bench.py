@@ -294,10 +294,18 @@ def main():
     attn_ms = sum(t for lbl, t in prof if lbl == "attn")
     exch_ms = sum(t for lbl, t in prof if lbl in ("allreduce", "allgather"))
     total_prof_ms = sum(t for _, t in prof)
-    achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9
+    # the same kernels back to back as their own graph-replayed stream: this is the launch duration the
+    # roofline line uses (the op-by-op profile adds an event and a drained pipeline to every launch)
+    gemv_stream_ms, n_gemv_stream = dec.time_ops(set(op_bytes), iters=10)
+    attn_stream_ms, n_attn = dec.time_ops({"attn"}, iters=10)
+    if world > 1:
+        gemv_stream_ms = tp.max_over_ranks(gemv_stream_ms)
+        attn_stream_ms = tp.max_over_ranks(attn_stream_ms)
+    achieved = gemv_bytes / (gemv_stream_ms * 1e-3) / 1e9
     ctx = min(ctx0 + min(args.steps, room) // 2, w["max_seq"] - 3)
     step_bytes = cfg.q8_weight_bytes() + B * ctx * cfg.kv_bytes_per_position()      # whole job, all ranks
     step_achieved = step_bytes / world / (ms_per_step * 1e-3) / 1e9                  # per GPU
+    attn_bytes = B * ctx * cfg.kv_bytes_per_position() // world                      # this rank's heads
 
     line = {
         "metric": "q8_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
@@ -310,7 +318,12 @@ def main():
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind, "kernel": "k_q8_gemv", "launches_per_step": n_gemv,
-                     "bytes_per_step": gemv_bytes, "ms_per_step_op_by_op": gemv_ms},
+                     "bytes_per_step": gemv_bytes, "us_per_launch": 1e3 * gemv_stream_ms / max(n_gemv_stream, 1),
+                     "ms_per_step_back_to_back": gemv_stream_ms, "ms_per_step_op_by_op": gemv_ms},
+        "roofline_attention": {"bound": "hbm", "kernel": "k_attn_decode", "launches_per_step": n_attn,
+                               "bytes_per_step": attn_bytes, "ms_per_step_back_to_back": attn_stream_ms,
+                               "achieved": attn_bytes / max(attn_stream_ms * 1e-3, 1e-12) / 1e9, "peak": peak, "unit": "GB/s",
+                               "frac": attn_bytes / max(attn_stream_ms * 1e-3, 1e-12) / 1e9 / peak},
         "roofline_step": {"bytes_per_token": step_bytes, "achieved_per_gpu": step_achieved, "frac": step_achieved / peak,
                           "roofline_tokens_per_s": B * world * peak * 1e9 / step_bytes},
         "profile_ms": {"gemv": gemv_ms, "attention": attn_ms, "exchange": exch_ms, "all_ops": total_prof_ms},

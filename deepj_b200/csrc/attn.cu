@@ -39,18 +39,52 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     __shared__ float s_m[G], s_l[G];
     __shared__ int s_last;
 
-    pdl_wait();
-    pdl_launch_dependents();
     const int split = blockIdx.x, splits = gridDim.x, h = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int group = lane / LPP, gl = lane % LPP;
-    int pos = (int)posbuf[b];
-    if (pos < 0) pos = 0;
-    if (pos >= maxSeq) pos = maxSeq - 1;
-    const int seq = pos + 1;
-    const int chunk = (seq + splits - 1) / splits;
-    const int start = split * chunk;
-    const int end = min(seq, start + chunk);
+    // The cache rows below the current position were written by earlier steps, not by the kernel
+    // this one depends on, so the first group of K/V rows is fetched BEFORE the wait and streams in
+    // while the projection kernel drains.  The position read here is re-read after the wait; in the
+    // (never observed) case that it moved, the speculative rows are dropped and fetched again.
+    auto read_pos = [&]() {
+        int v = (int)__ldcg(posbuf + b);
+        return v < 0 ? 0 : (v >= maxSeq ? maxSeq - 1 : v);
+    };
+    int pos = read_pos();
+    int seq = pos + 1;
+    int chunk = (seq + splits - 1) / splits;
+    int start = split * chunk;
+    int end = min(seq, start + chunk);
+    float* kbase = kcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
+    float* vbase = vcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
+    float kf[16], vf[16], kn[16], vn[16];
+    auto fetch_cached = [&](int p, bool valid, float (&kx)[16], float (&vx)[16]) {
+        if (valid) {
+            const float4* kp = reinterpret_cast<const float4*>(kbase + (size_t)p * HD);
+            const float4* vp = reinterpret_cast<const float4*>(vbase + (size_t)p * HD);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float4 a = __ldcs(kp + j), c = __ldcs(vp + j);
+                kx[4 * j] = a.x; kx[4 * j + 1] = a.y; kx[4 * j + 2] = a.z; kx[4 * j + 3] = a.w;
+                vx[4 * j] = c.x; vx[4 * j + 1] = c.y; vx[4 * j + 2] = c.z; vx[4 * j + 3] = c.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) { kx[j] = 0.0f; vx[j] = 0.0f; }
+        }
+    };
+    {
+        const int p0 = start + warp * PPW + group;
+        fetch_cached(p0, p0 < end && p0 != pos, kf, vf);
+    }
+    const int specPos = pos;
+    pdl_wait();
+    pdl_launch_dependents();
+    pos = read_pos();
+    seq = pos + 1;
+    chunk = (seq + splits - 1) / splits;
+    start = split * chunk;
+    end = min(seq, start + chunk);
     const int half = HD >> 1;
 
     // rotate 8 interleaved pairs held in v[16] by the table row of the current position
@@ -77,8 +111,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
         for (int j = 0; j < 4; j++) { float4 v = qp[j]; q[4 * j] = v.x; q[4 * j + 1] = v.y; q[4 * j + 2] = v.z; q[4 * j + 3] = v.w; }
         rotate(q);
     }
-    float* kbase = kcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
-    float* vbase = vcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
 
     // K and V slices of position p for this lane (zeros when the lane has no position)
     auto fetch = [&](int p, bool valid, float (&kf)[16], float (&vf)[16]) {
@@ -120,9 +152,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     for (int j = 0; j < 16; j++) acc[j] = 0.0f;
 
     // the loads of the next group of positions are in flight while this one is folded in
-    float kf[16], vf[16], kn[16], vn[16];
     int base = start + warp * PPW;
-    if (base < end) fetch(base + group, base + group < end, kf, vf);
+    if (base < end) {
+        const int p0 = base + group;
+        if (pos != specPos || (p0 == pos && p0 < end)) fetch(p0, p0 < end, kf, vf);      // the new token's lane, or a dropped speculation
+    }
     for (; base < end; base += G) {
         const bool valid = base + group < end;
         const int nbase = base + G;
@@ -200,7 +234,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
 }  // namespace
 
 int attn_decode_splits(int B, int H, int maxSeq) {
-    int want = (4 * g_num_sms + B * H - 1) / (B * H);
+    int want = (4 * g_num_sms) / (B * H);           // every CTA resident at once: a second, nearly empty wave would double the time
     int cap = (maxSeq + 63) / 64;
     int s = want < cap ? want : cap;
     return s < 1 ? 1 : s;

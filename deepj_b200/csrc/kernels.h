@@ -75,9 +75,12 @@ struct Q8LinearArgs {
     const float* residual; int ldr;
     float* out; int ldo;
     int M;
+    float* ws = nullptr; int* tickets = nullptr;    // workspace (q8_batch_ws_floats) and counters for the batched kernel (M ≥ 3)
 };
 void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s);
 bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s);
+bool launch_q8_linear_batch(const Q8LinearArgs& a, int m0, int rows, float* ws, int* tickets, cudaStream_t s);
+size_t q8_batch_ws_floats(int K, int N, bool swiglu);
 
 // ── decode attention ──
 struct AttnDecodeArgs {

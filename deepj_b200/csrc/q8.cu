@@ -506,6 +506,12 @@ void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
     p.out = a.out; p.ldo = a.ldo;
     p.K = a.w.K; p.N = a.w.N; p.Kp = a.w.Kp; p.nb = a.w.nb;
     const bool swiglu = a.w2.codes != nullptr;
+    if (g_gemv_mode == 2 && a.M >= 5 && a.ws != nullptr && a.w.K % 32 == 0 && a.w.Kp == a.w.K) {
+        // five or more rows share one pass over the weights, 16 at a time (up to four are two GEMV passes, which is as fast)
+        bool ok = true;
+        for (int m0 = 0; m0 < a.M && ok; m0 += 16) ok = launch_q8_linear_batch(a, m0, a.M - m0 < 16 ? a.M - m0 : 16, a.ws, a.tickets, s);
+        if (ok) return;
+    }
     if (g_gemv_mode == 2 && launch_q8_linear_tma(a, s)) return;
     if (g_gemv_mode >= 1 && p.K % 256 == 0 && gemv_mma_smem(p.K, 1) <= 200 * 1024) {
         // up to four activation rows share one pass over the weights

@@ -22,9 +22,11 @@
 // Measured dead ends, kept out of the code: a producer warp feeding a shared ring
 // through mbarriers reached 1.0 TB/s with cp.async and 1.6 TB/s with 1-D
 // cp.async.bulk row segments of 1 KB (per-copy cost of the bulk engine); fp16
-// mma.sync with byte-permute dequant was no faster than the FMA kernel.
+// mma.sync with byte-permute dequant was no faster than the FMA kernel; bulk L2
+// prefetch (cp.async.bulk.prefetch.L2) of the tiles ahead of the ring, or of the next
+// kernel's first weights as a CTA retires, made every shape 5–50 % slower.
 #include "kernels.h"
-#include <cuda_fp16.h>
+#include "q8_common.cuh"
 #include <cstdlib>
 
 namespace dj {
@@ -61,26 +63,12 @@ struct TmaParams {
     const float* residual; int ldr;
     float* out; int ldo;
     int K, N, Kp, nb, M;
+    int pre;                        // ring items a warp fetches before it waits for the previous kernel
     unsigned long long* trace;      // optional: six %globaltimer stamps of CTA 0 (phase tracing)
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-__device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
+constexpr int kStageRounds = 3;             // rows of up to 3·256·16 = 12288 values are staged from registers
 
 template <bool SWIGLU, int DEPTH>
 __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
@@ -100,7 +88,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     const int nPairs = (nBlocks + 1) >> 1;      // an odd block count leaves the last pair half empty
     unsigned char* myring = smem + (size_t)warp * DEPTH * kSlotBytes;
     const bool tracing = p.trace != nullptr && blockIdx.x == 0 && tid == 0;
-    if (tracing) p.trace[0] = gtime();
+    if (tracing) { p.trace[0] = gtime(); p.trace[6] = 0ull; }
 
     // ── copy issue: per-lane constants are hoisted; rows past N are clamped to the last row
     // (their results are never written), so the copy path carries no predicates ──
@@ -142,70 +130,53 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     // Weights never depend on the previous kernel, so streaming starts before the wait — but
     // only kPre items deep: every byte in flight on this SM queues ahead of the activation
     // loads that follow the wait (latency = bytes in flight / bandwidth).
-    constexpr int kPre = DEPTH - 1 < kPreMax ? DEPTH - 1 : kPreMax;
+    const int kPre = p.pre < DEPTH - 1 ? p.pre : DEPTH - 1;
     const bool haveWork = warp < nPairs;
     if (haveWork) {
-#pragma unroll
         for (int d = 0; d < kPre; d++) issue_next();
     }
     pdl_launch_dependents();
     if (tracing) p.trace[1] = gtime();
+    // the RMSNorm gain is a weight as well: fetch it before the wait when one round covers the row
+    const int nHalf = p.K >> 4;
+    const int rounds = (nHalf + kThreads - 1) / kThreads;
+    const bool gammaEarly = p.gamma != nullptr && rounds == 1;
+    float gpre[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) gpre[j] = 1.0f;
+    if (gammaEarly && tid < nHalf) load16(p.gamma + tid * 16, (reinterpret_cast<uintptr_t>(p.gamma) & 15) == 0, gpre);
     pdl_wait();
     if (tracing) p.trace[2] = gtime();
 
     // activations → three int8 digit columns + one power-of-two scale per 32-k block (RMSNorm
-    // fused).  A thread converts 16 consecutive values (half a block) per round.
-    const int nHalf = p.K >> 4;
+    // fused).  A thread converts 16 consecutive values (half a block) per round; all rounds of a
+    // row are loaded before anything is converted, so a row costs one load round trip.
     for (int m = 0; m < p.M; m++) {
         const float* xrow = p.x + (size_t)m * p.ldx;
         const bool vec = ((reinterpret_cast<uintptr_t>(xrow) | (p.gamma ? reinterpret_cast<uintptr_t>(p.gamma) : 0)) & 15) == 0;
-        float rms = 1.0f;
-        const bool oneRound = nHalf <= kThreads;
-        if (p.gamma && !oneRound) {
-            // wide rows: the sum of squares needs its own pass
-            float ss = 0.0f;
-            for (int k = tid; k < p.K; k += kThreads) { float v = xrow[k]; ss = fmaf(v, v, ss); }
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            __syncthreads();
-            if (lane == 0) s_red[warp] = ss;
-            __syncthreads();
-            ss = 0.0f;
-#pragma unroll
-            for (int q = 0; q < kWarps; q++) ss += s_red[q];
-            rms = sqrtf(ss * (1.0f / (float)p.K) + p.eps);
-        }
         int8_t* dcol = xd + (size_t)(kColsPerRow * m) * ldxs;
-        for (int hb0 = 0; hb0 < nHalf; hb0 += kThreads) {
-            const int hb = hb0 + tid;
-            const bool on = hb < nHalf;
-            float xv[16], gv[16];
-            if (on) {
-                if (vec) {
+        float* xscRow = xsc + (size_t)m * nBlocks;
+        if (rounds <= kStageRounds) {
+            float xv[kStageRounds][16];
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        float4 v4 = reinterpret_cast<const float4*>(xrow + hb * 16)[j];
-                        xv[4 * j] = v4.x; xv[4 * j + 1] = v4.y; xv[4 * j + 2] = v4.z; xv[4 * j + 3] = v4.w;
-                        if (p.gamma) {
-                            float4 g4 = reinterpret_cast<const float4*>(p.gamma + hb * 16)[j];
-                            gv[4 * j] = g4.x; gv[4 * j + 1] = g4.y; gv[4 * j + 2] = g4.z; gv[4 * j + 3] = g4.w;
-                        }
-                    }
-                } else {
+            for (int r = 0; r < kStageRounds; r++) {
+                const int hb = r * kThreads + tid;
+                if (r < rounds && hb < nHalf) load16(xrow + hb * 16, vec, xv[r]);
+                else {
 #pragma unroll
-                    for (int j = 0; j < 16; j++) { xv[j] = xrow[hb * 16 + j]; if (p.gamma) gv[j] = p.gamma[hb * 16 + j]; }
+                    for (int j = 0; j < 16; j++) xv[r][j] = 0.0f;
                 }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; j++) { xv[j] = 0.0f; gv[j] = 1.0f; }
             }
-            if (m == 0 && hb0 == 0 && haveWork) {
-#pragma unroll
+            if (m == 0 && haveWork) {
                 for (int d = kPre; d < DEPTH - 1; d++) issue_next();      // now fill the ring behind the activation loads
             }
-            if (p.gamma && oneRound) {
+            float inv = 1.0f;
+            if (p.gamma) {
                 float ss = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 16; j++) ss = fmaf(xv[j], xv[j], ss);
+                for (int r = 0; r < kStageRounds; r++)
+#pragma unroll
+                    for (int j = 0; j < 16; j++) ss = fmaf(xv[r][j], xv[r][j], ss);
                 for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
                 __syncthreads();
                 if (lane == 0) s_red[warp] = ss;
@@ -213,40 +184,64 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
                 ss = 0.0f;
 #pragma unroll
                 for (int q = 0; q < kWarps; q++) ss += s_red[q];
-                rms = sqrtf(ss * (1.0f / (float)p.K) + p.eps);      // RMSNorm1D.forward
+                inv = __frcp_rn(sqrtf(ss * (1.0f / (float)p.K) + p.eps));      // RMSNorm1D.forward: x / rms · γ
             }
-            float amax = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                if (p.gamma) xv[j] = __fdiv_rn(xv[j], rms) * gv[j];
-                amax = fmaxf(amax, fabsf(xv[j]));
-            }
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));      // the other half of the 32-k block
-            // s = 2^(exponent(amax)+2): |v|/s < 1/2, so the 23-bit fixed-point value fits three signed digits
-            int sbits = 0x3f800000;
-            if (amax > 0.0f && amax < 1e36f) sbits = (__float_as_int(amax) & 0x7f800000) + 0x01000000;
-            const float mul = __int_as_float(0x7f000000 - sbits) * 8388608.0f;     // 2^23 / s, exact
-            uint32_t w2[4], w1[4], w0[4];
+            for (int r = 0; r < kStageRounds; r++) {
+                const int hb = r * kThreads + tid;
+                const bool on = r < rounds && hb < nHalf;
+                if (p.gamma) {
+                    float gv[16];
+                    if (gammaEarly) {
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                w2[j] = 0u; w1[j] = 0u; w0[j] = 0u;
+                        for (int j = 0; j < 16; j++) gv[j] = gpre[j];
+                    } else if (on) load16(p.gamma + hb * 16, vec, gv);
+                    else {
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int q = __float2int_rn(xv[4 * j + i] * mul);
-                    const int e0 = ((q + 128) & 255) - 128;
-                    const int q1 = (q - e0) >> 8;
-                    const int e1 = ((q1 + 128) & 255) - 128;
-                    const int e2 = (q1 - e1) >> 8;
-                    w2[j] |= (uint32_t)(e2 & 255) << (8 * i);
-                    w1[j] |= (uint32_t)(e1 & 255) << (8 * i);
-                    w0[j] |= (uint32_t)(e0 & 255) << (8 * i);
+                        for (int j = 0; j < 16; j++) gv[j] = 1.0f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; j++) xv[r][j] = (xv[r][j] * inv) * gv[j];
                 }
+                if (r < rounds) digits16(xv[r], on, dcol, ldxs, hb, xscRow);
             }
-            if (on) {
-                *reinterpret_cast<uint4*>(dcol + hb * 16) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
-                *reinterpret_cast<uint4*>(dcol + ldxs + hb * 16) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
-                *reinterpret_cast<uint4*>(dcol + 2 * ldxs + hb * 16) = make_uint4(w0[0], w0[1], w0[2], w0[3]);
-                if ((hb & 1) == 0) xsc[(size_t)m * nBlocks + (hb >> 1)] = __int_as_float(sbits) * (1.0f / 8388608.0f);
+        } else {
+            // very wide rows: one pass for the sum of squares, then round by round
+            float inv = 1.0f;
+            if (p.gamma) {
+                float ss = 0.0f;
+                for (int k = tid; k < p.K; k += kThreads) { float v = xrow[k]; ss = fmaf(v, v, ss); }
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                __syncthreads();
+                if (lane == 0) s_red[warp] = ss;
+                __syncthreads();
+                ss = 0.0f;
+#pragma unroll
+                for (int q = 0; q < kWarps; q++) ss += s_red[q];
+                inv = __frcp_rn(sqrtf(ss * (1.0f / (float)p.K) + p.eps));
+            }
+            if (m == 0 && haveWork) {
+                for (int d = kPre; d < DEPTH - 1; d++) issue_next();
+            }
+            for (int r = 0; r < rounds; r++) {
+                const int hb = r * kThreads + tid;
+                const bool on = hb < nHalf;
+                float xv[16], gv[16];
+                if (on) load16(xrow + hb * 16, vec, xv);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) xv[j] = 0.0f;
+                }
+                if (p.gamma) {
+                    if (on) load16(p.gamma + hb * 16, vec, gv);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) gv[j] = 1.0f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; j++) xv[j] = (xv[j] * inv) * gv[j];
+                }
+                digits16(xv, on, dcol, ldxs, hb, xscRow);
             }
         }
     }
@@ -332,6 +327,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     }
     cp_async_wait<0>();
     if (tracing) p.trace[5] = gtime();
+    if (p.trace != nullptr && tid == 0) atomicMax(p.trace + 6, gtime());
 }
 
 size_t i8_smem_bytes(int K, int M, int depth) {
@@ -348,8 +344,13 @@ void launch_i8(const TmaParams& p, cudaStream_t s) {
     }
     int rowsPerTile = SWIGLU ? 8 : 16;
     int nTiles = (p.N + rowsPerTile - 1) / rowsPerTile;
+    // every CTA gets the same number of tiles (±1 only in the last round): the grid is the
+    // smallest one that keeps the rounds of the full grid
     int cap = 2 * g_num_sms;
-    int gx = nTiles < cap ? nTiles : cap;
+    int rounds = (nTiles + cap - 1) / cap;
+    int gx = (nTiles + rounds - 1) / rounds;
+    static const bool evenGrid = getenv("DEEPJ_CUDA_GEMV_FULLGRID") == nullptr;
+    if (!evenGrid) gx = nTiles < cap ? nTiles : cap;
     launch_k(k_q8_gemv_i8<SWIGLU, DEPTH>, dim3(gx), dim3(kThreads), i8_smem_bytes(p.K, p.M, DEPTH), s, true, p);
 }
 
@@ -391,6 +392,8 @@ bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s) {
         p.residual = a.residual ? a.residual + (size_t)m0 * a.ldr : nullptr; p.ldr = a.ldr;
         p.out = a.out + (size_t)m0 * a.ldo; p.ldo = a.ldo;
         p.K = K; p.N = a.w.N; p.Kp = a.w.Kp; p.nb = a.w.nb; p.M = rows;
+        static const int pre = getenv("DEEPJ_CUDA_GEMV_PRE") ? atoi(getenv("DEEPJ_CUDA_GEMV_PRE")) : kPreMax;
+        p.pre = pre;
         p.trace = trace_slot();
         if (swiglu) launch_i8_depth<true>(p, depth, s); else launch_i8_depth<false>(p, depth, s);
         m0 += rows;

@@ -294,6 +294,11 @@ void do_op(Ctx& ctx, const int32_t* c) {
             }
             a.out = f32(ctx, c[11], (size_t)out_off + sz(M - 1, ldo) + wb.N, "q8Linear") + out_off; a.ldo = ldo;
             a.M = M;
+            if (M >= 3) {
+                size_t need = q8_batch_ws_floats(wb.K, wb.N, false);
+                if (need > ctx.ws_need) ctx.ws_need = need;
+                a.ws = R.ws; a.tickets = R.tickets;
+            }
             if (go) launch_q8_linear(a, s);
             break;
         }
@@ -312,6 +317,11 @@ void do_op(Ctx& ctx, const int32_t* c) {
             a.w2 = q8view(wu); a.bias2 = f32_opt(ctx, c[9], wu.N, "q8SwiGLU");
             a.out = f32(ctx, c[10], (size_t)out_off + sz(M - 1, ldo) + wg.N, "q8SwiGLU") + out_off; a.ldo = ldo;
             a.M = M;
+            if (M >= 3) {
+                size_t need = q8_batch_ws_floats(wg.K, wg.N, true);
+                if (need > ctx.ws_need) ctx.ws_need = need;
+                a.ws = R.ws; a.tickets = R.tickets;
+            }
             if (go) launch_q8_linear(a, s);
             break;
         }
@@ -390,6 +400,7 @@ void do_op(Ctx& ctx, const int32_t* c) {
 
 int walk(Ctx& ctx, const int32_t* cmd, int len) {
     int pos = 0, nops = 0;
+
     while (pos < len) {
         int stride = op_stride(cmd[pos]);
         if (stride < 0) throw std::runtime_error("Unknown op code in command stream: " + std::to_string(cmd[pos]));

@@ -16,7 +16,7 @@ from __future__ import annotations
 import ctypes
 import math
 from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional
+from typing import Tuple, Callable, Dict, List, Optional
 
 import numpy as np
 
@@ -134,8 +134,8 @@ class Q8Decoder:
         self.B = int(batch)
         if tp_world < 1 or not (0 <= tp_rank < tp_world):
             raise ValueError("bad tensor-parallel rank / world size")
-        if cfg.n_heads % tp_world or cfg.d_ff % tp_world or cfg.vocab_size % tp_world or (cfg.d_ff // tp_world) % 32 or \
-                (cfg.d_model // tp_world) % 32:
+        if tp_world > 1 and (cfg.n_heads % tp_world or cfg.d_ff % tp_world or cfg.vocab_size % tp_world or
+                             (cfg.d_ff // tp_world) % 32 or (cfg.d_model // tp_world) % 32):
             raise ValueError("heads, dFF and vocab must divide by the tensor-parallel size, on 32-element block boundaries")
         self.tp_rank, self.tp_world = int(tp_rank), int(tp_world)
         self.h_local = cfg.n_heads // tp_world
@@ -317,7 +317,10 @@ class Q8Decoder:
         s: List[int] = []
         labels: List[str] = []
 
+        bounds: List[Tuple[int, int]] = []
+
         def op(label, *ints):
+            bounds.append((len(s), len(s) + len(ints)))
             s.extend(int(v) for v in ints)
             labels.append(label)
 
@@ -358,6 +361,7 @@ class Q8Decoder:
         if feed_back:
             op("feed_back", OP_COPY, I["next"], 0, I["tok"], 0, B)
         self._op_labels = labels
+        self._op_bounds = bounds
         return np.asarray(s, dtype=np.int32)
 
     def _streams(self):
@@ -458,6 +462,23 @@ class Q8Decoder:
         _lib.check(self.lib.deepj_cuda_profile_ops(host.ctypes.data, host.size, ms.ctypes.data, n, ctypes.byref(cnt)))
         self.position += 1
         return list(zip(self._op_labels, ms[: cnt.value].tolist()))
+
+    def time_ops(self, labels, iters: int = 20, warmup: int = 3) -> Tuple[float, int]:
+        """Device time of the ops whose label is in `labels`, run back to back as their own stream
+        (graph-replayed like the full step, at the current position): (ms per pass, ops per pass)."""
+        full = self._build(feed_back=False)
+        keep = [full[a:b] for lbl, (a, b) in zip(self._op_labels, self._op_bounds) if lbl in labels]
+        if not keep:
+            return 0.0, 0
+        sub = np.ascontiguousarray(np.concatenate(keep))
+        for _ in range(max(warmup, 3)):
+            _lib.check(self.lib.deepj_cuda_flush_ops(sub.ctypes.data, sub.size))
+        _lib.check(self.lib.deepj_cuda_timer_begin())
+        for _ in range(iters):
+            _lib.check(self.lib.deepj_cuda_flush_ops_async(sub.ctypes.data, sub.size))
+        ms = ctypes.c_float(0)
+        _lib.check(self.lib.deepj_cuda_timer_end(ctypes.byref(ms)))
+        return ms.value / iters, len(keep)
 
     def stats(self) -> Dict[str, int]:
         v = (ctypes.c_int64 * 6)()

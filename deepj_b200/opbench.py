@@ -86,7 +86,9 @@ def run(m: int, k: int, n: int, copies: int, iters: int, warmup: int, swiglu: bo
             res["trace_ns_median"] = {"prefetch_issue": float(np.median(d[:, 0])), "wait_prev": float(np.median(d[:, 1])),
                                       "stage_x": float(np.median(d[:, 2])), "first_tile": float(np.median(d[:, 3])),
                                       "rest": float(np.median(d[:, 4])), "start_minus_prev_end": float(np.median(gap)),
-                                      "start_to_start": float(np.median(np.diff(t[:, 0])))}
+                                      "start_to_start": float(np.median(np.diff(t[:, 0]))),
+                                      "last_cta_end_minus_cta0_end": float(np.median(t[:, 6] - t[:, 5])),
+                                      "wait_return_minus_prev_last_end": float(np.median(t[1:, 2] - t[:-1, 6]))}
     ids = list(range(base + 1, nid[0] + 1))
     _lib.check(lib.deepj_cuda_release_buffers((ctypes.c_int32 * len(ids))(*ids), len(ids)))
     return res
