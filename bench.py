@@ -208,6 +208,8 @@ def main():
         tp.connect(rank, world, max(B * cfg.d_model, B * cfg.vocab_size // world))
     t_load = time.perf_counter()
     dec.load_synthetic(w["seed"], w["std"])
+    if world > 1:
+        tp.barrier()          # the exchange kernel's wait for a peer is bounded: start stepping together
     rng = np.random.default_rng(w["seed"] + 1000)
     prompts = rng.integers(0, w["vocab"], size=(B, w["prompt"]))
     dec.reset()

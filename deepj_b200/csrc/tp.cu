@@ -4,17 +4,20 @@
 // Wo and down projections) and the LM head one gather of [B × V/g] logits.  At batch 1
 // these are 16 KB messages: latency, not bandwidth.  Each rank owns a communication
 // buffer (two parities × world slots) that every peer maps through CUDA IPC.  One kernel
-// per exchange:
-//   push   every rank stores its contribution into slot[parity][my rank] of EVERY peer
-//          (plain peer stores over NVLink), then publishes an epoch
-//          number in the peer's flag word;
-//   wait   until all ranks' flags for this epoch have arrived locally (bounded spin: when
-//          the bound expires the kernel records an error code and carries on, it never hangs);
-//   finish sum the slots in rank order (+ residual + bias) — every rank computes the same
-//          bits — or copy them side by side for the gather.
+// per exchange, no fence and no separate flag on the critical path:
+//   push   every value travels as an 8-byte word {bits, epoch}; a thread stores two of them
+//          (16 bytes) into slot[parity][my rank] of EVERY rank with plain peer stores;
+//   wait   the same thread polls its own words in all slots until their epoch fields show
+//          the current epoch (8-byte stores arrive whole, so a word whose epoch matches
+//          carries its value) — a bounded poll: when the bound expires the kernel records
+//          an error code and carries on, it never hangs;
+//   finish add the slots in rank order (+ residual + bias) — every rank computes the same
+//          bits — or place them side by side for the gather.
+// The cost is one NVLink one-way latency instead of store → system fence → flag.
 // Parity flips every exchange; a rank can be at most one exchange ahead of a peer (it needs
-// the peer's flag to finish), so two parities are enough.  Epochs live in device memory,
-// which makes the kernels replayable inside a captured CUDA graph.
+// the peer's words to finish), so two parities are enough and a stale word (epoch − 2) can
+// never be taken for a fresh one.  Epochs live in device memory, which makes the kernels
+// replayable inside a captured CUDA graph.
 #include "../../include/deepj_cuda.h"
 #include "kernels.h"
 
@@ -27,36 +30,36 @@ namespace {
 
 constexpr int kMaxWorld = 8;
 constexpr int kTpCtas = 8;                    // CTAs per exchange; each owns a contiguous chunk
-constexpr unsigned kTpSpinLimit = 1u << 24;   // ≈ seconds, then give up
+constexpr unsigned kTpSpinLimit = 1u << 22;   // polls of one word, ≈ seconds, then give up
 
 struct TpState {
     bool ready = false;
     int rank = 0, world = 1;
     size_t slot_floats = 0;
-    // layout of one rank's buffer: data[2][world][slot_floats] floats, then flags[world][kTpCtas] u32, then epochs[kTpCtas] u32
+    // layout of one rank's buffer: words[2][world][slot_floats] of {bits, epoch} (8 bytes each), then epochs[kTpCtas] u32
     void* local = nullptr;
     size_t bytes = 0;
     float* peer_data[kMaxWorld] = {};
-    unsigned* peer_flags[kMaxWorld] = {};
     unsigned* epochs = nullptr;
     void* opened[kMaxWorld] = {};
 } T;
 
 struct TpPtrs {
     float* data[kMaxWorld];
-    unsigned* flags[kMaxWorld];
 };
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+
+constexpr int kTpPairsPerThread = 1;      // 2 values per thread and pass: a 16 KB message spreads over all 2048 threads
 
 // mode 0: out[m][n] = residual[m][n] + bias[n] + Σ_r contribution_r[m][n]   (n_local == N)
 // mode 1: out[m][r·n_local + j] = contribution_r[m][j]
@@ -64,58 +67,68 @@ __global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int wor
                                                       const float* __restrict__ in, const float* __restrict__ bias,
                                                       const float* __restrict__ residual, float* __restrict__ out,
                                                       int M, int n_local, int mode, int* error) {
-    __shared__ int s_ok;
     pdl_wait();
     pdl_launch_dependents();
     const int cta = blockIdx.x, tid = threadIdx.x;
     const unsigned epoch = epochs[cta] + 1;
     const unsigned parity = epoch & 1u;
-    const int total = M * n_local;                                   // floats this rank contributes
-    const int per = ((total + kTpCtas - 1) / kTpCtas + 3) & ~3;       // chunk, multiple of 4 floats
-    const int lo = min(total, cta * per), hi = min(total, lo + per);
-
-    // push my chunk into slot[parity][rank] of every rank (myself included)
-    const size_t slot = ((size_t)parity * world + rank) * slot_floats;
-    for (int r = 0; r < world; r++) {
-        float* dst = P.data[r] + slot;
-        for (int i = lo + tid * 4; i < hi; i += blockDim.x * 4) {
-            if (i + 3 < hi) *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(in + i);
-            else for (int j = i; j < hi; j++) dst[j] = in[j];
+    const int total = M * n_local;                       // floats this rank contributes
+    const int pairs = (total + 1) >> 1;
+    const size_t slotWords = (size_t)parity * world * slot_floats;      // in 8-byte words
+    for (int p0 = (cta * blockDim.x + tid) * kTpPairsPerThread; p0 < pairs; p0 += gridDim.x * blockDim.x * kTpPairsPerThread) {
+        // push: my values of these pairs into my slot on every rank (myself included)
+        uint4 w[kTpPairsPerThread];
+#pragma unroll
+        for (int q = 0; q < kTpPairsPerThread; q++) {
+            const int i = 2 * (p0 + q);
+            const float a = i < total ? in[i] : 0.0f, b = i + 1 < total ? in[i + 1] : 0.0f;
+            w[q] = make_uint4(__float_as_uint(a), epoch, __float_as_uint(b), epoch);
         }
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) {
-        for (int r = 0; r < world; r++) st_release_sys_u32(P.flags[r] + rank * kTpCtas + cta, epoch);
-    }
-    // wait for every rank's chunk of this epoch
-    if (tid < world) {
-        const unsigned* f = P.flags[rank] + tid * kTpCtas + cta;
-        bool ok = false;
-        for (unsigned it = 0; it < kTpSpinLimit; it++) {
-            if ((int)(ld_volatile_u32(f) - epoch) >= 0) { ok = true; break; }
-            __nanosleep(64);
+        for (int r = 0; r < world; r++) {
+            uint4* dst = reinterpret_cast<uint4*>(P.data[r]) + (slotWords + (size_t)rank * slot_floats) / 2;
+#pragma unroll
+            for (int q = 0; q < kTpPairsPerThread; q++)
+                if (p0 + q < pairs) st_volatile_v4(dst + p0 + q, w[q]);
         }
-        if (!ok) atomicExch(error, 100 + tid);
-    }
-    __syncthreads();
-    __threadfence_system();
-    (void)s_ok;
-    const float* mine = P.data[rank] + (size_t)parity * world * slot_floats;
-    if (mode == 0) {
-        for (int i = lo + tid; i < hi; i += blockDim.x) {
-            const int n = i % n_local;
-            float v = residual ? residual[i] : 0.0f;
-            if (bias) v += bias[n];
-            float s = 0.0f;
-            for (int r = 0; r < world; r++) s += __ldcv(mine + (size_t)r * slot_floats + i);     // rank order: same bits everywhere
-            out[i] = v + s;
+        // wait + finish: the same pairs from every rank's slot in my own buffer, in rank order
+        float sa[kTpPairsPerThread], sb[kTpPairsPerThread];
+#pragma unroll
+        for (int q = 0; q < kTpPairsPerThread; q++) { sa[q] = 0.0f; sb[q] = 0.0f; }
+        for (int r = 0; r < world; r++) {
+            const uint4* src = reinterpret_cast<const uint4*>(P.data[rank]) + (slotWords + (size_t)r * slot_floats) / 2;
+#pragma unroll
+            for (int q = 0; q < kTpPairsPerThread; q++) {
+                if (p0 + q >= pairs) continue;
+                uint4 v = ld_volatile_v4(src + p0 + q);
+                for (unsigned it = 0; (v.y != epoch || v.w != epoch) && it < kTpSpinLimit; it++) {
+                    __nanosleep(32);
+                    v = ld_volatile_v4(src + p0 + q);
+                }
+                if (v.y != epoch || v.w != epoch) atomicExch(error, 100 + r);
+                const float a = __uint_as_float(v.x), b = __uint_as_float(v.z);
+                const int i = 2 * (p0 + q);
+                if (mode == 0) { sa[q] += a; sb[q] += b; }
+                else {
+                    if (i < total) out[(size_t)(i / n_local) * n_local * world + (size_t)r * n_local + i % n_local] = a;
+                    if (i + 1 < total) out[(size_t)((i + 1) / n_local) * n_local * world + (size_t)r * n_local + (i + 1) % n_local] = b;
+                }
+            }
         }
-    } else {
-        for (int i = lo + tid; i < hi; i += blockDim.x) {
-            const int m = i / n_local, j = i % n_local;
-            for (int r = 0; r < world; r++)
-                out[(size_t)m * n_local * world + (size_t)r * n_local + j] = __ldcv(mine + (size_t)r * slot_floats + i);
+        if (mode == 0) {
+#pragma unroll
+            for (int q = 0; q < kTpPairsPerThread; q++) {
+                const int i = 2 * (p0 + q);
+                if (i < total) {
+                    float v = residual ? residual[i] : 0.0f;
+                    if (bias) v += bias[i % n_local];
+                    out[i] = v + sa[q];
+                }
+                if (i + 1 < total) {
+                    float v = residual ? residual[i + 1] : 0.0f;
+                    if (bias) v += bias[(i + 1) % n_local];
+                    out[i + 1] = v + sb[q];
+                }
+            }
         }
     }
     __syncthreads();
@@ -134,7 +147,7 @@ void launch_tp_exchange(const float* in, const float* bias, const float* residua
         throw std::runtime_error("tensor-parallel exchange of " + std::to_string((size_t)M * n_local) + " floats exceeds the slot size " +
                                  std::to_string(T.slot_floats));
     TpPtrs P;
-    for (int r = 0; r < kMaxWorld; r++) { P.data[r] = T.peer_data[r]; P.flags[r] = T.peer_flags[r]; }
+    for (int r = 0; r < kMaxWorld; r++) { P.data[r] = T.peer_data[r]; }
     launch_k(k_tp_exchange, dim3(kTpCtas), dim3(256), 0, s, true, P, T.rank, T.world, T.slot_floats, T.epochs, in, bias, residual, out,
              M, n_local, mode, g_dev_error);
 }
@@ -153,8 +166,8 @@ int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void*
         if (slot_floats <= 0 || slot_floats % 4 != 0) throw std::runtime_error("tp_create: slot size must be a positive multiple of 4 floats");
         if (T.local) throw std::runtime_error("tp_create: already created");
         T.rank = rank; T.world = world; T.slot_floats = (size_t)slot_floats;
-        const size_t dataBytes = (size_t)2 * world * slot_floats * sizeof(float);
-        T.bytes = dataBytes + (size_t)(world + 1) * kTpCtas * sizeof(unsigned);
+        const size_t dataBytes = (size_t)2 * world * slot_floats * 8;       // {bits, epoch} per value
+        T.bytes = dataBytes + (size_t)kTpCtas * sizeof(unsigned);
         DJ_CUDA_CHECK(cudaMalloc(&T.local, T.bytes));
         DJ_CUDA_CHECK(cudaMemset(T.local, 0, T.bytes));
         DJ_CUDA_CHECK(cudaDeviceSynchronize());
@@ -170,7 +183,7 @@ int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void*
 int deepj_cuda_tp_connect(const void* handles, int32_t world) {
     try {
         if (!T.local || world != T.world) throw std::runtime_error("tp_connect: call tp_create first, with the same world size");
-        const size_t dataFloats = (size_t)2 * T.world * T.slot_floats;
+        const size_t dataBytes = (size_t)2 * T.world * T.slot_floats * 8;
         for (int r = 0; r < T.world; r++) {
             void* base = T.local;
             if (r != T.rank) {
@@ -180,9 +193,8 @@ int deepj_cuda_tp_connect(const void* handles, int32_t world) {
                 T.opened[r] = base;
             }
             T.peer_data[r] = (float*)base;
-            T.peer_flags[r] = (unsigned*)((float*)base + dataFloats);
         }
-        T.epochs = T.peer_flags[T.rank] + (size_t)T.world * kTpCtas;
+        T.epochs = (unsigned*)((char*)T.local + dataBytes);
         T.ready = true;
         return 0;
     } catch (const std::exception& e) { set_last_error(e.what()); return 1; }

@@ -31,6 +31,7 @@ def main():
     tp.connect(rank, world, max(B * cfg.d_model, B * cfg.vocab_size // world))
     dec.load_weights(weight_getter(om, cfg))
     om.apply_q8()
+    tp.barrier()              # the exchange kernel's wait for a peer is bounded: start stepping together
     rng = np.random.default_rng(5)
     prompts = rng.integers(0, cfg.vocab_size, size=(B, 12))
     dec.reset()
