@@ -25,6 +25,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 constexpr int kAttnWarps = 4;
+constexpr int kMaxSplits = 256;             // split partials a head can have (the merge keeps their weights in shared memory)
 
 template <int LPP>   // lanes per position = hd / 16
 __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
@@ -46,6 +47,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     // this one depends on, so the first group of K/V rows is fetched BEFORE the wait and streams in
     // while the projection kernel drains.  The position read here is re-read after the wait; in the
     // (never observed) case that it moved, the speculative rows are dropped and fetched again.
+    const int half = HD >> 1;
     auto read_pos = [&]() {
         int v = (int)__ldcg(posbuf + b);
         return v < 0 ? 0 : (v >= maxSeq ? maxSeq - 1 : v);
@@ -77,40 +79,47 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
         const int p0 = start + warp * PPW + group;
         fetch_cached(p0, p0 < end && p0 != pos, kf, vf);
     }
-    const int specPos = pos;
-    pdl_wait();
-    pdl_launch_dependents();
-    pos = read_pos();
-    seq = pos + 1;
-    chunk = (seq + splits - 1) / splits;
-    start = split * chunk;
-    end = min(seq, start + chunk);
-    const int half = HD >> 1;
-
-    // rotate 8 interleaved pairs held in v[16] by the table row of the current position
-    auto rotate = [&](float (&v)[16]) {
+    // the rotation tables are constants: the row of the speculative position is fetched before the wait too
+    float cs[8], sn[8];
+    auto load_tables = [&](float (&cs)[8], float (&sn)[8]) {
         const float4* cp = reinterpret_cast<const float4*>(cosT + (size_t)pos * half + gl * 8);
         const float4* sp = reinterpret_cast<const float4*>(sinT + (size_t)pos * half + gl * 8);
 #pragma unroll
         for (int j = 0; j < 2; j++) {
             const float4 c4 = cp[j], s4 = sp[j];
-            const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float x0 = v[8 * j + 2 * i], x1 = v[8 * j + 2 * i + 1];
-                v[8 * j + 2 * i] = x0 * cs[i] - x1 * sn[i];
-                v[8 * j + 2 * i + 1] = x0 * sn[i] + x1 * cs[i];
-            }
+            cs[4 * j] = c4.x; cs[4 * j + 1] = c4.y; cs[4 * j + 2] = c4.z; cs[4 * j + 3] = c4.w;
+            sn[4 * j] = s4.x; sn[4 * j + 1] = s4.y; sn[4 * j + 2] = s4.z; sn[4 * j + 3] = s4.w;
         }
     };
+    load_tables(cs, sn);
+    const int specPos = pos;
+    pdl_wait();
+    pdl_launch_dependents();
+    // the query row does not depend on the position: its loads go out together with the position's
     const float* rowp = qkv + (size_t)b * ld;
     float q[16];
     {
         const float4* qp = reinterpret_cast<const float4*>(rowp + q_off + h * HD + gl * 16);
 #pragma unroll
         for (int j = 0; j < 4; j++) { float4 v = qp[j]; q[4 * j] = v.x; q[4 * j + 1] = v.y; q[4 * j + 2] = v.z; q[4 * j + 3] = v.w; }
-        rotate(q);
     }
+    pos = read_pos();
+    if (pos != specPos) load_tables(cs, sn);
+    seq = pos + 1;
+    chunk = (seq + splits - 1) / splits;
+    start = split * chunk;
+    end = min(seq, start + chunk);
+
+    // rotate 8 interleaved pairs held in v[16] by the table row of the current position (cs, sn)
+    auto rotate = [&](float (&v)[16], const float (&cs)[8], const float (&sn)[8]) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float x0 = v[2 * i], x1 = v[2 * i + 1];
+            v[2 * i] = x0 * cs[i] - x1 * sn[i];
+            v[2 * i + 1] = x0 * sn[i] + x1 * cs[i];
+        }
+    };
+    rotate(q, cs, sn);
 
     // K and V slices of position p for this lane (zeros when the lane has no position)
     auto fetch = [&](int p, bool valid, float (&kf)[16], float (&vf)[16]) {
@@ -124,7 +133,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
                 kf[4 * j] = a.x; kf[4 * j + 1] = a.y; kf[4 * j + 2] = a.z; kf[4 * j + 3] = a.w;
                 vf[4 * j] = c.x; vf[4 * j + 1] = c.y; vf[4 * j + 2] = c.z; vf[4 * j + 3] = c.w;
             }
-            rotate(kf);
+            float ck[8], sk[8];              // fetched again here (a cache hit) rather than kept live through the loop
+            load_tables(ck, sk);
+            rotate(kf, ck, sk);
             float4* kd = reinterpret_cast<float4*>(kbase + (size_t)p * HD);
             float4* vd = reinterpret_cast<float4*>(vbase + (size_t)p * HD);
 #pragma unroll
@@ -216,16 +227,31 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // Thread sp fetches split sp's (m, l); the weights exp(m_sp − M) are shared through shared memory, and the
+    // partial rows are requested eight splits at a time, so the merge costs a few load round trips in all.
     const float* pbase = ws + ((size_t)b * H + h) * splits * (HD + 2);
+    float* s_w = &s_acc[0][0];                  // reused: the CTA's own partial has been written out
+    float* s_ml = s_w + kMaxSplits;
+    for (int sp = threadIdx.x; sp < splits; sp += blockDim.x) {
+        s_w[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD);
+        s_ml[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD + 1);
+    }
+    __syncthreads();
     float M = -INFINITY;
-    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, __ldcg(pbase + (size_t)sp * (HD + 2) + HD));
+    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, s_w[sp]);
+    float L = 0.0f;
+    for (int sp = 0; sp < splits; sp++) L = fmaf(s_ml[sp], expf(s_w[sp] - M), L);
+    __syncthreads();
+    for (int sp = threadIdx.x; sp < splits; sp += blockDim.x) s_w[sp] = expf(s_w[sp] - M);
+    __syncthreads();
     for (int j = threadIdx.x; j < HD; j += blockDim.x) {
-        float a = 0.0f, L = 0.0f;
-        for (int sp = 0; sp < splits; sp++) {
-            const float* pp = pbase + (size_t)sp * (HD + 2);
-            const float e = expf(__ldcg(pp + HD) - M);
-            a = fmaf(__ldcg(pp + j), e, a);
-            L = fmaf(__ldcg(pp + HD + 1), e, L);
+        float a = 0.0f;
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float part[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) part[q] = s0 + q < splits ? __ldcg(pbase + (size_t)(s0 + q) * (HD + 2) + j) : 0.0f;
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (s0 + q < splits) a = fmaf(part[q], s_w[s0 + q], a);
         }
         out[(size_t)b * ldo + h * HD + j] = a / L;
     }
@@ -237,6 +263,7 @@ int attn_decode_splits(int B, int H, int maxSeq) {
     int want = (4 * g_num_sms) / (B * H);           // every CTA resident at once: a second, nearly empty wave would double the time
     int cap = (maxSeq + 63) / 64;
     int s = want < cap ? want : cap;
+    if (s > 256) s = 256;                           // the merge keeps one weight per split in shared memory
     return s < 1 ? 1 : s;
 }
 size_t attn_decode_ws_floats(int B, int H, int hd, int splits) {

@@ -81,6 +81,9 @@ void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s);
 bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s);
 bool launch_q8_linear_batch(const Q8LinearArgs& a, int m0, int rows, float* ws, int* tickets, cudaStream_t s);
 size_t q8_batch_ws_floats(int K, int N, bool swiglu);
+bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s);
+size_t q8_tc_ws_floats(int M, int K);
+constexpr int kTcMinRows = 17;            // from this many activation rows on, a Q8 linear runs on the tcgen05 path
 
 // ── decode attention ──
 struct AttnDecodeArgs {

@@ -506,6 +506,8 @@ void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
     p.out = a.out; p.ldo = a.ldo;
     p.K = a.w.K; p.N = a.w.N; p.Kp = a.w.Kp; p.nb = a.w.nb;
     const bool swiglu = a.w2.codes != nullptr;
+    static const bool noTc = getenv("DEEPJ_CUDA_NO_TC") != nullptr;
+    if (g_gemv_mode == 2 && !noTc && a.M >= kTcMinRows && a.ws != nullptr && launch_q8_linear_tc(a, a.ws, s)) return;
     if (g_gemv_mode == 2 && a.M >= 5 && a.ws != nullptr && a.w.K % 32 == 0 && a.w.Kp == a.w.K) {
         // five or more rows share one pass over the weights, 16 at a time (up to four are two GEMV passes, which is as fast)
         bool ok = true;

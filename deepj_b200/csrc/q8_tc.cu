@@ -1,0 +1,421 @@
+// Q8 linear for many activation rows (prefill): tcgen05 tensor-core tiles with the
+// accumulator in tensor memory.
+//
+// With M in the hundreds the work is a dense contraction, 2·M·K·N flops against K·N weight
+// bytes, and belongs on the 5th-generation tensor cores.  The Q8 format keeps one fp32 scale per
+// 32 weights, so the weights cannot stay int8 inside one long accumulation; instead each
+// 128 × 64 weight tile is dequantised on the fly, exactly once per CTA, into fp16:
+//     w = code · scale  (fp32)   →   w_hi = fp16(w),  w_lo = fp16(w − w_hi)
+// and the activations are split the same way by a pre-pass (x_hi, x_lo, after a power-of-two row
+// scaling that keeps fp16 in range; RMSNorm is applied there too).  Three MMAs per k-step,
+//     D += X_hi·W_hi + X_lo·W_hi + X_hi·W_lo,
+// carry ≈ 22 bits of each operand into the fp32 accumulator — the dropped lo·lo term is 2^-22
+// relative — so the prefill path stays inside the decode path's tolerance at one third of the
+// fp16 tensor peak.
+//
+// One CTA per 128 × 128 output tile, ten warps:
+//   warps 0-7  dequantise (a thread owns half a weight row of the tile: 32 code bytes + a scale per
+//              k-tile from global memory, the next four k-tiles' already in registers) and write the
+//              W_hi / W_lo tiles in the 128-byte-swizzled K-major layout the MMA reads; afterwards
+//              they are the epilogue: tcgen05.ld of a 32 × 64 piece of the accumulator each, row scale,
+//              bias, residual or SiLU-gate, 128-byte row stores through a shared-memory transpose;
+//   warp 8     one thread streams the activation tiles: the pre-pass leaves every 128 × 64 tile
+//              as a ready shared-memory image (hi and lo adjacent, 32 KB), so a stage is ONE
+//              plain bulk copy completing on an mbarrier — no tensor map;
+//   warp 9     one thread issues the MMAs and commits each stage back to its "empty" barrier.
+// Three stages of 64 KB.  Every wait is bounded: when a bound expires the CTA records an error
+// code, stops waiting for anything, frees its tensor memory and returns.
+#include "kernels.h"
+#include "q8_common.cuh"
+#include <cuda_fp16.h>
+
+namespace dj {
+namespace {
+
+constexpr int kTileM = 128, kTileN = 128, kTileK = 64;
+constexpr int kStages = 3;
+constexpr int kATileBytes = kTileM * kTileK * 2;         // one fp16 tile: 16 KB
+constexpr int kBTileBytes = kTileN * kTileK * 2;
+constexpr int kStageBytes = 2 * kATileBytes + 2 * kBTileBytes;      // X_hi, X_lo, W_hi, W_lo
+constexpr int kDqWarps = 8;                              // dequantising (later: epilogue) warps; then one copy warp, one MMA warp
+constexpr int kTcThreads = (kDqWarps + 2) * 32;
+constexpr unsigned kTcWaitLimit = 1u << 22;              // try_wait rounds before a wait gives up
+constexpr int kTmemCols = 128;
+
+// byte offset of 16-byte chunk c (0-7) of row r inside a 128-byte-swizzled K-major tile of 64 halves per row
+__host__ __device__ __forceinline__ int swz_off(int r, int c) { return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; `abort_flag` (shared) short-circuits every later wait of the CTA once one has expired.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error, int code) {
+    for (unsigned it = 0; it < kTcWaitLimit; it++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(error, code);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128-byte swizzle: 8-row groups 1024 bytes apart (stride byte offset), leading offset unused (1),
+// descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// fp16 × fp16 → fp32, both operands K-major, M = 128, N = 128
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));      // first source → upper half
+    return r;
+}
+
+// ───────────── pre-pass: fp32 activations → hi/lo fp16 tile images ─────────────
+// One warp per activation row.  Output tiles [m-tile][k-tile]{hi 16 KB, lo 16 KB}; rowscale[m] undoes the
+// power-of-two scaling in the GEMM epilogue.  Rows ≥ M of the last m-tile are written as zeros.
+__global__ void __launch_bounds__(256) k_x_to_f16_tiles(const float* __restrict__ x, int ldx, const float* __restrict__ gamma, float eps,
+                                                         int M, int K, unsigned char* __restrict__ tiles, float* __restrict__ rowscale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int m = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int mPad = (M + kTileM - 1) / kTileM * kTileM;
+    if (m >= mPad) return;
+    const int nK = K / kTileK;
+    unsigned char* mt = tiles + (size_t)(m / kTileM) * nK * (2 * kATileBytes);
+    const int r = m % kTileM;
+    if (m >= M) {
+        for (int c = lane; c < nK * 8; c += 32) {
+            unsigned char* t = mt + (size_t)(c >> 3) * (2 * kATileBytes) + swz_off(r, c & 7);
+            *reinterpret_cast<uint4*>(t) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(t + kATileBytes) = make_uint4(0, 0, 0, 0);
+        }
+        if (lane == 0) rowscale[m] = 0.0f;
+        return;
+    }
+    const float* xr = x + (size_t)m * ldx;
+    float ss = 0.0f, amax = 0.0f;
+    for (int k = lane * 4; k < K; k += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + k);
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        float4 g = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (gamma) g = *reinterpret_cast<const float4*>(gamma + k);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x * g.x), fabsf(v.y * g.y)), fmaxf(fabsf(v.z * g.z), fabsf(v.w * g.w))));
+    }
+    for (int o = 16; o > 0; o >>= 1) { ss += __shfl_xor_sync(0xffffffffu, ss, o); amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o)); }
+    float inv = 1.0f;
+    if (gamma) inv = __frcp_rn(sqrtf(ss * (1.0f / (float)K) + eps));      // RMSNorm1D.forward: x / rms · γ
+    amax *= inv;
+    // 2^-e brings the row's largest value into [512, 1024)
+    int ebits = 0x3f800000;
+    if (amax > 0.0f && amax < 1e30f) ebits = __float_as_int(amax) & 0x7f800000;
+    const float down = __int_as_float(0x7f000000 - ebits) * 512.0f;
+    if (lane == 0) rowscale[m] = __int_as_float(ebits) * (1.0f / 512.0f);
+    for (int c = lane; c < nK * 8; c += 32) {          // chunk c: values 8c … 8c+7
+        const float4 a = *reinterpret_cast<const float4*>(xr + c * 8), b = *reinterpret_cast<const float4*>(xr + c * 8 + 4);
+        float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        if (gamma) {
+            const float4 ga = *reinterpret_cast<const float4*>(gamma + c * 8), gb = *reinterpret_cast<const float4*>(gamma + c * 8 + 4);
+            const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = (v[j] * inv) * g[j];
+        }
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float p = v[2 * j] * down, q = v[2 * j + 1] * down;
+            hi[j] = pack_h2(p, q);
+            const float2 back = __half22float2(*reinterpret_cast<const __half2*>(&hi[j]));
+            lo[j] = pack_h2(p - back.x, q - back.y);
+        }
+        unsigned char* t = mt + (size_t)(c >> 3) * (2 * kATileBytes) + swz_off(r, c & 7);
+        *reinterpret_cast<uint4*>(t) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(t + kATileBytes) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
+struct TcParams {
+    const unsigned char* xtiles; const float* rowscale;
+    const int8_t* codes; const float* scales; const float* bias;
+    const float* residual; int ldr;
+    float* out; int ldo;
+    int M, N, K, Kp, nb;
+    int mode;               // 0: out = acc + bias (+ residual);  1: out = SiLU(out) · (acc + bias)   (SwiGLU's second GEMM)
+    int* error;
+    unsigned long long* trace;      // optional: thread 0 of CTA (0,0) sums the time it spends waiting / converting / fencing
+};
+
+__global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ __align__(8) unsigned long long s_bar[3 * kStages + 1];
+    __shared__ uint32_t s_tmem;
+    __shared__ volatile int s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * kTileN, m0 = blockIdx.y * kTileM;
+    const int nK = p.K / kTileK;
+    // the swizzled tiles want 1024-byte alignment: the dynamic segment carries 1 KB of slack for it
+    const uint32_t smem_raw = smem_u32(smem);
+    const uint32_t smem_s = (smem_raw + 1023u) & ~1023u;
+    unsigned char* const smem_al = smem + (smem_s - smem_raw);
+    auto bar_fullA = [&](int s) { return smem_u32(&s_bar[s]); };
+    auto bar_fullB = [&](int s) { return smem_u32(&s_bar[kStages + s]); };
+    auto bar_empty = [&](int s) { return smem_u32(&s_bar[2 * kStages + s]); };
+    const uint32_t bar_acc = smem_u32(&s_bar[3 * kStages]);
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; s++) { mbar_init(bar_fullA(s), 1); mbar_init(bar_fullB(s), kDqWarps * 32); mbar_init(bar_empty(s), 1); }
+        mbar_init(bar_acc, 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kDqWarps) tmem_alloc(smem_u32(&s_tmem), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem;
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (warp < kDqWarps) {
+        // ── dequantise: thread (r, half) owns 32 of the 64 codes of weight row n0 + r per k-tile ──
+        const int r = tid & 127, half = tid >> 7;
+        const int n = n0 + r;
+        const bool live = n < p.N;
+        const int8_t* crow = p.codes + (size_t)(live ? n : 0) * p.Kp + half * 32;
+        const float* srow = p.scales + (size_t)(live ? n : 0) * p.nb + half;
+        // the codes of the next kAhead k-tiles are always in flight in registers: one k-tile of MMA time is
+        // shorter than a load round trip, and these threads are all the memory parallelism the weights get
+        constexpr int kAhead = 4;
+        uint4 buf[kAhead][2]; float bsc[kAhead];
+        auto load_k = [&](int kt, uint4 (&c)[2], float& sc) {
+            const bool on = live && kt < nK;
+            c[0] = on ? __ldg(reinterpret_cast<const uint4*>(crow + (size_t)kt * kTileK)) : make_uint4(0, 0, 0, 0);
+            c[1] = on ? __ldg(reinterpret_cast<const uint4*>(crow + (size_t)kt * kTileK) + 1) : make_uint4(0, 0, 0, 0);
+            sc = on ? __ldg(srow + kt * 2) : 0.0f;
+        };
+#pragma unroll
+        for (int a = 0; a < kAhead; a++) load_k(a, buf[a], bsc[a]);
+        const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
+        unsigned long long tWait = 0, tConv = 0, tFence = 0, tStart = tracing ? gtime() : 0;
+        for (int kt0 = 0; kt0 < nK; kt0 += kAhead) {
+#pragma unroll
+            for (int a = 0; a < kAhead; a++) {
+                const int kt = kt0 + a;
+                if (kt >= nK) break;
+                const int s = kt % kStages;
+                const uint4 cur[2] = {buf[a][0], buf[a][1]};
+                const float scale = bsc[a];
+                load_k(kt + kAhead, buf[a], bsc[a]);
+                unsigned long long t0 = tracing ? gtime() : 0;
+                if (kt >= kStages) mbar_wait(bar_empty(s), ((kt / kStages) - 1) & 1, &s_abort, p.error, 201);
+                unsigned long long t1 = tracing ? gtime() : 0;
+                unsigned char* bhi = smem_al + (size_t)s * kStageBytes + 2 * kATileBytes;
+                unsigned char* blo = bhi + kBTileBytes;
+#pragma unroll
+                for (int j = 0; j < 2; j++) {                  // 16 codes → two 16-byte chunks of hi and of lo
+                    // No conversion-pipe instruction but the two packed fp16 roundings per weight pair:
+                    // code → float through the 2^23 trick (byte under exponent 0x4B is 8388608 + code + 128),
+                    // w_hi = w with the mantissa cut to 10 bits (exactly an fp16 value), w_lo = w − w_hi (exact in fp32).
+                    const uint32_t w4[4] = {cur[j].x ^ 0x80808080u, cur[j].y ^ 0x80808080u, cur[j].z ^ 0x80808080u, cur[j].w ^ 0x80808080u};
+                    uint32_t hi[8], lo[8];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        float f[4], h[4];
+#pragma unroll
+                        for (int b = 0; b < 4; b++) {
+                            const float big = __uint_as_float(__byte_perm(w4[q], 0x4B000000u, 0x7650 + b));   // bytes {w.b, 0, 0, 0x4B}
+                            f[b] = (big - 8388736.0f) * scale;
+                            h[b] = __uint_as_float(__float_as_uint(f[b]) & 0xFFFFE000u);
+                        }
+                        hi[2 * q] = pack_h2(h[0], h[1]); hi[2 * q + 1] = pack_h2(h[2], h[3]);
+                        lo[2 * q] = pack_h2(f[0] - h[0], f[1] - h[1]); lo[2 * q + 1] = pack_h2(f[2] - h[2], f[3] - h[3]);
+                    }
+                    const int o0 = swz_off(r, 4 * half + 2 * j), o1 = swz_off(r, 4 * half + 2 * j + 1);
+                    *reinterpret_cast<uint4*>(bhi + o0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(bhi + o1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                    *reinterpret_cast<uint4*>(blo + o0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4*>(blo + o1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                }
+                unsigned long long t2 = tracing ? gtime() : 0;
+                fence_proxy_async_smem();                      // generic-proxy stores → visible to the tensor-core (async) proxy
+                mbar_arrive(bar_fullB(s));
+                if (tracing) { const unsigned long long t3 = gtime(); tWait += t1 - t0; tConv += t2 - t1; tFence += t3 - t2; }
+            }
+        }
+        if (tracing) { p.trace[0] = tStart; p.trace[1] = tStart + tWait; p.trace[2] = p.trace[1] + tConv; p.trace[3] = p.trace[2] + tFence; p.trace[4] = gtime(); }
+        // ── epilogue: warp w reads accumulator rows 32(w%4) … +31, columns 64(w/4) … +63; each 32 × 32 block goes
+        // through a padded shared-memory square so that a warp stores 128 contiguous bytes of one output row ──
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_acc, 0, &s_abort, p.error, 202));
+        tc_fence_after();
+        const int q4 = warp & 3, chalf = warp >> 2;
+        const int mrow = m0 + q4 * 32 + lane;
+        const float rs = (ok && mrow < p.M) ? p.rowscale[mrow] : 0.0f;
+        float* stg = reinterpret_cast<float*>(smem_al) + warp * (32 * 33);       // the pipeline stages are idle by now
+#pragma unroll 1
+        for (int c0 = chalf * 64; c0 < chalf * 64 + 64; c0 += 32) {
+            uint32_t v[32];
+            if (ok) tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);      // warp-uniform
+            else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) v[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j++) stg[lane * 33 + j] = __uint_as_float(v[j]) * rs;
+            __syncwarp();
+            const int nn = n0 + c0 + lane;
+            const float bv = (p.bias && nn < p.N) ? p.bias[nn] : 0.0f;
+            for (int i = 0; i < 32; i++) {
+                const int m = m0 + q4 * 32 + i;
+                if (!ok || m >= p.M || nn >= p.N) continue;
+                float val = stg[i * 33 + lane] + bv;
+                float* o = p.out + (size_t)m * p.ldo + nn;
+                if (p.mode == 0) {
+                    if (p.residual) val += p.residual[(size_t)m * p.ldr + nn];
+                    *o = val;
+                } else {
+                    const float gte = *o;
+                    const float sig = 1.0f / (1.0f + expf(-gte));
+                    *o = (gte * sig) * val;
+                }
+            }
+            __syncwarp();
+        }
+        if (tracing) { p.trace[5] = gtime(); p.trace[6] = p.trace[5]; }
+        tc_fence_before();
+    } else if (warp == kDqWarps) {
+        // ── activation tiles: one bulk copy of 32 KB (hi + lo) per stage ──
+        if (lane == 0) {
+            const unsigned char* src = p.xtiles + (size_t)blockIdx.y * nK * (2 * kATileBytes);
+            for (int kt = 0; kt < nK; kt++) {
+                const int s = kt % kStages;
+                if (kt >= kStages && !mbar_wait(bar_empty(s), ((kt / kStages) - 1) & 1, &s_abort, p.error, 203)) break;
+                mbar_arrive_expect_tx(bar_fullA(s), 2 * kATileBytes);
+                bulk_g2s(smem_s + (uint32_t)s * kStageBytes, src + (size_t)kt * (2 * kATileBytes), 2 * kATileBytes, bar_fullA(s));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ── MMA issue: one thread ──
+        if (lane == 0) {
+            bool ok = true;
+            for (int kt = 0; kt < nK && ok; kt++) {
+                const int s = kt % kStages;
+                const uint32_t ph = (kt / kStages) & 1;
+                ok = mbar_wait(bar_fullA(s), ph, &s_abort, p.error, 204) && mbar_wait(bar_fullB(s), ph, &s_abort, p.error, 205);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_hi = smem_s + (uint32_t)s * kStageBytes, a_lo = a_hi + kATileBytes;
+                const uint32_t b_hi = a_hi + 2 * kATileBytes, b_lo = b_hi + kBTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < kTileK / 16; ks++) {
+                    const uint32_t off = ks * 32;          // 16 halves along K inside the swizzled row
+                    umma_f16(tmem_base, umma_desc(a_hi + off), umma_desc(b_hi + off), kIdesc, (kt | ks) != 0);
+                    umma_f16(tmem_base, umma_desc(a_lo + off), umma_desc(b_hi + off), kIdesc, 1);
+                    umma_f16(tmem_base, umma_desc(a_hi + off), umma_desc(b_lo + off), kIdesc, 1);
+                }
+                umma_commit(bar_empty(s));                 // arrives when the MMAs above have finished reading the stage
+            }
+            if (ok) umma_commit(bar_acc);
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    if (warp == kDqWarps) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+constexpr size_t kTcSmem = (size_t)kStages * kStageBytes + 1024;
+
+}  // namespace
+
+size_t q8_tc_ws_floats(int M, int K) {
+    const size_t mPad = (size_t)(M + kTileM - 1) / kTileM * kTileM;
+    return mPad * K + mPad;          // hi + lo halves = 4 bytes per value, then the row scales
+}
+
+// out = x · W (+ fused norm / bias / residual / SiLU-gate) for M ≥ 1 rows on the tensor cores.
+// Returns false when the shape is outside the kernel's domain (K must be a multiple of 64).
+bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s) {
+    const int K = a.w.K, N = a.w.N, M = a.M;
+    if (K % kTileK != 0 || a.w.Kp != K || ws == nullptr || M < 1) return false;
+    if (((uintptr_t)a.x & 15) != 0 || a.ldx % 4 != 0 || (a.gamma && ((uintptr_t)a.gamma & 15) != 0)) return false;
+    static bool attrSet = false;
+    if (!attrSet) {
+        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+        attrSet = true;
+    }
+    const int mTiles = (M + kTileM - 1) / kTileM, nTiles = (N + kTileN - 1) / kTileN;
+    const size_t mPad = (size_t)mTiles * kTileM;
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(ws);
+    float* rowscale = ws + mPad * K;
+    launch_k(k_x_to_f16_tiles, dim3((unsigned)(mPad / 8)), dim3(256), 0, s, true, a.x, a.ldx, a.gamma, a.eps, M, K, tiles, rowscale);
+    TcParams p;
+    p.xtiles = tiles; p.rowscale = rowscale;
+    p.codes = a.w.codes; p.scales = a.w.scales; p.bias = a.bias;
+    p.residual = a.residual; p.ldr = a.ldr;
+    p.out = a.out; p.ldo = a.ldo;
+    p.M = M; p.N = N; p.K = K; p.Kp = a.w.Kp; p.nb = a.w.nb;
+    p.mode = 0; p.error = g_dev_error; p.trace = trace_slot();
+    launch_k(k_q8_gemm_tc, dim3(nTiles, mTiles), dim3(kTcThreads), kTcSmem, s, true, p);
+    if (a.w2.codes != nullptr) {
+        // SwiGLU: the gate projection is in `out`; the up projection's epilogue multiplies SiLU(gate) into it
+        p.codes = a.w2.codes; p.scales = a.w2.scales; p.bias = a.bias2; p.residual = nullptr; p.mode = 1;
+        launch_k(k_q8_gemm_tc, dim3(nTiles, mTiles), dim3(kTcThreads), kTcSmem, s, true, p);
+    }
+    return true;
+}
+
+}  // namespace dj

@@ -14,10 +14,13 @@ pytestmark = pytest.mark.gpu
 ATOL, RTOL = 1e-4, 1e-4      # the reference's GPU-vs-CPU comparator: |e-a| <= atol + rtol*|e|
 
 
-def close(expected, actual, atol=ATOL, rtol=RTOL):
+def close(expected, actual, atol=ATOL, rtol=RTOL, floor=0.0):
+    """|error| ≤ atol + rtol·|expected| + floor·max|expected|.  The floor term is for the many-row kernels,
+    whose tensor-core accumulation carries ≈ 2^-18 of the output scale (the stated Q8 tolerance is 2e-3 of it)."""
     err = np.abs(expected - actual)
-    bound = atol + rtol * np.abs(expected)
-    assert np.all(err <= bound), f"max err {err.max()} (bound {bound[np.argmax(err - bound)]})"
+    bound = atol + rtol * np.abs(expected) + floor * float(np.abs(expected).max())
+    worst = np.unravel_index(np.argmax(err - bound), err.shape)
+    assert np.all(err <= bound), f"max err {err.max()} at {worst}: expected {expected[worst]}, got {actual[worst]} (bound {bound[worst]})"
 
 
 class Dev:
@@ -125,7 +128,8 @@ def oracle_rmsnorm(x, gamma):
 
 @pytest.mark.parametrize("M,K,N", [(1, 256, 256), (1, 688, 256), (3, 256, 688), (1, 4096, 512), (2, 2048, 100),
                                    (1, 11008, 64), (1, 100, 33), (1, 512, 2048), (1, 5632, 128), (6, 512, 40), (4, 4096, 24), (1, 1376, 64), (2, 96, 20), (1, 2752, 33),
-                                   (5, 1376, 200), (16, 4096, 512), (16, 96, 20), (7, 2752, 33), (40, 512, 300), (9, 11008, 64)])
+                                   (5, 1376, 200), (16, 4096, 512), (16, 96, 20), (7, 2752, 33), (40, 512, 300), (9, 11008, 64),
+                                   (17, 256, 128), (64, 4096, 512), (130, 512, 300), (512, 2048, 256), (40, 96, 20), (300, 64, 8)])
 @pytest.mark.parametrize("fused", ["plain", "norm_bias_res"])
 def test_q8_linear_matches_oracle(dev, M, K, N, fused):
     rng = np.random.default_rng(K * 7 + N + M)
@@ -145,11 +149,12 @@ def test_q8_linear_matches_oracle(dev, M, K, N, fused):
         expected = (oracle.matmul(oracle_rmsnorm(x, gamma), Wq) + bias) + res
         gb, bb, rb = dev.buf(K, gamma), dev.buf(N, bias), dev.buf(M * N, res)
         dev.flush([OP_Q8_LINEAR, xb, 0, K, gb, float_bits(1e-6), q, bb, rb, 0, N, ob, 0, N, M])
-    close(expected, dev.get(ob, M * N).reshape(M, N))
+    close(expected, dev.get(ob, M * N).reshape(M, N), floor=2e-5 if M >= 5 else 0.0)
 
 
 @pytest.mark.parametrize("M,K,F", [(1, 256, 688), (2, 256, 100), (1, 4096, 256), (1, 2048, 5632),
-                                   (3, 256, 688), (16, 4096, 256), (5, 2048, 100), (20, 512, 72)])
+                                   (3, 256, 688), (16, 4096, 256), (5, 2048, 100), (20, 512, 72),
+                                   (64, 512, 256), (200, 4096, 200)])
 def test_q8_swiglu_matches_oracle(dev, M, K, F):
     rng = np.random.default_rng(K + F)
     x = rng.standard_normal((M, K)).astype(np.float32)
@@ -166,7 +171,7 @@ def test_q8_swiglu_matches_oracle(dev, M, K, F):
     qg, qu = dev.q8(Wg), dev.q8(Wu)
     xb, gb, bgb, bub, ob = dev.buf(M * K, x), dev.buf(K, gamma), dev.buf(F, bg), dev.buf(F, bu), dev.buf(M * F)
     dev.flush([OP_Q8_SWIGLU, xb, 0, K, gb, float_bits(1e-6), qg, bgb, qu, bub, ob, 0, F, M])
-    close(expected, dev.get(ob, M * F).reshape(M, F))
+    close(expected, dev.get(ob, M * F).reshape(M, F), floor=2e-5 if M >= 5 else 0.0)
 
 
 def test_q8_linear_strided_windows(dev):
