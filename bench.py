@@ -213,8 +213,10 @@ def main():
     rng = np.random.default_rng(w["seed"] + 1000)
     prompts = rng.integers(0, w["vocab"], size=(B, w["prompt"]))
     dec.reset()
-    nxt = dec.prefill(prompts)
     t_load = time.perf_counter() - t_load
+    t_prefill = time.perf_counter()
+    nxt = dec.prefill(prompts)          # one GPU: many-row path (tcgen05 GEMMs, chunk attention); several: one step per token
+    t_prefill = time.perf_counter() - t_prefill
 
     lib = dec.lib
     from deepj_b200 import _lib
@@ -330,6 +332,8 @@ def main():
                           "roofline_tokens_per_s": B * world * peak * 1e9 / step_bytes},
         "profile_ms": {"gemv": gemv_ms, "attention": attn_ms, "exchange": exch_ms, "all_ops": total_prof_ms},
         "setup_s": t_load,
+        "prefill": {"tokens": int(B * w["prompt"]), "seconds": t_prefill, "tokens_per_s": B * w["prompt"] / max(t_prefill, 1e-9),
+                    "path": "chunked, many-row kernels" if world == 1 and w["prompt"] >= 32 else "one decode step per position"},
     }
     if not args.no_cpu_baseline and rank == 0:
         v, used, sample = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))

@@ -27,12 +27,33 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 constexpr int kAttnWarps = 4;
 constexpr int kMaxSplits = 256;             // split partials a head can have (the merge keeps their weights in shared memory)
 
+// Prompt chunk: row z = (sequence b, token t) of the projection buffer holds k and v of position pos[b] + t.
+// One thread per interleaved pair: rotate k (x0·c − x1·s, x0·s + x1·c — RotaryEmbedding.java:81-122), copy v.
+__global__ void k_kv_append(const float* __restrict__ qkv, int k_off, int v_off, int ld, float* __restrict__ kcache,
+                            float* __restrict__ vcache, int maxSeq, const float* __restrict__ posbuf,
+                            const float* __restrict__ cosT, const float* __restrict__ sinT, int H, int hd, int T) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int h = blockIdx.x, z = blockIdx.y, i = threadIdx.x;
+    const int b = z / T, tok = z - b * T;
+    const int p = (int)posbuf[b] + tok;
+    if (p < 0 || p >= maxSeq) return;
+    const float* row = qkv + (size_t)z * ld;
+    const float2 k2 = *reinterpret_cast<const float2*>(row + k_off + h * hd + 2 * i);
+    const float2 v2 = *reinterpret_cast<const float2*>(row + v_off + h * hd + 2 * i);
+    const float c = cosT[(size_t)p * (hd >> 1) + i], s = sinT[(size_t)p * (hd >> 1) + i];
+    const size_t dst = (((size_t)b * H + h) * maxSeq + p) * hd + 2 * i;
+    *reinterpret_cast<float2*>(kcache + dst) = make_float2(k2.x * c - k2.y * s, k2.x * s + k2.y * c);
+    *reinterpret_cast<float2*>(vcache + dst) = v2;
+}
+
 template <int LPP>   // lanes per position = hd / 16
 __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
         const float* __restrict__ qkv, int q_off, int k_off, int v_off, int ld,
         float* __restrict__ kcache, float* __restrict__ vcache, int maxSeq,
         const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
-        float* __restrict__ ws, int* __restrict__ tickets, float* __restrict__ out, int ldo, int H, float scale) {
+        float* __restrict__ ws, int* __restrict__ tickets, float* __restrict__ out, int ldo, int H, float scale,
+        int T, int append) {
     constexpr int HD = LPP * 16;
     constexpr int PPW = 32 / LPP;                 // positions per warp iteration
     constexpr int G = kAttnWarps * PPW;           // position groups per CTA
@@ -40,7 +61,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     __shared__ float s_m[G], s_l[G];
     __shared__ int s_last;
 
-    const int split = blockIdx.x, splits = gridDim.x, h = blockIdx.y, b = blockIdx.z;
+    // row z of the projection / output buffers is token t of sequence b: T = 1 (and append) for a decode step;
+    // T > 1 for a prompt chunk, whose k/v rows the append kernel has already written
+    const int split = blockIdx.x, splits = gridDim.x, h = blockIdx.y, z = blockIdx.z;
+    const int b = z / T, tok = z - b * T;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int group = lane / LPP, gl = lane % LPP;
     // The cache rows below the current position were written by earlier steps, not by the kernel
@@ -49,7 +73,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     // (never observed) case that it moved, the speculative rows are dropped and fetched again.
     const int half = HD >> 1;
     auto read_pos = [&]() {
-        int v = (int)__ldcg(posbuf + b);
+        int v = (int)__ldcg(posbuf + b) + tok;
         return v < 0 ? 0 : (v >= maxSeq ? maxSeq - 1 : v);
     };
     int pos = read_pos();
@@ -77,7 +101,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     };
     {
         const int p0 = start + warp * PPW + group;
-        fetch_cached(p0, p0 < end && p0 != pos, kf, vf);
+        fetch_cached(p0, T == 1 && p0 < end && p0 != pos, kf, vf);      // a chunk's own rows were written by the kernel before this one
     }
     // the rotation tables are constants: the row of the speculative position is fetched before the wait too
     float cs[8], sn[8];
@@ -96,7 +120,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     pdl_wait();
     pdl_launch_dependents();
     // the query row does not depend on the position: its loads go out together with the position's
-    const float* rowp = qkv + (size_t)b * ld;
+    const float* rowp = qkv + (size_t)z * ld;
     float q[16];
     {
         const float4* qp = reinterpret_cast<const float4*>(rowp + q_off + h * HD + gl * 16);
@@ -123,7 +147,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
 
     // K and V slices of position p for this lane (zeros when the lane has no position)
     auto fetch = [&](int p, bool valid, float (&kf)[16], float (&vf)[16]) {
-        if (valid && p == pos) {
+        if (valid && p == pos && append) {
             // the new token: k and v come from the projections; rotate k, append both to the cache
             const float4* kp = reinterpret_cast<const float4*>(rowp + k_off + h * HD + gl * 16);
             const float4* vp = reinterpret_cast<const float4*>(rowp + v_off + h * HD + gl * 16);
@@ -166,7 +190,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     int base = start + warp * PPW;
     if (base < end) {
         const int p0 = base + group;
-        if (pos != specPos || (p0 == pos && p0 < end)) fetch(p0, p0 < end, kf, vf);      // the new token's lane, or a dropped speculation
+        if (T > 1 || pos != specPos || (p0 == pos && p0 < end)) fetch(p0, p0 < end, kf, vf);      // the new token's lane, a prompt chunk, or a dropped speculation
     }
     for (; base < end; base += G) {
         const bool valid = base + group < end;
@@ -195,7 +219,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     for (int j = 0; j < 16; j++) s_acc[g][gl * 16 + j] = acc[j];
     if (gl == 0) { s_m[g] = m; s_l[g] = l; }
     __syncthreads();
-    float* mine = ws + (((size_t)b * H + h) * splits + split) * (HD + 2);
+    float* mine = ws + (((size_t)z * H + h) * splits + split) * (HD + 2);
     for (int j = threadIdx.x; j < HD; j += blockDim.x) {
         float M = -INFINITY;
         for (int gg = 0; gg < G; gg++) M = fmaxf(M, s_m[gg]);
@@ -213,23 +237,23 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     if (splits == 1) {
         // nothing to merge
         __syncthreads();
-        for (int j = threadIdx.x; j < HD; j += blockDim.x) out[(size_t)b * ldo + h * HD + j] = mine[j] / mine[HD + 1];
+        for (int j = threadIdx.x; j < HD; j += blockDim.x) out[(size_t)z * ldo + h * HD + j] = mine[j] / mine[HD + 1];
         return;
     }
     // ── the last CTA of this head merges the split partials ──
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const int ticket = atomicAdd(&tickets[b * H + h], 1);
+        const int ticket = atomicAdd(&tickets[z * H + h], 1);
         s_last = ticket == splits - 1;
-        if (s_last) tickets[b * H + h] = 0;          // ready for the next launch
+        if (s_last) tickets[z * H + h] = 0;          // ready for the next launch
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
     // Thread sp fetches split sp's (m, l); the weights exp(m_sp − M) are shared through shared memory, and the
     // partial rows are requested eight splits at a time, so the merge costs a few load round trips in all.
-    const float* pbase = ws + ((size_t)b * H + h) * splits * (HD + 2);
+    const float* pbase = ws + ((size_t)z * H + h) * splits * (HD + 2);
     float* s_w = &s_acc[0][0];                  // reused: the CTA's own partial has been written out
     float* s_ml = s_w + kMaxSplits;
     for (int sp = threadIdx.x; sp < splits; sp += blockDim.x) {
@@ -253,7 +277,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
 #pragma unroll
             for (int q = 0; q < 8; q++) if (s0 + q < splits) a = fmaf(part[q], s_w[s0 + q], a);
         }
-        out[(size_t)b * ldo + h * HD + j] = a / L;
+        out[(size_t)z * ldo + h * HD + j] = a / L;
     }
 }
 
@@ -274,12 +298,22 @@ void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s) {
     int lpp = a.hd / 16;
     if (a.hd % 16 != 0 || (lpp != 1 && lpp != 2 && lpp != 4 && lpp != 8 && lpp != 16 && lpp != 32))
         throw std::runtime_error("attention: head dim " + std::to_string(a.hd) + " is not one of 16,32,64,128,256,512");
-    dim3 grid(a.splits, a.H, a.B), block(kAttnWarps * 32);
-    if (a.B * a.H > kAttnTickets) throw std::runtime_error("attention: batch × heads exceeds " + std::to_string(kAttnTickets));
+    const int T = a.T < 1 ? 1 : a.T;
+    const long rows = (long)a.B * T;
+    if (rows > 65535) throw std::runtime_error("attention: more than 65535 rows in one launch");
+    dim3 grid(a.splits, a.H, (unsigned)rows), block(kAttnWarps * 32);
+    if (a.splits > 1 && rows * a.H > kAttnTickets / 2) throw std::runtime_error("attention: rows × heads exceeds " + std::to_string(kAttnTickets / 2));
+    if (T > 1) {
+        // the chunk's keys (rotated) and values go into the cache first; the attention kernel then only reads
+        dim3 ag(a.H, (unsigned)rows);
+        launch_k(k_kv_append, ag, dim3(a.hd / 2), 0, s, true, (const float*)a.qkv, a.k_off, a.v_off, a.ld, a.kcache, a.vcache, a.maxSeq,
+                 a.pos, a.cosT, a.sinT, a.H, a.hd, T);
+    }
+    const int append = T == 1 ? 1 : 0;
     int* tickets = a.tickets;
 #define DJ_ATTN_CASE(L)                                                                                              \
     case L: launch_k(k_attn_decode<L>, grid, block, 0, s, true, (const float*)a.qkv, a.q_off, a.k_off, a.v_off, a.ld, \
-                     a.kcache, a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.ws, tickets, a.out, a.ldo, a.H, a.scale); break;
+                     a.kcache, a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.ws, tickets, a.out, a.ldo, a.H, a.scale, T, append); break;
     switch (lpp) {
         DJ_ATTN_CASE(1) DJ_ATTN_CASE(2) DJ_ATTN_CASE(4) DJ_ATTN_CASE(8) DJ_ATTN_CASE(16) DJ_ATTN_CASE(32)
     }

@@ -97,6 +97,7 @@ struct AttnDecodeArgs {
     float scale;
     float* ws;                                 // split partials: [B][H][splits][hd + 2]
     int* tickets;                              // [B·H] zero-initialised, self-resetting counters
+    int T = 1;                                 // tokens per sequence in this call: 1 = decode step, > 1 = prompt chunk (rows b·T + t)
     int splits;
 };
 constexpr int kAttnTickets = 1 << 16;

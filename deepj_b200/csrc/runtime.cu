@@ -157,6 +157,7 @@ int op_stride(int op) {
         case DEEPJ_OP_Q8_LINEAR: return 15;
         case DEEPJ_OP_Q8_SWIGLU: return 14;
         case DEEPJ_OP_ATTN_DECODE: return 17;
+        case DEEPJ_OP_ATTN_PREFILL: return 18;
         case DEEPJ_OP_ARGMAX_ROWS: return 5;
         case DEEPJ_OP_ADD_SCALAR_INPLACE: return 4;
         case DEEPJ_OP_COPY: return 6;
@@ -327,10 +328,15 @@ void do_op(Ctx& ctx, const int32_t* c) {
             if (go) launch_q8_linear(a, s);
             break;
         }
-        case DEEPJ_OP_ATTN_DECODE: {
-            // [op, qkv, q_off, k_off, v_off, ld, kv, layer, pos, cos, sin, out, out_off, ldo, B, H, hd]
+        case DEEPJ_OP_ATTN_DECODE:
+        case DEEPJ_OP_ATTN_PREFILL: {
+            // [op, qkv, q_off, k_off, v_off, ld, kv, layer, pos, cos, sin, out, out_off, ldo, B, H, hd (, T)]
+            // prefill: rows b·T + t of qkv / out are tokens pos[b] + t, t < T, of sequence b
             int q_off = c[2], k_off = c[3], v_off = c[4], ld = c[5], layer = c[7], out_off = c[12], ldo = c[13];
             int B = c[14], H = c[15], hd = c[16];
+            const int T = op == DEEPJ_OP_ATTN_PREFILL ? c[17] : 1;
+            require(T >= 1 && (long)B * T <= 65535, "attnPrefill", "bad token count");
+            const int rows = B * T;
             Buf& kv = find_buf(ctx, c[6], kKV, "attnDecode");
             require(B >= 1 && H >= 1 && hd >= 2, "attnDecode", "bad dimension");
             require(B <= kv.B && H == kv.H && hd == kv.hd, "attnDecode", "shape does not match the KV cache");
@@ -341,18 +347,18 @@ void do_op(Ctx& ctx, const int32_t* c) {
             int maxOff = std::max(q_off, std::max(k_off, v_off));
             require(ld >= maxOff + d && ldo >= d, "attnDecode", "row stride smaller than the row");
             AttnDecodeArgs a = {};
-            a.qkv = f32(ctx, c[1], sz(B - 1, ld) + maxOff + d, "attnDecode"); a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.ld = ld;
+            a.qkv = f32(ctx, c[1], sz(rows - 1, ld) + maxOff + d, "attnDecode"); a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.ld = ld;
             size_t plane = (size_t)kv.layers * kv.B * kv.H * kv.maxSeq * kv.hd;
             size_t layerOff = (size_t)layer * kv.B * kv.H * kv.maxSeq * kv.hd;
             a.kcache = (float*)kv.ptr + layerOff; a.vcache = (float*)kv.ptr + plane + layerOff;
             a.maxSeq = kv.maxSeq;
             a.pos = f32(ctx, c[8], B, "attnDecode");
             a.cosT = f32(ctx, c[9], sz(kv.maxSeq, hd / 2), "attnDecode"); a.sinT = f32(ctx, c[10], sz(kv.maxSeq, hd / 2), "attnDecode");
-            a.out = f32(ctx, c[11], (size_t)out_off + sz(B - 1, ldo) + d, "attnDecode") + out_off; a.ldo = ldo;
-            a.B = B; a.H = H; a.hd = hd;
+            a.out = f32(ctx, c[11], (size_t)out_off + sz(rows - 1, ldo) + d, "attnDecode") + out_off; a.ldo = ldo;
+            a.B = B; a.H = H; a.hd = hd; a.T = T;
             a.scale = (float)(1.0 / std::sqrt((double)hd));     // MultiHeadSelfAttention.java:44
-            a.splits = attn_decode_splits(B, H, kv.maxSeq);
-            size_t need = attn_decode_ws_floats(B, H, hd, a.splits);
+            a.splits = attn_decode_splits(rows, H, kv.maxSeq);
+            size_t need = attn_decode_ws_floats(rows, H, hd, a.splits);
             if (need > ctx.ws_need) ctx.ws_need = need;
             a.ws = R.ws;
             a.tickets = R.tickets;

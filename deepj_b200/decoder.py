@@ -21,7 +21,7 @@ from typing import Tuple, Callable, Dict, List, Optional
 import numpy as np
 
 from . import _lib
-from .compute_graph import (OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_COPY, OP_EMBED_GATHER,
+from .compute_graph import (OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_ATTN_PREFILL, OP_COPY, OP_EMBED_GATHER,
                             OP_Q8_LINEAR, OP_Q8_SWIGLU, OP_TP_ALLGATHER, OP_TP_ALLREDUCE, float_bits)
 
 RMS_EPS = 1e-6      # layers/transformer/norm/RMSNorm1D.java:30
@@ -153,6 +153,9 @@ class Q8Decoder:
         self._stream_host: Optional[np.ndarray] = None
         self._stream_dev: Optional[np.ndarray] = None
         self._op_labels: List[str] = []
+        self._prefill_ids: Dict[str, int] = {}
+        self._prefill_cap = 0
+        self._prefill_streams: Dict[int, np.ndarray] = {}
         self.position = 0
         self._alloc_state()
 
@@ -424,14 +427,99 @@ class Q8Decoder:
     def next_tokens(self) -> np.ndarray:
         return self._download(self.ids["next"], self.B).astype(np.int64)
 
-    def prefill(self, prompts) -> np.ndarray:
-        """Feed the prompt one position at a time (every sequence the same length);
-        returns the greedy pick after the last prompt token."""
+    PREFILL_CHUNK = 512      # prompt tokens per sequence and pass of the many-row path
+
+    def _build_prefill(self, T: int) -> np.ndarray:
+        """The stream of one prompt chunk: T tokens of every sequence at once, B·T activation rows through the
+        many-row Q8 kernels and the chunk attention op; the last token's hidden state lands in the decode
+        buffers and the positions advance by T.  (Single GPU; the row-major layout is row = b·T + t.)"""
+        c, B, I, P = self.cfg, self.B, self.ids, self._prefill_ids
+        d, dl, Fl, Hl = c.d_model, self.d_local, self.f_local, self.h_local
+        M = B * T
+        eps = float_bits(RMS_EPS)
+        s: List[int] = []
+
+        def linear(x, x_off, ldx, gamma, w, bias, res, ldr, out, ldo):
+            s.extend(int(v) for v in (OP_Q8_LINEAR, x, x_off, ldx, gamma, eps, w, bias, res, 0, ldr, out, 0, ldo, M))
+
+        s.extend((OP_EMBED_GATHER, I["emb"], P["tok"], P["x"], M, d, c.vocab_size))
+        for l in range(c.n_layers):
+            if c.kind == "llama":
+                linear(P["x"], 0, d, I[f"g1.{l}"], I[f"Wqkv.{l}"], -1, -1, 0, P["qkv"], 3 * dl)
+            else:
+                r = c.q_rank + c.kv_rank
+                linear(P["x"], 0, d, I[f"g1.{l}"], I[f"Wdqkv.{l}"], -1, -1, 0, P["lat"], r)
+                linear(P["lat"], 0, r, -1, I[f"Wuq.{l}"], -1, -1, 0, P["qkv"], 3 * dl)
+                s.extend(int(v) for v in (OP_Q8_LINEAR, P["lat"], c.q_rank, r, -1, eps, I[f"Wukv.{l}"], -1, -1, 0, 0, P["qkv"], dl, 3 * dl, M))
+            s.extend(int(v) for v in (OP_ATTN_PREFILL, P["qkv"], 0, dl, 2 * dl, 3 * dl, I["kv"], l, I["pos"], I["cos"], I["sin"],
+                                      P["att"], 0, dl, B, Hl, c.head_dim, T))
+            linear(P["att"], 0, dl, -1, I[f"Wo.{l}"], -1, P["x"], d, P["x2"], d)
+            s.extend(int(v) for v in (OP_Q8_SWIGLU, P["x2"], 0, d, I[f"g2.{l}"], eps, I[f"Wg.{l}"], I[f"bg.{l}"], I[f"Wu.{l}"],
+                                      I[f"bu.{l}"], P["h"], 0, Fl, M))
+            linear(P["h"], 0, Fl, -1, I[f"Wd.{l}"], I[f"bd.{l}"], P["x2"], d, P["x"], d)
+        for b in range(B):
+            s.extend((OP_COPY, P["x"], (b * T + T - 1) * d, I["x"], b * d, d))
+        s.extend((OP_ADD_SCALAR_INPLACE, I["pos"], float_bits(float(T)), B))
+        return np.asarray(s, dtype=np.int32)
+
+    def _head_stream(self) -> np.ndarray:
+        """Final norm + LM head + greedy pick on the hidden state in the decode buffer."""
+        c, B, I = self.cfg, self.B, self.ids
+        s = [OP_Q8_LINEAR, I["x"], 0, c.d_model, I["gF"], float_bits(RMS_EPS), I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0, c.vocab_size, B,
+             OP_ARGMAX_ROWS, I["logits"], I["next"], B, c.vocab_size]
+        return np.asarray(s, dtype=np.int32)
+
+    def prefill(self, prompts, chunked: Optional[bool] = None) -> np.ndarray:
+        """Feed the prompt (every sequence the same length); returns the greedy pick after its last token.
+        Prompts of 32 tokens or more go through the many-row path in chunks of PREFILL_CHUNK tokens per
+        sequence (tensor-core GEMMs, chunk attention); shorter ones, and tensor-parallel runs, one decode step
+        per position."""
         p = np.asarray(prompts, dtype=np.int64).reshape(self.B, -1)
-        nxt = None
-        for t in range(p.shape[1]):
-            nxt = self.step(p[:, t])
-        return nxt
+        T_all = p.shape[1]
+        if chunked is None:
+            chunked = self.tp_world == 1 and T_all >= 32
+        if not chunked or T_all == 0:
+            nxt = None
+            for t in range(T_all):
+                nxt = self.step(p[:, t])
+            return nxt
+        if self.tp_world > 1:
+            raise ValueError("the chunked prefill path runs on one GPU")
+        if np.any(p < 0) or np.any(p >= self.cfg.vocab_size):
+            raise ValueError(f"Token id out of range: {int(p[(p < 0) | (p >= self.cfg.vocab_size)][0])}")
+        if self.position + T_all > self.cfg.max_seq_len:
+            raise ValueError(f"seqLen {self.position + T_all} exceeds maxSeqLen {self.cfg.max_seq_len}")
+        C = min(self.PREFILL_CHUNK, T_all, max(1, 65535 // self.B))
+        self._ensure_prefill_buffers(C)
+        done = 0
+        while done < T_all:
+            T = min(C, T_all - done)
+            if T not in self._prefill_streams:
+                self._prefill_streams[T] = self._build_prefill(T)
+            st = self._prefill_streams[T]
+            self._upload(self._prefill_ids["tok"], p[:, done:done + T].astype(np.float32).reshape(-1))
+            _lib.check(self.lib.deepj_cuda_flush_ops(st.ctypes.data, st.size))
+            done += T
+            self.position += T
+        hs = self._head_stream()
+        _lib.check(self.lib.deepj_cuda_flush_ops(hs.ctypes.data, hs.size))
+        return self.next_tokens()
+
+    def _ensure_prefill_buffers(self, C: int) -> None:
+        if self._prefill_cap >= C:
+            return
+        if self._prefill_ids:
+            self._release(list(self._prefill_ids.values()))
+        c, M = self.cfg, self.B * C
+        sizes = {"tok": M, "x": M * c.d_model, "x2": M * c.d_model, "qkv": M * 3 * self.d_local, "att": M * self.d_local,
+                 "h": M * self.f_local}
+        if c.kind == "deepseek":
+            sizes["lat"] = M * (c.q_rank + c.kv_rank)
+        self._prefill_ids = {}
+        for name, n in sizes.items():
+            self._prefill_ids[name] = self._f32("", n)
+        self._prefill_cap = C
+        self._prefill_streams = {}
 
     def generate_greedy(self, prompt, max_new_tokens: int, keep_logits: bool = False):
         """TextGenerator.generate with topK = 1 (models/TextGenerator.java:66-100)

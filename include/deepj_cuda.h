@@ -158,6 +158,9 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
  *  70 COPY              [op, src, src_off, dst, dst_off, n]
  *  71 TP_ALLREDUCE      [op, in, bias, residual, out, M, N]   out = residual + bias + sum over ranks of in (rank order)
  *  72 TP_ALLGATHER      [op, in, out, M, n_local]             out[m][r*n_local + j] = in of rank r
+ *  73 ATTN_PREFILL      [op, qkv, q_off, k_off, v_off, ld, kv, layer, pos, cos, sin, out, out_off, ldo, B, H, hd, T]
+ *                        a prompt chunk: row b*T + t is token pos[b] + t of sequence b; the chunk's k (rotated)
+ *                        and v are appended first, then every row attends causally over 0..pos[b]+t
  */
 #define DEEPJ_OP_EMBED_GATHER        64
 #define DEEPJ_OP_Q8_LINEAR           65
@@ -168,6 +171,7 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
 #define DEEPJ_OP_COPY                70
 #define DEEPJ_OP_TP_ALLREDUCE        71
 #define DEEPJ_OP_TP_ALLGATHER        72
+#define DEEPJ_OP_ATTN_PREFILL        73
 
 #ifdef __cplusplus
 }
