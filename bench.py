@@ -70,7 +70,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.idx)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+                                          "-lms", "20", "-i", str(self.idx)], stdout=self.tmp, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
