@@ -251,31 +251,41 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // Thread sp fetches split sp's (m, l); the weights exp(m_sp − M) are shared through shared memory, and the
-    // partial rows are requested eight splits at a time, so the merge costs a few load round trips in all.
+    // Every thread requests its own column of up to 24 split partials together with the (m, l) pairs, so the
+    // merge costs one load round trip (more splits: further rounds of 24).
     const float* pbase = ws + ((size_t)z * H + h) * splits * (HD + 2);
-    float* s_w = &s_acc[0][0];                  // reused: the CTA's own partial has been written out
-    float* s_ml = s_w + kMaxSplits;
+    float* s_m2 = &s_acc[0][0];                 // reused: the CTA's own partial has been written out
+    float* s_l2 = s_m2 + kMaxSplits;
     for (int sp = threadIdx.x; sp < splits; sp += blockDim.x) {
-        s_w[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD);
-        s_ml[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD + 1);
+        s_m2[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD);
+        s_l2[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD + 1);
     }
+    constexpr int kBatch = 24;
+    const int j0 = threadIdx.x;                 // HD ≤ 512 = 4 columns per thread at most; the first one is prefetched here
+    float first[kBatch];
+#pragma unroll
+    for (int q = 0; q < kBatch; q++) first[q] = (j0 < HD && q < splits) ? __ldcg(pbase + (size_t)q * (HD + 2) + j0) : 0.0f;
     __syncthreads();
     float M = -INFINITY;
-    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, s_w[sp]);
+    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, s_m2[sp]);
     float L = 0.0f;
-    for (int sp = 0; sp < splits; sp++) L = fmaf(s_ml[sp], expf(s_w[sp] - M), L);
+    for (int sp = 0; sp < splits; sp++) L = fmaf(s_l2[sp], expf(s_m2[sp] - M), L);
     __syncthreads();
-    for (int sp = threadIdx.x; sp < splits; sp += blockDim.x) s_w[sp] = expf(s_w[sp] - M);
+    for (int sp = threadIdx.x; sp < splits; sp += blockDim.x) s_m2[sp] = expf(s_m2[sp] - M);
     __syncthreads();
     for (int j = threadIdx.x; j < HD; j += blockDim.x) {
         float a = 0.0f;
-        for (int s0 = 0; s0 < splits; s0 += 8) {
-            float part[8];
+        for (int s0 = 0; s0 < splits; s0 += kBatch) {
+            float part[kBatch];
+            if (j == j0 && s0 == 0) {
 #pragma unroll
-            for (int q = 0; q < 8; q++) part[q] = s0 + q < splits ? __ldcg(pbase + (size_t)(s0 + q) * (HD + 2) + j) : 0.0f;
+                for (int q = 0; q < kBatch; q++) part[q] = first[q];
+            } else {
 #pragma unroll
-            for (int q = 0; q < 8; q++) if (s0 + q < splits) a = fmaf(part[q], s_w[s0 + q], a);
+                for (int q = 0; q < kBatch; q++) part[q] = s0 + q < splits ? __ldcg(pbase + (size_t)(s0 + q) * (HD + 2) + j) : 0.0f;
+            }
+#pragma unroll
+            for (int q = 0; q < kBatch; q++) if (s0 + q < splits) a = fmaf(part[q], s_m2[s0 + q], a);
         }
         out[(size_t)z * ldo + h * HD + j] = a / L;
     }

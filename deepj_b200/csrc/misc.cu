@@ -62,6 +62,129 @@ __global__ void k_argmax_rows(const float* __restrict__ in, float* __restrict__ 
     }
 }
 
+// Temperature / top-k sampling with the reference's semantics (models/TextGenerator.java:104-151): indices in
+// stable descending order of the logits (Float.compare, lowest index first among equals), the first k of them,
+// p_i = (float) exp((double)(logit_i / T − max)), a sequential float sum, p_i /= sum, and the first i whose running
+// sum reaches r (r = Random.nextFloat(), drawn by the host and passed per row).  One CTA of 1024 threads per row;
+// k ≤ 1024.  The k-th largest key is found by an 8-bit radix select (four passes over the row), the candidates are
+// gathered (equal keys by ascending index) and sorted by (key, −index) with a bitonic network in shared memory.
+constexpr int kSampleMaxK = 1024;
+
+__global__ void __launch_bounds__(1024) k_sample_topk(const float* __restrict__ logits, const float* __restrict__ rbuf,
+                                                       float* __restrict__ out, int rows, int cols, int topK, float temperature) {
+    __shared__ unsigned s_hist[256];
+    __shared__ unsigned long long s_cand[kSampleMaxK];
+    __shared__ float s_p[kSampleMaxK];
+    __shared__ unsigned s_scan[1024];
+    __shared__ unsigned s_prefix, s_need, s_cnt;
+    __shared__ float s_red[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x;
+    const float* d = logits + (size_t)blockIdx.x * cols;
+    const int k = topK < cols ? topK : cols;
+    auto ukey = [&](int c) { return (unsigned)order_key(d[c]) ^ 0x80000000u; };      // ascending unsigned = Float.compare order
+
+    // ── the k-th largest key ──
+    unsigned prefix = 0, mask = 0, need = (unsigned)k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) s_hist[tid] = 0;
+        __syncthreads();
+        for (int c = tid; c < cols; c += blockDim.x) {
+            const unsigned key = ukey(c);
+            if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            unsigned acc = 0; int chosen = 0;
+            for (int b = 255; b >= 0; b--) {
+                if (acc + s_hist[b] >= need) { chosen = b; break; }
+                acc += s_hist[b];
+            }
+            s_prefix = prefix | ((unsigned)chosen << shift);
+            s_need = need - acc;
+        }
+        __syncthreads();
+        prefix = s_prefix; need = s_need; mask |= 255u << shift;
+        __syncthreads();
+    }
+    const unsigned T = prefix;                       // need = how many of the keys equal to T belong to the top k
+    const unsigned nGreater = (unsigned)k - need;
+
+    // ── candidates: every key above T, and the `need` lowest indices among the keys equal to T ──
+    if (tid == 0) s_cnt = 0;
+    __syncthreads();
+    for (int c = tid; c < cols; c += blockDim.x) {
+        const unsigned key = ukey(c);
+        if (key > T) {
+            const unsigned pos = atomicAdd(&s_cnt, 1u);
+            if (pos < (unsigned)kSampleMaxK) s_cand[pos] = ((unsigned long long)key << 32) | (0xFFFFFFFFu - (unsigned)c);
+        }
+    }
+    const int chunk = (cols + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int lo = min(cols, tid * chunk), hi = min(cols, lo + chunk);
+    unsigned mine = 0;
+    for (int c = lo; c < hi; c++) mine += ukey(c) == T;
+    s_scan[tid] = mine;
+    __syncthreads();
+    for (int o = 1; o < (int)blockDim.x; o <<= 1) {      // inclusive scan over the threads, in index order
+        const unsigned v = tid >= o ? s_scan[tid - o] : 0u;
+        __syncthreads();
+        s_scan[tid] += v;
+        __syncthreads();
+    }
+    unsigned rank = s_scan[tid] - mine;
+    for (int c = lo; c < hi && rank < need; c++) {
+        if (ukey(c) == T) {
+            s_cand[nGreater + rank] = ((unsigned long long)T << 32) | (0xFFFFFFFFu - (unsigned)c);
+            rank++;
+        }
+    }
+    int P = 1;
+    while (P < k) P <<= 1;
+    for (int i = k + tid; i < P; i += blockDim.x) s_cand[i] = 0ull;
+    // ── descending bitonic sort of (key, −index) ──
+    for (int size = 2; size <= P; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            const int i = tid, j = tid ^ stride;
+            if (j > i && j < P) {
+                const unsigned long long a = s_cand[i], b = s_cand[j];
+                const bool desc = (i & size) == 0;
+                if (desc ? a < b : a > b) { s_cand[i] = b; s_cand[j] = a; }
+            }
+        }
+    }
+    __syncthreads();
+    // ── probabilities of the k candidates, then the sequential sums of the reference ──
+    float v = -INFINITY;
+    int idx = 0;
+    if (tid < k) {
+        idx = (int)(0xFFFFFFFFu - (unsigned)(s_cand[tid] & 0xFFFFFFFFull));
+        v = d[idx] / temperature;
+    }
+    float mx = (tid < k && v == v) ? v : -INFINITY;      // `if (v > max) max = v` never takes a NaN
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((tid & 31) == 0) s_red[tid >> 5] = mx;
+    __syncthreads();
+    mx = s_red[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) mx = fmaxf(mx, s_red[w]);
+    if (tid < k) s_p[tid] = (float)exp((double)(v - mx));
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.0f;
+        for (int i = 0; i < k; i++) sum += s_p[i];
+        const float r = rbuf[blockIdx.x];
+        float cum = 0.0f;
+        int pick = k - 1;
+        for (int i = 0; i < k; i++) {
+            cum += s_p[i] / sum;
+            if (r <= cum) { pick = i; break; }
+        }
+        out[blockIdx.x] = (float)(int)(0xFFFFFFFFu - (unsigned)(s_cand[pick] & 0xFFFFFFFFull));
+    }
+}
+
 __global__ void k_add_scalar_inplace(float* __restrict__ buf, float v, int n) {
     pdl_wait();
     pdl_launch_dependents();
@@ -111,6 +234,12 @@ void launch_embed_gather(const float* table, const float* ids, float* out, int r
 void launch_argmax_rows(const float* in, float* out, int rows, int cols, cudaStream_t s) {
     if (rows <= 0) return;
     launch_k(k_argmax_rows, dim3(rows), dim3(1024), 0, s, true, in, out, rows, cols);
+}
+void launch_sample_topk(const float* logits, const float* r, float* out, int rows, int cols, int topK, float temperature, cudaStream_t s) {
+    if (rows <= 0) return;
+    if (topK < 1 || topK > kSampleMaxK) throw std::runtime_error("sampleTopK: topK must be in 1.." + std::to_string(kSampleMaxK) + " on the device sampler");
+    if (!(temperature > 0.0f)) throw std::runtime_error("temperature must be > 0");
+    launch_k(k_sample_topk, dim3(rows), dim3(1024), 0, s, true, logits, r, out, rows, cols, topK, temperature);
 }
 void launch_add_scalar_inplace(float* buf, float v, int n, cudaStream_t s) {
     if (n <= 0) return;

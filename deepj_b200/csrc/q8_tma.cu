@@ -64,6 +64,7 @@ struct TmaParams {
     float* out; int ldo;
     int K, N, Kp, nb, M;
     int pre;                        // ring items a warp fetches before it waits for the previous kernel
+    int mid;                        // ring items in flight while the activations are staged; the rest of the ring fills afterwards
     unsigned long long* trace;      // optional: six %globaltimer stamps of CTA 0 (phase tracing)
 };
 
@@ -131,6 +132,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     // only kPre items deep: every byte in flight on this SM queues ahead of the activation
     // loads that follow the wait (latency = bytes in flight / bandwidth).
     const int kPre = p.pre < DEPTH - 1 ? p.pre : DEPTH - 1;
+    const int kMid = p.mid < DEPTH - 1 ? (p.mid > kPre ? p.mid : kPre) : DEPTH - 1;
     const bool haveWork = warp < nPairs;
     if (haveWork) {
         for (int d = 0; d < kPre; d++) issue_next();
@@ -168,7 +170,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
                 }
             }
             if (m == 0 && haveWork) {
-                for (int d = kPre; d < DEPTH - 1; d++) issue_next();      // now fill the ring behind the activation loads
+                for (int d = kPre; d < kMid; d++) issue_next();      // more of the ring behind the activation loads
             }
             float inv = 1.0f;
             if (p.gamma) {
@@ -221,7 +223,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
                 inv = __frcp_rn(sqrtf(ss * (1.0f / (float)p.K) + p.eps));
             }
             if (m == 0 && haveWork) {
-                for (int d = kPre; d < DEPTH - 1; d++) issue_next();
+                for (int d = kPre; d < kMid; d++) issue_next();
             }
             for (int r = 0; r < rounds; r++) {
                 const int hb = r * kThreads + tid;
@@ -246,6 +248,9 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
         }
     }
     __syncthreads();
+    if (haveWork) {
+        for (int d = kMid; d < DEPTH - 1; d++) issue_next();      // the rest of the ring: nothing latency-critical queues behind it now
+    }
     if (tracing) p.trace[3] = gtime();
 
     // lane (g,t) feeds MMA column g: activation row g/4, digit g%4 (digit 3 does not exist)
@@ -394,6 +399,8 @@ bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s) {
         p.K = K; p.N = a.w.N; p.Kp = a.w.Kp; p.nb = a.w.nb; p.M = rows;
         static const int pre = getenv("DEEPJ_CUDA_GEMV_PRE") ? atoi(getenv("DEEPJ_CUDA_GEMV_PRE")) : kPreMax;
         p.pre = pre;
+        static const int mid = getenv("DEEPJ_CUDA_GEMV_MID") ? atoi(getenv("DEEPJ_CUDA_GEMV_MID")) : 4;
+        p.mid = mid;
         p.trace = trace_slot();
         if (swiglu) launch_i8_depth<true>(p, depth, s); else launch_i8_depth<false>(p, depth, s);
         m0 += rows;

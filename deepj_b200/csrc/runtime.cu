@@ -158,6 +158,7 @@ int op_stride(int op) {
         case DEEPJ_OP_Q8_SWIGLU: return 14;
         case DEEPJ_OP_ATTN_DECODE: return 17;
         case DEEPJ_OP_ATTN_PREFILL: return 18;
+        case DEEPJ_OP_SAMPLE_TOPK: return 8;
         case DEEPJ_OP_ARGMAX_ROWS: return 5;
         case DEEPJ_OP_ADD_SCALAR_INPLACE: return 4;
         case DEEPJ_OP_COPY: return 6;
@@ -369,6 +370,18 @@ void do_op(Ctx& ctx, const int32_t* c) {
             int rows = c[3], cols = c[4]; require(rows >= 0 && cols >= 1, "argmaxRows", "bad dimension");
             const float* a = f32(ctx, c[1], sz(rows, cols), "argmaxRows"); float* o = f32(ctx, c[2], rows, "argmaxRows");
             if (go) launch_argmax_rows(a, o, rows, cols, s);
+            break;
+        }
+        case DEEPJ_OP_SAMPLE_TOPK: {     // [op, logits, r, out, rows, cols, topK, temperatureBits]
+            int rows = c[4], cols = c[5], topK = c[6];
+            require(rows >= 0 && cols >= 1, "sampleTopK", "bad dimension");
+            require(topK >= 1 && topK <= 1024, "sampleTopK", "topK must be in 1..1024 on the device sampler");
+            const float temperature = bits_to_float(c[7]);
+            require(temperature > 0.0f, "sampleTopK", "temperature must be > 0");
+            const float* lg = f32(ctx, c[1], sz(rows, cols), "sampleTopK");
+            const float* rr = f32(ctx, c[2], rows, "sampleTopK");
+            float* o = f32(ctx, c[3], rows, "sampleTopK");
+            if (go) launch_sample_topk(lg, rr, o, rows, cols, topK, temperature, s);
             break;
         }
         case DEEPJ_OP_ADD_SCALAR_INPLACE: {

@@ -21,7 +21,7 @@ from typing import Tuple, Callable, Dict, List, Optional
 import numpy as np
 
 from . import _lib
-from .compute_graph import (OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_ATTN_PREFILL, OP_COPY, OP_EMBED_GATHER,
+from .compute_graph import (OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_ATTN_PREFILL, OP_COPY, OP_EMBED_GATHER, OP_SAMPLE_TOPK,
                             OP_Q8_LINEAR, OP_Q8_SWIGLU, OP_TP_ALLGATHER, OP_TP_ALLREDUCE, float_bits)
 
 RMS_EPS = 1e-6      # layers/transformer/norm/RMSNorm1D.java:30
@@ -211,6 +211,7 @@ class Q8Decoder:
             self._f32("part", B * d)
             self._f32("logits_local", B * self.v_local)
         self._f32("next", B)
+        self._f32("r", B)                # one Random.nextFloat() per sequence for the device sampler
         if c.kind == "deepseek":
             self._f32("lat", B * (c.q_rank + c.kv_rank))
         kv = self._new_id()
@@ -311,7 +312,7 @@ class Q8Decoder:
         return codes, scales
 
     # ── the per-token stream ──
-    def _build(self, feed_back: bool) -> np.ndarray:
+    def _build(self, feed_back: bool, sampler: Optional[Tuple[int, float]] = None) -> np.ndarray:
         c, B, I = self.cfg, self.B, self.ids
         d, V = c.d_model, c.vocab_size
         dl, Fl, Vl, Hl = self.d_local, self.f_local, self.v_local, self.h_local
@@ -359,7 +360,10 @@ class Q8Decoder:
             op("allgather", OP_TP_ALLGATHER, I["logits_local"], I["logits"], B, Vl)
         else:
             linear("lm_head", I["x"], 0, d, I["gF"], I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0, V)
-        op("argmax", OP_ARGMAX_ROWS, I["logits"], I["next"], B, V)
+        if sampler is None:
+            op("argmax", OP_ARGMAX_ROWS, I["logits"], I["next"], B, V)
+        else:
+            op("sample", OP_SAMPLE_TOPK, I["logits"], I["r"], I["next"], B, V, sampler[0], float_bits(sampler[1]))
         op("advance", OP_ADD_SCALAR_INPLACE, I["pos"], float_bits(1.0), B)
         if feed_back:
             op("feed_back", OP_COPY, I["next"], 0, I["tok"], 0, B)
@@ -520,6 +524,39 @@ class Q8Decoder:
             self._prefill_ids[name] = self._f32("", n)
         self._prefill_cap = C
         self._prefill_streams = {}
+
+    def generate(self, prompt, max_new_tokens: int, temperature: float = 1.0, top_k: int = 40, seed: int = 0) -> np.ndarray:
+        """TextGenerator.generate for batch 1 (models/TextGenerator.java:66-151) with the draw on the device:
+        temperature / top-k sampling, one `java.util.Random(seed).nextFloat()` per new token, the logits never
+        leave the GPU.  The device sampler takes topK in 1..1024 (the reference's 0 = whole vocabulary is not offered)."""
+        from .jrandom import JavaRandom
+        if max_new_tokens < 0:
+            raise ValueError("maxNewTokens must be >= 0")
+        if not temperature > 0.0:
+            raise ValueError("temperature must be > 0")
+        if top_k < 1 or top_k > 1024:
+            raise ValueError("topK must be in 1..1024 on the device sampler")
+        if self.B != 1:
+            raise ValueError("generate drives one sequence")
+        rnd = JavaRandom(seed)
+        c, I = self.cfg, self.ids
+        pick = np.asarray([OP_SAMPLE_TOPK, I["logits"], I["r"], I["next"], 1, c.vocab_size, top_k, float_bits(float(temperature))], dtype=np.int32)
+        step = self._build(feed_back=False, sampler=(top_k, float(temperature)))
+        self.reset()
+        self.prefill(np.asarray(prompt).reshape(1, -1))              # leaves the last prompt position's logits on the device
+        out = []
+        for i in range(max_new_tokens):
+            self._upload(I["r"], np.asarray([rnd.next_float()], dtype=np.float32))
+            if i == 0:
+                _lib.check(self.lib.deepj_cuda_flush_ops(pick.ctypes.data, pick.size))
+            else:
+                if self.position + 1 > c.max_seq_len:
+                    raise ValueError(f"seqLen {self.position + 1} exceeds maxSeqLen {c.max_seq_len}")
+                self._upload(I["tok"], np.asarray([out[-1]], dtype=np.float32))
+                _lib.check(self.lib.deepj_cuda_flush_ops(step.ctypes.data, step.size))
+                self.position += 1
+            out.append(int(self.next_tokens()[0]))
+        return np.asarray(out, dtype=np.int64)
 
     def generate_greedy(self, prompt, max_new_tokens: int, keep_logits: bool = False):
         """TextGenerator.generate with topK = 1 (models/TextGenerator.java:66-100)

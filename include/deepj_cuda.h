@@ -161,6 +161,9 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
  *  73 ATTN_PREFILL      [op, qkv, q_off, k_off, v_off, ld, kv, layer, pos, cos, sin, out, out_off, ldo, B, H, hd, T]
  *                        a prompt chunk: row b*T + t is token pos[b] + t of sequence b; the chunk's k (rotated)
  *                        and v are appended first, then every row attends causally over 0..pos[b]+t
+ *  74 SAMPLE_TOPK       [op, logits, r, out, rows, cols, topK, temperatureBits]
+ *                        TextGenerator.sampleFromLogits per row (stable descending order, first topK <= 1024,
+ *                        float softmax of logit/T, first index whose running sum reaches r[row]); r = Random.nextFloat()
  */
 #define DEEPJ_OP_EMBED_GATHER        64
 #define DEEPJ_OP_Q8_LINEAR           65
@@ -172,6 +175,7 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
 #define DEEPJ_OP_TP_ALLREDUCE        71
 #define DEEPJ_OP_TP_ALLGATHER        72
 #define DEEPJ_OP_ATTN_PREFILL        73
+#define DEEPJ_OP_SAMPLE_TOPK         74
 
 #ifdef __cplusplus
 }

@@ -1056,6 +1056,30 @@ int oracle_model_decode_step(void* m, int32_t token, float* logits) {
     ORACLE_TRY decodeStep(*(Model*)m, token, logits); ORACLE_CATCH
 }
 int32_t oracle_greedy_pick(const float* logits, int32_t n) { return greedyPick(logits, n); }
+// TextGenerator.sampleFromLogits (models/TextGenerator.java:104-151): stable descending order under Float.compare,
+// the first topK indices (0 = all), p_i = (float) Math.exp(logit_i / T - max) with max over the scaled logits,
+// a sequential float sum, p_i /= sum, then the first i with r <= running sum (r = Random.nextFloat()).
+int32_t oracle_sample_topk(const float* logits, int32_t n, float temperature, int32_t topK, float r) {
+    std::vector<int32_t> order(n);
+    for (int i = 0; i < n; i++) order[i] = i;
+    auto key = [&](int i) {            // Float.compare's total order as a signed integer
+        float v = logits[i];
+        int32_t b;
+        if (v != v) b = 0x7fc00000; else std::memcpy(&b, &v, 4);
+        return b ^ ((b >> 31) & 0x7fffffff);
+    };
+    std::stable_sort(order.begin(), order.end(), [&](int i, int j) { return key(i) > key(j); });
+    int k = topK == 0 ? n : std::min(topK, n);
+    float mx = -INFINITY;
+    for (int i = 0; i < k; i++) { float v = logits[order[i]] / temperature; if (v > mx) mx = v; }
+    std::vector<float> p(k);
+    float sum = 0.0f;
+    for (int i = 0; i < k; i++) { p[i] = (float)std::exp((double)(logits[order[i]] / temperature - mx)); sum += p[i]; }
+    for (int i = 0; i < k; i++) p[i] /= sum;
+    float cum = 0.0f;
+    for (int i = 0; i < k; i++) { cum += p[i]; if (r <= cum) return order[i]; }
+    return order[k - 1];
+}
 // Reference-faithful greedy generation: full re-forward of the context per token
 // (models/TextGenerator.java:81-100), window = last maxSeq ids (:172-175).
 int oracle_generate_greedy(void* mp, const int32_t* prompt, int32_t nPrompt, int32_t maxNew,

@@ -60,6 +60,8 @@ def lib() -> ctypes.CDLL:
     L.oracle_greedy_pick.restype = _i32
     L.oracle_greedy_pick.argtypes = [_vp, _i32]
     L.oracle_generate_greedy.argtypes = [_vp, _vp, _i32, _i32, _i32, _vp, _vp]
+    L.oracle_sample_topk.restype = _i32
+    L.oracle_sample_topk.argtypes = [_vp, _i32, ctypes.c_float, _i32, ctypes.c_float]
     L.oracle_alloc_buffers.argtypes = [_vp, _vp, _i32]
     L.oracle_upload_buffer.argtypes = [_i32, _vp, _i32]
     L.oracle_download_buffer.argtypes = [_i32, _vp, _i32]
@@ -210,6 +212,11 @@ class OracleModel:
 def greedy_pick(logits: np.ndarray) -> int:
     logits = np.ascontiguousarray(logits, dtype=np.float32)
     return lib().oracle_greedy_pick(logits.ctypes.data, logits.size)
+
+
+def sample_topk(logits: np.ndarray, temperature: float, top_k: int, r: float) -> int:
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    return lib().oracle_sample_topk(logits.ctypes.data, logits.size, temperature, top_k, r)
 
 
 class OracleRuntime:

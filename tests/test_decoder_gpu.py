@@ -170,6 +170,31 @@ def test_chunked_prefill_equals_token_by_token(kind, d_ff):
         assert np.array_equal(np.asarray(toks), tok_b[b])
 
 
+def test_checkpoint_import_decodes_like_the_weights_it_was_written_from(tmp_path):
+    """A model saved in the reference's ModelSerializer format and imported through deepj_b200.checkpoint
+    quantizes to the same Q8 codes and generates the same tokens as the weights handed over directly."""
+    from deepj_b200 import checkpoint
+    cfg = DecoderConfig("llama", 256, 64, 128, 4, 2, 352)
+    om = oracle.OracleModel("llama", 256, 64, 128, 4, 2, 352, seed=31)
+    direct = weight_getter(om, cfg)
+    params = []
+    for name, layer, shape in checkpoint.parameter_layout(cfg):
+        params.append(np.asarray(direct(name, layer), dtype=np.float32).reshape(shape))
+    path = tmp_path / "llama.bin"
+    checkpoint.write_parameters(path, params)
+    prompt = list(np.random.default_rng(2).integers(0, 256, size=12))
+    outs = []
+    for get in (direct, checkpoint.weight_getter(cfg, path)):
+        dec = Q8Decoder(cfg, batch=1)
+        dec.load_weights(get)
+        codes, scales = dec.q8_arrays("Wd.1")
+        toks = dec.generate_greedy(prompt, 10)
+        dec.close()
+        outs.append((codes, scales, np.asarray(toks)))
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1].view(np.uint32), outs[1][1].view(np.uint32))
+    assert np.array_equal(outs[0][2], outs[1][2])
+
+
 def test_synthetic_weights_match_oracle_generator_and_decode():
     """Device-generated synthetic weights are the oracle's generator bit for bit, and a
     mid-sized model decodes to the oracle's logits."""

@@ -1,0 +1,70 @@
+"""Device sampling (op 74) against the oracle's restatement of TextGenerator.sampleFromLogits
+(models/TextGenerator.java:104-151), and sampled generation end to end."""
+import numpy as np
+import pytest
+
+import oracle
+from deepj_b200.compute_graph import OP_SAMPLE_TOPK, float_bits
+from deepj_b200.decoder import DecoderConfig, Q8Decoder
+from test_decoder_gpu import weight_getter
+from test_q8_gpu import Dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def dev():
+    d = Dev(3 << 20)
+    yield d
+    d.close()
+
+
+@pytest.mark.parametrize("V,top_k,temperature", [(32000, 1, 1.0), (32000, 5, 0.7), (32000, 40, 1.0), (32000, 1024, 2.5),
+                                                 (7, 40, 1.0), (1000, 1000, 0.3), (257, 64, 1.3)])
+def test_sample_topk_matches_oracle(dev, V, top_k, temperature):
+    rng = np.random.default_rng(V + top_k)
+    rows = 6
+    logits = rng.standard_normal((rows, V)).astype(np.float32) * 3.0
+    logits[1] = np.round(logits[1] * 2.0) / 2.0              # many exact ties: the stable order decides
+    logits[2, :] = 0.25                                      # all equal: the lowest indices are the top k
+    logits[3, ::3] = -0.0
+    logits[3, 1::3] = 0.0                                    # Float.compare puts −0.0 below +0.0
+    r = np.asarray([0.0, 0.37, 0.999999, 0.5, 0.81, 1.0 - 2.0 ** -24], dtype=np.float32)
+    lb, rb, ob = dev.buf(rows * V, logits), dev.buf(rows, r), dev.buf(rows)
+    dev.flush([OP_SAMPLE_TOPK, lb, rb, ob, rows, V, top_k, float_bits(temperature)])
+    got = dev.get(ob, rows).astype(np.int64)
+    want = np.asarray([oracle.sample_topk(logits[i], temperature, top_k, float(r[i])) for i in range(rows)])
+    assert np.array_equal(got, want), (got, want)
+
+
+def test_sampler_rejects_what_it_does_not_cover(dev):
+    lb, rb, ob = dev.buf(8), dev.buf(1), dev.buf(1)
+    for top_k, t in ((0, 1.0), (1025, 1.0), (4, 0.0), (4, -1.0)):
+        with pytest.raises(Exception):
+            dev.flush([OP_SAMPLE_TOPK, lb, rb, ob, 1, 8, top_k, float_bits(t)])
+
+
+def test_sampled_generation_matches_oracle_loop():
+    """generate(): Random(seed).nextFloat() per token on the host, everything else on the device; the same loop
+    over the oracle's KV-cached logits picks the same tokens."""
+    cfg = DecoderConfig("llama", 256, 64, 128, 4, 2, 352)
+    om = oracle.OracleModel("llama", 256, 64, 128, 4, 2, 352, seed=17)
+    dec = Q8Decoder(cfg, batch=1)
+    dec.load_weights(weight_getter(om, cfg))
+    om.apply_q8()
+    prompt = list(np.random.default_rng(9).integers(0, 256, size=9))
+    for temperature, top_k, seed in ((0.8, 20, 5), (1.5, 3, 11)):
+        got = dec.generate(prompt, 12, temperature=temperature, top_k=top_k, seed=seed)
+        rnd = oracle.JRandom(seed)
+        om.reset_cache()
+        lg = None
+        for t in prompt:
+            lg = om.decode_step(int(t))
+        want = []
+        for i in range(12):
+            tok = oracle.sample_topk(lg, temperature, top_k, rnd.next_float())
+            want.append(tok)
+            if i + 1 < 12:
+                lg = om.decode_step(tok)
+        assert np.array_equal(got, np.asarray(want)), (got, want)
+    dec.close()
