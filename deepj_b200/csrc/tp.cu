@@ -30,7 +30,7 @@ namespace {
 
 constexpr int kMaxWorld = 8;
 constexpr int kTpCtas = 8;                    // CTAs per exchange; each owns a contiguous chunk
-constexpr unsigned kTpSpinLimit = 1u << 22;   // polls of one word, ≈ seconds, then give up
+constexpr unsigned kTpSpinLimit = 1u << 21;   // polls of one word (≈ a second), then give up
 
 struct TpState {
     bool ready = false;
@@ -42,6 +42,7 @@ struct TpState {
     float* peer_data[kMaxWorld] = {};
     unsigned* epochs = nullptr;
     void* opened[kMaxWorld] = {};
+    void* absent[kMaxWorld] = {};      // stand-ins for ranks that never connect (tp_connect without handles)
 } T;
 
 struct TpPtrs {
@@ -186,7 +187,12 @@ int deepj_cuda_tp_connect(const void* handles, int32_t world) {
         const size_t dataBytes = (size_t)2 * T.world * T.slot_floats * 8;
         for (int r = 0; r < T.world; r++) {
             void* base = T.local;
-            if (r != T.rank) {
+            if (r != T.rank && handles == nullptr) {
+                // nobody will ever write here: this rank's pushes land in it, and its own buffer never sees rank r
+                DJ_CUDA_CHECK(cudaMalloc(&base, T.bytes));
+                DJ_CUDA_CHECK(cudaMemset(base, 0, T.bytes));
+                T.absent[r] = base;
+            } else if (r != T.rank) {
                 cudaIpcMemHandle_t h;
                 std::memcpy(&h, (const char*)handles + (size_t)r * 64, 64);
                 DJ_CUDA_CHECK(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
@@ -200,10 +206,20 @@ int deepj_cuda_tp_connect(const void* handles, int32_t world) {
     } catch (const std::exception& e) { set_last_error(e.what()); return 1; }
 }
 
+int deepj_cuda_clear_device_error(void) {
+    try {
+        if (runtime_stream() == nullptr || g_dev_error == nullptr) return 0;
+        DJ_CUDA_CHECK(cudaStreamSynchronize(runtime_stream()));
+        DJ_CUDA_CHECK(cudaMemset(g_dev_error, 0, sizeof(int)));
+        return 0;
+    } catch (const std::exception& e) { set_last_error(e.what()); return 1; }
+}
+
 int deepj_cuda_tp_destroy(void) {
     try {
         if (runtime_stream()) cudaStreamSynchronize(runtime_stream());
         for (int r = 0; r < kMaxWorld; r++) if (T.opened[r]) { cudaIpcCloseMemHandle(T.opened[r]); T.opened[r] = nullptr; }
+        for (int r = 0; r < kMaxWorld; r++) if (T.absent[r]) { cudaFree(T.absent[r]); T.absent[r] = nullptr; }
         if (T.local) cudaFree(T.local);
         T = TpState();
         return 0;

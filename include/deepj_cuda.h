@@ -115,10 +115,15 @@ int deepj_cuda_kv_alloc(int32_t kv_id, int32_t layers, int32_t batch, int32_t he
  * the host exchanges the handles by any means (the Python runner uses torch.distributed),
  * then every rank calls tp_connect with all handles in rank order.  After that op codes 71
  * and 72 may appear in streams; every rank must flush the same sequence of them.  Waits
- * inside the exchange kernel are bounded; an expired wait sets stats counter [5]. */
+ * inside the exchange kernel are bounded; an expired wait sets stats counter [5] to
+ * 100 + the rank whose data did not arrive, the kernel finishes and the context stays usable.
+ * tp_connect(NULL, world) maps every other rank to a private buffer that nobody fills: the
+ * way to see the bounded wait expire (a peer that never shows up) without a second process.
+ * deepj_cuda_clear_device_error() zeroes counter [5] again. */
 int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void* handle_out64);
 int deepj_cuda_tp_connect(const void* handles, int32_t world);
 int deepj_cuda_tp_destroy(void);
+int deepj_cuda_clear_device_error(void);
 
 /* Decode attention for callers that must not allocate.  No counterpart in the reference.
  *
