@@ -321,7 +321,11 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "k_q8_gemv", "launches_per_step": n_gemv,
+                     # DRAM bytes per launch (read + write), scaled by K·N from the ncu capture of the K=4096, N=12288
+                     # launch (56.869 MB measured against 56.69 MB algorithmic): the full-size step is too large to capture
+                     "traffic": (gemv_bytes / max(n_gemv, 1)) * (56.869 / 56.69), "traffic_unit": "bytes per launch (average)",
+                     "traffic_source": "profiles/q8_gemv_i8_k4096_n12288_ncu.md, scaled by algorithmic bytes",
+                     "peak_kind": peak_kind, "kernel": "k_q8_gemv", "launches_per_step": n_gemv,
                      "bytes_per_step": gemv_bytes, "us_per_launch": 1e3 * gemv_stream_ms / max(n_gemv_stream, 1),
                      "ms_per_step_back_to_back": gemv_stream_ms, "ms_per_step_op_by_op": gemv_ms},
         "roofline_attention": {"bound": "hbm", "kernel": "k_attn_decode", "launches_per_step": n_attn,

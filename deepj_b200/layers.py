@@ -52,6 +52,39 @@ class RMSNorm1D:
         return x.divideBroadcastCols(rms).multiplyBroadcastRows(self.gamma)
 
 
+class LayerNorm1D:
+    """layers/transformer/norm/LayerNorm1D.java:33-71 — per-row mean and (population) variance,
+    (x − mean) / sqrt(var + 1e-5) · γ + β."""
+
+    EPS = 1e-5
+
+    def __init__(self, dim: int, gamma: Optional[np.ndarray] = None, beta: Optional[np.ndarray] = None):
+        if dim <= 0:
+            raise ValueError("dim must be > 0")
+        self.dim = dim
+        self.gamma = Tensor(1, dim, gamma if gamma is not None else np.ones(dim, dtype=np.float32))
+        self.beta = Tensor(1, dim, beta if beta is not None else np.zeros(dim, dtype=np.float32))
+
+    def forward(self, x: Tensor) -> Tensor:
+        if x.cols != self.dim:
+            raise ValueError(f"Expected cols={self.dim} got {x.cols}")
+        mean = x.meanAlongRows()
+        std = x.varianceAlongRows().addScalar(self.EPS).sqrt()
+        xhat = x.subtractBroadcastCols(mean).divideBroadcastCols(std)
+        return xhat.multiplyBroadcastRows(self.gamma).addBroadcastRows(self.beta)
+
+
+class FNN:
+    """layers/FNN.java:62-80 with one hidden layer and GELU, the GPT block's MLP
+    (blocks/GPTTransformerBlock.java:54): Linear → GELU → Linear."""
+
+    def __init__(self, hidden: Linear, out: Linear):
+        self.hidden, self.out = hidden, out
+
+    def forward(self, x: Tensor) -> Tensor:
+        return self.out.forward(self.hidden.forward(x).geluActivation())
+
+
 class RotaryEmbedding:
     """transformer/embeddings/RotaryEmbedding.java:52-122 — interleaved pairs, applied
     on the host after a materialise, as the reference does."""
@@ -222,6 +255,44 @@ class DecoderOnlyModel:
         for b in self.blocks:
             x = b.forward(x)
         return self.lmHead.forward(self.normF.forward(x))
+
+
+class GPTModel(DecoderOnlyModel):
+    """models/gpt/GPTModel.java:26-54: learned positional embedding added to the token embedding,
+    LayerNorm blocks with a GELU MLP, plain (un-rotated) causal attention, final LayerNorm."""
+
+    def __init__(self, emb, pos: np.ndarray, blocks, normF: LayerNorm1D, lmHead: Linear, maxSeqLen: int):
+        super().__init__(emb, blocks, normF, lmHead, maxSeqLen)
+        self.posEmb = Tensor(pos.shape[0], pos.shape[1], pos)
+
+    def forward(self, inputIds: Sequence[int]) -> Tensor:
+        for i in inputIds:
+            if i < 0 or i >= self.vocabSize:
+                raise ValueError(f"Token id out of range: {i}")       # Embedding.java:30-32
+        if len(inputIds) > self.maxSeqLen:
+            raise ValueError(f"seqLen {len(inputIds)} exceeds maxSeq {self.maxSeqLen}")      # PositionalEmbedding.java:27
+        x = Tensor.sliceRows(self.tokEmb, inputIds, self.dModel).add(
+            Tensor.sliceRows(self.posEmb, list(range(len(inputIds))), self.dModel))
+        for b in self.blocks:
+            x = b.forward(x)
+        return self.lmHead.forward(self.normF.forward(x))
+
+
+def build_gpt_model(vocab: int, max_seq: int, d: int, heads: int, layers: int, d_ff: int,
+                    get: Callable[[str, int], np.ndarray]) -> GPTModel:
+    """A GPT model from a weight getter: "emb" [V×d], "pos" [maxSeq×d]; per layer "g1","b1","g2","b2" (LayerNorm
+    gain / shift), "Wq","Wk","Wv","Wo" [d×d], "W1" [d×dFF], "c1", "W2" [dFF×d], "c2"; "gF","bF","Wlm" [d×V], "blm"."""
+    def arr(name, layer, shape=None):
+        a = np.asarray(get(name, layer), dtype=np.float32)
+        return a.reshape(shape) if shape else a.reshape(-1)
+
+    blocks = []
+    for l in range(layers):
+        attn = MultiHeadSelfAttention(d, heads, True, arr("Wq", l, (d, d)), arr("Wk", l, (d, d)), arr("Wv", l, (d, d)), arr("Wo", l, (d, d)))
+        mlp = FNN(Linear(arr("W1", l, (d, d_ff)), arr("c1", l)), Linear(arr("W2", l, (d_ff, d)), arr("c2", l)))
+        blocks.append(TransformerBlock(LayerNorm1D(d, arr("g1", l), arr("b1", l)), LayerNorm1D(d, arr("g2", l), arr("b2", l)), attn, mlp))
+    return GPTModel(arr("emb", -1, (vocab, d)), arr("pos", -1, (max_seq, d)), blocks, LayerNorm1D(d, arr("gF", -1), arr("bF", -1)),
+                    Linear(arr("Wlm", -1, (d, vocab)), arr("blm", -1)), max_seq)
 
 
 def build_model(cfg, get: Callable[[str, int], np.ndarray]) -> DecoderOnlyModel:

@@ -125,6 +125,30 @@ def test_unmodified_layer_stack_runs_on_cuda_backend(kind):
     cb.releaseResources()
 
 
+def test_gpt_layer_stack_runs_on_cuda_backend():
+    """Drop-in for the GPT family: the same layer stack (LayerNorm, GELU MLP, learned positions, plain causal
+    attention) over CudaBackend and over the oracle's interpreter — same logits, same greedy tokens."""
+    import gpt_ref
+    from deepj_b200.layers import build_gpt_model
+    shape = dict(vocab=97, max_seq=16, d=32, heads=4, layers=2, d_ff=80)
+    w, get = gpt_ref.make_weights(seed=6, **shape)
+    ids = [3, 96, 0, 41, 41, 7, 12]
+    ob = GraphBackend(oracle.OracleRuntime())
+    Tensor.setBackend(ob)
+    om = build_gpt_model(get=get, **shape)
+    expected = om.forward(ids).numpy()
+    exp_tokens = TextGenerator.generate(om.forward, 16, ids, 4, 1.0, 1)
+    ob.releaseResources()
+    cb = CudaBackend(0)
+    Tensor.setBackend(cb)
+    model = build_gpt_model(get=get, **shape)
+    got = model.forward(ids).numpy()
+    assert float(np.abs(got - expected).max()) <= 1e-5 * float(np.abs(expected).max())
+    assert float(np.abs(got - gpt_ref.forward(w, ids, 32, 4, 2)).max()) <= 1e-4 * float(np.abs(expected).max())
+    assert TextGenerator.generate(model.forward, 16, ids, 4, 1.0, 1) == exp_tokens
+    cb.releaseResources()
+
+
 # ── malformed streams are rejected before any launch ──
 def flush_raw(ints):
     lib = _lib.load()
