@@ -24,7 +24,11 @@
 // cp.async.bulk row segments of 1 KB (per-copy cost of the bulk engine); fp16
 // mma.sync with byte-permute dequant was no faster than the FMA kernel; bulk L2
 // prefetch (cp.async.bulk.prefetch.L2) of the tiles ahead of the ring, or of the next
-// kernel's first weights as a CTA retires, made every shape 5–50 % slower.
+// kernel's first weights as a CTA retires, made every shape 5–50 % slower; running the
+// decode attention inside this kernel for the QKV projection (clusters of 8 CTAs per
+// head, cluster barrier, partials merged through distributed shared memory) was correct
+// but 2 % slower per token than the two launches, whose attention kernel already starts
+// its K/V stream before the projection has finished.
 #include "kernels.h"
 #include "q8_common.cuh"
 #include <cstdlib>

@@ -195,6 +195,14 @@ def test_checkpoint_import_decodes_like_the_weights_it_was_written_from(tmp_path
     assert np.array_equal(outs[0][2], outs[1][2])
 
 
+def test_head_dim_128_matches_oracle():
+    """Head dim 128 (the 7B shape's; 8 lanes per cached position in the attention kernel): logits and greedy tokens
+    against the oracle over 40 positions."""
+    cfg = DecoderConfig("llama", 256, 64, 256, 2, 2, 512)
+    prompt = list(np.random.default_rng(3).integers(0, 256, size=24))
+    run_parity(cfg, seed=23, prompt=prompt, n_new=16)
+
+
 def test_synthetic_weights_match_oracle_generator_and_decode():
     """Device-generated synthetic weights are the oracle's generator bit for bit, and a
     mid-sized model decodes to the oracle's logits."""
