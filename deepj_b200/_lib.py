@@ -28,6 +28,8 @@ SIGNATURES = {
     "deepj_cuda_shutdown": (ctypes.c_int, []),
     "deepj_cuda_flush_ops_async": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32]),
     "deepj_cuda_synchronize": (ctypes.c_int, []),
+    "deepj_cuda_pinned_alloc": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64]),
+    "deepj_cuda_pinned_free": (ctypes.c_int, [ctypes.c_void_p]),
     "deepj_cuda_timer_begin": (ctypes.c_int, []),
     "deepj_cuda_timer_end": (ctypes.c_int, [_f32p]),
     "deepj_cuda_profile_ops": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int32, _i32p]),

@@ -633,6 +633,17 @@ int deepj_cuda_flush_ops(const int32_t* cmd, int32_t len) { DJ_TRY flush(cmd, le
 int deepj_cuda_flush_ops_async(const int32_t* cmd, int32_t len) { DJ_TRY flush(cmd, len, false); DJ_CATCH }
 int deepj_cuda_synchronize(void) { DJ_TRY ensure_init(); DJ_CUDA_CHECK(cudaStreamSynchronize(R.stream)); DJ_CATCH }
 
+// Page-locked host memory for the per-step token / result staging: uploads from and downloads into it are true
+// asynchronous DMA transfers on the library's stream.
+int deepj_cuda_pinned_alloc(void** out, int64_t bytes) {
+    DJ_TRY
+    ensure_init();
+    if (out == nullptr || bytes <= 0) throw std::runtime_error("pinned_alloc: bad arguments");
+    DJ_CUDA_CHECK(cudaMallocHost(out, (size_t)bytes));
+    DJ_CATCH
+}
+int deepj_cuda_pinned_free(void* p) { DJ_TRY if (p) DJ_CUDA_CHECK(cudaFreeHost(p)); DJ_CATCH }
+
 int deepj_cuda_timer_begin(void) { DJ_TRY ensure_init(); DJ_CUDA_CHECK(cudaEventRecord(R.t0, R.stream)); DJ_CATCH }
 int deepj_cuda_timer_end(float* ms) {
     DJ_TRY

@@ -153,6 +153,7 @@ class Q8Decoder:
         self._stream_host: Optional[np.ndarray] = None
         self._stream_dev: Optional[np.ndarray] = None
         self._op_labels: List[str] = []
+        self._pin_ptr = None
         self._prefill_ids: Dict[str, int] = {}
         self._prefill_cap = 0
         self._prefill_streams: Dict[int, np.ndarray] = {}
@@ -393,15 +394,28 @@ class Q8Decoder:
         self._upload(self.ids["pos"], np.full(self.B, float(position), dtype=np.float32))
         self.position = int(position)
 
+    def _pinned(self) -> Tuple[np.ndarray, np.ndarray]:
+        """Page-locked staging for the ids going up and the picks coming down each step ([B] floats each)."""
+        if self._pin_ptr is None:
+            ptr = ctypes.c_void_p()
+            _lib.check(self.lib.deepj_cuda_pinned_alloc(ctypes.byref(ptr), 8 * self.B))
+            self._pin_ptr = ptr
+            buf = (ctypes.c_float * (2 * self.B)).from_address(ptr.value)
+            arr = np.frombuffer(buf, dtype=np.float32)
+            self._pin_tok, self._pin_next = arr[:self.B], arr[self.B:]
+        return self._pin_tok, self._pin_next
+
     def set_tokens(self, tokens) -> None:
         t = np.asarray(tokens, dtype=np.int64).reshape(-1)
         if t.size != self.B:
             raise ValueError(f"expected {self.B} token ids, got {t.size}")
         # Embedding.forward range check (transformer/embeddings/Embedding.java:30-32)
-        for v in t:
-            if v < 0 or v >= self.cfg.vocab_size:
-                raise ValueError(f"Token id out of range: {int(v)}")
-        self._upload(self.ids["tok"], t.astype(np.float32))
+        if t.min() < 0 or t.max() >= self.cfg.vocab_size:
+            bad = t[(t < 0) | (t >= self.cfg.vocab_size)][0]
+            raise ValueError(f"Token id out of range: {int(bad)}")
+        tok, _ = self._pinned()
+        tok[:] = t
+        _lib.check(self.lib.deepj_cuda_upload_buffer(self.ids["tok"], tok.ctypes.data, self.B))
 
     def step(self, tokens) -> np.ndarray:
         """One token per sequence through host buffers: upload the ids, flush the
@@ -410,9 +424,12 @@ class Q8Decoder:
             raise ValueError(f"seqLen {self.position + 1} exceeds maxSeqLen {self.cfg.max_seq_len}")
         host, _ = self._streams()
         self.set_tokens(tokens)
-        _lib.check(self.lib.deepj_cuda_flush_ops(host.ctypes.data, host.size))
+        # enqueue the stream behind the upload and let the download's synchronisation be the only one of the step
+        _lib.check(self.lib.deepj_cuda_flush_ops_async(host.ctypes.data, host.size))
         self.position += 1
-        return self._download(self.ids["next"], self.B).astype(np.int64)
+        _, nxt = self._pinned()
+        _lib.check(self.lib.deepj_cuda_download_buffer(self.ids["next"], nxt.ctypes.data, self.B))
+        return nxt.astype(np.int64)
 
     def step_device(self, n_steps: int = 1, sync: bool = True) -> None:
         """n greedy steps with the picked token fed back on the device (no host copies)."""
@@ -612,5 +629,8 @@ class Q8Decoder:
                 "kernels_per_replay": v[3], "workspace_bytes": v[4], "device_error": v[5]}
 
     def close(self) -> None:
+        if self._pin_ptr is not None:
+            self.lib.deepj_cuda_pinned_free(self._pin_ptr)
+            self._pin_ptr = None
         if self._owned:
             self._release(list(self._owned))

@@ -63,6 +63,9 @@ int deepj_cuda_shutdown(void);
 /* Same as deepj_cuda_flush_ops but returns after enqueueing. */
 int deepj_cuda_flush_ops_async(const int32_t* cmd, int32_t len);
 int deepj_cuda_synchronize(void);
+/* Page-locked host memory for staging buffers that are uploaded / downloaded every step. */
+int deepj_cuda_pinned_alloc(void** out, int64_t bytes);
+int deepj_cuda_pinned_free(void* p);
 
 /* Device-time measurement on the library's stream (CUDA events). */
 int deepj_cuda_timer_begin(void);
