@@ -14,8 +14,8 @@
 // fp16 tensor peak.
 //
 // One CTA per 128 × 128 output tile, ten warps:
-//   warps 0-7  dequantise (a thread owns half a weight row of the tile: 32 code bytes + a scale per
-//              k-tile from global memory, the next four k-tiles' already in registers) and write the
+//   warps 0-7  dequantise, as two groups of four that take the k-tiles in turn (a thread owns a weight row of
+//              the tile: 64 code bytes + 2 scales per k-tile from global memory, its next three already in registers) and write the
 //              W_hi / W_lo tiles in the 128-byte-swizzled K-major layout the MMA reads; afterwards
 //              they are the epilogue: tcgen05.ld of a 32 × 64 piece of the accumulator each, row scale,
 //              bias, residual or SiLU-gate, 128-byte row stores through a shared-memory transpose;
@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     const uint32_t bar_acc = smem_u32(&s_bar[3 * kStages]);
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; s++) { mbar_init(bar_fullA(s), 1); mbar_init(bar_fullB(s), kDqWarps * 32); mbar_init(bar_empty(s), 1); }
+        for (int s = 0; s < kStages; s++) { mbar_init(bar_fullA(s), 1); mbar_init(bar_fullB(s), 128); mbar_init(bar_empty(s), 1); }
         mbar_init(bar_acc, 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -231,46 +231,52 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     pdl_launch_dependents();
 
     if (warp < kDqWarps) {
-        // ── dequantise: thread (r, half) owns 32 of the 64 codes of weight row n0 + r per k-tile ──
-        const int r = tid & 127, half = tid >> 7;
+        // ── dequantise: two groups of four warps take the k-tiles in turn (group g: k-tiles g, g+2, …), thread r of a
+        // group owns weight row n0 + r.  While one group waits for its stage or sits in its proxy fence, the other
+        // converts: the tensor pipe is fed at the conversion's issue rate, not at the sum of the three. ──
+        const int r = tid & 127, grp = tid >> 7;
         const int n = n0 + r;
         const bool live = n < p.N;
-        const int8_t* crow = p.codes + (size_t)(live ? n : 0) * p.Kp + half * 32;
-        const float* srow = p.scales + (size_t)(live ? n : 0) * p.nb + half;
-        // the codes of the next kAhead k-tiles are always in flight in registers: one k-tile of MMA time is
+        const int8_t* crow = p.codes + (size_t)(live ? n : 0) * p.Kp;
+        const float* srow = p.scales + (size_t)(live ? n : 0) * p.nb;
+        // the codes of this group's next kAhead k-tiles are always in flight in registers: one k-tile of MMA time is
         // shorter than a load round trip, and these threads are all the memory parallelism the weights get
-        constexpr int kAhead = 4;
-        uint4 buf[kAhead][2]; float bsc[kAhead];
-        auto load_k = [&](int kt, uint4 (&c)[2], float& sc) {
+        constexpr int kAhead = 3;
+        uint4 buf[kAhead][4]; float bsc[kAhead][2];
+        auto load_k = [&](int kt, uint4 (&c)[4], float (&sc)[2]) {
             const bool on = live && kt < nK;
-            c[0] = on ? __ldg(reinterpret_cast<const uint4*>(crow + (size_t)kt * kTileK)) : make_uint4(0, 0, 0, 0);
-            c[1] = on ? __ldg(reinterpret_cast<const uint4*>(crow + (size_t)kt * kTileK) + 1) : make_uint4(0, 0, 0, 0);
-            sc = on ? __ldg(srow + kt * 2) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; j++) c[j] = on ? __ldg(reinterpret_cast<const uint4*>(crow + (size_t)kt * kTileK) + j) : make_uint4(0, 0, 0, 0);
+            sc[0] = on ? __ldg(srow + kt * 2) : 0.0f;
+            sc[1] = on ? __ldg(srow + kt * 2 + 1) : 0.0f;
         };
 #pragma unroll
-        for (int a = 0; a < kAhead; a++) load_k(a, buf[a], bsc[a]);
+        for (int a = 0; a < kAhead; a++) load_k(grp + 2 * a, buf[a], bsc[a]);
         const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
         unsigned long long tWait = 0, tConv = 0, tFence = 0, tStart = tracing ? gtime() : 0;
-        for (int kt0 = 0; kt0 < nK; kt0 += kAhead) {
+        for (int kt0 = grp; kt0 < nK; kt0 += 2 * kAhead) {
 #pragma unroll
             for (int a = 0; a < kAhead; a++) {
-                const int kt = kt0 + a;
+                const int kt = kt0 + 2 * a;
                 if (kt >= nK) break;
                 const int s = kt % kStages;
-                const uint4 cur[2] = {buf[a][0], buf[a][1]};
-                const float scale = bsc[a];
-                load_k(kt + kAhead, buf[a], bsc[a]);
+                uint4 cur[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) cur[j] = buf[a][j];
+                const float sc0 = bsc[a][0], sc1 = bsc[a][1];
+                load_k(kt + 2 * kAhead, buf[a], bsc[a]);
                 unsigned long long t0 = tracing ? gtime() : 0;
                 if (kt >= kStages) mbar_wait(bar_empty(s), ((kt / kStages) - 1) & 1, &s_abort, p.error, 201);
                 unsigned long long t1 = tracing ? gtime() : 0;
                 unsigned char* bhi = smem_al + (size_t)s * kStageBytes + 2 * kATileBytes;
                 unsigned char* blo = bhi + kBTileBytes;
 #pragma unroll
-                for (int j = 0; j < 2; j++) {                  // 16 codes → two 16-byte chunks of hi and of lo
+                for (int j = 0; j < 4; j++) {                  // 16 codes → two 16-byte chunks of hi and of lo
                     // No conversion-pipe instruction but the two packed fp16 roundings per weight pair:
                     // code → float through the 2^23 trick (byte under exponent 0x4B is 8388608 + code + 128),
                     // w_hi = w with the mantissa cut to 10 bits (exactly an fp16 value), w_lo = w − w_hi (exact in fp32).
                     const uint32_t w4[4] = {cur[j].x ^ 0x80808080u, cur[j].y ^ 0x80808080u, cur[j].z ^ 0x80808080u, cur[j].w ^ 0x80808080u};
+                    const float scale = j < 2 ? sc0 : sc1;
                     uint32_t hi[8], lo[8];
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
@@ -284,7 +290,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
                         hi[2 * q] = pack_h2(h[0], h[1]); hi[2 * q + 1] = pack_h2(h[2], h[3]);
                         lo[2 * q] = pack_h2(f[0] - h[0], f[1] - h[1]); lo[2 * q + 1] = pack_h2(f[2] - h[2], f[3] - h[3]);
                     }
-                    const int o0 = swz_off(r, 4 * half + 2 * j), o1 = swz_off(r, 4 * half + 2 * j + 1);
+                    const int o0 = swz_off(r, 2 * j), o1 = swz_off(r, 2 * j + 1);
                     *reinterpret_cast<uint4*>(bhi + o0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                     *reinterpret_cast<uint4*>(bhi + o1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
                     *reinterpret_cast<uint4*>(blo + o0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
