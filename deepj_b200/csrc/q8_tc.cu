@@ -4,8 +4,8 @@
 // With M in the hundreds the work is a dense contraction, 2·M·K·N flops against K·N weight
 // bytes, and belongs on the 5th-generation tensor cores.  The Q8 format keeps one fp32 scale per
 // 32 weights, so the weights cannot stay int8 inside one long accumulation; instead each
-// 128 × 64 weight tile is dequantised on the fly, exactly once per CTA, into fp16:
-//     w = code · scale  (fp32)   →   w_hi = fp16(w),  w_lo = fp16(w − w_hi)
+// 256 × 32 weight tile is dequantised on the fly, exactly once per CTA, into two fp16 tiles with
+//     w_hi + w_lo = code · scale   to ≈ 22 bits  (packed fp16 arithmetic, see the conversion loop)
 // and the activations are split the same way by a pre-pass (x_hi, x_lo, after a power-of-two row
 // scaling that keeps fp16 in range; RMSNorm is applied there too).  Three MMAs per k-step,
 //     D += X_hi·W_hi + X_lo·W_hi + X_hi·W_lo,
@@ -13,18 +13,19 @@
 // relative — so the prefill path stays inside the decode path's tolerance at one third of the
 // fp16 tensor peak.
 //
-// One CTA per 128 × 128 output tile, ten warps:
-//   warps 0-7  dequantise, as two groups of four that take the k-tiles in turn (a thread owns a weight row of
-//              the tile: 64 code bytes + 2 scales per k-tile from global memory, its next three already in registers) and write the
-//              W_hi / W_lo tiles in the 128-byte-swizzled K-major layout the MMA reads; afterwards
-//              they are the epilogue: tcgen05.ld of a 32 × 64 piece of the accumulator each, row scale,
-//              bias, residual or SiLU-gate, 128-byte row stores through a shared-memory transpose;
-//   warp 8     one thread streams the activation tiles: the pre-pass leaves every 128 × 64 tile
-//              as a ready shared-memory image (hi and lo adjacent, 32 KB), so a stage is ONE
-//              plain bulk copy completing on an mbarrier — no tensor map;
-//   warp 9     one thread issues the MMAs and commits each stage back to its "empty" barrier.
-// Three stages of 64 KB.  Every wait is bounded: when a bound expires the CTA records an error
-// code, stops waiting for anything, frees its tensor memory and returns.
+// One CTA per 128 (activation rows) × 256 (weight rows) output tile, k-tiles of 32, ten warps:
+//   warps 0-7  dequantise, as two groups of four that take the k-tiles in turn (a thread owns two weight rows of
+//              the tile: 32 code bytes + a scale each per k-tile from global memory, its next three k-tiles
+//              already in registers) and write the W_hi / W_lo tiles in the 64-byte-swizzled K-major layout the
+//              MMA reads; afterwards they are the epilogue: tcgen05.ld of a 32 × 128 piece of the accumulator
+//              each, row scale, bias, residual or SiLU-gate, 128-byte row stores through a shared-memory transpose;
+//   warp 8     one thread streams the activation tiles: the pre-pass leaves every 128 × 32 tile as a ready
+//              shared-memory image (hi and lo adjacent, 16 KB), so a stage is ONE plain bulk copy completing
+//              on an mbarrier — no tensor map;
+//   warp 9     one thread issues the MMAs (128 × 256 × 16, accumulator = 256 columns of tensor memory) and
+//              commits each stage back to its "empty" barriers.
+// Four activation stages of 16 KB and four weight stages of 32 KB.  Every wait is bounded: when a bound
+// expires the CTA records an error code, stops waiting for anything, frees its tensor memory and returns.
 #include "kernels.h"
 #include "q8_common.cuh"
 #include <cuda_fp16.h>
@@ -32,18 +33,20 @@
 namespace dj {
 namespace {
 
-constexpr int kTileM = 128, kTileN = 128, kTileK = 64;
-constexpr int kStages = 3;
-constexpr int kATileBytes = kTileM * kTileK * 2;         // one fp16 tile: 16 KB
-constexpr int kBTileBytes = kTileN * kTileK * 2;
-constexpr int kStageBytes = 2 * kATileBytes + 2 * kBTileBytes;      // X_hi, X_lo, W_hi, W_lo
-constexpr int kDqWarps = 8;                              // dequantising (later: epilogue) warps; then one copy warp, one MMA warp
+constexpr int kTileM = 128, kTileN = 256, kTileK = 32;
+constexpr int kStagesA = 4, kStagesB = 4;                // activation copies need the depth (L2 latency), dequantised tiles do not
+constexpr int kATileBytes = kTileM * kTileK * 2;         // one fp16 activation tile: 8 KB
+constexpr int kBTileBytes = kTileN * kTileK * 2;         // one fp16 weight tile: 16 KB
+constexpr int kStageABytes = 2 * kATileBytes;            // X_hi, X_lo
+constexpr int kStageBBytes = 2 * kBTileBytes;            // W_hi, W_lo
+constexpr int kDqWarps = 8;                              // dequantising (later: epilogue) warps, one weight row per thread; then one copy warp, one MMA warp
 constexpr int kTcThreads = (kDqWarps + 2) * 32;
 constexpr unsigned kTcWaitLimit = 1u << 22;              // try_wait rounds before a wait gives up
-constexpr int kTmemCols = 128;
+constexpr int kTmemCols = 256;
 
-// byte offset of 16-byte chunk c (0-7) of row r inside a 128-byte-swizzled K-major tile of 64 halves per row
-__host__ __device__ __forceinline__ int swz_off(int r, int c) { return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4); }
+// byte offset of 16-byte chunk c (0-3) of row r inside a 64-byte-swizzled K-major tile of 32 halves per row:
+// 8-row groups of 512 bytes, the chunk index XORed with bits 1-2 of the row
+__host__ __device__ __forceinline__ int swz_off(int r, int c) { return (r >> 3) * 512 + (r & 7) * 64 + ((c ^ ((r >> 1) & 3)) << 4); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -103,18 +106,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// K-major, 128-byte swizzle: 8-row groups 1024 bytes apart (stride byte offset), leading offset unused (1),
-// descriptor version 1, layout type 2.
+// K-major, 64-byte swizzle: 8-row groups 512 bytes apart (stride byte offset), leading offset unused (1),
+// descriptor version 1, layout type 4.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
     d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)(512 >> 4) << 32;
     d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
+    d |= (uint64_t)4 << 61;
     return d;
 }
-// fp16 × fp16 → fp32, both operands K-major, M = 128, N = 128
+// fp16 × fp16 → fp32, both operands K-major, M = 128, N = 256
 constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
 
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
@@ -138,8 +141,8 @@ __global__ void __launch_bounds__(256) k_x_to_f16_tiles(const float* __restrict_
     unsigned char* mt = tiles + (size_t)(m / kTileM) * nK * (2 * kATileBytes);
     const int r = m % kTileM;
     if (m >= M) {
-        for (int c = lane; c < nK * 8; c += 32) {
-            unsigned char* t = mt + (size_t)(c >> 3) * (2 * kATileBytes) + swz_off(r, c & 7);
+        for (int c = lane; c < nK * 4; c += 32) {
+            unsigned char* t = mt + (size_t)(c >> 2) * (2 * kATileBytes) + swz_off(r, c & 3);
             *reinterpret_cast<uint4*>(t) = make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4*>(t + kATileBytes) = make_uint4(0, 0, 0, 0);
         }
@@ -164,7 +167,7 @@ __global__ void __launch_bounds__(256) k_x_to_f16_tiles(const float* __restrict_
     if (amax > 0.0f && amax < 1e30f) ebits = __float_as_int(amax) & 0x7f800000;
     const float down = __int_as_float(0x7f000000 - ebits) * 512.0f;
     if (lane == 0) rowscale[m] = __int_as_float(ebits) * (1.0f / 512.0f);
-    for (int c = lane; c < nK * 8; c += 32) {          // chunk c: values 8c … 8c+7
+    for (int c = lane; c < nK * 4; c += 32) {          // chunk c: values 8c … 8c+7
         const float4 a = *reinterpret_cast<const float4*>(xr + c * 8), b = *reinterpret_cast<const float4*>(xr + c * 8 + 4);
         float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
         if (gamma) {
@@ -181,7 +184,7 @@ __global__ void __launch_bounds__(256) k_x_to_f16_tiles(const float* __restrict_
             const float2 back = __half22float2(*reinterpret_cast<const __half2*>(&hi[j]));
             lo[j] = pack_h2(p - back.x, q - back.y);
         }
-        unsigned char* t = mt + (size_t)(c >> 3) * (2 * kATileBytes) + swz_off(r, c & 7);
+        unsigned char* t = mt + (size_t)(c >> 2) * (2 * kATileBytes) + swz_off(r, c & 3);
         *reinterpret_cast<uint4*>(t) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         *reinterpret_cast<uint4*>(t + kATileBytes) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
@@ -200,7 +203,7 @@ struct TcParams {
 
 __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_bar[3 * kStages + 1];
+    __shared__ __align__(8) unsigned long long s_bar[2 * kStagesA + 2 * kStagesB + 1];
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_abort;
 
@@ -211,13 +214,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     const uint32_t smem_raw = smem_u32(smem);
     const uint32_t smem_s = (smem_raw + 1023u) & ~1023u;
     unsigned char* const smem_al = smem + (smem_s - smem_raw);
+    // layout: activation stages [kStagesA][X_hi 8 KB | X_lo 8 KB], then weight stages [kStagesB][W_hi 16 KB | W_lo 16 KB]
+    const uint32_t smemB_s = smem_s + kStagesA * kStageABytes;
+    unsigned char* const smemB = smem_al + kStagesA * kStageABytes;
     auto bar_fullA = [&](int s) { return smem_u32(&s_bar[s]); };
-    auto bar_fullB = [&](int s) { return smem_u32(&s_bar[kStages + s]); };
-    auto bar_empty = [&](int s) { return smem_u32(&s_bar[2 * kStages + s]); };
-    const uint32_t bar_acc = smem_u32(&s_bar[3 * kStages]);
+    auto bar_emptyA = [&](int s) { return smem_u32(&s_bar[kStagesA + s]); };
+    auto bar_fullB = [&](int s) { return smem_u32(&s_bar[2 * kStagesA + s]); };
+    auto bar_emptyB = [&](int s) { return smem_u32(&s_bar[2 * kStagesA + kStagesB + s]); };
+    const uint32_t bar_acc = smem_u32(&s_bar[2 * kStagesA + 2 * kStagesB]);
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; s++) { mbar_init(bar_fullA(s), 1); mbar_init(bar_fullB(s), 128); mbar_init(bar_empty(s), 1); }
+        for (int s = 0; s < kStagesA; s++) { mbar_init(bar_fullA(s), 1); mbar_init(bar_emptyA(s), 1); }
+        for (int s = 0; s < kStagesB; s++) { mbar_init(bar_fullB(s), 128); mbar_init(bar_emptyB(s), 1); }
         mbar_init(bar_acc, 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -231,24 +239,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     pdl_launch_dependents();
 
     if (warp < kDqWarps) {
-        // ── dequantise: two groups of four warps take the k-tiles in turn (group g: k-tiles g, g+2, …), thread r of a
-        // group owns weight row n0 + r.  While one group waits for its stage or sits in its proxy fence, the other
-        // converts: the tensor pipe is fed at the conversion's issue rate, not at the sum of the three. ──
+        // ── dequantise: two groups of four warps take the k-tiles in turn (group g: k-tiles g, g+2, …); thread r of a
+        // group owns weight rows n0 + r and n0 + r + 128 of the 256-row tile (32 code bytes and one scale each per
+        // k-tile, the group's next kAhead k-tiles already in registers).  While one group waits for its stage or
+        // sits in its proxy fence, the other converts. ──
         const int r = tid & 127, grp = tid >> 7;
-        const int n = n0 + r;
-        const bool live = n < p.N;
-        const int8_t* crow = p.codes + (size_t)(live ? n : 0) * p.Kp;
-        const float* srow = p.scales + (size_t)(live ? n : 0) * p.nb;
-        // the codes of this group's next kAhead k-tiles are always in flight in registers: one k-tile of MMA time is
-        // shorter than a load round trip, and these threads are all the memory parallelism the weights get
-        constexpr int kAhead = 3;
-        uint4 buf[kAhead][4]; float bsc[kAhead][2];
-        auto load_k = [&](int kt, uint4 (&c)[4], float (&sc)[2]) {
-            const bool on = live && kt < nK;
+        const int8_t* crow[2]; const float* srow[2]; bool live[2];
 #pragma unroll
-            for (int j = 0; j < 4; j++) c[j] = on ? __ldg(reinterpret_cast<const uint4*>(crow + (size_t)kt * kTileK) + j) : make_uint4(0, 0, 0, 0);
-            sc[0] = on ? __ldg(srow + kt * 2) : 0.0f;
-            sc[1] = on ? __ldg(srow + kt * 2 + 1) : 0.0f;
+        for (int h = 0; h < 2; h++) {
+            const int n = n0 + r + 128 * h;
+            live[h] = n < p.N;
+            crow[h] = p.codes + (size_t)(live[h] ? n : 0) * p.Kp;
+            srow[h] = p.scales + (size_t)(live[h] ? n : 0) * p.nb;
+        }
+        constexpr int kAhead = 3;
+        uint4 buf[kAhead][2][2]; float bsc[kAhead][2];
+        auto load_k = [&](int kt, uint4 (&c)[2][2], float (&sc)[2]) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const bool on = live[h] && kt < nK;
+                c[h][0] = on ? __ldg(reinterpret_cast<const uint4*>(crow[h] + (size_t)kt * kTileK)) : make_uint4(0, 0, 0, 0);
+                c[h][1] = on ? __ldg(reinterpret_cast<const uint4*>(crow[h] + (size_t)kt * kTileK) + 1) : make_uint4(0, 0, 0, 0);
+                sc[h] = on ? __ldg(srow[h] + kt) : 0.0f;
+            }
         };
 #pragma unroll
         for (int a = 0; a < kAhead; a++) load_k(grp + 2 * a, buf[a], bsc[a]);
@@ -259,42 +272,56 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
             for (int a = 0; a < kAhead; a++) {
                 const int kt = kt0 + 2 * a;
                 if (kt >= nK) break;
-                const int s = kt % kStages;
-                uint4 cur[4];
+                const int s = kt % kStagesB;
+                uint4 cur[2][2]; float scl[2];
 #pragma unroll
-                for (int j = 0; j < 4; j++) cur[j] = buf[a][j];
-                const float sc0 = bsc[a][0], sc1 = bsc[a][1];
+                for (int h = 0; h < 2; h++) { cur[h][0] = buf[a][h][0]; cur[h][1] = buf[a][h][1]; scl[h] = bsc[a][h]; }
                 load_k(kt + 2 * kAhead, buf[a], bsc[a]);
                 unsigned long long t0 = tracing ? gtime() : 0;
-                if (kt >= kStages) mbar_wait(bar_empty(s), ((kt / kStages) - 1) & 1, &s_abort, p.error, 201);
+                if (kt >= kStagesB) mbar_wait(bar_emptyB(s), ((kt / kStagesB) - 1) & 1, &s_abort, p.error, 201);
                 unsigned long long t1 = tracing ? gtime() : 0;
-                unsigned char* bhi = smem_al + (size_t)s * kStageBytes + 2 * kATileBytes;
+                unsigned char* bhi = smemB + (size_t)s * kStageBBytes;
                 unsigned char* blo = bhi + kBTileBytes;
+                // The block's scale (times 2^12, undone in the epilogue, so that it sits in fp16's normal range) as
+                // s_hi + s_lo, both fp16.  Per pair of codes, all in packed fp16 arithmetic:
+                //   c    = the codes as fp16, exactly (sign flip, byte under exponent 0x64, subtract 1152)
+                //   w_hi = rn(c · s_hi)
+                //   w_lo = rn(c · s_lo + (c · s_hi − w_hi))      — the product's rounding error is exact in one fma
+                // so w_hi + w_lo carries ≈ 22 bits of c · scale at 2.75 instructions per weight.
 #pragma unroll
-                for (int j = 0; j < 4; j++) {                  // 16 codes → two 16-byte chunks of hi and of lo
-                    // No conversion-pipe instruction but the two packed fp16 roundings per weight pair:
-                    // code → float through the 2^23 trick (byte under exponent 0x4B is 8388608 + code + 128),
-                    // w_hi = w with the mantissa cut to 10 bits (exactly an fp16 value), w_lo = w − w_hi (exact in fp32).
-                    const uint32_t w4[4] = {cur[j].x ^ 0x80808080u, cur[j].y ^ 0x80808080u, cur[j].z ^ 0x80808080u, cur[j].w ^ 0x80808080u};
-                    const float scale = j < 2 ? sc0 : sc1;
-                    uint32_t hi[8], lo[8];
+                for (int h = 0; h < 2; h++) {
+                    const int row = r + 128 * h;
+                    const float sv = scl[h] * 4096.0f;
+                    const __half sh1 = __float2half_rn(sv);
+                    const __half sl1 = __float2half_rn(sv - __half2float(sh1));
+                    const __half2 sh = __half2half2(sh1), sl = __half2half2(sl1);
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        float f[4], h[4];
+                    for (int j = 0; j < 2; j++) {                  // 16 codes → two 16-byte chunks of hi and of lo
+                        const uint32_t w4[4] = {cur[h][j].x, cur[h][j].y, cur[h][j].z, cur[h][j].w};
+                        uint32_t hi[8], lo[8];
 #pragma unroll
-                        for (int b = 0; b < 4; b++) {
-                            const float big = __uint_as_float(__byte_perm(w4[q], 0x4B000000u, 0x7650 + b));   // bytes {w.b, 0, 0, 0x4B}
-                            f[b] = (big - 8388736.0f) * scale;
-                            h[b] = __uint_as_float(__float_as_uint(f[b]) & 0xFFFFE000u);
+                        for (int q = 0; q < 4; q++) {
+                            const uint32_t u = w4[q] ^ 0x80808080u;
+                            uint32_t c01 = __byte_perm(u, 0x64646464u, 0x4140), c23 = __byte_perm(u, 0x64646464u, 0x4342);
+                            const uint32_t k1152 = 0x64806480u;
+                            asm("sub.f16x2 %0, %1, %2;" : "=r"(c01) : "r"(c01), "r"(k1152));
+                            asm("sub.f16x2 %0, %1, %2;" : "=r"(c23) : "r"(c23), "r"(k1152));
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                const __half2 c = *reinterpret_cast<const __half2*>(e == 0 ? &c01 : &c23);
+                                const __half2 wh = __hmul2(c, sh);
+                                const __half2 er = __hfma2(c, sh, __hneg2(wh));
+                                const __half2 wl = __hfma2(c, sl, er);
+                                hi[2 * q + e] = *reinterpret_cast<const uint32_t*>(&wh);
+                                lo[2 * q + e] = *reinterpret_cast<const uint32_t*>(&wl);
+                            }
                         }
-                        hi[2 * q] = pack_h2(h[0], h[1]); hi[2 * q + 1] = pack_h2(h[2], h[3]);
-                        lo[2 * q] = pack_h2(f[0] - h[0], f[1] - h[1]); lo[2 * q + 1] = pack_h2(f[2] - h[2], f[3] - h[3]);
+                        const int o0 = swz_off(row, 2 * j), o1 = swz_off(row, 2 * j + 1);
+                        *reinterpret_cast<uint4*>(bhi + o0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                        *reinterpret_cast<uint4*>(bhi + o1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                        *reinterpret_cast<uint4*>(blo + o0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        *reinterpret_cast<uint4*>(blo + o1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
                     }
-                    const int o0 = swz_off(r, 2 * j), o1 = swz_off(r, 2 * j + 1);
-                    *reinterpret_cast<uint4*>(bhi + o0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4*>(bhi + o1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-                    *reinterpret_cast<uint4*>(blo + o0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                    *reinterpret_cast<uint4*>(blo + o1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
                 }
                 unsigned long long t2 = tracing ? gtime() : 0;
                 fence_proxy_async_smem();                      // generic-proxy stores → visible to the tensor-core (async) proxy
@@ -303,16 +330,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
             }
         }
         if (tracing) { p.trace[0] = tStart; p.trace[1] = tStart + tWait; p.trace[2] = p.trace[1] + tConv; p.trace[3] = p.trace[2] + tFence; p.trace[4] = gtime(); }
-        // ── epilogue: warp w reads accumulator rows 32(w%4) … +31, columns 64(w/4) … +63; each 32 × 32 block goes
+        // ── epilogue: warp w reads accumulator rows 32(w%4) … +31, columns 128(w/4) … +127; each 32 × 32 block goes
         // through a padded shared-memory square so that a warp stores 128 contiguous bytes of one output row ──
         const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_acc, 0, &s_abort, p.error, 202));
         tc_fence_after();
         const int q4 = warp & 3, chalf = warp >> 2;
         const int mrow = m0 + q4 * 32 + lane;
-        const float rs = (ok && mrow < p.M) ? p.rowscale[mrow] : 0.0f;
+        const float rs = (ok && mrow < p.M) ? p.rowscale[mrow] * (1.0f / 4096.0f) : 0.0f;       // the weights carry 2^12
         float* stg = reinterpret_cast<float*>(smem_al) + warp * (32 * 33);       // the pipeline stages are idle by now
 #pragma unroll 1
-        for (int c0 = chalf * 64; c0 < chalf * 64 + 64; c0 += 32) {
+        for (int c0 = chalf * 128; c0 < chalf * 128 + 128; c0 += 32) {
             uint32_t v[32];
             if (ok) tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);      // warp-uniform
             else {
@@ -343,14 +370,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
         if (tracing) { p.trace[5] = gtime(); p.trace[6] = p.trace[5]; }
         tc_fence_before();
     } else if (warp == kDqWarps) {
-        // ── activation tiles: one bulk copy of 32 KB (hi + lo) per stage ──
+        // ── activation tiles: one bulk copy of 16 KB (hi + lo) per stage ──
         if (lane == 0) {
-            const unsigned char* src = p.xtiles + (size_t)blockIdx.y * nK * (2 * kATileBytes);
+            const unsigned char* src = p.xtiles + (size_t)blockIdx.y * nK * kStageABytes;
             for (int kt = 0; kt < nK; kt++) {
-                const int s = kt % kStages;
-                if (kt >= kStages && !mbar_wait(bar_empty(s), ((kt / kStages) - 1) & 1, &s_abort, p.error, 203)) break;
-                mbar_arrive_expect_tx(bar_fullA(s), 2 * kATileBytes);
-                bulk_g2s(smem_s + (uint32_t)s * kStageBytes, src + (size_t)kt * (2 * kATileBytes), 2 * kATileBytes, bar_fullA(s));
+                const int s = kt % kStagesA;
+                if (kt >= kStagesA && !mbar_wait(bar_emptyA(s), ((kt / kStagesA) - 1) & 1, &s_abort, p.error, 203)) break;
+                mbar_arrive_expect_tx(bar_fullA(s), kStageABytes);
+                bulk_g2s(smem_s + (uint32_t)s * kStageABytes, src + (size_t)kt * kStageABytes, kStageABytes, bar_fullA(s));
             }
         }
         __syncwarp();
@@ -359,13 +386,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
         if (lane == 0) {
             bool ok = true;
             for (int kt = 0; kt < nK && ok; kt++) {
-                const int s = kt % kStages;
-                const uint32_t ph = (kt / kStages) & 1;
-                ok = mbar_wait(bar_fullA(s), ph, &s_abort, p.error, 204) && mbar_wait(bar_fullB(s), ph, &s_abort, p.error, 205);
+                const int sa = kt % kStagesA, sb = kt % kStagesB;
+                ok = mbar_wait(bar_fullA(sa), (kt / kStagesA) & 1, &s_abort, p.error, 204) &&
+                     mbar_wait(bar_fullB(sb), (kt / kStagesB) & 1, &s_abort, p.error, 205);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_hi = smem_s + (uint32_t)s * kStageBytes, a_lo = a_hi + kATileBytes;
-                const uint32_t b_hi = a_hi + 2 * kATileBytes, b_lo = b_hi + kBTileBytes;
+                const uint32_t a_hi = smem_s + (uint32_t)sa * kStageABytes, a_lo = a_hi + kATileBytes;
+                const uint32_t b_hi = smemB_s + (uint32_t)sb * kStageBBytes, b_lo = b_hi + kBTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < kTileK / 16; ks++) {
                     const uint32_t off = ks * 32;          // 16 halves along K inside the swizzled row
@@ -373,7 +400,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
                     umma_f16(tmem_base, umma_desc(a_lo + off), umma_desc(b_hi + off), kIdesc, 1);
                     umma_f16(tmem_base, umma_desc(a_hi + off), umma_desc(b_lo + off), kIdesc, 1);
                 }
-                umma_commit(bar_empty(s));                 // arrives when the MMAs above have finished reading the stage
+                umma_commit(bar_emptyA(sa));               // both arrive when the MMAs above have finished reading the stages
+                umma_commit(bar_emptyB(sb));
             }
             if (ok) umma_commit(bar_acc);
         }
@@ -383,7 +411,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     if (warp == kDqWarps) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
-constexpr size_t kTcSmem = (size_t)kStages * kStageBytes + 1024;
+constexpr size_t kTcSmem = (size_t)kStagesA * kStageABytes + (size_t)kStagesB * kStageBBytes + 1024;
 
 }  // namespace
 
