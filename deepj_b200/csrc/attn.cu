@@ -16,6 +16,7 @@
 #include "../../include/deepj_cuda.h"
 #include "kernels.h"
 #include <cmath>
+#include <cstdlib>
 
 namespace dj {
 
@@ -291,6 +292,137 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     }
 }
 
+
+// ───────────── prompt chunks: tiled causal attention ─────────────
+// Row-wise decode attention re-reads every key once per query row.  For a chunk of T ≥ 32 tokens this kernel
+// lets 32 consecutive query rows of one head share each 64-key tile of K and V through shared memory (fp32 on the
+// CUDA cores, online softmax per row):  S = Q·Kᵀ (Q rotated and pre-scaled at load, K transposed in shared memory
+// so that four keys are one 16-byte read), mask, running max / sum, P through shared memory, O += P·V.
+// grid (query tiles, heads, sequences), 256 threads: thread (rg, cg) = (t / 16, t % 16) owns rows 2rg, 2rg+1 —
+// the 16 lanes of a row pair are contiguous, row reductions are half-warp shuffles.
+constexpr int kPQ = 32, kPK = 64;
+
+template <int HD>
+__global__ void __launch_bounds__(256, 2) k_attn_prefill_tiled(
+        const float* __restrict__ qkv, int q_off, int ld, const float* __restrict__ kcache, const float* __restrict__ vcache,
+        int maxSeq, const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
+        float* __restrict__ out, int ldo, int H, float scale, int T) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int kKtStride = kPK + 1;
+    float* Qs = sm;                                 // [32][HD]
+    float* Kt = Qs + kPQ * HD;                      // [HD][65]   (transposed key tile)
+    float* Vs = Kt + HD * kKtStride;                // [64][HD]
+    float* Ps = Vs + kPK * HD;                      // [32][68]
+    constexpr int kPsStride = kPK + 4;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, rg = tid >> 4, cg = tid & 15;
+    const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int t0 = qt * kPQ;
+    int pos0 = (int)posbuf[b];
+    pos0 = pos0 < 0 ? 0 : pos0;
+    const int half = HD >> 1;
+    // Q tile: rotate (interleaved pairs) at position pos0 + t and fold in the 1/sqrt(hd) scale
+    for (int i = tid; i < kPQ * half; i += 256) {
+        const int r = i / half, pr = i % half;
+        const int t = t0 + r;
+        float x0 = 0.0f, x1 = 0.0f;
+        if (t < T && pos0 + t < maxSeq) {
+            const float2 v = *reinterpret_cast<const float2*>(qkv + (size_t)(b * T + t) * ld + q_off + h * HD + 2 * pr);
+            const float c = cosT[(size_t)(pos0 + t) * half + pr], s = sinT[(size_t)(pos0 + t) * half + pr];
+            x0 = (v.x * c - v.y * s) * scale;
+            x1 = (v.x * s + v.y * c) * scale;
+        }
+        Qs[r * HD + 2 * pr] = x0;
+        Qs[r * HD + 2 * pr + 1] = x1;
+    }
+    const float* kb = kcache + ((size_t)b * H + h) * maxSeq * HD;
+    const float* vb = vcache + ((size_t)b * H + h) * maxSeq * HD;
+    const int lastKey = min(maxSeq - 1, pos0 + min(T, t0 + kPQ) - 1);       // newest key any row of this tile may see
+    const int r0 = 2 * rg, r1 = 2 * rg + 1;
+    const int lim0 = pos0 + t0 + r0, lim1 = pos0 + t0 + r1;                  // row r attends to keys ≤ lim
+    constexpr int kOC = HD / 16;                                             // output columns per thread
+    float o0[kOC], o1[kOC];
+#pragma unroll
+    for (int j = 0; j < kOC; j++) { o0[j] = 0.0f; o1[j] = 0.0f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    for (int k0 = 0; k0 <= lastKey; k0 += kPK) {
+        __syncthreads();                            // the previous tile's K, V and P are no longer read (first round: Q is written)
+        // K tile, transposed, and V tile
+        for (int i = tid; i < kPK * (HD / 4); i += 256) {
+            const int key = i / (HD / 4), d4 = i % (HD / 4);
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (k0 + key <= lastKey) {
+                kv = __ldg(reinterpret_cast<const float4*>(kb + (size_t)(k0 + key) * HD) + d4);
+                vv = __ldg(reinterpret_cast<const float4*>(vb + (size_t)(k0 + key) * HD) + d4);
+            }
+            Kt[(4 * d4 + 0) * kKtStride + key] = kv.x; Kt[(4 * d4 + 1) * kKtStride + key] = kv.y;
+            Kt[(4 * d4 + 2) * kKtStride + key] = kv.z; Kt[(4 * d4 + 3) * kKtStride + key] = kv.w;
+            *reinterpret_cast<float4*>(Vs + key * HD + 4 * d4) = vv;
+        }
+        __syncthreads();
+        // S = Q·Kᵀ for rows r0, r1 and keys 4cg … 4cg+3
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+        for (int d = 0; d < HD; d++) {
+            const float q0 = Qs[r0 * HD + d], q1 = Qs[r1 * HD + d];
+            const float* kr = Kt + d * kKtStride + 4 * cg;
+#pragma unroll
+            for (int j = 0; j < 4; j++) { s0[j] = fmaf(q0, kr[j], s0[j]); s1[j] = fmaf(q1, kr[j], s1[j]); }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int key = k0 + 4 * cg + j;
+            if (key > lim0 || key > lastKey) s0[j] = -INFINITY;
+            if (key > lim1 || key > lastKey) s1[j] = -INFINITY;
+            mx0 = fmaxf(mx0, s0[j]); mx1 = fmaxf(mx1, s1[j]);
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) { mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o)); }
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float c0 = mn0 > -INFINITY ? expf(m0 - mn0) : 1.0f, c1 = mn1 > -INFINITY ? expf(m1 - mn1) : 1.0f;
+        float ps0 = 0.0f, ps1 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float p0 = s0[j] > -INFINITY ? expf(s0[j] - mn0) : 0.0f, p1 = s1[j] > -INFINITY ? expf(s1[j] - mn1) : 0.0f;
+            Ps[r0 * kPsStride + 4 * cg + j] = p0; Ps[r1 * kPsStride + 4 * cg + j] = p1;
+            ps0 += p0; ps1 += p1;
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) { ps0 += __shfl_xor_sync(0xffffffffu, ps0, o); ps1 += __shfl_xor_sync(0xffffffffu, ps1, o); }
+        l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+        m0 = mn0; m1 = mn1;
+#pragma unroll
+        for (int j = 0; j < kOC; j++) { o0[j] *= c0; o1[j] *= c1; }
+        __syncthreads();
+        // O += P·V for rows r0, r1 and columns kOC·cg … kOC·cg + kOC − 1
+        const int nk = min(kPK, lastKey - k0 + 1);
+        for (int key = 0; key < nk; key++) {
+            const float p0 = Ps[r0 * kPsStride + key], p1 = Ps[r1 * kPsStride + key];
+            const float* vr = Vs + key * HD + kOC * cg;
+#pragma unroll
+            for (int j = 0; j < kOC; j += 4) {
+                const float4 v4 = *reinterpret_cast<const float4*>(vr + j);
+                o0[j] = fmaf(p0, v4.x, o0[j]); o0[j + 1] = fmaf(p0, v4.y, o0[j + 1]); o0[j + 2] = fmaf(p0, v4.z, o0[j + 2]); o0[j + 3] = fmaf(p0, v4.w, o0[j + 3]);
+                o1[j] = fmaf(p1, v4.x, o1[j]); o1[j + 1] = fmaf(p1, v4.y, o1[j + 1]); o1[j + 2] = fmaf(p1, v4.z, o1[j + 2]); o1[j + 3] = fmaf(p1, v4.w, o1[j + 3]);
+            }
+        }
+    }
+    if (t0 + r0 < T && l0 > 0.0f) {
+        float* dst = out + (size_t)(b * T + t0 + r0) * ldo + h * HD + kOC * cg;
+#pragma unroll
+        for (int j = 0; j < kOC; j++) dst[j] = o0[j] / l0;
+    }
+    if (t0 + r1 < T && l1 > 0.0f) {
+        float* dst = out + (size_t)(b * T + t0 + r1) * ldo + h * HD + kOC * cg;
+#pragma unroll
+        for (int j = 0; j < kOC; j++) dst[j] = o1[j] / l1;
+    }
+}
+
+template <int HD> constexpr size_t prefill_tiled_smem() { return (size_t)(kPQ * HD + HD * (kPK + 1) + kPK * HD + kPQ * (kPK + 4)) * 4; }
+
 }  // namespace
 
 int attn_decode_splits(int B, int H, int maxSeq) {
@@ -318,6 +450,22 @@ void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s) {
         dim3 ag(a.H, (unsigned)rows);
         launch_k(k_kv_append, ag, dim3(a.hd / 2), 0, s, true, (const float*)a.qkv, a.k_off, a.v_off, a.ld, a.kcache, a.vcache, a.maxSeq,
                  a.pos, a.cosT, a.sinT, a.H, a.hd, T);
+    }
+    static const bool noTiled = getenv("DEEPJ_CUDA_NO_TILED_PREFILL") != nullptr;
+    if (T >= kPQ && !noTiled && (a.hd == 64 || a.hd == 128)) {
+        dim3 tg((T + kPQ - 1) / kPQ, a.H, a.B);
+        if (a.hd == 128) {
+            static bool attr = false;
+            if (!attr) { DJ_CUDA_CHECK(cudaFuncSetAttribute(k_attn_prefill_tiled<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_tiled_smem<128>())); attr = true; }
+            launch_k(k_attn_prefill_tiled<128>, tg, dim3(256), prefill_tiled_smem<128>(), s, true, (const float*)a.qkv, a.q_off, a.ld,
+                     (const float*)a.kcache, (const float*)a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.out, a.ldo, a.H, a.scale, T);
+        } else {
+            static bool attr = false;
+            if (!attr) { DJ_CUDA_CHECK(cudaFuncSetAttribute(k_attn_prefill_tiled<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_tiled_smem<64>())); attr = true; }
+            launch_k(k_attn_prefill_tiled<64>, tg, dim3(256), prefill_tiled_smem<64>(), s, true, (const float*)a.qkv, a.q_off, a.ld,
+                     (const float*)a.kcache, (const float*)a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.out, a.ldo, a.H, a.scale, T);
+        }
+        return;
     }
     const int append = T == 1 ? 1 : 0;
     int* tickets = a.tickets;
