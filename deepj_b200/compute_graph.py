@@ -54,7 +54,7 @@ for _op in (OP_CROSS_ENTROPY_LOSS, OP_CROSS_ENTROPY_GRADIENT, OP_SOFTMAX_BACKWAR
     OP_METADATA[_op] = (6, (1, 2, 3))
 OP_METADATA[OP_LAYERNORM_BACKWARD] = (7, (1, 2, 3, 4))
 OP_METADATA[OP_ADAMW_UPDATE] = (13, (1, 2, 3, 4))
-# fused ops: the extension point the survey of the reference calls for — the recorder
+# fused ops extend the reference's table: the recorder
 # must know their strides or orphan detection treats them as "references everything"
 OP_METADATA[OP_EMBED_GATHER] = (7, (1, 2, 3))
 OP_METADATA[OP_Q8_LINEAR] = (15, (1, 4, 6, 7, 8, 11))
