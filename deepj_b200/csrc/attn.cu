@@ -296,8 +296,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
 // ───────────── prompt chunks: tiled causal attention ─────────────
 // Row-wise decode attention re-reads every key once per query row.  For a chunk of T ≥ 32 tokens this kernel
 // lets 32 consecutive query rows of one head share each 64-key tile of K and V through shared memory (fp32 on the
-// CUDA cores, online softmax per row):  S = Q·Kᵀ (Q rotated and pre-scaled at load, K transposed in shared memory
-// so that four keys are one 16-byte read), mask, running max / sum, P through shared memory, O += P·V.
+// CUDA cores, online softmax per row):  S = Q·Kᵀ (Q rotated and pre-scaled at load, the K tile's 16-byte chunks
+// XOR-swizzled so that the 16-byte reads of a quarter warp never share a bank), mask, running max / sum, P through
+// shared memory, O += P·V.
 // grid (query tiles, heads, sequences), 256 threads: thread (rg, cg) = (t / 16, t % 16) owns rows 2rg, 2rg+1 —
 // the 16 lanes of a row pair are contiguous, row reductions are half-warp shuffles.
 constexpr int kPQ = 32, kPK = 64;
@@ -308,10 +309,9 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tiled(
         int maxSeq, const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
         float* __restrict__ out, int ldo, int H, float scale, int T) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int kKtStride = kPK + 1;
     float* Qs = sm;                                 // [32][HD]
-    float* Kt = Qs + kPQ * HD;                      // [HD][65]   (transposed key tile)
-    float* Vs = Kt + HD * kKtStride;                // [64][HD]
+    float* Ks = Qs + kPQ * HD;                      // [64][HD], 16-byte chunks XOR-swizzled by (key / 4) % 8
+    float* Vs = Ks + kPK * HD;                      // [64][HD]
     float* Ps = Vs + kPK * HD;                      // [32][68]
     constexpr int kPsStride = kPK + 4;
     pdl_wait();
@@ -356,19 +356,23 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tiled(
                 kv = __ldg(reinterpret_cast<const float4*>(kb + (size_t)(k0 + key) * HD) + d4);
                 vv = __ldg(reinterpret_cast<const float4*>(vb + (size_t)(k0 + key) * HD) + d4);
             }
-            Kt[(4 * d4 + 0) * kKtStride + key] = kv.x; Kt[(4 * d4 + 1) * kKtStride + key] = kv.y;
-            Kt[(4 * d4 + 2) * kKtStride + key] = kv.z; Kt[(4 * d4 + 3) * kKtStride + key] = kv.w;
+            *reinterpret_cast<float4*>(Ks + key * HD + 4 * (d4 ^ ((key >> 2) & 7))) = kv;
             *reinterpret_cast<float4*>(Vs + key * HD + 4 * d4) = vv;
         }
         __syncthreads();
         // S = Q·Kᵀ for rows r0, r1 and keys 4cg … 4cg+3
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-        for (int d = 0; d < HD; d++) {
-            const float q0 = Qs[r0 * HD + d], q1 = Qs[r1 * HD + d];
-            const float* kr = Kt + d * kKtStride + 4 * cg;
+        const int sw = cg & 7;                      // (key / 4) % 8 of this thread's four keys
+#pragma unroll 4
+        for (int c = 0; c < HD / 4; c++) {
+            const float4 q0 = *reinterpret_cast<const float4*>(Qs + r0 * HD + 4 * c);
+            const float4 q1 = *reinterpret_cast<const float4*>(Qs + r1 * HD + 4 * c);
 #pragma unroll
-            for (int j = 0; j < 4; j++) { s0[j] = fmaf(q0, kr[j], s0[j]); s1[j] = fmaf(q1, kr[j], s1[j]); }
+            for (int j = 0; j < 4; j++) {
+                const float4 k4 = *reinterpret_cast<const float4*>(Ks + (4 * cg + j) * HD + 4 * (c ^ sw));
+                s0[j] = fmaf(q0.x, k4.x, s0[j]); s0[j] = fmaf(q0.y, k4.y, s0[j]); s0[j] = fmaf(q0.z, k4.z, s0[j]); s0[j] = fmaf(q0.w, k4.w, s0[j]);
+                s1[j] = fmaf(q1.x, k4.x, s1[j]); s1[j] = fmaf(q1.y, k4.y, s1[j]); s1[j] = fmaf(q1.z, k4.z, s1[j]); s1[j] = fmaf(q1.w, k4.w, s1[j]);
+            }
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -421,7 +425,7 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tiled(
     }
 }
 
-template <int HD> constexpr size_t prefill_tiled_smem() { return (size_t)(kPQ * HD + HD * (kPK + 1) + kPK * HD + kPQ * (kPK + 4)) * 4; }
+template <int HD> constexpr size_t prefill_tiled_smem() { return (size_t)(kPQ * HD + kPK * HD + kPK * HD + kPQ * (kPK + 4)) * 4; }
 
 }  // namespace
 

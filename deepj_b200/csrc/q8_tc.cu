@@ -34,7 +34,7 @@ namespace dj {
 namespace {
 
 constexpr int kTileM = 128, kTileN = 256, kTileK = 32;
-constexpr int kStagesA = 4, kStagesB = 4;                // activation copies need the depth (L2 latency), dequantised tiles do not
+constexpr int kStagesA = 4, kStagesB = 3;                // activation copies need the depth (L2 latency), dequantised tiles do not
 constexpr int kATileBytes = kTileM * kTileK * 2;         // one fp16 activation tile: 8 KB
 constexpr int kBTileBytes = kTileN * kTileK * 2;         // one fp16 weight tile: 16 KB
 constexpr int kStageABytes = 2 * kATileBytes;            // X_hi, X_lo
@@ -43,6 +43,7 @@ constexpr int kDqWarps = 8;                              // dequantising (later:
 constexpr int kTcThreads = (kDqWarps + 2) * 32;
 constexpr unsigned kTcWaitLimit = 1u << 22;              // try_wait rounds before a wait gives up
 constexpr int kTmemCols = 256;
+constexpr int kRawRow = 144;                             // bytes per weight row in the raw-code buffer: 4 k-tiles of codes + their scales
 
 // byte offset of 16-byte chunk c (0-3) of row r inside a 64-byte-swizzled K-major tile of 32 halves per row:
 // 8-row groups of 512 bytes, the chunk index XORed with bits 1-2 of the row
@@ -203,7 +204,7 @@ struct TcParams {
 
 __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_bar[2 * kStagesA + 2 * kStagesB + 1];
+    __shared__ __align__(8) unsigned long long s_bar[2 * kStagesA + 2 * kStagesB + 5];
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_abort;
 
@@ -222,11 +223,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     auto bar_fullB = [&](int s) { return smem_u32(&s_bar[2 * kStagesA + s]); };
     auto bar_emptyB = [&](int s) { return smem_u32(&s_bar[2 * kStagesA + kStagesB + s]); };
     const uint32_t bar_acc = smem_u32(&s_bar[2 * kStagesA + 2 * kStagesB]);
+    const uint32_t bar_rawFull = smem_u32(&s_bar[2 * kStagesA + 2 * kStagesB + 1]);
+    const uint32_t bar_rawEmpty = smem_u32(&s_bar[2 * kStagesA + 2 * kStagesB + 2]);
+    unsigned char* const raw = smemB + kStagesB * kStageBBytes;          // [256 rows][128 code bytes + 4 scales]
 
     if (tid == 0) {
         for (int s = 0; s < kStagesA; s++) { mbar_init(bar_fullA(s), 1); mbar_init(bar_emptyA(s), 1); }
         for (int s = 0; s < kStagesB; s++) { mbar_init(bar_fullB(s), 128); mbar_init(bar_emptyB(s), 1); }
         mbar_init(bar_acc, 1);
+        mbar_init(bar_rawFull, kDqWarps * 32);
+        mbar_init(bar_rawEmpty, kDqWarps * 32);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -240,43 +246,53 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
 
     if (warp < kDqWarps) {
         // ── dequantise: two groups of four warps take the k-tiles in turn (group g: k-tiles g, g+2, …); thread r of a
-        // group owns weight rows n0 + r and n0 + r + 128 of the 256-row tile (32 code bytes and one scale each per
-        // k-tile, the group's next kAhead k-tiles already in registers).  While one group waits for its stage or
-        // sits in its proxy fence, the other converts. ──
+        // group owns weight rows n0 + r and n0 + r + 128 of the 256-row tile.  The raw codes and scales of four
+        // k-tiles at a time (256 rows × 128 code bytes + 4 scales) come through a shared-memory buffer filled with
+        // cp.async in row-contiguous runs — a warp's copy instruction touches 4 lines, where a load per row owner
+        // touched 32 and kept L1TEX saturated; every thread lifts its own pieces into registers, the buffer is
+        // refilled for the next four k-tiles behind a barrier, and the conversion runs from registers. ──
         const int r = tid & 127, grp = tid >> 7;
-        const int8_t* crow[2]; const float* srow[2]; bool live[2];
+        const int nG = nK / 4;
+        auto issue_group = [&](int G) {
+            // chunk q = tid + 256·i → row q / 8 (clamped: rows past N are never stored), 16-byte piece q % 8
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int n = n0 + r + 128 * h;
-            live[h] = n < p.N;
-            crow[h] = p.codes + (size_t)(live[h] ? n : 0) * p.Kp;
-            srow[h] = p.scales + (size_t)(live[h] ? n : 0) * p.nb;
-        }
-        constexpr int kAhead = 3;
-        uint4 buf[kAhead][2][2]; float bsc[kAhead][2];
-        auto load_k = [&](int kt, uint4 (&c)[2][2], float (&sc)[2]) {
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const bool on = live[h] && kt < nK;
-                c[h][0] = on ? __ldg(reinterpret_cast<const uint4*>(crow[h] + (size_t)kt * kTileK)) : make_uint4(0, 0, 0, 0);
-                c[h][1] = on ? __ldg(reinterpret_cast<const uint4*>(crow[h] + (size_t)kt * kTileK) + 1) : make_uint4(0, 0, 0, 0);
-                sc[h] = on ? __ldg(srow[h] + kt) : 0.0f;
+            for (int i = 0; i < 8; i++) {
+                const int row = (tid >> 3) + 32 * i, c = tid & 7;
+                const int n = min(n0 + row, p.N - 1);
+                cp_async16(raw + row * kRawRow + c * 16, p.codes + (size_t)n * p.Kp + (size_t)G * 128 + c * 16);
             }
+            const int n = min(n0 + tid, p.N - 1);
+            cp_async16(raw + tid * kRawRow + 128, p.scales + (size_t)n * p.nb + (size_t)G * 4);
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar_rawFull) : "memory");
         };
-#pragma unroll
-        for (int a = 0; a < kAhead; a++) load_k(grp + 2 * a, buf[a], bsc[a]);
+        issue_group(0);
         const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
         unsigned long long tWait = 0, tConv = 0, tFence = 0, tStart = tracing ? gtime() : 0;
-        for (int kt0 = grp; kt0 < nK; kt0 += 2 * kAhead) {
+        for (int G = 0; G < nG; G++) {
+            uint4 cur4[2][2][2]; float scl4[2][2];            // [own k-tile of the group][row][16-byte half]
+            mbar_wait(bar_rawFull, G & 1, &s_abort, p.error, 206);
 #pragma unroll
-            for (int a = 0; a < kAhead; a++) {
-                const int kt = kt0 + 2 * a;
-                if (kt >= nK) break;
+            for (int o = 0; o < 2; o++)
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const unsigned char* src = raw + (r + 128 * h) * kRawRow;
+                    const int j = grp + 2 * o;                   // k-tile inside the group
+                    cur4[o][h][0] = *reinterpret_cast<const uint4*>(src + 32 * j);
+                    cur4[o][h][1] = *reinterpret_cast<const uint4*>(src + 32 * j + 16);
+                    scl4[o][h] = *reinterpret_cast<const float*>(src + 128 + 4 * j);
+                }
+            mbar_arrive(bar_rawEmpty);
+            if (G + 1 < nG) {
+                mbar_wait(bar_rawEmpty, G & 1, &s_abort, p.error, 207);      // every thread has lifted its pieces
+                issue_group(G + 1);
+            }
+#pragma unroll
+            for (int o = 0; o < 2; o++) {
+                const int kt = 4 * G + grp + 2 * o;
                 const int s = kt % kStagesB;
                 uint4 cur[2][2]; float scl[2];
 #pragma unroll
-                for (int h = 0; h < 2; h++) { cur[h][0] = buf[a][h][0]; cur[h][1] = buf[a][h][1]; scl[h] = bsc[a][h]; }
-                load_k(kt + 2 * kAhead, buf[a], bsc[a]);
+                for (int h = 0; h < 2; h++) { cur[h][0] = cur4[o][h][0]; cur[h][1] = cur4[o][h][1]; scl[h] = scl4[o][h]; }
                 unsigned long long t0 = tracing ? gtime() : 0;
                 if (kt >= kStagesB) mbar_wait(bar_emptyB(s), ((kt / kStagesB) - 1) & 1, &s_abort, p.error, 201);
                 unsigned long long t1 = tracing ? gtime() : 0;
@@ -411,7 +427,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     if (warp == kDqWarps) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
-constexpr size_t kTcSmem = (size_t)kStagesA * kStageABytes + (size_t)kStagesB * kStageBBytes + 1024;
+constexpr size_t kTcSmem = (size_t)kStagesA * kStageABytes + (size_t)kStagesB * kStageBBytes + (size_t)kTileN * kRawRow + 1024;
 
 }  // namespace
 
@@ -424,7 +440,7 @@ size_t q8_tc_ws_floats(int M, int K) {
 // Returns false when the shape is outside the kernel's domain (K must be a multiple of 64).
 bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s) {
     const int K = a.w.K, N = a.w.N, M = a.M;
-    if (K % kTileK != 0 || a.w.Kp != K || ws == nullptr || M < 1) return false;
+    if (K % 128 != 0 || a.w.Kp != K || ws == nullptr || M < 1) return false;      // raw codes travel four k-tiles (and their 4 scales = 16 bytes) at a time
     if (((uintptr_t)a.x & 15) != 0 || a.ldx % 4 != 0 || (a.gamma && ((uintptr_t)a.gamma & 15) != 0)) return false;
     static bool attrSet = false;
     if (!attrSet) {
