@@ -107,7 +107,9 @@ void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s);
 
 // ── misc ──
 void launch_embed_gather(const float* table, const float* ids, float* out, int rows, int d, int vocab, cudaStream_t s);
-void launch_argmax_rows(const float* in, float* out, int rows, int cols, cudaStream_t s);
+// scratch: 2·16·rows ints of partial (key, index) pairs, tickets: rows zeroed self-resetting counters (rows ≤ kArgmaxRowsMax)
+constexpr int kArgmaxRowsMax = 4096;
+void launch_argmax_rows(const float* in, float* out, int rows, int cols, int* scratch, int* tickets, cudaStream_t s);
 void launch_sample_topk(const float* logits, const float* r, float* out, int rows, int cols, int topK, float temperature, cudaStream_t s);
 void launch_add_scalar_inplace(float* buf, float v, int n, cudaStream_t s);
 void launch_copy(const float* src, float* dst, long long n, cudaStream_t s);

@@ -31,34 +31,57 @@ __device__ __forceinline__ int order_key(float v) {
 }
 
 // Greedy pick: the first index of the largest value (a stable descending sort
-// keeps the lowest index among equals).  One CTA per row.
-__global__ void k_argmax_rows(const float* __restrict__ in, float* __restrict__ out, int rows, int cols) {
-    __shared__ int s_key[32];
-    __shared__ int s_idx[32];
+// keeps the lowest index among equals).  grid (parts, rows): every CTA reduces its slice of the row to one
+// (key, index) pair; the CTA that arrives last at the row (a self-resetting ticket) reduces the parts.  One CTA
+// per row costs a full load round trip per 1024 columns — 18 µs for a 32000-entry row.
+constexpr int kArgmaxParts = 16;
+__global__ void __launch_bounds__(256) k_argmax_rows(const float* __restrict__ in, float* __restrict__ out, int rows, int cols,
+                                                      int* __restrict__ scratch, int* __restrict__ tickets) {
+    __shared__ int s_key[8];
+    __shared__ int s_idx[8];
+    __shared__ int s_last;
     pdl_wait();
     pdl_launch_dependents();
-    int r = blockIdx.x;
+    const int part = blockIdx.x, parts = gridDim.x, r = blockIdx.y;
     const float* d = in + (size_t)r * cols;
+    const int per = ((cols + parts - 1) / parts + 3) & ~3;
+    const int lo = min(cols, part * per), hi = min(cols, lo + per);
     int bestKey = INT_MIN, bestIdx = INT_MAX;
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    for (int c = lo + (int)threadIdx.x; c < hi; c += blockDim.x) {
         int k = order_key(d[c]);
         if (k > bestKey || (k == bestKey && c < bestIdx)) { bestKey = k; bestIdx = c; }
     }
-    for (int o = 16; o > 0; o >>= 1) {
-        int k2 = __shfl_xor_sync(0xffffffffu, bestKey, o), i2 = __shfl_xor_sync(0xffffffffu, bestIdx, o);
-        if (k2 > bestKey || (k2 == bestKey && i2 < bestIdx)) { bestKey = k2; bestIdx = i2; }
-    }
-    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    auto warp_best = [&]() {
+        for (int o = 16; o > 0; o >>= 1) {
+            int k2 = __shfl_xor_sync(0xffffffffu, bestKey, o), i2 = __shfl_xor_sync(0xffffffffu, bestIdx, o);
+            if (k2 > bestKey || (k2 == bestKey && i2 < bestIdx)) { bestKey = k2; bestIdx = i2; }
+        }
+    };
+    warp_best();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     if (lane == 0) { s_key[warp] = bestKey; s_idx[warp] = bestIdx; }
     __syncthreads();
     if (warp == 0) {
         bestKey = lane < nw ? s_key[lane] : INT_MIN;
         bestIdx = lane < nw ? s_idx[lane] : INT_MAX;
-        for (int o = 16; o > 0; o >>= 1) {
-            int k2 = __shfl_xor_sync(0xffffffffu, bestKey, o), i2 = __shfl_xor_sync(0xffffffffu, bestIdx, o);
-            if (k2 > bestKey || (k2 == bestKey && i2 < bestIdx)) { bestKey = k2; bestIdx = i2; }
+        warp_best();
+        if (parts == 1) { if (lane == 0) out[r] = (float)bestIdx; return; }
+        if (lane == 0) {
+            scratch[((size_t)r * parts + part) * 2] = bestKey;
+            scratch[((size_t)r * parts + part) * 2 + 1] = bestIdx;
+            __threadfence();
+            const int t = atomicAdd(&tickets[r], 1);
+            s_last = t == parts - 1;
+            if (s_last) tickets[r] = 0;
         }
-        if (lane == 0) out[r] = (float)bestIdx;
+        __syncwarp();
+        if (__shfl_sync(0xffffffffu, lane == 0 ? s_last : 0, 0)) {
+            __threadfence();
+            bestKey = lane < parts ? __ldcg(scratch + ((size_t)r * parts + lane) * 2) : INT_MIN;
+            bestIdx = lane < parts ? __ldcg(scratch + ((size_t)r * parts + lane) * 2 + 1) : INT_MAX;
+            warp_best();
+            if (lane == 0) out[r] = (float)bestIdx;
+        }
     }
 }
 
@@ -231,9 +254,11 @@ void launch_embed_gather(const float* table, const float* ids, float* out, int r
     if (rows <= 0) return;
     launch_k(k_embed_gather, dim3(rows), dim3(256), 0, s, true, table, ids, out, rows, d, vocab);
 }
-void launch_argmax_rows(const float* in, float* out, int rows, int cols, cudaStream_t s) {
+void launch_argmax_rows(const float* in, float* out, int rows, int cols, int* scratch, int* tickets, cudaStream_t s) {
     if (rows <= 0) return;
-    launch_k(k_argmax_rows, dim3(rows), dim3(1024), 0, s, true, in, out, rows, cols);
+    // short rows, or more rows than ticket counters: one CTA per row
+    const int parts = (cols >= 4096 && rows <= kArgmaxRowsMax && scratch != nullptr) ? kArgmaxParts : 1;
+    launch_k(k_argmax_rows, dim3(parts, rows), dim3(256), 0, s, true, in, out, rows, cols, scratch, tickets);
 }
 void launch_sample_topk(const float* logits, const float* r, float* out, int rows, int cols, int topK, float temperature, cudaStream_t s) {
     if (rows <= 0) return;

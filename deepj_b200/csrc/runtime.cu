@@ -86,8 +86,10 @@ void ensure_init() {
         DJ_CUDA_CHECK(cudaMemset(g_trace, 0, (size_t)kTraceSlots * 8 * sizeof(unsigned long long)));
         R.graphs_enabled = false;      // slots are handed out per launch, which a replayed graph would not do
     }
-    DJ_CUDA_CHECK(cudaMalloc((void**)&R.tickets, kAttnTickets * sizeof(int)));
-    DJ_CUDA_CHECK(cudaMemset(R.tickets, 0, kAttnTickets * sizeof(int)));
+    // ticket counters of the split-attention merge and the batched linear, then the greedy pick's (kArgmaxRowsMax)
+    // and its partial pairs (2 · 16 per row)
+    DJ_CUDA_CHECK(cudaMalloc((void**)&R.tickets, (kAttnTickets + kArgmaxRowsMax * 33) * sizeof(int)));
+    DJ_CUDA_CHECK(cudaMemset(R.tickets, 0, (kAttnTickets + kArgmaxRowsMax * 33) * sizeof(int)));
     DJ_CUDA_CHECK(cudaMalloc((void**)&g_dev_error, sizeof(int)));
     DJ_CUDA_CHECK(cudaMemset(g_dev_error, 0, sizeof(int)));
     R.inited = true;
@@ -368,7 +370,7 @@ void do_op(Ctx& ctx, const int32_t* c) {
         case DEEPJ_OP_ARGMAX_ROWS: {
             int rows = c[3], cols = c[4]; require(rows >= 0 && cols >= 1, "argmaxRows", "bad dimension");
             const float* a = f32(ctx, c[1], sz(rows, cols), "argmaxRows"); float* o = f32(ctx, c[2], rows, "argmaxRows");
-            if (go) launch_argmax_rows(a, o, rows, cols, s);
+            if (go) launch_argmax_rows(a, o, rows, cols, R.tickets + kAttnTickets + kArgmaxRowsMax, R.tickets + kAttnTickets, s);
             break;
         }
         case DEEPJ_OP_SAMPLE_TOPK: {     // [op, logits, r, out, rows, cols, topK, temperatureBits]

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 import oracle
-from deepj_b200.compute_graph import OP_SAMPLE_TOPK, float_bits
+from deepj_b200.compute_graph import OP_ARGMAX_ROWS, OP_SAMPLE_TOPK, float_bits
 from deepj_b200.decoder import DecoderConfig, Q8Decoder
 from test_decoder_gpu import weight_getter
 from test_q8_gpu import Dev
@@ -35,6 +35,25 @@ def test_sample_topk_matches_oracle(dev, V, top_k, temperature):
     got = dev.get(ob, rows).astype(np.int64)
     want = np.asarray([oracle.sample_topk(logits[i], temperature, top_k, float(r[i])) for i in range(rows)])
     assert np.array_equal(got, want), (got, want)
+
+
+@pytest.mark.parametrize("V", [7, 1000, 4096, 32000, 50257])
+def test_argmax_rows_is_the_first_index_of_a_stable_descending_sort(dev, V):
+    """Greedy pick (TextGenerator with topK = 1): lowest index among equal maxima, −0.0 below +0.0, NaN above
+    everything — also when the row is reduced by several CTAs (long rows) and the maxima sit in different slices."""
+    rng = np.random.default_rng(V)
+    rows = 5
+    x = rng.standard_normal((rows, V)).astype(np.float32)
+    x[1, :] = 0.5                                                        # all equal → index 0
+    x[2, V - 1] = 9.0; x[2, V // 2] = 9.0; x[2, 3] = 9.0                 # equal maxima in different slices → index 3
+    x[3, :] = -1.0; x[3, V - 2] = -0.0; x[3, V // 3] = 0.0               # +0.0 beats −0.0
+    x[4, V // 2 + 1] = np.nan                                            # NaN sorts above +inf
+    xb, ob = dev.buf(rows * V, x), dev.buf(rows)
+    dev.flush([OP_ARGMAX_ROWS, xb, ob, rows, V])
+    got = dev.get(ob, rows).astype(np.int64)
+    want = np.asarray([oracle.greedy_pick(x[i]) for i in range(rows)])
+    assert np.array_equal(got, want), (got, want)
+    assert list(got[1:]) == [0, 3, V // 3, V // 2 + 1]
 
 
 def test_sampler_rejects_what_it_does_not_cover(dev):
