@@ -74,6 +74,20 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def wait_ready(self, timeout_s: float = 3.0):
+        """nvidia-smi takes a moment to come up (longer on a box with many GPUs): hold the timed region back until
+        its first sample is in the file."""
+        if self.proc is None:
+            return
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < timeout_s:
+            try:
+                if os.path.getsize(self.tmp.name) > 0:
+                    return
+            except OSError:
+                return
+            time.sleep(0.02)
+
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
@@ -240,6 +254,7 @@ def main():
     ctx0 = dec.position
     sampler = ClockSampler(local_rank)
     sampler.start()
+    sampler.wait_ready()
     _lib.check(lib.deepj_cuda_synchronize())
     if world > 1:
         tp.barrier()
