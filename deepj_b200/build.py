@@ -44,10 +44,19 @@ def _newer(target: str, sources: list[str]) -> bool:
     return all(os.path.getmtime(s) <= t for s in sources)
 
 
+def _jni_includes() -> list[str]:
+    """Include paths of the JDK named by JAVA_HOME; with them csrc/jni_shim.cpp adds the JNI natives."""
+    home = os.environ.get("JAVA_HOME", "")
+    inc = os.path.join(home, "include")
+    if not home or not os.path.exists(os.path.join(inc, "jni.h")):
+        return []
+    return ["-I", inc, "-I", os.path.join(inc, "linux")]
+
+
 def _compile(src: str, obj: str, headers: list[str], verbose: bool) -> str:
     if _newer(obj, [src] + headers):
         return ""
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-c", src, "-o", obj]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), *_jni_includes(), "-c", src, "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{res.stdout}\n{res.stderr}")
