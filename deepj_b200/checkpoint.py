@@ -8,7 +8,9 @@ the attention matrices, `gate.W, gate.b, up.W, up.b, down.W, down.b`
 (blocks/LlamaTransformerBlock.java:45-47, SwiGLULayer.java:91-97, Linear.java:54-56); the
 final norm's gamma; `lmHead.W, lmHead.b`.  Attention matrices: `Wq, Wk, Wv, Wo`
 (MultiHeadSelfAttention.java:256-258) or, for DeepSeek blocks, `Wdq, Wuq, Wdkv, Wuk, Wuv, Wo`
-(MultiHeadLatentAttention.java:174-176).
+(MultiHeadLatentAttention.java:174-176).  A GPT model (`kind="gpt"`) adds the position table after the token
+embedding, has `gamma, beta` per LayerNorm, and `W1, c1, W2, c2` for its MLP (models/gpt/GPTModel.java:63-67,
+blocks/GPTTransformerBlock.java:61-63, norm/LayerNorm1D.java:80-82, layers/FNN.java:110-114).
 
 `read_parameters` parses the file, `named_parameters` checks the shapes against a
 `DecoderConfig` and names them the way `Q8Decoder.load_weights` asks for them, and
@@ -73,6 +75,15 @@ def parameter_layout(cfg: DecoderConfig) -> List[Tuple[str, int, Tuple[int, int]
     """(name, layer, shape) of every parameter in `parameters()` order; layer −1 = not in a block."""
     d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
     out: List[Tuple[str, int, Tuple[int, int]]] = [("emb", -1, (V, d))]
+    if cfg.kind == "gpt":
+        # GPTModel.embeddingParameters (models/gpt/GPTModel.java:63-67), GPTTransformerBlock.subLayers
+        # (ln1, ln2, attn, mlp), LayerNorm1D.parameters (gamma, beta), FNN.parameters (W, b per Linear)
+        out.append(("pos", -1, (cfg.max_seq_len, d)))
+        for l in range(cfg.n_layers):
+            out += [("g1", l, (1, d)), ("b1", l, (1, d)), ("g2", l, (1, d)), ("b2", l, (1, d))]
+            out += [(n, l, (d, d)) for n in ("Wq", "Wk", "Wv", "Wo")]
+            out += [("W1", l, (d, F)), ("c1", l, (1, F)), ("W2", l, (F, d)), ("c2", l, (1, d))]
+        return out + [("gF", -1, (1, d)), ("bF", -1, (1, d)), ("Wlm", -1, (d, V)), ("blm", -1, (1, V))]
     if cfg.kind == "llama":
         attn = [("Wq", (d, d)), ("Wk", (d, d)), ("Wv", (d, d)), ("Wo", (d, d))]
     else:
@@ -106,5 +117,5 @@ def weight_getter(cfg: DecoderConfig, source: Union[PathLike, List[np.ndarray]])
 
     def get(name: str, layer: int) -> np.ndarray:
         a = named[(name, layer if (name, layer) in named else -1)]
-        return a.reshape(-1) if a.shape[0] == 1 and name[0] in "gb" else a
+        return a.reshape(-1) if a.shape[0] == 1 and name[0] in "gbc" else a
     return get

@@ -76,9 +76,16 @@ struct Q8LinearArgs {
     float* out; int ldo;
     int M;
     float* ws = nullptr; int* tickets = nullptr;    // workspace (q8_batch_ws_floats) and counters for the batched kernel (M ≥ 3)
+    // GPT blocks: beta != nullptr turns the fused norm into LayerNorm1D (mean and biased variance, γ and β);
+    // act == 1 applies GELU after the bias.  The GEMV fuses both; the many-row kernels get them from a
+    // normalising pass into ln_ws ([M × K] floats) before and an activation pass over `out` after.
+    const float* beta = nullptr; int act = 0; float* ln_ws = nullptr;
 };
 void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s);
 bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s);
+bool q8_tma_fuses_gpt(const Q8LinearArgs& a);     // true when launch_q8_linear_tma can take beta / act itself
+void launch_layernorm_rows(const float* x, int ldx, const float* gamma, const float* beta, float eps, float* out, int K, int M, cudaStream_t s);
+void launch_gelu_rows(float* buf, int ld, int N, int M, cudaStream_t s);
 bool launch_q8_linear_batch(const Q8LinearArgs& a, int m0, int rows, float* ws, int* tickets, cudaStream_t s);
 size_t q8_batch_ws_floats(int K, int N, bool swiglu);
 bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s);

@@ -13,6 +13,7 @@
 // through shuffles and a double-buffered shared-memory slot.  RMSNorm is fused
 // into the activation load, bias / residual / SiLU-gate into the epilogue.
 #include "kernels.h"
+#include "q8_common.cuh"
 #include <cuda_fp16.h>
 
 namespace dj {
@@ -266,7 +267,80 @@ void launch_q8_quantize(const float* src, int src_ld, int K, int n_cols, int8_t*
     launch_k(k_q8_quantize, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, s, false, src, src_ld, K, n_cols, codes, scales, Kp, nb);
 }
 
-void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
+namespace {
+
+// LayerNorm1D.forward row by row (norm/LayerNorm1D.java:34-71 over CpuBackend.meanAlongRows /
+// varianceAlongRows, tensor/cpu/CpuBackend.java:242-268): one CTA per row, two block reductions.
+__global__ void __launch_bounds__(256) k_layernorm_rows(const float* __restrict__ x, int ldx, const float* __restrict__ gamma,
+                                                        const float* __restrict__ beta, float eps, float* __restrict__ out, int K) {
+    __shared__ float red[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* row = x + (size_t)blockIdx.x * ldx;
+    float* o = out + (size_t)blockIdx.x * K;
+    auto block_sum = [&](float v) {
+        for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+        __syncthreads();
+        if (lane == 0) red[warp] = v;
+        __syncthreads();
+        float t = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 8; q++) t += red[q];
+        return t;
+    };
+    float sm = 0.0f;
+    for (int k = tid; k < K; k += 256) sm += row[k];
+    const float mean = block_sum(sm) * (1.0f / (float)K);
+    float ss = 0.0f;
+    for (int k = tid; k < K; k += 256) { const float d = row[k] - mean; ss = fmaf(d, d, ss); }
+    const float stdv = sqrtf(block_sum(ss) * (1.0f / (float)K) + eps);
+    for (int k = tid; k < K; k += 256) o[k] = __fdiv_rn(row[k] - mean, stdv) * gamma[k] + beta[k];
+}
+
+__global__ void k_gelu_rows(float* __restrict__ buf, int ld, int N, long long total) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float* p = buf + (size_t)(i / N) * ld + (i % N);
+    *p = gelu_ref(*p);
+}
+
+}  // namespace
+
+void launch_layernorm_rows(const float* x, int ldx, const float* gamma, const float* beta, float eps, float* out, int K, int M, cudaStream_t s) {
+    if (M <= 0 || K <= 0) return;
+    launch_k(k_layernorm_rows, dim3(M), dim3(256), 0, s, false, x, ldx, gamma, beta, eps, out, K);
+}
+
+void launch_gelu_rows(float* buf, int ld, int N, int M, cudaStream_t s) {
+    const long long total = (long long)M * N;
+    if (total <= 0) return;
+    launch_k(k_gelu_rows, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, false, buf, ld, N, total);
+}
+
+namespace {
+void dispatch_q8_linear(const Q8LinearArgs& a, cudaStream_t s);
+}
+
+void launch_q8_linear(const Q8LinearArgs& a0, cudaStream_t s) {
+    if (a0.M <= 0 || a0.w.N <= 0) return;
+    if (a0.beta == nullptr && a0.act == 0) { dispatch_q8_linear(a0, s); return; }
+    // GPT blocks: up to four rows go through the GEMV, which takes LayerNorm and GELU itself; the many-row
+    // kernels see already normalised rows and get the activation applied to their output afterwards
+    if (g_gemv_mode == 2 && a0.M < 5 && q8_tma_fuses_gpt(a0)) { dispatch_q8_linear(a0, s); return; }
+    Q8LinearArgs a = a0;
+    if (a.beta != nullptr) {
+        if (a.ln_ws == nullptr) throw std::runtime_error("Q8 linear: LayerNorm needs its workspace");
+        launch_layernorm_rows(a.x, a.ldx, a.gamma, a.beta, a.eps, a.ln_ws, a.w.K, a.M, s);
+        a.x = a.ln_ws; a.ldx = a.w.K; a.gamma = nullptr; a.beta = nullptr;
+    }
+    a.act = 0;
+    dispatch_q8_linear(a, s);
+    if (a0.act == 1) launch_gelu_rows(a.out, a.ldo, a.w.N, a.M, s);
+}
+
+namespace {
+
+void dispatch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
+
     if (a.M <= 0 || a.w.N <= 0) return;
     GemvParams p;
     p.x = a.x; p.ldx = a.ldx; p.gamma = a.gamma; p.eps = a.eps;
@@ -288,5 +362,7 @@ void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
     if (swiglu) launch_gemv_dispatch<true>(p, a.M, s);
     else launch_gemv_dispatch<false>(p, a.M, s);
 }
+
+}  // namespace
 
 }  // namespace dj

@@ -25,6 +25,15 @@ __device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t 
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// GELU as the reference's CPU backend computes it (tensor/cpu/CpuBackend.java:338-343): the tanh
+// form in fp32 with the square root and tanh evaluated in double and rounded.
+__device__ __forceinline__ float gelu_ref(float x) {
+    const float c = (float)sqrt((double)(2.0f / 3.14159274101257324f));
+    const float x3 = x * x * x;
+    const float t = c * (x + 0.044715f * x3);
+    return 0.5f * x * (1.0f + (float)tanh((double)t));
+}
+
 __device__ __forceinline__ void load16(const float* src, bool vec, float (&v)[16]) {
     if (vec) {
 #pragma unroll

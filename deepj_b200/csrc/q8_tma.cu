@@ -62,6 +62,7 @@ constexpr int kColsPerRow = 3;              // digit columns per activation row 
 struct TmaParams {
     const float* x; int ldx;
     const float* gamma; float eps;
+    const float* beta; int act;     // GPT instantiation only: LayerNorm shift (null = RMSNorm / none) and 1 = GELU after the bias
     const int8_t* codes; const float* scales; const float* bias;
     const int8_t* codes2; const float* scales2; const float* bias2;
     const float* residual; int ldr;
@@ -75,7 +76,9 @@ struct TmaParams {
 
 constexpr int kStageRounds = 3;             // rows of up to 3·256·16 = 12288 values are staged from registers
 
-template <bool SWIGLU, int DEPTH>
+// GPT = true adds LayerNorm1D (norm/LayerNorm1D.java:34-71: mean, biased variance, (x − mean)/√(var + eps)·γ + β)
+// to the staging and GELU to the epilogue; the Llama / DeepSeek instantiation carries neither.
+template <bool SWIGLU, int DEPTH, bool GPT>
 __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     // layout: rings [warps][DEPTH][kSlotBytes], digits int8 [3M][K+pad], block scales fp32 [M][K/32], partials [2][warps][16][8]
@@ -159,7 +162,8 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     // row are loaded before anything is converted, so a row costs one load round trip.
     for (int m = 0; m < p.M; m++) {
         const float* xrow = p.x + (size_t)m * p.ldx;
-        const bool vec = ((reinterpret_cast<uintptr_t>(xrow) | (p.gamma ? reinterpret_cast<uintptr_t>(p.gamma) : 0)) & 15) == 0;
+        bool vec = ((reinterpret_cast<uintptr_t>(xrow) | (p.gamma ? reinterpret_cast<uintptr_t>(p.gamma) : 0)) & 15) == 0;
+        if (GPT && p.beta) vec = vec && (reinterpret_cast<uintptr_t>(p.beta) & 15) == 0;
         int8_t* dcol = xd + (size_t)(kColsPerRow * m) * ldxs;
         float* xscRow = xsc + (size_t)m * nBlocks;
         if (rounds <= kStageRounds) {
@@ -177,7 +181,38 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
                 for (int d = kPre; d < kMid; d++) issue_next();      // more of the ring behind the activation loads
             }
             float inv = 1.0f;
-            if (p.gamma) {
+            const bool layerNorm = GPT && p.gamma && p.beta;
+            if (layerNorm) {
+                // padding lanes hold zeros: they add nothing to the sum, and are masked out of the squared deviations
+                float sm = 0.0f;
+#pragma unroll
+                for (int r = 0; r < kStageRounds; r++)
+#pragma unroll
+                    for (int j = 0; j < 16; j++) sm += xv[r][j];
+                for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+                __syncthreads();
+                if (lane == 0) s_red[warp] = sm;
+                __syncthreads();
+                sm = 0.0f;
+#pragma unroll
+                for (int q = 0; q < kWarps; q++) sm += s_red[q];
+                const float mean = sm * (1.0f / (float)p.K);
+                float ss = 0.0f;
+#pragma unroll
+                for (int r = 0; r < kStageRounds; r++) {
+                    const bool on = r < rounds && r * kThreads + tid < nHalf;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) { xv[r][j] = on ? xv[r][j] - mean : 0.0f; ss = fmaf(xv[r][j], xv[r][j], ss); }
+                }
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                __syncthreads();
+                if (lane == 0) s_red[warp] = ss;
+                __syncthreads();
+                ss = 0.0f;
+#pragma unroll
+                for (int q = 0; q < kWarps; q++) ss += s_red[q];
+                inv = __frcp_rn(sqrtf(ss * (1.0f / (float)p.K) + p.eps));
+            } else if (p.gamma) {
                 float ss = 0.0f;
 #pragma unroll
                 for (int r = 0; r < kStageRounds; r++)
@@ -208,6 +243,11 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
                     }
 #pragma unroll
                     for (int j = 0; j < 16; j++) xv[r][j] = (xv[r][j] * inv) * gv[j];
+                    if (layerNorm && on) {
+                        load16(p.beta + hb * 16, vec, gv);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) xv[r][j] += gv[j];
+                    }
                 }
                 if (r < rounds) digits16(xv[r], on, dcol, ldxs, hb, xscRow);
             }
@@ -328,6 +368,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
                 p.out[(size_t)em * p.ldo + en] = (v * sig) * u;          // SiLU(gate) ⊙ up
             } else {
                 if (p.bias) v += ebias;
+                if (GPT && p.act == 1) v = gelu_ref(v);
                 if (p.residual) v += eres;
                 p.out[(size_t)em * p.ldo + en] = v;
             }
@@ -344,11 +385,11 @@ size_t i8_smem_bytes(int K, int M, int depth) {
            (size_t)2 * kWarps * 128 * 4;
 }
 
-template <bool SWIGLU, int DEPTH>
+template <bool SWIGLU, int DEPTH, bool GPT>
 void launch_i8(const TmaParams& p, cudaStream_t s) {
     static bool attrSet = false;
     if (!attrSet) {
-        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemv_i8<SWIGLU, DEPTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
+        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemv_i8<SWIGLU, DEPTH, GPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
         attrSet = true;
     }
     int rowsPerTile = SWIGLU ? 8 : 16;
@@ -360,19 +401,19 @@ void launch_i8(const TmaParams& p, cudaStream_t s) {
     int gx = (nTiles + rounds - 1) / rounds;
     static const bool evenGrid = getenv("DEEPJ_CUDA_GEMV_FULLGRID") == nullptr;
     if (!evenGrid) gx = nTiles < cap ? nTiles : cap;
-    launch_k(k_q8_gemv_i8<SWIGLU, DEPTH>, dim3(gx), dim3(kThreads), i8_smem_bytes(p.K, p.M, DEPTH), s, true, p);
+    launch_k(k_q8_gemv_i8<SWIGLU, DEPTH, GPT>, dim3(gx), dim3(kThreads), i8_smem_bytes(p.K, p.M, DEPTH), s, true, p);
 }
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool GPT>
 void launch_i8_depth(const TmaParams& p, int depth, cudaStream_t s) {
     switch (depth) {
-        case 3: launch_i8<SWIGLU, 3>(p, s); break;
-        case 4: launch_i8<SWIGLU, 4>(p, s); break;
-        case 5: launch_i8<SWIGLU, 5>(p, s); break;
-        case 6: launch_i8<SWIGLU, 6>(p, s); break;
-        case 7: launch_i8<SWIGLU, 7>(p, s); break;
-        case 8: launch_i8<SWIGLU, 8>(p, s); break;
-        default: launch_i8<SWIGLU, 9>(p, s); break;
+        case 3: launch_i8<SWIGLU, 3, GPT>(p, s); break;
+        case 4: launch_i8<SWIGLU, 4, GPT>(p, s); break;
+        case 5: launch_i8<SWIGLU, 5, GPT>(p, s); break;
+        case 6: launch_i8<SWIGLU, 6, GPT>(p, s); break;
+        case 7: launch_i8<SWIGLU, 7, GPT>(p, s); break;
+        case 8: launch_i8<SWIGLU, 8, GPT>(p, s); break;
+        default: launch_i8<SWIGLU, 9, GPT>(p, s); break;
     }
 }
 
@@ -381,10 +422,19 @@ void launch_i8_depth(const TmaParams& p, int depth, cudaStream_t s) {
 // Returns false when the shape is outside this kernel's domain (the caller falls
 // back to the FMA kernel).  Two CTAs share an SM, so a CTA may use half of its
 // shared memory: the ring takes what the activation digits leave.
+bool q8_tma_fuses_gpt(const Q8LinearArgs& a) {
+    const int K = a.w.K;
+    if (K % 32 != 0 || a.w.Kp != K || a.w2.codes != nullptr) return false;
+    if (i8_smem_bytes(K, 1, 3) > 111 * 1024) return false;
+    return (K >> 4) <= kStageRounds * kThreads;      // LayerNorm lives in the register staging path only
+}
+
 bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s) {
     const int K = a.w.K;
     if (K % 32 != 0 || a.w.Kp != K) return false;
     const bool swiglu = a.w2.codes != nullptr;
+    const bool gpt = a.beta != nullptr || a.act != 0;
+    if (gpt && !q8_tma_fuses_gpt(a)) return false;
     const size_t budget = 111 * 1024;
     if (i8_smem_bytes(K, 1, 3) > budget) return false;
     for (int m0 = 0; m0 < a.M;) {
@@ -396,6 +446,7 @@ bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s) {
         while (depth > 3 && i8_smem_bytes(K, rows, depth) > budget) depth--;
         TmaParams p;
         p.x = a.x + (size_t)m0 * a.ldx; p.ldx = a.ldx; p.gamma = a.gamma; p.eps = a.eps;
+        p.beta = a.beta; p.act = a.act;
         p.codes = a.w.codes; p.scales = a.w.scales; p.bias = a.bias;
         p.codes2 = a.w2.codes; p.scales2 = a.w2.scales; p.bias2 = a.bias2;
         p.residual = a.residual ? a.residual + (size_t)m0 * a.ldr : nullptr; p.ldr = a.ldr;
@@ -406,7 +457,9 @@ bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s) {
         static const int mid = getenv("DEEPJ_CUDA_GEMV_MID") ? atoi(getenv("DEEPJ_CUDA_GEMV_MID")) : 4;
         p.mid = mid;
         p.trace = trace_slot();
-        if (swiglu) launch_i8_depth<true>(p, depth, s); else launch_i8_depth<false>(p, depth, s);
+        if (swiglu) launch_i8_depth<true, false>(p, depth, s);
+        else if (gpt) launch_i8_depth<false, true>(p, depth, s);
+        else launch_i8_depth<false, false>(p, depth, s);
         m0 += rows;
     }
     return true;

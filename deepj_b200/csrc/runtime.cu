@@ -156,6 +156,7 @@ int op_stride(int op) {
         case 20: return 13;
         case DEEPJ_OP_EMBED_GATHER: return 7;
         case DEEPJ_OP_Q8_LINEAR: return 15;
+        case DEEPJ_OP_Q8_LINEAR_LN: return 17;
         case DEEPJ_OP_Q8_SWIGLU: return 14;
         case DEEPJ_OP_ATTN_DECODE: return 17;
         case DEEPJ_OP_ATTN_PREFILL: return 18;
@@ -280,29 +281,46 @@ void do_op(Ctx& ctx, const int32_t* c) {
             if (go) launch_embed_gather(table, ids, o, rows, d, vocab, s);
             break;
         }
-        case DEEPJ_OP_Q8_LINEAR: {
-            // [op, x, x_off, ldx, gamma, epsBits, w, bias, residual, res_off, ldr, out, out_off, ldo, M]
-            int x_off = c[2], ldx = c[3], res_off = c[9], ldr = c[10], out_off = c[12], ldo = c[13], M = c[14];
-            Buf& wb = find_buf(ctx, c[6], kQ8, "q8Linear");
+        case DEEPJ_OP_Q8_LINEAR:
+        case DEEPJ_OP_Q8_LINEAR_LN: {
+            // 65: [op, x, x_off, ldx, gamma, epsBits, w, bias, residual, res_off, ldr, out, out_off, ldo, M]
+            // 75: [op, x, x_off, ldx, gamma, beta, epsBits, w, bias, residual, res_off, ldr, out, out_off, ldo, M, act]
+            const bool ln = op == DEEPJ_OP_Q8_LINEAR_LN;
+            const int32_t* e = ln ? c + 1 : c;          // fields from epsBits on sit one slot later in op 75
+            int x_off = c[2], ldx = c[3], res_off = e[9], ldr = e[10], out_off = e[12], ldo = e[13], M = e[14];
+            Buf& wb = find_buf(ctx, e[6], kQ8, "q8Linear");
             require(M >= 1 && x_off >= 0 && out_off >= 0 && res_off >= 0, "q8Linear", "bad M or offset");
             require(ldx >= wb.K && ldo >= wb.N, "q8Linear", "row stride smaller than the row");
             Q8LinearArgs a = {};
             a.x = f32(ctx, c[1], (size_t)x_off + sz(M - 1, ldx) + wb.K, "q8Linear") + x_off; a.ldx = ldx;
-            a.gamma = f32_opt(ctx, c[4], wb.K, "q8Linear"); a.eps = bits_to_float(c[5]);
+            a.gamma = f32_opt(ctx, c[4], wb.K, "q8Linear"); a.eps = bits_to_float(e[5]);
             a.w = q8view(wb);
-            a.bias = f32_opt(ctx, c[7], wb.N, "q8Linear");
-            if (c[8] >= 0) {
+            a.bias = f32_opt(ctx, e[7], wb.N, "q8Linear");
+            if (e[8] >= 0) {
                 require(ldr >= wb.N, "q8Linear", "residual stride smaller than the row");
-                a.residual = f32(ctx, c[8], (size_t)res_off + sz(M - 1, ldr) + wb.N, "q8Linear") + res_off; a.ldr = ldr;
+                a.residual = f32(ctx, e[8], (size_t)res_off + sz(M - 1, ldr) + wb.N, "q8Linear") + res_off; a.ldr = ldr;
             }
-            a.out = f32(ctx, c[11], (size_t)out_off + sz(M - 1, ldo) + wb.N, "q8Linear") + out_off; a.ldo = ldo;
+            a.out = f32(ctx, e[11], (size_t)out_off + sz(M - 1, ldo) + wb.N, "q8Linear") + out_off; a.ldo = ldo;
             a.M = M;
+            size_t need = 0;
             if (M >= 3) {
-                size_t need = q8_batch_ws_floats(wb.K, wb.N, false);
+                need = q8_batch_ws_floats(wb.K, wb.N, false);
                 if (M >= kTcMinRows) need = std::max(need, q8_tc_ws_floats(M, wb.K));
-                if (need > ctx.ws_need) ctx.ws_need = need;
                 a.ws = R.ws; a.tickets = R.tickets;
             }
+            if (ln) {
+                a.act = c[16];
+                require(a.act == 0 || a.act == 1, "q8LinearLN", "activation must be 0 (none) or 1 (GELU)");
+                require(a.act == 0 || a.residual == nullptr, "q8LinearLN", "an activation and a residual cannot be combined");
+                a.beta = f32_opt(ctx, c[5], wb.K, "q8LinearLN");
+                require((a.beta == nullptr) == (a.gamma == nullptr), "q8LinearLN", "LayerNorm needs both gamma and beta (or neither)");
+                if (a.beta != nullptr) {             // room for the normalised rows when the kernel chosen cannot fuse the norm
+                    need = (need + 31) & ~(size_t)31;      // 128-byte aligned rows for the vector loads that follow
+                    a.ln_ws = R.ws + need;
+                    need += sz(M, wb.K);
+                }
+            }
+            if (need > ctx.ws_need) ctx.ws_need = need;
             if (go) launch_q8_linear(a, s);
             break;
         }

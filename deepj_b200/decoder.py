@@ -1,4 +1,4 @@
-"""Q8 decoder runner: DeepJ's LlamaModel / DeepSeekModel forward for ONE new token per
+"""Q8 decoder runner: DeepJ's LlamaModel / DeepSeekModel / GPTModel forward for ONE new token per
 sequence, recorded as a ComputeGraph command stream of fused decode ops and replayed
 through `deepj_cuda_flush_ops` (one flush per token; the library turns the repeated
 stream into a CUDA graph).
@@ -10,6 +10,12 @@ per block `x2 = x + attn(rmsnorm(x)); x = x2 + swiglu(rmsnorm(x2))`
 DeepSeekTransformerBlock.java:54-57) → final RMSNorm → LM head, then the greedy pick
 of models/TextGenerator.java (topK = 1).  K and V of earlier positions come from a
 cache in HBM instead of being recomputed.
+
+`kind="gpt"` records the GPT family instead (models/gpt/GPTModel.java:52-54,
+blocks/GPTTransformerBlock.java:66-74): token + learned position embedding, per block
+`x2 = x + attn(layernorm(x)); x = x2 + W2·gelu(W1·layernorm(x2) + c1) + c2` with plain
+(un-rotated) causal attention, a final LayerNorm and the LM head.  LayerNorm and GELU are
+fused into the Q8 projections (op 75); the attention op runs with an identity rotation table.
 """
 from __future__ import annotations
 
@@ -21,17 +27,18 @@ from typing import Tuple, Callable, Dict, List, Optional
 import numpy as np
 
 from . import _lib
-from .compute_graph import (OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_ATTN_PREFILL, OP_COPY, OP_EMBED_GATHER, OP_SAMPLE_TOPK,
+from .compute_graph import (OP_ADD, OP_Q8_LINEAR_LN, OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_ATTN_PREFILL, OP_COPY, OP_EMBED_GATHER, OP_SAMPLE_TOPK,
                             OP_Q8_LINEAR, OP_Q8_SWIGLU, OP_TP_ALLGATHER, OP_TP_ALLREDUCE, float_bits)
 
 RMS_EPS = 1e-6      # layers/transformer/norm/RMSNorm1D.java:30
+LN_EPS = 1e-5       # layers/transformer/norm/LayerNorm1D.java (EPS)
 
 
 @dataclass(frozen=True)
 class DecoderConfig:
     """Field-for-field the reference's LlamaConfig / DeepSeekConfig records
     (models/llama/LlamaConfig.java:10-22, models/deepseek/DeepSeekConfig.java)."""
-    kind: str            # "llama" | "deepseek"
+    kind: str            # "llama" | "deepseek" | "gpt"
     vocab_size: int
     max_seq_len: int
     d_model: int
@@ -43,8 +50,8 @@ class DecoderConfig:
 
     def __post_init__(self):
         # models/TransformerConfig.java:19-31
-        if self.kind not in ("llama", "deepseek"):
-            raise ValueError("kind must be 'llama' or 'deepseek'")
+        if self.kind not in ("llama", "deepseek", "gpt"):
+            raise ValueError("kind must be 'llama', 'deepseek' or 'gpt'")
         for name in ("vocab_size", "max_seq_len", "d_model", "n_heads", "n_layers", "d_ff"):
             if getattr(self, name) <= 0:
                 raise ValueError(f"{name} must be > 0")
@@ -64,11 +71,13 @@ class DecoderConfig:
         construction order (MultiHeadSelfAttention.java:47-50,
         MultiHeadLatentAttention.java:82-87, SwiGLULayer.java:56-58)."""
         d, f = self.d_model, self.d_ff
-        if self.kind == "llama":
+        if self.kind in ("llama", "gpt"):
             attn = [("Wq", d, d), ("Wk", d, d), ("Wv", d, d), ("Wo", d, d)]
         else:
             attn = [("Wdq", d, self.q_rank), ("Wuq", self.q_rank, d), ("Wdkv", d, self.kv_rank),
                     ("Wuk", self.kv_rank, d), ("Wuv", self.kv_rank, d), ("Wo", d, d)]
+        if self.kind == "gpt":
+            return attn + [("W1", d, f), ("W2", f, d)]          # layers/FNN.java: one hidden layer
         return attn + [("Wg", d, f), ("Wu", d, f), ("Wd", f, d)]
 
     def q8_weight_bytes(self) -> int:
@@ -111,6 +120,11 @@ def shard_plan(cfg: DecoderConfig, rank: int, world: int) -> List[tuple]:
     32-element Q8 block boundary.  MLA's low-rank down-projections are replicated."""
     c, r = cfg, rank
     d, dl, Fl = c.d_model, c.d_model // world, c.d_ff // world
+    if c.kind == "gpt":
+        if world != 1:
+            raise ValueError("the GPT stream runs on one GPU")
+        return [("Wqkv", d, [("Wq", 0, 0, d), ("Wk", 0, 0, d), ("Wv", 0, 0, d)]), ("Wo", d, [("Wo", 0, 0, d)]),
+                ("W1", d, [("W1", 0, 0, c.d_ff)]), ("W2", c.d_ff, [("W2", 0, 0, d)])]
     if c.kind == "llama":
         plan = [("Wqkv", d, [("Wq", 0, r * dl, dl), ("Wk", 0, r * dl, dl), ("Wv", 0, r * dl, dl)])]
     else:
@@ -134,6 +148,8 @@ class Q8Decoder:
         self.B = int(batch)
         if tp_world < 1 or not (0 <= tp_rank < tp_world):
             raise ValueError("bad tensor-parallel rank / world size")
+        if tp_world > 1 and cfg.kind == "gpt":
+            raise ValueError("the GPT stream runs on one GPU")
         if tp_world > 1 and (cfg.n_heads % tp_world or cfg.d_ff % tp_world or cfg.vocab_size % tp_world or
                              (cfg.d_ff // tp_world) % 32 or (cfg.d_model // tp_world) % 32):
             raise ValueError("heads, dFF and vocab must divide by the tensor-parallel size, on 32-element block boundaries")
@@ -197,7 +213,13 @@ class Q8Decoder:
     def _alloc_state(self) -> None:
         c, B = self.cfg, self.B
         d = c.d_model
-        cos, sin = rope_tables(c.head_dim, c.max_seq_len)
+        if c.kind == "gpt":
+            # no rotary embedding: cos 1 / sin 0 make the attention op's rotation the identity
+            half = c.head_dim // 2
+            cos, sin = np.ones((c.max_seq_len, half), dtype=np.float32), np.zeros((c.max_seq_len, half), dtype=np.float32)
+            self._f32("xp", B * d)       # the positional-embedding rows of the current tokens
+        else:
+            cos, sin = rope_tables(c.head_dim, c.max_seq_len)
         self._f32("cos", cos.size, cos)
         self._f32("sin", sin.size, sin)
         self._f32("tok", B)              # current token ids (floats holding ints)
@@ -259,10 +281,16 @@ class Q8Decoder:
             self._f32(f"g2.{l}", c.d_model, vec("g2", l, c.d_model))
             for obj, K, parts in self._shard_plan():
                 self._q8_from_parts(f"{obj}.{l}", K, parts, fill_layer(l))
+            if c.kind == "gpt":
+                for name, n in (("b1", c.d_model), ("b2", c.d_model), ("c1", c.d_ff), ("c2", c.d_model)):
+                    self._f32(f"{name}.{l}", n, vec(name, l, n))
+                continue
             self._f32(f"bg.{l}", Fl, vec("bg", l, c.d_ff)[r * Fl:(r + 1) * Fl])
             self._f32(f"bu.{l}", Fl, vec("bu", l, c.d_ff)[r * Fl:(r + 1) * Fl])
             self._f32(f"bd.{l}", c.d_model, vec("bd", l, c.d_model))
         self._f32("gF", c.d_model, vec("gF", -1, c.d_model))
+        if c.kind == "gpt":
+            self._f32("bF", c.d_model, vec("bF", -1, c.d_model))
         self._q8_from_parts("Wlm", c.d_model, [("Wlm", 0, r * Vl, Vl)], fill_layer(-1))
         self._f32("blm", Vl, vec("blm", -1, c.vocab_size)[r * Vl:(r + 1) * Vl])
         self.loaded = True
@@ -278,6 +306,8 @@ class Q8Decoder:
         """
         c = self.cfg
         self._f32("emb", c.vocab_size * c.d_model, get("emb", -1))
+        if c.kind == "gpt":
+            self._f32("posemb", c.max_seq_len * c.d_model, get("pos", -1))
         self._load(lambda l: (lambda ref, tmp: self._upload(tmp, get(ref, l))),
                    lambda name, l, n: np.asarray(get(name, l), dtype=np.float32).reshape(-1))
 
@@ -299,6 +329,9 @@ class Q8Decoder:
 
         emb = self._f32("emb", c.vocab_size * c.d_model)
         _lib.check(self.lib.deepj_cuda_synth_fill(emb, seed, 0, std, 0, c.vocab_size * c.d_model))
+        if c.kind == "gpt":
+            pos = self._f32("posemb", c.max_seq_len * c.d_model)
+            _lib.check(self.lib.deepj_cuda_synth_fill(pos, seed, 2 + c.n_layers * len(per_layer), std, 0, c.max_seq_len * c.d_model))
         self._load(fill_layer, lambda name, l, n: (np.ones(n, dtype=np.float32) if name.startswith("g") else np.zeros(n, dtype=np.float32)))
 
     def q8_arrays(self, name: str):
@@ -333,7 +366,11 @@ class Q8Decoder:
             op(label, OP_Q8_LINEAR, x, x_off, ldx, gamma, eps, w, bias, res, res_off, ldr, out, out_off, ldo, B)
 
         op("embed", OP_EMBED_GATHER, I["emb"], I["tok"], I["x"], B, d, V)
-        for l in range(c.n_layers):
+        if c.kind == "gpt":
+            self._gpt_blocks(op, I["x"], I["x2"], I["xp"], I["qkv"], I["att"], I["h"], I["pos"], B, 1)
+            op("lm_head", OP_Q8_LINEAR_LN, I["x"], 0, d, I["gF"], I["bF"], float_bits(LN_EPS), I["Wlm"], I["blm"], -1, 0, 0,
+               I["logits"], 0, V, B, 0)
+        for l in range(c.n_layers if c.kind != "gpt" else 0):
             if c.kind == "llama":
                 linear("qkv", I["x"], 0, d, I[f"g1.{l}"], I[f"Wqkv.{l}"], -1, -1, 0, 0, I["qkv"], 0, 3 * dl)
             else:
@@ -359,7 +396,7 @@ class Q8Decoder:
         if tp:
             linear("lm_head", I["x"], 0, d, I["gF"], I["Wlm"], I["blm"], -1, 0, 0, I["logits_local"], 0, Vl)
             op("allgather", OP_TP_ALLGATHER, I["logits_local"], I["logits"], B, Vl)
-        else:
+        elif c.kind != "gpt":
             linear("lm_head", I["x"], 0, d, I["gF"], I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0, V)
         if sampler is None:
             op("argmax", OP_ARGMAX_ROWS, I["logits"], I["next"], B, V)
@@ -371,6 +408,26 @@ class Q8Decoder:
         self._op_labels = labels
         self._op_bounds = bounds
         return np.asarray(s, dtype=np.int32)
+
+    def _gpt_blocks(self, op, x, x2, xp, qkv, att, h, pos_ids, B: int, T: int) -> None:
+        """The GPT part of a stream between the token gather and the final norm, for M = B·T rows: add the learned
+        position rows (embeddings/PositionalEmbedding.java:26-33; `pos_ids` holds one position per row), then per
+        block LayerNorm→QKV, attention, Wo + residual, LayerNorm→W1 + c1→GELU, W2 + c2 + residual."""
+        c, I = self.cfg, self.ids
+        d, F, M = c.d_model, c.d_ff, B * T
+        eps = float_bits(LN_EPS)
+        op("pos_embed", OP_EMBED_GATHER, I["posemb"], pos_ids, xp, M, d, c.max_seq_len)
+        op("pos_add", OP_ADD, x, xp, x, M * d)
+        for l in range(c.n_layers):
+            op("qkv", OP_Q8_LINEAR_LN, x, 0, d, I[f"g1.{l}"], I[f"b1.{l}"], eps, I[f"Wqkv.{l}"], -1, -1, 0, 0, qkv, 0, 3 * d, M, 0)
+            if T == 1:
+                op("attn", OP_ATTN_DECODE, qkv, 0, d, 2 * d, 3 * d, I["kv"], l, I["pos"], I["cos"], I["sin"], att, 0, d, B, c.n_heads, c.head_dim)
+            else:
+                op("attn", OP_ATTN_PREFILL, qkv, 0, d, 2 * d, 3 * d, I["kv"], l, I["pos"], I["cos"], I["sin"], att, 0, d, B, c.n_heads,
+                   c.head_dim, T)
+            op("wo", OP_Q8_LINEAR, att, 0, d, -1, 0, I[f"Wo.{l}"], -1, x, 0, d, x2, 0, d, M)
+            op("ffn_up", OP_Q8_LINEAR_LN, x2, 0, d, I[f"g2.{l}"], I[f"b2.{l}"], eps, I[f"W1.{l}"], I[f"c1.{l}"], -1, 0, 0, h, 0, F, M, 1)
+            op("ffn_down", OP_Q8_LINEAR, h, 0, F, -1, 0, I[f"W2.{l}"], I[f"c2.{l}"], x2, 0, d, x, 0, d, M)
 
     def _streams(self):
         if not self.loaded:
@@ -464,7 +521,10 @@ class Q8Decoder:
             s.extend(int(v) for v in (OP_Q8_LINEAR, x, x_off, ldx, gamma, eps, w, bias, res, 0, ldr, out, 0, ldo, M))
 
         s.extend((OP_EMBED_GATHER, I["emb"], P["tok"], P["x"], M, d, c.vocab_size))
-        for l in range(c.n_layers):
+        if c.kind == "gpt":
+            self._gpt_blocks(lambda _label, *ints: s.extend(int(v) for v in ints), P["x"], P["x2"], P["xp"], P["qkv"], P["att"], P["h"],
+                             P["ppos"], B, T)
+        for l in range(c.n_layers if c.kind != "gpt" else 0):
             if c.kind == "llama":
                 linear(P["x"], 0, d, I[f"g1.{l}"], I[f"Wqkv.{l}"], -1, -1, 0, P["qkv"], 3 * dl)
             else:
@@ -486,8 +546,12 @@ class Q8Decoder:
     def _head_stream(self) -> np.ndarray:
         """Final norm + LM head + greedy pick on the hidden state in the decode buffer."""
         c, B, I = self.cfg, self.B, self.ids
-        s = [OP_Q8_LINEAR, I["x"], 0, c.d_model, I["gF"], float_bits(RMS_EPS), I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0, c.vocab_size, B,
-             OP_ARGMAX_ROWS, I["logits"], I["next"], B, c.vocab_size]
+        if c.kind == "gpt":
+            s = [OP_Q8_LINEAR_LN, I["x"], 0, c.d_model, I["gF"], I["bF"], float_bits(LN_EPS), I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0,
+                 c.vocab_size, B, 0]
+        else:
+            s = [OP_Q8_LINEAR, I["x"], 0, c.d_model, I["gF"], float_bits(RMS_EPS), I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0, c.vocab_size, B]
+        s += [OP_ARGMAX_ROWS, I["logits"], I["next"], B, c.vocab_size]
         return np.asarray(s, dtype=np.int32)
 
     def prefill(self, prompts, chunked: Optional[bool] = None) -> np.ndarray:
@@ -519,6 +583,9 @@ class Q8Decoder:
                 self._prefill_streams[T] = self._build_prefill(T)
             st = self._prefill_streams[T]
             self._upload(self._prefill_ids["tok"], p[:, done:done + T].astype(np.float32).reshape(-1))
+            if self.cfg.kind == "gpt":       # row b·T + t sits at position (start of the chunk) + t
+                rows = np.tile(np.arange(self.position, self.position + T, dtype=np.float32), self.B)
+                self._upload(self._prefill_ids["ppos"], rows)
             _lib.check(self.lib.deepj_cuda_flush_ops(st.ctypes.data, st.size))
             done += T
             self.position += T
@@ -536,6 +603,8 @@ class Q8Decoder:
                  "h": M * self.f_local}
         if c.kind == "deepseek":
             sizes["lat"] = M * (c.q_rank + c.kv_rank)
+        if c.kind == "gpt":
+            sizes["xp"], sizes["ppos"] = M * c.d_model, M
         self._prefill_ids = {}
         for name, n in sizes.items():
             self._prefill_ids[name] = self._f32("", n)

@@ -172,6 +172,10 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
  *  74 SAMPLE_TOPK       [op, logits, r, out, rows, cols, topK, temperatureBits]
  *                        TextGenerator.sampleFromLogits per row (stable descending order, first topK <= 1024,
  *                        float softmax of logit/T, first index whose running sum reaches r[row]); r = Random.nextFloat()
+ *  75 Q8_LINEAR_LN      [op, x, x_off, ldx, gamma, beta, epsBits, w, bias, residual, res_off, ldr, out, out_off, ldo, M, act]
+ *                        the GPT blocks' projection: out = act(layernorm(x; gamma, beta, eps) · W + bias) (+residual),
+ *                        LayerNorm1D semantics (mean, biased variance); act 0 = none, 1 = GELU (tanh form);
+ *                        gamma = beta = -1 skips the norm
  */
 #define DEEPJ_OP_EMBED_GATHER        64
 #define DEEPJ_OP_Q8_LINEAR           65
@@ -184,6 +188,7 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
 #define DEEPJ_OP_TP_ALLGATHER        72
 #define DEEPJ_OP_ATTN_PREFILL        73
 #define DEEPJ_OP_SAMPLE_TOPK         74
+#define DEEPJ_OP_Q8_LINEAR_LN       75
 
 #ifdef __cplusplus
 }

@@ -37,6 +37,21 @@ def test_layout_follows_parameters_order():
     assert [s for _, _, s in lay[3:9]] == [(8, 4), (4, 8), (8, 2), (2, 8), (2, 8), (8, 8)]
 
 
+def test_gpt_layout_follows_parameters_order():
+    """GPTModel.embeddingParameters (token, position), GPTTransformerBlock.subLayers (ln1, ln2, attn, mlp) with
+    LayerNorm1D's (gamma, beta) and FNN's (W, b) pairs, final norm, LM head."""
+    cfg = DecoderConfig("gpt", 11, 16, 8, 2, 2, 24)
+    lay = parameter_layout(cfg)
+    names = [(n, l) for n, l, _ in lay]
+    assert names[:2] == [("emb", -1), ("pos", -1)] and lay[1][2] == (16, 8)
+    assert names[2:14] == [("g1", 0), ("b1", 0), ("g2", 0), ("b2", 0), ("Wq", 0), ("Wk", 0), ("Wv", 0), ("Wo", 0),
+                           ("W1", 0), ("c1", 0), ("W2", 0), ("c2", 0)]
+    assert names[-4:] == [("gF", -1), ("bF", -1), ("Wlm", -1), ("blm", -1)]
+    assert len(names) == 2 + 2 * 12 + 4
+    get = weight_getter(cfg, random_params(cfg, 3))
+    assert get("c1", 1).shape == (24,) and get("W1", 1).shape == (8, 24) and get("pos", -1).shape == (16, 8)
+
+
 def test_reads_the_java_stream_bit_for_bit(tmp_path):
     cfg = DecoderConfig("llama", 11, 16, 8, 2, 2, 24)
     params = random_params(cfg)
