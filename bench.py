@@ -43,6 +43,9 @@ WORKLOADS = {
     # BASELINE configs[3]: DeepSeek shape (qRank = dModel/2 assumed)
     "deepseek_q8_decode_b1": dict(kind="deepseek", vocab=32000, d=2048, heads=16, layers=16, d_ff=5632, max_seq=1280,
                                   prompt=1024, batch=1, seed=5, std=0.02, q_rank=1024, kv_rank=512),
+    # the GPT family at GPT-2 XL's shape (not a BASELINE config: the fused LayerNorm / GELU projections at speed)
+    "gpt2xl_q8_decode_b1": dict(kind="gpt", vocab=50257, d=1600, heads=25, layers=48, d_ff=6400, max_seq=1024,
+                                prompt=512, batch=1, seed=11, std=0.02),
     # BASELINE configs[0]: tiny Llama (latency-bound; no roofline claim)
     "tiny_llama_q8_decode_b1": dict(kind="llama", vocab=256, d=256, heads=8, layers=4, d_ff=688, max_seq=256,
                                     prompt=32, batch=1, seed=42, std=0.1),
@@ -193,6 +196,9 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
+        if w["kind"] == "gpt":
+            print(json.dumps({"impl": "reference", "unavailable": "no compiled CPU restatement of the GPT blocks (numpy one in tests/gpt_ref.py)"}))
+            return
         run_reference(args, w, args.workload)
         return
 
@@ -303,6 +309,10 @@ def main():
     op_bytes = {"qkv": q8b(d, 3 * dl) + 4 * B * (d + 3 * dl), "wo": q8b(dl, d) + 4 * B * (dl + 2 * d),
                 "swiglu": 2 * q8b(d, Fl) + 4 * B * (d + Fl), "down": q8b(Fl, d) + 4 * B * (Fl + 2 * d),
                 "lm_head": q8b(d, Vl) + 4 * B * (d + Vl)}
+    if cfg.kind == "gpt":
+        F = cfg.d_ff
+        op_bytes = {"qkv": q8b(d, 3 * d) + 4 * B * (d + 3 * d), "wo": q8b(d, d) + 4 * B * (d + 2 * d), "ffn_up": q8b(d, F) + 4 * B * (d + F),
+                    "ffn_down": q8b(F, d) + 4 * B * (F + 2 * d), "lm_head": q8b(d, Vl) + 4 * B * (d + Vl)}
     if cfg.kind == "deepseek":
         r = cfg.q_rank + cfg.kv_rank
         op_bytes.update({"mla_down": q8b(d, r) + 4 * B * (d + r), "mla_up_q": q8b(cfg.q_rank, dl) + 4 * B * (cfg.q_rank + dl),
@@ -354,7 +364,9 @@ def main():
         "prefill": {"tokens": int(B * w["prompt"]), "seconds": t_prefill, "tokens_per_s": B * w["prompt"] / max(t_prefill, 1e-9),
                     "path": "chunked, many-row kernels" if world == 1 and w["prompt"] >= 32 else "one decode step per position"},
     }
-    if not args.no_cpu_baseline and rank == 0:
+    if cfg.kind == "gpt":
+        line["cpu_baseline"] = None      # the C++ restatement covers the Llama / DeepSeek blocks; GPT's is numpy, in the tests
+    elif not args.no_cpu_baseline and rank == 0:
         v, used, sample = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": used, "kind": "port", "sample": sample}
     if rank == 0:
