@@ -156,6 +156,20 @@ def cpu_decode_sample(w, threads: int):
     return 1.0 / t_token, used, sample
 
 
+def cpu_full_reforward_sample(w, threads: int, n_new: int = 8):
+    """The reference's own generation loop on the CPU oracle: every new token re-forwards the whole
+    context (models/TextGenerator.java:91-100), fp32 weights.  Only for shapes a CPU finishes in seconds."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle
+    oracle.lib().oracle_set_threads(threads)
+    om = oracle.OracleModel(w["kind"], w["vocab"], w["max_seq"], w["d"], w["heads"], w["layers"], w["d_ff"],
+                            w.get("q_rank", 0), w.get("kv_rank", 0), seed=w["seed"], init_mode=1, std=w["std"])
+    prompt = list(np.random.default_rng(w["seed"] + 1000).integers(0, w["vocab"], size=w["prompt"]))
+    t0 = time.perf_counter()
+    om.generate_greedy(prompt, n_new, use_cache=False)
+    return n_new / (time.perf_counter() - t0)
+
+
 def run_reference(args, w, name):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -369,6 +383,8 @@ def main():
     elif not args.no_cpu_baseline and rank == 0:
         v, used, sample = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": used, "kind": "port", "sample": sample}
+        if w["d"] <= 256:      # the tiny configuration: also the reference-faithful loop, full re-forward per token
+            line["cpu_baseline"]["full_reforward_tokens_per_s"] = cpu_full_reforward_sample(w, used)
     if rank == 0:
         print(json.dumps(line), flush=True)
     dec.close()
