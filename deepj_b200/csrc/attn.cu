@@ -456,6 +456,8 @@ void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s) {
                  a.pos, a.cosT, a.sinT, a.H, a.hd, T);
     }
     static const bool noTiled = getenv("DEEPJ_CUDA_NO_TILED_PREFILL") != nullptr;
+    static const bool noMma = getenv("DEEPJ_CUDA_NO_MMA_PREFILL") != nullptr;
+    if (T >= kPQ && !noTiled && !noMma && launch_attn_prefill_mma(a, s)) return;      // tensor-core tiles (attn_mma.cu)
     if (T >= kPQ && !noTiled && (a.hd == 64 || a.hd == 128)) {
         dim3 tg((T + kPQ - 1) / kPQ, a.H, a.B);
         if (a.hd == 128) {

@@ -111,6 +111,7 @@ constexpr int kAttnTickets = 1 << 16;
 size_t attn_decode_ws_floats(int B, int H, int hd, int splits);
 int attn_decode_splits(int B, int H, int maxSeq);
 void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s);
+bool launch_attn_prefill_mma(const AttnDecodeArgs& a, cudaStream_t s);     // prompt chunks on the tensor cores (head dim 64 / 128)
 
 // ── misc ──
 void launch_embed_gather(const float* table, const float* ids, float* out, int rows, int d, int vocab, cudaStream_t s);
