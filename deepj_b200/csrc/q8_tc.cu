@@ -13,7 +13,9 @@
 // relative — so the prefill path stays inside the decode path's tolerance at one third of the
 // fp16 tensor peak.
 //
-// One CTA per 128 (activation rows) × 256 (weight rows) output tile, k-tiles of 32, ten warps:
+// One CTA per 128 (activation rows) × 256 (weight rows) output tile, or — when the launch has enough tiles to
+// keep every SM busy that way — per pair of them: two 128 × 256 accumulators fill the SM's tensor memory and
+// share every dequantised weight tile, which halves the conversion work per flop.  k-tiles of 32, ten warps:
 //   warps 0-7  dequantise, as two groups of four that take the k-tiles in turn (a thread owns two weight rows of
 //              the tile: 32 code bytes + a scale each per k-tile from global memory, its next three k-tiles
 //              already in registers) and write the W_hi / W_lo tiles in the 64-byte-swizzled K-major layout the
@@ -22,9 +24,9 @@
 //   warp 8     one thread streams the activation tiles: the pre-pass leaves every 128 × 32 tile as a ready
 //              shared-memory image (hi and lo adjacent, 16 KB), so a stage is ONE plain bulk copy completing
 //              on an mbarrier — no tensor map;
-//   warp 9     one thread issues the MMAs (128 × 256 × 16, accumulator = 256 columns of tensor memory) and
-//              commits each stage back to its "empty" barriers.
-// Four activation stages of 16 KB and four weight stages of 32 KB.  Every wait is bounded: when a bound
+//   warp 9     one thread issues the MMAs (128 × 256 × 16, three per accumulator and 16-k step, each accumulator
+//              256 columns of tensor memory) and commits each stage back to its "empty" barriers.
+// 64 KB of activation stages (four of one 128-row tile, or two of a pair) and three weight stages of 32 KB.  Every wait is bounded: when a bound
 // expires the CTA records an error code, stops waiting for anything, frees its tensor memory and returns.
 #include "kernels.h"
 #include "q8_common.cuh"
@@ -34,15 +36,16 @@ namespace dj {
 namespace {
 
 constexpr int kTileM = 128, kTileN = 256, kTileK = 32;
-constexpr int kStagesA = 4, kStagesB = 3;                // activation copies need the depth (L2 latency), dequantised tiles do not
+constexpr int kStagesA = 4, kStagesB = 3;                // activation stages: four of one 128-row tile, or two of a pair of tiles
 constexpr int kATileBytes = kTileM * kTileK * 2;         // one fp16 activation tile: 8 KB
 constexpr int kBTileBytes = kTileN * kTileK * 2;         // one fp16 weight tile: 16 KB
-constexpr int kStageABytes = 2 * kATileBytes;            // X_hi, X_lo
+constexpr int kAImageBytes = 2 * kATileBytes;            // X_hi, X_lo of one 128-row tile, as the pre-pass lays them down
+constexpr int kARegionBytes = kStagesA * kAImageBytes;   // 64 KB of activation stages either way
 constexpr int kStageBBytes = 2 * kBTileBytes;            // W_hi, W_lo
 constexpr int kDqWarps = 8;                              // dequantising (later: epilogue) warps, one weight row per thread; then one copy warp, one MMA warp
 constexpr int kTcThreads = (kDqWarps + 2) * 32;
 constexpr unsigned kTcWaitLimit = 1u << 22;              // try_wait rounds before a wait gives up
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;                            // two 128 × 256 fp32 accumulators: all of tensor memory
 constexpr int kRawRow = 144;                             // bytes per weight row in the raw-code buffer: 4 k-tiles of codes + their scales
 
 // byte offset of 16-byte chunk c (0-3) of row r inside a 64-byte-swizzled K-major tile of 32 halves per row:
@@ -197,6 +200,8 @@ struct TcParams {
     const float* residual; int ldr;
     float* out; int ldo;
     int M, N, K, Kp, nb;
+    int mTiles;             // 128-row activation tiles
+    int pair;               // 1: a CTA takes tiles 2·blockIdx.y and 2·blockIdx.y + 1 (the second may not exist), two accumulators; 0: tile blockIdx.y
     int mode;               // 0: out = acc + bias (+ residual);  1: out = SiLU(out) · (acc + bias)   (SwiGLU's second GEMM)
     int* error;
     unsigned long long* trace;      // optional: thread 0 of CTA (0,0) sums the time it spends waiting / converting / fencing
@@ -209,15 +214,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     __shared__ volatile int s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * kTileN, m0 = blockIdx.y * kTileM;
+    const int tile0 = p.pair ? 2 * (int)blockIdx.y : (int)blockIdx.y;
+    const int n0 = blockIdx.x * kTileN, m0 = tile0 * kTileM;
+    const bool has1 = p.pair && tile0 + 1 < p.mTiles;           // a second 128-row tile for the second accumulator
+    const int nStA = p.pair ? kStagesA / 2 : kStagesA;          // activation stages in use, and their size
+    const uint32_t stABytes = p.pair ? 2 * kAImageBytes : kAImageBytes;
     const int nK = p.K / kTileK;
     // the swizzled tiles want 1024-byte alignment: the dynamic segment carries 1 KB of slack for it
     const uint32_t smem_raw = smem_u32(smem);
     const uint32_t smem_s = (smem_raw + 1023u) & ~1023u;
     unsigned char* const smem_al = smem + (smem_s - smem_raw);
-    // layout: activation stages [kStagesA][X_hi 8 KB | X_lo 8 KB], then weight stages [kStagesB][W_hi 16 KB | W_lo 16 KB]
-    const uint32_t smemB_s = smem_s + kStagesA * kStageABytes;
-    unsigned char* const smemB = smem_al + kStagesA * kStageABytes;
+    // layout: activation stages [kStagesA][tile 0: X_hi 8 KB | X_lo 8 KB][tile 1: the same], then weight stages [kStagesB][W_hi 16 KB | W_lo 16 KB]
+    const uint32_t smemB_s = smem_s + kARegionBytes;
+    unsigned char* const smemB = smem_al + kARegionBytes;
     auto bar_fullA = [&](int s) { return smem_u32(&s_bar[s]); };
     auto bar_emptyA = [&](int s) { return smem_u32(&s_bar[kStagesA + s]); };
     auto bar_fullB = [&](int s) { return smem_u32(&s_bar[2 * kStagesA + s]); };
@@ -351,13 +360,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
         const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_acc, 0, &s_abort, p.error, 202));
         tc_fence_after();
         const int q4 = warp & 3, chalf = warp >> 2;
-        const int mrow = m0 + q4 * 32 + lane;
-        const float rs = (ok && mrow < p.M) ? p.rowscale[mrow] * (1.0f / 4096.0f) : 0.0f;       // the weights carry 2^12
         float* stg = reinterpret_cast<float*>(smem_al) + warp * (32 * 33);       // the pipeline stages are idle by now
+#pragma unroll 1
+        for (int acc = 0; acc < (has1 ? 2 : 1); acc++) {
+        const int mbase = m0 + acc * kTileM + q4 * 32;
+        const int mrow = mbase + lane;
+        const float rs = (ok && mrow < p.M) ? p.rowscale[mrow] * (1.0f / 4096.0f) : 0.0f;       // the weights carry 2^12
 #pragma unroll 1
         for (int c0 = chalf * 128; c0 < chalf * 128 + 128; c0 += 32) {
             uint32_t v[32];
-            if (ok) tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);      // warp-uniform
+            if (ok) tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(acc * kTileN + c0), v);      // warp-uniform
             else {
 #pragma unroll
                 for (int j = 0; j < 32; j++) v[j] = 0u;
@@ -368,7 +380,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
             const int nn = n0 + c0 + lane;
             const float bv = (p.bias && nn < p.N) ? p.bias[nn] : 0.0f;
             for (int i = 0; i < 32; i++) {
-                const int m = m0 + q4 * 32 + i;
+                const int m = mbase + i;
                 if (!ok || m >= p.M || nn >= p.N) continue;
                 float val = stg[i * 33 + lane] + bv;
                 float* o = p.out + (size_t)m * p.ldo + nn;
@@ -383,17 +395,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
             }
             __syncwarp();
         }
+        }
         if (tracing) { p.trace[5] = gtime(); p.trace[6] = p.trace[5]; }
         tc_fence_before();
     } else if (warp == kDqWarps) {
-        // ── activation tiles: one bulk copy of 16 KB (hi + lo) per stage ──
+        // ── activation tiles: one bulk copy of 16 KB (hi + lo) per 128-row tile and stage ──
         if (lane == 0) {
-            const unsigned char* src = p.xtiles + (size_t)blockIdx.y * nK * kStageABytes;
+            const unsigned char* src = p.xtiles + (size_t)tile0 * nK * kAImageBytes;
             for (int kt = 0; kt < nK; kt++) {
-                const int s = kt % kStagesA;
-                if (kt >= kStagesA && !mbar_wait(bar_emptyA(s), ((kt / kStagesA) - 1) & 1, &s_abort, p.error, 203)) break;
-                mbar_arrive_expect_tx(bar_fullA(s), kStageABytes);
-                bulk_g2s(smem_s + (uint32_t)s * kStageABytes, src + (size_t)kt * kStageABytes, kStageABytes, bar_fullA(s));
+                const int s = kt % nStA;
+                if (kt >= nStA && !mbar_wait(bar_emptyA(s), ((kt / nStA) - 1) & 1, &s_abort, p.error, 203)) break;
+                mbar_arrive_expect_tx(bar_fullA(s), has1 ? 2 * kAImageBytes : kAImageBytes);
+                bulk_g2s(smem_s + (uint32_t)s * stABytes, src + (size_t)kt * kAImageBytes, kAImageBytes, bar_fullA(s));
+                if (has1)
+                    bulk_g2s(smem_s + (uint32_t)s * stABytes + kAImageBytes, src + (size_t)(nK + kt) * kAImageBytes, kAImageBytes, bar_fullA(s));
             }
         }
         __syncwarp();
@@ -402,12 +417,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
         if (lane == 0) {
             bool ok = true;
             for (int kt = 0; kt < nK && ok; kt++) {
-                const int sa = kt % kStagesA, sb = kt % kStagesB;
-                ok = mbar_wait(bar_fullA(sa), (kt / kStagesA) & 1, &s_abort, p.error, 204) &&
+                const int sa = kt % nStA, sb = kt % kStagesB;
+                ok = mbar_wait(bar_fullA(sa), (kt / nStA) & 1, &s_abort, p.error, 204) &&
                      mbar_wait(bar_fullB(sb), (kt / kStagesB) & 1, &s_abort, p.error, 205);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_hi = smem_s + (uint32_t)sa * kStageABytes, a_lo = a_hi + kATileBytes;
+                const uint32_t a_hi = smem_s + (uint32_t)sa * stABytes, a_lo = a_hi + kATileBytes;
                 const uint32_t b_hi = smemB_s + (uint32_t)sb * kStageBBytes, b_lo = b_hi + kBTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < kTileK / 16; ks++) {
@@ -415,6 +430,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
                     umma_f16(tmem_base, umma_desc(a_hi + off), umma_desc(b_hi + off), kIdesc, (kt | ks) != 0);
                     umma_f16(tmem_base, umma_desc(a_lo + off), umma_desc(b_hi + off), kIdesc, 1);
                     umma_f16(tmem_base, umma_desc(a_hi + off), umma_desc(b_lo + off), kIdesc, 1);
+                    if (has1) {                            // the same weight tile against the second 128 rows → accumulator 2
+                        umma_f16(tmem_base + kTileN, umma_desc(a_hi + kAImageBytes + off), umma_desc(b_hi + off), kIdesc, (kt | ks) != 0);
+                        umma_f16(tmem_base + kTileN, umma_desc(a_lo + kAImageBytes + off), umma_desc(b_hi + off), kIdesc, 1);
+                        umma_f16(tmem_base + kTileN, umma_desc(a_hi + kAImageBytes + off), umma_desc(b_lo + off), kIdesc, 1);
+                    }
                 }
                 umma_commit(bar_emptyA(sa));               // both arrive when the MMAs above have finished reading the stages
                 umma_commit(bar_emptyB(sb));
@@ -427,7 +447,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     if (warp == kDqWarps) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
-constexpr size_t kTcSmem = (size_t)kStagesA * kStageABytes + (size_t)kStagesB * kStageBBytes + (size_t)kTileN * kRawRow + 1024;
+constexpr size_t kTcSmem = (size_t)kARegionBytes + (size_t)kStagesB * kStageBBytes + (size_t)kTileN * kRawRow + 1024;
 
 }  // namespace
 
@@ -452,18 +472,26 @@ bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s) {
     unsigned char* tiles = reinterpret_cast<unsigned char*>(ws);
     float* rowscale = ws + mPad * K;
     launch_k(k_x_to_f16_tiles, dim3((unsigned)(mPad / 8)), dim3(256), 0, s, true, a.x, a.ldx, a.gamma, a.eps, M, K, tiles, rowscale);
+    // Two accumulators per CTA halve the conversion work per flop but also the number of CTAs, and a paired CTA
+    // takes 1.55–1.7 × as long as a single one: pair when the rounds of CTAs over the SMs it saves outweigh that.
+    static const int pairEnv = getenv("DEEPJ_CUDA_TC_PAIR") ? atoi(getenv("DEEPJ_CUDA_TC_PAIR")) : -1;
+    const long single = (long)nTiles * mTiles, paired = (long)nTiles * ((mTiles + 1) / 2);
+    const long roundsSingle = (single + g_num_sms - 1) / g_num_sms, roundsPaired = (paired + g_num_sms - 1) / g_num_sms;
+    bool pair = mTiles >= 2 && 1.7 * (double)roundsPaired < (double)roundsSingle;
+    if (pairEnv >= 0) pair = pairEnv != 0 && mTiles >= 2;
+    const dim3 grid(nTiles, pair ? (mTiles + 1) / 2 : mTiles);
     TcParams p;
     p.xtiles = tiles; p.rowscale = rowscale;
     p.codes = a.w.codes; p.scales = a.w.scales; p.bias = a.bias;
     p.residual = a.residual; p.ldr = a.ldr;
     p.out = a.out; p.ldo = a.ldo;
-    p.M = M; p.N = N; p.K = K; p.Kp = a.w.Kp; p.nb = a.w.nb;
+    p.M = M; p.N = N; p.K = K; p.Kp = a.w.Kp; p.nb = a.w.nb; p.mTiles = mTiles; p.pair = pair ? 1 : 0;
     p.mode = 0; p.error = g_dev_error; p.trace = trace_slot();
-    launch_k(k_q8_gemm_tc, dim3(nTiles, mTiles), dim3(kTcThreads), kTcSmem, s, true, p);
+    launch_k(k_q8_gemm_tc, grid, dim3(kTcThreads), kTcSmem, s, true, p);
     if (a.w2.codes != nullptr) {
         // SwiGLU: the gate projection is in `out`; the up projection's epilogue multiplies SiLU(gate) into it
         p.codes = a.w2.codes; p.scales = a.w2.scales; p.bias = a.bias2; p.residual = nullptr; p.mode = 1;
-        launch_k(k_q8_gemm_tc, dim3(nTiles, mTiles), dim3(kTcThreads), kTcSmem, s, true, p);
+        launch_k(k_q8_gemm_tc, grid, dim3(kTcThreads), kTcSmem, s, true, p);
     }
     return true;
 }

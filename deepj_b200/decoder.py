@@ -505,7 +505,7 @@ class Q8Decoder:
     def next_tokens(self) -> np.ndarray:
         return self._download(self.ids["next"], self.B).astype(np.int64)
 
-    PREFILL_CHUNK = 1024     # prompt tokens per sequence and pass of the many-row path (fills the 128 × 256 GEMM tiles of a 4096-wide layer)
+    PREFILL_CHUNK = 2048     # prompt tokens per sequence and pass of the many-row path (enough 128 × 256 tiles for the GEMM to pair them)
 
     def _build_prefill(self, T: int) -> np.ndarray:
         """The stream of one prompt chunk: T tokens of every sequence at once, B·T activation rows through the
