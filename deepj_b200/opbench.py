@@ -1,4 +1,5 @@
-"""Q8 matmul operator benchmark: `python -m deepj_b200.opbench --m 1 --k 4096 --n 11008`.
+"""Operator benchmark: `python -m deepj_b200.opbench --m 1 --k 4096 --n 11008` (Q8 matmul) or
+`python -m deepj_b200.opbench --attn-prefill --heads 32 --head-dim 128 --tokens 1024 --pos0 1024` (prompt-chunk attention).
 
 Times the fused Q8 linear op (y = x·W, W quantized to Q8) through the C ABI.  The
 weights of one GEMV (19-51 MB) fit in the B200's L2, so the stream cycles through
@@ -94,6 +95,54 @@ def run(m: int, k: int, n: int, copies: int, iters: int, warmup: int, swiglu: bo
     return res
 
 
+def run_attn_prefill(heads: int, hd: int, tokens: int, pos0: int, batch: int, iters: int, warmup: int, device: int = 0, seed: int = 1):
+    """Times op 73 (prompt-chunk attention: append + causal attention of `tokens` rows per sequence behind
+    `pos0` cached positions).  Useful flops = 4·hd per (query, visible key) pair and head."""
+    from .compute_graph import OP_ATTN_PREFILL
+    from .decoder import rope_tables
+    lib = _lib.load()
+    _lib.check(lib.deepj_cuda_init(device))
+    base = 1 << 26
+    ids = []
+
+    def f32(count, data=None):
+        i = base + 1 + len(ids)
+        ids.append(i)
+        _lib.check(lib.deepj_cuda_alloc_buffers((ctypes.c_int32 * 1)(i), (ctypes.c_int32 * 1)(count), 1))
+        if data is not None:
+            d = np.ascontiguousarray(data, dtype=np.float32)
+            _lib.check(lib.deepj_cuda_upload_buffer(i, d.ctypes.data, d.size))
+        return i
+
+    d, max_seq = heads * hd, pos0 + tokens
+    rng = np.random.default_rng(seed)
+    cos, sin = rope_tables(hd, max_seq)
+    cb, sb = f32(cos.size, cos), f32(sin.size, sin)
+    kv = base + 1 + len(ids)
+    ids.append(kv)
+    _lib.check(lib.deepj_cuda_kv_alloc(kv, 1, batch, heads, max_seq, hd))
+    xb = f32(batch * tokens * 3 * d, rng.standard_normal((batch * tokens, 3 * d)).astype(np.float32))
+    ob, pb = f32(batch * tokens * d), f32(batch, np.full(batch, float(pos0)))
+    if pos0 > 0:       # fill the cache below pos0 with one earlier chunk of the same rows (timing only)
+        fill = [OP_ATTN_PREFILL, xb, 0, d, 2 * d, 3 * d, kv, 0, f32(batch, np.zeros(batch)), cb, sb, ob, 0, d, batch, heads, hd, min(pos0, tokens)]
+        c0 = np.asarray(fill, dtype=np.int32)
+        _lib.check(lib.deepj_cuda_flush_ops(c0.ctypes.data, c0.size))
+    cmd = np.asarray([OP_ATTN_PREFILL, xb, 0, d, 2 * d, 3 * d, kv, 0, pb, cb, sb, ob, 0, d, batch, heads, hd, tokens], dtype=np.int32)
+    for _ in range(max(warmup, 3)):
+        _lib.check(lib.deepj_cuda_flush_ops(cmd.ctypes.data, cmd.size))
+    _lib.check(lib.deepj_cuda_timer_begin())
+    for _ in range(iters):
+        _lib.check(lib.deepj_cuda_flush_ops_async(cmd.ctypes.data, cmd.size))
+    ms = ctypes.c_float(0)
+    _lib.check(lib.deepj_cuda_timer_end(ctypes.byref(ms)))
+    us = ms.value * 1e3 / iters
+    pairs = batch * heads * (tokens * pos0 + tokens * (tokens + 1) // 2)
+    res = {"op": "attn_prefill", "heads": heads, "head_dim": hd, "tokens": tokens, "pos0": pos0, "batch": batch, "us_per_launch": us,
+           "useful_tflop_per_s": 4.0 * hd * pairs / (us * 1e-6) / 1e12}
+    _lib.check(lib.deepj_cuda_release_buffers((ctypes.c_int32 * len(ids))(*ids), len(ids)))
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int, default=1)
@@ -104,7 +153,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--norm", action="store_true")
+    ap.add_argument("--attn-prefill", action="store_true", help="time op 73 instead: --heads --head-dim --tokens --pos0 --batch")
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--tokens", type=int, default=1024)
+    ap.add_argument("--pos0", type=int, default=1024)
+    ap.add_argument("--batch", type=int, default=1)
     a = ap.parse_args()
+    if a.attn_prefill:
+        print(json.dumps(run_attn_prefill(a.heads, a.head_dim, a.tokens, a.pos0, a.batch, a.iters, a.warmup)))
+        return
     print(json.dumps(run(a.m, a.k, a.n, a.copies, a.iters, a.warmup, a.swiglu, a.norm)))
 
 
