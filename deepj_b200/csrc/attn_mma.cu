@@ -8,9 +8,11 @@
 // ≈ 2^-22 of the product) — the same split the many-row Q8 projection uses.
 //
 // grid (ceil(T / 64), heads, sequences), 128 threads.  Warp w owns query rows 16w … 16w+15 of the
-// tile; the CTA walks the keys in tiles of 64: K and V rows come from the fp32 cache, are split and
+// tile; the CTA walks the keys in tiles of 32: K and V rows come from the fp32 cache, are split and
 // laid down in shared memory as fp16 [key][dim] (row stride dim + 8 halves, so the eight rows an
-// ldmatrix fetches fall into different banks), S stays in registers, the online softmax is the
+// ldmatrix fetches fall into different banks) — into the stage that is not being multiplied, the
+// global loads of the next tile's K issued before this tile's Q·Kᵀ and those of its V before the
+// softmax and P·V, so that their latency is covered by tensor work — S stays in registers, the online softmax is the
 // usual running max / sum per row in fp32, and P goes back into the tensor cores straight from the
 // S registers (an S accumulator pair is exactly an A-operand pair of the next MMA).
 // V is consumed through ldmatrix.trans, so no transposed copy is needed.
@@ -27,7 +29,7 @@ namespace dj {
 namespace {
 
 constexpr int kMQ = 64;     // query rows per CTA
-constexpr int kMK = 64;     // keys per tile
+constexpr int kMK = 32;     // keys per tile (two tiles are resident: one being multiplied, one being filled)
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -107,66 +109,73 @@ __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
     for (int j = 0; j < 2 * KS; j++) { o[j][0] = 0.0f; o[j][1] = 0.0f; o[j][2] = 0.0f; o[j][3] = 0.0f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 
-    for (int k0 = 0; k0 <= lastKey; k0 += kMK) {
-        __syncthreads();                            // the previous tile is no longer read (first round: Q is written)
-        // four rounds of loads are in flight before the first conversion
-        constexpr int kPer = kMK * (HD / 4) / 128;       // float4 pairs per thread and tile
-        static_assert(kPer % 4 == 0, "tile loads come in groups of four");
-#pragma unroll 1
-        for (int i0 = 0; i0 < kPer; i0 += 4) {
-            float4 kv[4], vv[4];
+    // A thread's share of one 32-key tile of K (or of V): kPer float4 pieces, piece u = tid + 128·u.
+    constexpr int kPer = kMK * (HD / 4) / 128;
+    float4 pre[kPer];
+    auto fetch = [&](const float* base, int k0) {
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int i = tid + (i0 + u) * 128;
-                const int key = i / (HD / 4), d4 = i % (HD / 4);
-                kv[u] = make_float4(0.f, 0.f, 0.f, 0.f); vv[u] = kv[u];
-                if (k0 + key <= lastKey) {
-                    kv[u] = __ldg(reinterpret_cast<const float4*>(kb + (size_t)(k0 + key) * HD) + d4);
-                    vv[u] = __ldg(reinterpret_cast<const float4*>(vb + (size_t)(k0 + key) * HD) + d4);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int i = tid + (i0 + u) * 128;
-                const int key = i / (HD / 4), d4 = i % (HD / 4);
-                uint2 hi, lo;
-                split2(kv[u].x, kv[u].y, hi.x, lo.x); split2(kv[u].z, kv[u].w, hi.y, lo.y);
-                *reinterpret_cast<uint2*>(Kh + key * LDS + 4 * d4) = hi;
-                *reinterpret_cast<uint2*>(Kl + key * LDS + 4 * d4) = lo;
-                split2(vv[u].x, vv[u].y, hi.x, lo.x); split2(vv[u].z, vv[u].w, hi.y, lo.y);
-                *reinterpret_cast<uint2*>(Vh + key * LDS + 4 * d4) = hi;
-                *reinterpret_cast<uint2*>(Vl + key * LDS + 4 * d4) = lo;
-            }
+        for (int u = 0; u < kPer; u++) {
+            const int i = tid + u * 128;
+            const int key = i / (HD / 4), d4 = i % (HD / 4);
+            pre[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k0 + key <= lastKey) pre[u] = __ldg(reinterpret_cast<const float4*>(base + (size_t)(k0 + key) * HD) + d4);
         }
-        __syncthreads();
-
-        // S = Q·Kᵀ: 16 rows × 64 keys per warp, eight n-tiles of eight keys
-        float s[8][4];
+    };
+    auto put = [&](__half* hiT, __half* loT) {      // split what `fetch` brought and lay it down as fp16 [key][dim]
 #pragma unroll
-        for (int j = 0; j < 8; j++) { s[j][0] = 0.0f; s[j][1] = 0.0f; s[j][2] = 0.0f; s[j][3] = 0.0f; }
+        for (int u = 0; u < kPer; u++) {
+            const int i = tid + u * 128;
+            const int key = i / (HD / 4), d4 = i % (HD / 4);
+            uint2 hi, lo;
+            split2(pre[u].x, pre[u].y, hi.x, lo.x); split2(pre[u].z, pre[u].w, hi.y, lo.y);
+            *reinterpret_cast<uint2*>(hiT + key * LDS + 4 * d4) = hi;
+            *reinterpret_cast<uint2*>(loT + key * LDS + 4 * d4) = lo;
+        }
+    };
+    constexpr int kStageHalves = 4 * kMK * LDS;     // K_hi, K_lo, V_hi, V_lo of one tile
+    constexpr uint32_t kStageBytes = kStageHalves * 2;
+
+    // first tile into stage 0
+    fetch(kb, 0); put(Kh, Kl);
+    fetch(vb, 0); put(Vh, Vl);
+    __syncthreads();
+    const int nTiles = lastKey / kMK + 1;
+    for (int it = 0; it < nTiles; it++) {
+        const int k0 = it * kMK;
+        const uint32_t cur = (uint32_t)(it & 1) * kStageBytes;
+        __half* const nKh = Kh + ((it + 1) & 1) * kStageHalves;
+        const bool more = it + 1 < nTiles;
+        if (more) fetch(kb, k0 + kMK);              // the next tile's keys travel while this tile's Q·Kᵀ runs
+
+        // S = Q·Kᵀ: 16 rows × 32 keys per warp, four n-tiles of eight keys
+        float s[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) { s[j][0] = 0.0f; s[j][1] = 0.0f; s[j][2] = 0.0f; s[j][3] = 0.0f; }
 #pragma unroll
         for (int kk = 0; kk < KS; kk++) {
-            uint32_t ah[4], al[4], bh[4][4], bl[4][4];
+            uint32_t ah[4], al[4], bh[2][4], bl[2][4];
             ldsm_x4(ah, qAddr + kk * 32);
             ldsm_x4(al, qAddr + qlDelta + kk * 32);
 #pragma unroll
-            for (int np = 0; np < 4; np++) {        // two n-tiles (16 keys) per ldmatrix
-                const uint32_t a = kAddr + (uint32_t)(np * 16 * LDS * 2) + kk * 32;
+            for (int np = 0; np < 2; np++) {        // two n-tiles (16 keys) per ldmatrix
+                const uint32_t a = kAddr + cur + (uint32_t)(np * 16 * LDS * 2) + kk * 32;
                 ldsm_x4(bh[np], a);
                 ldsm_x4(bl[np], a + klDelta);
             }
-            // three passes over the eight accumulators: consecutive MMAs never wait on each other's result
+            // three passes over the four accumulators: consecutive MMAs never wait on each other's result
 #pragma unroll
-            for (int np = 0; np < 4; np++) { mma_f16(s[2 * np], ah, bh[np][0], bh[np][1]); mma_f16(s[2 * np + 1], ah, bh[np][2], bh[np][3]); }
+            for (int np = 0; np < 2; np++) { mma_f16(s[2 * np], ah, bh[np][0], bh[np][1]); mma_f16(s[2 * np + 1], ah, bh[np][2], bh[np][3]); }
 #pragma unroll
-            for (int np = 0; np < 4; np++) { mma_f16(s[2 * np], al, bh[np][0], bh[np][1]); mma_f16(s[2 * np + 1], al, bh[np][2], bh[np][3]); }
+            for (int np = 0; np < 2; np++) { mma_f16(s[2 * np], al, bh[np][0], bh[np][1]); mma_f16(s[2 * np + 1], al, bh[np][2], bh[np][3]); }
 #pragma unroll
-            for (int np = 0; np < 4; np++) { mma_f16(s[2 * np], ah, bl[np][0], bl[np][1]); mma_f16(s[2 * np + 1], ah, bl[np][2], bl[np][3]); }
+            for (int np = 0; np < 2; np++) { mma_f16(s[2 * np], ah, bl[np][0], bl[np][1]); mma_f16(s[2 * np + 1], ah, bl[np][2], bl[np][3]); }
         }
+        if (more) { put(nKh, nKh + kMK * LDS); fetch(vb, k0 + kMK); }      // … and its values while the softmax and P·V run
+
         // causal mask, running max
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
+        for (int j = 0; j < 4; j++) {
 #pragma unroll
             for (int e = 0; e < 2; e++) {
                 const int key = k0 + j * 8 + 2 * t4 + e;
@@ -181,7 +190,7 @@ __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
         const float c0 = mn0 > -INFINITY ? expf(m0 - mn0) : 1.0f, c1 = mn1 > -INFINITY ? expf(m1 - mn1) : 1.0f;
         float ps0 = 0.0f, ps1 = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
+        for (int j = 0; j < 4; j++) {
 #pragma unroll
             for (int e = 0; e < 2; e++) {
                 const float p0 = s[j][e] > -INFINITY ? expf(s[j][e] - mn0) : 0.0f;
@@ -192,12 +201,14 @@ __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
         }
         l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;     // per-lane partial sums: the four lanes of a row are added at the end
         m0 = mn0; m1 = mn1;
+        if (c0 != 1.0f || c1 != 1.0f) {             // the running maxima rarely move after the first tiles
 #pragma unroll
-        for (int j = 0; j < 2 * KS; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+            for (int j = 0; j < 2 * KS; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+        }
 
         // O += P·V: the S registers of n-tiles 2kk, 2kk+1 are the A operand of key step kk
 #pragma unroll
-        for (int kk = 0; kk < 4; kk++) {
+        for (int kk = 0; kk < kMK / 16; kk++) {
             uint32_t ph[4], pl[4];
             split2(s[2 * kk][0], s[2 * kk][1], ph[0], pl[0]);
             split2(s[2 * kk][2], s[2 * kk][3], ph[1], pl[1]);
@@ -208,7 +219,7 @@ __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
                 uint32_t bh[4][4], bl[4][4];
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    const uint32_t a = vAddr + (uint32_t)(kk * 16 * LDS * 2) + (c4 + q) * 32;
+                    const uint32_t a = vAddr + cur + (uint32_t)(kk * 16 * LDS * 2) + (c4 + q) * 32;
                     ldsm_x4_t(bh[q], a);
                     ldsm_x4_t(bl[q], a + klDelta);
                 }
@@ -220,6 +231,8 @@ __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
                 for (int q = 0; q < 4; q++) { mma_f16(o[2 * (c4 + q)], ph, bl[q][0], bl[q][1]); mma_f16(o[2 * (c4 + q) + 1], ph, bl[q][2], bl[q][3]); }
             }
         }
+        if (more) put(nKh + 2 * kMK * LDS, nKh + 3 * kMK * LDS);
+        __syncthreads();                            // the next stage is complete, and nobody still reads this one
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
@@ -235,7 +248,7 @@ __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
     }
 }
 
-template <int HD> constexpr size_t prefill_mma_smem() { return (size_t)(2 * kMQ + 4 * kMK) * (HD + 8) * sizeof(__half); }
+template <int HD> constexpr size_t prefill_mma_smem() { return (size_t)(2 * kMQ + 2 * 4 * kMK) * (HD + 8) * sizeof(__half); }
 
 template <int HD>
 void launch_mma(const AttnDecodeArgs& a, int T, cudaStream_t s) {
