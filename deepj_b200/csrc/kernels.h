@@ -90,6 +90,7 @@ bool launch_q8_linear_batch(const Q8LinearArgs& a, int m0, int rows, float* ws, 
 size_t q8_batch_ws_floats(int K, int N, bool swiglu);
 bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s);
 size_t q8_tc_ws_floats(int M, int K);
+double q8_tc_estimate_us(int M, int K, int N);
 constexpr int kTcMinRows = 17;            // from this many activation rows on, a Q8 linear runs on the tcgen05 path
 
 // ── decode attention ──

@@ -351,8 +351,16 @@ void dispatch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
     p.K = a.w.K; p.N = a.w.N; p.Kp = a.w.Kp; p.nb = a.w.nb;
     const bool swiglu = a.w2.codes != nullptr;
     static const bool noTc = getenv("DEEPJ_CUDA_NO_TC") != nullptr;
-    if (g_gemv_mode == 2 && !noTc && a.M >= kTcMinRows && a.ws != nullptr && launch_q8_linear_tc(a, a.ws, s)) return;
-    if (g_gemv_mode == 2 && a.M >= 5 && a.ws != nullptr && a.w.K % 32 == 0 && a.w.Kp == a.w.K) {
+    const bool batchOk = g_gemv_mode == 2 && a.M >= 5 && a.ws != nullptr && a.w.K % 32 == 0 && a.w.Kp == a.w.K;
+    // A few dozen rows leave most SMs without a 128 × 256 tile: passes of the 16-row kernel (≈ 0.9 ps per weight and
+    // pass, measured) win until the tensor-core grid fills up.
+    bool preferBatch = false;
+    if (batchOk && a.M >= kTcMinRows && a.M <= 256) {
+        const double batchUs = (double)((a.M + 15) / 16) * 0.9e-6 * (double)a.w.K * (double)a.w.N;
+        preferBatch = batchUs < q8_tc_estimate_us(a.M, a.w.K, a.w.N);
+    }
+    if (g_gemv_mode == 2 && !noTc && !preferBatch && a.M >= kTcMinRows && a.ws != nullptr && launch_q8_linear_tc(a, a.ws, s)) return;
+    if (batchOk) {
         // five or more rows share one pass over the weights, 16 at a time (up to four are two GEMV passes, which is as fast)
         bool ok = true;
         for (int m0 = 0; m0 < a.M && ok; m0 += 16) ok = launch_q8_linear_batch(a, m0, a.M - m0 < 16 ? a.M - m0 : 16, a.ws, a.tickets, s);

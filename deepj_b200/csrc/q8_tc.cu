@@ -451,6 +451,18 @@ constexpr size_t kTcSmem = (size_t)kARegionBytes + (size_t)kStagesB * kStageBByt
 
 }  // namespace
 
+// Rough duration of launch_q8_linear_tc in µs, for the choice between this path and passes of the 16-row kernel
+// when M is small: a CTA needs ≈ 0.75 µs per 32-k tile (1.2 µs when it carries two accumulators), CTAs run in
+// rounds over the SMs, and the activation pre-pass costs a few µs.
+double q8_tc_estimate_us(int M, int K, int N) {
+    const long mTiles = (M + kTileM - 1) / kTileM, nTiles = (N + kTileN - 1) / kTileN;
+    const long single = nTiles * mTiles, paired = nTiles * ((mTiles + 1) / 2);
+    const long roundsSingle = (single + g_num_sms - 1) / g_num_sms, roundsPaired = (paired + g_num_sms - 1) / g_num_sms;
+    const double perTile = 0.75 * (K / kTileK);
+    const double t = mTiles >= 2 && 1.7 * (double)roundsPaired < (double)roundsSingle ? 1.6 * perTile * roundsPaired : perTile * roundsSingle;
+    return t + 5.0;
+}
+
 size_t q8_tc_ws_floats(int M, int K) {
     const size_t mPad = (size_t)(M + kTileM - 1) / kTileM * kTileM;
     return mPad * K + mPad;          // hi + lo halves = 4 bytes per value, then the row scales

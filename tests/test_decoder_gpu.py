@@ -133,18 +133,18 @@ def test_chunked_prefill_equals_token_by_token(kind, d_ff):
     within 2e-3 of the logit range — in practice ~1e-5 — the same greedy tokens, also on the steps that follow,
     and the oracle's tokens."""
     if kind == "llama":
-        cfg = DecoderConfig("llama", 512, 128, 256, 4, 2, d_ff)
-        om = oracle.OracleModel("llama", 512, 128, 256, 4, 2, d_ff, seed=12)
+        cfg = DecoderConfig("llama", 512, 400, 256, 4, 2, d_ff)
+        om = oracle.OracleModel("llama", 512, 400, 256, 4, 2, d_ff, seed=12)
     else:
-        cfg = DecoderConfig("deepseek", 512, 128, 256, 4, 2, d_ff, q_rank=128, kv_rank=64)
-        om = oracle.OracleModel("deepseek", 512, 128, 256, 4, 2, d_ff, 128, 64, seed=12)
+        cfg = DecoderConfig("deepseek", 512, 400, 256, 4, 2, d_ff, q_rank=128, kv_rank=64)
+        om = oracle.OracleModel("deepseek", 512, 400, 256, 4, 2, d_ff, 128, 64, seed=12)
     get = weight_getter(om, cfg)
     rng = np.random.default_rng(4)
-    prompts = rng.integers(0, 512, size=(2, 80))
+    prompts = rng.integers(0, 512, size=(2, 330))      # chunks of 150, 150, 30 tokens: 300 rows (tcgen05 path), then 60 (16-row kernel)
 
     def run(chunked):
         dec = Q8Decoder(cfg, batch=2)
-        dec.PREFILL_CHUNK = 32
+        dec.PREFILL_CHUNK = 150
         dec.load_weights(get)
         dec.reset()
         nxt = dec.prefill(prompts, chunked=chunked)

@@ -23,10 +23,10 @@ def dev():
     d.close()
 
 
-# rows 1-4: the GEMV with the norm and the activation fused; 6 and 16: the 16-row kernel behind a
-# normalising pass; 40: the tcgen05 path; K = 100: the FMA fallback (no 32-element blocks)
+# rows 1-4: the GEMV with the norm and the activation fused; 6, 16 and 40: the 16-row kernel behind a
+# normalising pass; 300: the tcgen05 path; K = 100: the FMA fallback (no 32-element blocks)
 @pytest.mark.parametrize("M,K,N", [(1, 256, 96), (2, 512, 40), (4, 4096, 64), (3, 768, 33), (6, 512, 72), (16, 256, 128),
-                                   (40, 256, 300), (1, 100, 24), (5, 100, 24)])
+                                   (40, 256, 300), (300, 256, 300), (1, 100, 24), (5, 100, 24)])
 @pytest.mark.parametrize("act", [0, 1])
 def test_layernorm_q8_linear_gelu(dev, M, K, N, act):
     rng = np.random.default_rng(M * 1000 + K + N + act)
@@ -111,14 +111,14 @@ def test_gpt_decoder_matches_the_numpy_forward():
 def test_gpt_chunked_prefill_equals_token_by_token_and_the_reference():
     """Prompt chunks (tcgen05 GEMMs behind the normalising pass, chunk attention, position rows per token) leave the
     same cache and logits as one step per position; two sequences, three chunks with a ragged last one."""
-    V, S, d, H, L, F = 256, 96, 128, 4, 2, 256
+    V, S, d, H, L, F = 256, 360, 128, 4, 2, 256
     cfg = DecoderConfig("gpt", V, S, d, H, L, F)
     w, get = gpt_ref.make_weights(V, S, d, H, L, F, seed=8)
-    prompts = np.random.default_rng(6).integers(0, V, size=(2, 70))
+    prompts = np.random.default_rng(6).integers(0, V, size=(2, 330))     # chunks of 150, 150, 30: 300 rows, then 60
 
     def run(chunked):
         dec = Q8Decoder(cfg, batch=2)
-        dec.PREFILL_CHUNK = 32
+        dec.PREFILL_CHUNK = 150
         dec.load_weights(get)
         dec.reset()
         nxt = dec.prefill(prompts, chunked=chunked)

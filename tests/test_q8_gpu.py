@@ -129,7 +129,8 @@ def oracle_rmsnorm(x, gamma):
 @pytest.mark.parametrize("M,K,N", [(1, 256, 256), (1, 688, 256), (3, 256, 688), (1, 4096, 512), (2, 2048, 100),
                                    (1, 11008, 64), (1, 100, 33), (1, 512, 2048), (1, 5632, 128), (6, 512, 40), (4, 4096, 24), (1, 1376, 64), (2, 96, 20), (1, 2752, 33),
                                    (5, 1376, 200), (16, 4096, 512), (16, 96, 20), (7, 2752, 33), (40, 512, 300), (9, 11008, 64),
-                                   (17, 256, 128), (64, 4096, 512), (130, 512, 300), (512, 2048, 256), (40, 96, 20), (300, 64, 8)])
+                                   (17, 256, 128), (64, 4096, 512), (130, 512, 300), (512, 2048, 256), (40, 96, 20), (300, 64, 8),
+                                   (257, 256, 128), (300, 512, 300), (640, 128, 520)])
 @pytest.mark.parametrize("fused", ["plain", "norm_bias_res"])
 def test_q8_linear_matches_oracle(dev, M, K, N, fused):
     rng = np.random.default_rng(K * 7 + N + M)
@@ -154,7 +155,7 @@ def test_q8_linear_matches_oracle(dev, M, K, N, fused):
 
 @pytest.mark.parametrize("M,K,F", [(1, 256, 688), (2, 256, 100), (1, 4096, 256), (1, 2048, 5632),
                                    (3, 256, 688), (16, 4096, 256), (5, 2048, 100), (20, 512, 72),
-                                   (64, 512, 256), (200, 4096, 200)])
+                                   (64, 512, 256), (200, 4096, 200), (300, 512, 256)])
 def test_q8_swiglu_matches_oracle(dev, M, K, F):
     rng = np.random.default_rng(K + F)
     x = rng.standard_normal((M, K)).astype(np.float32)
