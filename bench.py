@@ -235,11 +235,13 @@ def main():
     room = w["max_seq"] - w["prompt"] - 1          # decode steps that fit behind the prompt
     if room < 8:
         raise SystemExit("the context window of this workload leaves no room to decode")
-    dec = Q8Decoder(cfg, batch=B, device=local_rank, tp_rank=rank, tp_world=world)
+    # exchange slots sized for a prompt chunk (rows x d partial sums per exchange), capped at 64 MB per slot
+    slot = max(B * cfg.d_model, B * cfg.vocab_size // world, min(B * min(w["prompt"], Q8Decoder.PREFILL_CHUNK) * cfg.d_model, 16 << 20))
+    dec = Q8Decoder(cfg, batch=B, device=local_rank, tp_rank=rank, tp_world=world, tp_slot_floats=slot if world > 1 else 0)
     if world > 1:
-        # weights are split by rows/columns over the ranks; [B x d] partial sums and the logits
+        # weights are split by rows/columns over the ranks; [rows x d] partial sums and the logits
         # shards cross NVLink through the library's own peer-memory exchange kernel
-        tp.connect(rank, world, max(B * cfg.d_model, B * cfg.vocab_size // world))
+        tp.connect(rank, world, slot)
     t_load = time.perf_counter()
     dec.load_synthetic(w["seed"], w["std"])
     if world > 1:
@@ -249,7 +251,7 @@ def main():
     dec.reset()
     t_load = time.perf_counter() - t_load
     t_prefill = time.perf_counter()
-    nxt = dec.prefill(prompts)          # one GPU: many-row path (tcgen05 GEMMs, chunk attention); several: one step per token
+    nxt = dec.prefill(prompts)          # many-row path (tcgen05 GEMMs, chunk attention; partial sums exchanged per chunk under tensor parallelism)
     t_prefill = time.perf_counter() - t_prefill
 
     lib = dec.lib
@@ -376,7 +378,7 @@ def main():
         "profile_ms": {"gemv": gemv_ms, "attention": attn_ms, "exchange": exch_ms, "all_ops": total_prof_ms},
         "setup_s": t_load,
         "prefill": {"tokens": int(B * w["prompt"]), "seconds": t_prefill, "tokens_per_s": B * w["prompt"] / max(t_prefill, 1e-9),
-                    "path": "chunked, many-row kernels" if world == 1 and w["prompt"] >= 32 else "one decode step per position"},
+                    "path": "chunked, many-row kernels" if w["prompt"] >= 32 else "one decode step per position"},
     }
     if cfg.kind == "gpt":
         line["cpu_baseline"] = None      # the C++ restatement covers the Llama / DeepSeek blocks; GPT's is numpy, in the tests

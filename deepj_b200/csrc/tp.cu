@@ -29,14 +29,14 @@ namespace dj {
 namespace {
 
 constexpr int kMaxWorld = 8;
-constexpr int kTpCtas = 8;                    // CTAs per exchange; each owns a contiguous chunk
+constexpr int kTpCtas = 8;                    // CTAs of a decode-sized exchange (larger messages get more)
 constexpr unsigned kTpSpinLimit = 1u << 21;   // polls of one word (≈ a second), then give up
 
 struct TpState {
     bool ready = false;
     int rank = 0, world = 1;
     size_t slot_floats = 0;
-    // layout of one rank's buffer: words[2][world][slot_floats] of {bits, epoch} (8 bytes each), then epochs[kTpCtas] u32
+    // layout of one rank's buffer: words[2][world][slot_floats] of {bits, epoch} (8 bytes each), then the exchange counter and the retire ticket (u32 each, private to this rank)
     void* local = nullptr;
     size_t bytes = 0;
     float* peer_data[kMaxWorld] = {};
@@ -71,7 +71,10 @@ __global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int wor
     pdl_wait();
     pdl_launch_dependents();
     const int cta = blockIdx.x, tid = threadIdx.x;
-    const unsigned epoch = epochs[cta] + 1;
+    // One exchange counter for the whole launch: it moves only when the launch's last CTA retires (ticket below),
+    // i.e. after every CTA has read it here, and the next launch reads it behind its dependency wait.  Every rank
+    // runs the same sequence of exchanges, so the ranks agree on it without ever communicating it.
+    const unsigned epoch = *reinterpret_cast<volatile unsigned*>(epochs) + 1;
     const unsigned parity = epoch & 1u;
     const int total = M * n_local;                       // floats this rank contributes
     const int pairs = (total + 1) >> 1;
@@ -133,7 +136,14 @@ __global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int wor
         }
     }
     __syncthreads();
-    if (tid == 0) epochs[cta] = epoch;
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(epochs + 1, 1u) == gridDim.x - 1) {
+            epochs[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned*>(epochs) = epoch;
+        }
+    }
 }
 
 }  // namespace
@@ -149,7 +159,12 @@ void launch_tp_exchange(const float* in, const float* bias, const float* residua
                                  std::to_string(T.slot_floats));
     TpPtrs P;
     for (int r = 0; r < kMaxWorld; r++) { P.data[r] = T.peer_data[r]; }
-    launch_k(k_tp_exchange, dim3(kTpCtas), dim3(256), 0, s, true, P, T.rank, T.world, T.slot_floats, T.epochs, in, bias, residual, out,
+    // a decode step's 16 KB message spreads over kTpCtas CTAs; a prompt chunk's megabytes over up to two CTAs per SM
+    const long pairs = ((long)M * n_local + 1) / 2;
+    long ctas = (pairs + 255) / 256;
+    if (ctas < kTpCtas) ctas = kTpCtas;
+    if (ctas > 2L * g_num_sms) ctas = 2L * g_num_sms;
+    launch_k(k_tp_exchange, dim3((unsigned)ctas), dim3(256), 0, s, true, P, T.rank, T.world, T.slot_floats, T.epochs, in, bias, residual, out,
              M, n_local, mode, g_dev_error);
 }
 

@@ -143,9 +143,12 @@ class Q8Decoder:
     """
 
     def __init__(self, cfg: DecoderConfig, batch: int = 1, device: int = 0, id_base: int = 1 << 24,
-                 tp_rank: int = 0, tp_world: int = 1):
+                 tp_rank: int = 0, tp_world: int = 1, tp_slot_floats: int = 0):
+        """`tp_slot_floats`: the slot size the exchange buffer was (or will be) connected with (`tp.connect`); it
+        bounds the rows a tensor-parallel prompt chunk may have (rows × dModel floats per exchange)."""
         self.cfg = cfg
         self.B = int(batch)
+        self.tp_slot_floats = int(tp_slot_floats)
         if tp_world < 1 or not (0 <= tp_rank < tp_world):
             raise ValueError("bad tensor-parallel rank / world size")
         if tp_world > 1 and cfg.kind == "gpt":
@@ -510,7 +513,8 @@ class Q8Decoder:
     def _build_prefill(self, T: int) -> np.ndarray:
         """The stream of one prompt chunk: T tokens of every sequence at once, B·T activation rows through the
         many-row Q8 kernels and the chunk attention op; the last token's hidden state lands in the decode
-        buffers and the positions advance by T.  (Single GPU; the row-major layout is row = b·T + t.)"""
+        buffers and the positions advance by T.  The row-major layout is row = b·T + t.  Under tensor parallelism
+        the Wo and down projections leave partial sums that the exchange op adds over the ranks, M rows at a time."""
         c, B, I, P = self.cfg, self.B, self.ids, self._prefill_ids
         d, dl, Fl, Hl = c.d_model, self.d_local, self.f_local, self.h_local
         M = B * T
@@ -534,10 +538,18 @@ class Q8Decoder:
                 s.extend(int(v) for v in (OP_Q8_LINEAR, P["lat"], c.q_rank, r, -1, eps, I[f"Wukv.{l}"], -1, -1, 0, 0, P["qkv"], dl, 3 * dl, M))
             s.extend(int(v) for v in (OP_ATTN_PREFILL, P["qkv"], 0, dl, 2 * dl, 3 * dl, I["kv"], l, I["pos"], I["cos"], I["sin"],
                                       P["att"], 0, dl, B, Hl, c.head_dim, T))
-            linear(P["att"], 0, dl, -1, I[f"Wo.{l}"], -1, P["x"], d, P["x2"], d)
+            if self.tp_world > 1:       # row-parallel projections leave partial sums; the exchange adds them (+ residual, + bias)
+                linear(P["att"], 0, dl, -1, I[f"Wo.{l}"], -1, -1, 0, P["part"], d)
+                s.extend((OP_TP_ALLREDUCE, P["part"], -1, P["x"], P["x2"], M, d))
+            else:
+                linear(P["att"], 0, dl, -1, I[f"Wo.{l}"], -1, P["x"], d, P["x2"], d)
             s.extend(int(v) for v in (OP_Q8_SWIGLU, P["x2"], 0, d, I[f"g2.{l}"], eps, I[f"Wg.{l}"], I[f"bg.{l}"], I[f"Wu.{l}"],
                                       I[f"bu.{l}"], P["h"], 0, Fl, M))
-            linear(P["h"], 0, Fl, -1, I[f"Wd.{l}"], I[f"bd.{l}"], P["x2"], d, P["x"], d)
+            if self.tp_world > 1:
+                linear(P["h"], 0, Fl, -1, I[f"Wd.{l}"], -1, -1, 0, P["part"], d)
+                s.extend((OP_TP_ALLREDUCE, P["part"], I[f"bd.{l}"], P["x2"], P["x"], M, d))
+            else:
+                linear(P["h"], 0, Fl, -1, I[f"Wd.{l}"], I[f"bd.{l}"], P["x2"], d, P["x"], d)
         for b in range(B):
             s.extend((OP_COPY, P["x"], (b * T + T - 1) * d, I["x"], b * d, d))
         s.extend((OP_ADD_SCALAR_INPLACE, I["pos"], float_bits(float(T)), B))
@@ -549,6 +561,9 @@ class Q8Decoder:
         if c.kind == "gpt":
             s = [OP_Q8_LINEAR_LN, I["x"], 0, c.d_model, I["gF"], I["bF"], float_bits(LN_EPS), I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0,
                  c.vocab_size, B, 0]
+        elif self.tp_world > 1:
+            s = [OP_Q8_LINEAR, I["x"], 0, c.d_model, I["gF"], float_bits(RMS_EPS), I["Wlm"], I["blm"], -1, 0, 0, I["logits_local"], 0, self.v_local, B,
+                 OP_TP_ALLGATHER, I["logits_local"], I["logits"], B, self.v_local]
         else:
             s = [OP_Q8_LINEAR, I["x"], 0, c.d_model, I["gF"], float_bits(RMS_EPS), I["Wlm"], I["blm"], -1, 0, 0, I["logits"], 0, c.vocab_size, B]
         s += [OP_ARGMAX_ROWS, I["logits"], I["next"], B, c.vocab_size]
@@ -557,24 +572,27 @@ class Q8Decoder:
     def prefill(self, prompts, chunked: Optional[bool] = None) -> np.ndarray:
         """Feed the prompt (every sequence the same length); returns the greedy pick after its last token.
         Prompts of 32 tokens or more go through the many-row path in chunks of PREFILL_CHUNK tokens per
-        sequence (tensor-core GEMMs, chunk attention); shorter ones, and tensor-parallel runs, one decode step
-        per position."""
+        sequence (tensor-core GEMMs, chunk attention); shorter ones one decode step per position.  Under tensor
+        parallelism a chunk's rows × dModel must fit the exchange slot (`tp_slot_floats`), which bounds the chunk."""
         p = np.asarray(prompts, dtype=np.int64).reshape(self.B, -1)
         T_all = p.shape[1]
+        tp_rows = self.tp_slot_floats // self.cfg.d_model // self.B if self.tp_world > 1 else 0      # tokens per sequence and chunk
         if chunked is None:
-            chunked = self.tp_world == 1 and T_all >= 32
+            chunked = T_all >= 32 and (self.tp_world == 1 or tp_rows >= 16)
         if not chunked or T_all == 0:
             nxt = None
             for t in range(T_all):
                 nxt = self.step(p[:, t])
             return nxt
-        if self.tp_world > 1:
-            raise ValueError("the chunked prefill path runs on one GPU")
+        if self.tp_world > 1 and tp_rows < 1:
+            raise ValueError("the exchange slot (tp_slot_floats) is smaller than one token per sequence")
         if np.any(p < 0) or np.any(p >= self.cfg.vocab_size):
             raise ValueError(f"Token id out of range: {int(p[(p < 0) | (p >= self.cfg.vocab_size)][0])}")
         if self.position + T_all > self.cfg.max_seq_len:
             raise ValueError(f"seqLen {self.position + T_all} exceeds maxSeqLen {self.cfg.max_seq_len}")
         C = min(self.PREFILL_CHUNK, T_all, max(1, 65535 // self.B))
+        if self.tp_world > 1:
+            C = min(C, tp_rows)
         self._ensure_prefill_buffers(C)
         done = 0
         while done < T_all:
@@ -605,6 +623,8 @@ class Q8Decoder:
             sizes["lat"] = M * (c.q_rank + c.kv_rank)
         if c.kind == "gpt":
             sizes["xp"], sizes["ppos"] = M * c.d_model, M
+        if self.tp_world > 1:
+            sizes["part"] = M * c.d_model
         self._prefill_ids = {}
         for name, n in sizes.items():
             self._prefill_ids[name] = self._f32("", n)

@@ -26,14 +26,17 @@ def main():
         cfg = DecoderConfig("deepseek", 512, 64, 512, 8, 2, 1024, q_rank=256, kv_rank=128)
     om = oracle.OracleModel(cfg.kind, cfg.vocab_size, cfg.max_seq_len, cfg.d_model, cfg.n_heads, cfg.n_layers, cfg.d_ff,
                             cfg.q_rank, cfg.kv_rank, seed=21)
-    B = 2
-    dec = Q8Decoder(cfg, batch=B, device=local, tp_rank=rank, tp_world=world)
-    tp.connect(rank, world, max(B * cfg.d_model, B * cfg.vocab_size // world))
+    B, T = 2, 40
+    # slots large enough for a 24-token chunk per sequence: the 40-token prompt goes through the many-row path in
+    # two chunks (24 + 16 tokens, 48 and 32 rows per exchange), the steps after it through the decode path
+    slot = max(B * 24 * cfg.d_model, B * cfg.vocab_size // world)
+    dec = Q8Decoder(cfg, batch=B, device=local, tp_rank=rank, tp_world=world, tp_slot_floats=slot)
+    tp.connect(rank, world, slot)
     dec.load_weights(weight_getter(om, cfg))
     om.apply_q8()
     tp.barrier()              # the exchange kernel's wait for a peer is bounded: start stepping together
     rng = np.random.default_rng(5)
-    prompts = rng.integers(0, cfg.vocab_size, size=(B, 12))
+    prompts = rng.integers(0, cfg.vocab_size, size=(B, T))
     dec.reset()
     nxt = dec.prefill(prompts)
     got_tokens = [nxt.copy()]
