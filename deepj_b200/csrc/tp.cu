@@ -29,14 +29,16 @@ namespace dj {
 namespace {
 
 constexpr int kMaxWorld = 8;
-constexpr int kTpCtas = 8;                    // CTAs of a decode-sized exchange (larger messages get more)
+constexpr int kTpCtas = 8;                    // CTAs of a decode-sized exchange
+constexpr int kTpCtasLarge = 296;             // CTAs of a chunk-sized exchange (a fixed number: the per-CTA counters depend on it)
+constexpr long kTpLargePairs = 1L << 16;      // messages above 2^17 floats take the large grid
 constexpr unsigned kTpSpinLimit = 1u << 21;   // polls of one word (≈ a second), then give up
 
 struct TpState {
     bool ready = false;
     int rank = 0, world = 1;
     size_t slot_floats = 0;
-    // layout of one rank's buffer: words[2][world][slot_floats] of {bits, epoch} (8 bytes each), then the exchange counter and the retire ticket (u32 each, private to this rank)
+    // layout of one rank's buffer: words[2][world][slot_floats] of {bits, epoch} (8 bytes each), then the per-CTA exchange counters (u32; kTpCtas for the small grid, kTpCtasLarge for the large one; private to this rank)
     void* local = nullptr;
     size_t bytes = 0;
     float* peer_data[kMaxWorld] = {};
@@ -64,18 +66,19 @@ constexpr int kTpPairsPerThread = 1;      // 2 values per thread and pass: a 16 
 
 // mode 0: out[m][n] = residual[m][n] + bias[n] + Σ_r contribution_r[m][n]   (n_local == N)
 // mode 1: out[m][r·n_local + j] = contribution_r[m][j]
-__global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int world, size_t slot_floats, unsigned* epochs,
+__global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int world, size_t slot_floats, unsigned* epochs, unsigned tag,
                                                       const float* __restrict__ in, const float* __restrict__ bias,
                                                       const float* __restrict__ residual, float* __restrict__ out,
                                                       int M, int n_local, int mode, int* error) {
     pdl_wait();
     pdl_launch_dependents();
     const int cta = blockIdx.x, tid = threadIdx.x;
-    // One exchange counter for the whole launch: it moves only when the launch's last CTA retires (ticket below),
-    // i.e. after every CTA has read it here, and the next launch reads it behind its dependency wait.  Every rank
-    // runs the same sequence of exchanges, so the ranks agree on it without ever communicating it.
-    const unsigned epoch = *reinterpret_cast<volatile unsigned*>(epochs) + 1;
-    const unsigned parity = epoch & 1u;
+    // Every CTA counts the exchanges it has taken part in; all ranks run the same sequence of exchanges with the same
+    // grids, so CTA i of every rank agrees on the count without communicating it.  The two grid sizes (decode-sized
+    // and chunk-sized messages) keep separate counters, and `tag` keeps their words apart in the shared slots.
+    const unsigned count = (epochs[cta] + 1) & 0x7fffffffu;
+    const unsigned epoch = count | tag;
+    const unsigned parity = count & 1u;
     const int total = M * n_local;                       // floats this rank contributes
     const int pairs = (total + 1) >> 1;
     const size_t slotWords = (size_t)parity * world * slot_floats;      // in 8-byte words
@@ -136,14 +139,7 @@ __global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int wor
         }
     }
     __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        if (atomicAdd(epochs + 1, 1u) == gridDim.x - 1) {
-            epochs[1] = 0u;
-            __threadfence();
-            *reinterpret_cast<volatile unsigned*>(epochs) = epoch;
-        }
-    }
+    if (tid == 0) epochs[cta] = count;
 }
 
 }  // namespace
@@ -159,12 +155,12 @@ void launch_tp_exchange(const float* in, const float* bias, const float* residua
                                  std::to_string(T.slot_floats));
     TpPtrs P;
     for (int r = 0; r < kMaxWorld; r++) { P.data[r] = T.peer_data[r]; }
-    // a decode step's 16 KB message spreads over kTpCtas CTAs; a prompt chunk's megabytes over up to two CTAs per SM
+    // a decode step's message (16 KB … 256 KB) spreads over kTpCtas CTAs; a prompt chunk's megabytes over kTpCtasLarge
     const long pairs = ((long)M * n_local + 1) / 2;
-    long ctas = (pairs + 255) / 256;
-    if (ctas < kTpCtas) ctas = kTpCtas;
-    if (ctas > 2L * g_num_sms) ctas = 2L * g_num_sms;
-    launch_k(k_tp_exchange, dim3((unsigned)ctas), dim3(256), 0, s, true, P, T.rank, T.world, T.slot_floats, T.epochs, in, bias, residual, out,
+    static const long largePairs = getenv("DEEPJ_CUDA_TP_LARGE_PAIRS") ? atol(getenv("DEEPJ_CUDA_TP_LARGE_PAIRS")) : kTpLargePairs;   // same on every rank
+    const bool large = pairs > largePairs;
+    launch_k(k_tp_exchange, dim3(large ? kTpCtasLarge : kTpCtas), dim3(256), 0, s, true, P, T.rank, T.world, T.slot_floats,
+             large ? T.epochs + kTpCtas : T.epochs, large ? 0x80000000u : 0u, in, bias, residual, out,
              M, n_local, mode, g_dev_error);
 }
 
@@ -183,7 +179,7 @@ int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void*
         if (T.local) throw std::runtime_error("tp_create: already created");
         T.rank = rank; T.world = world; T.slot_floats = (size_t)slot_floats;
         const size_t dataBytes = (size_t)2 * world * slot_floats * 8;       // {bits, epoch} per value
-        T.bytes = dataBytes + (size_t)kTpCtas * sizeof(unsigned);
+        T.bytes = dataBytes + (size_t)(kTpCtas + kTpCtasLarge) * sizeof(unsigned);
         DJ_CUDA_CHECK(cudaMalloc(&T.local, T.bytes));
         DJ_CUDA_CHECK(cudaMemset(T.local, 0, T.bytes));
         DJ_CUDA_CHECK(cudaDeviceSynchronize());
