@@ -210,9 +210,6 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
-        if w["kind"] == "gpt":
-            print(json.dumps({"impl": "reference", "unavailable": "no compiled CPU restatement of the GPT blocks (numpy one in tests/gpt_ref.py)"}))
-            return
         run_reference(args, w, args.workload)
         return
 
@@ -380,9 +377,7 @@ def main():
         "prefill": {"tokens": int(B * w["prompt"]), "seconds": t_prefill, "tokens_per_s": B * w["prompt"] / max(t_prefill, 1e-9),
                     "path": "chunked, many-row kernels" if w["prompt"] >= 32 else "one decode step per position"},
     }
-    if cfg.kind == "gpt":
-        line["cpu_baseline"] = None      # the C++ restatement covers the Llama / DeepSeek blocks; GPT's is numpy, in the tests
-    elif not args.no_cpu_baseline and rank == 0:
+    if not args.no_cpu_baseline and rank == 0:
         v, used, sample = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": used, "kind": "port", "sample": sample}
         if w["d"] <= 256:      # the tiny configuration: also the reference-faithful loop, full re-forward per token

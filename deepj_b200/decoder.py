@@ -250,6 +250,8 @@ class Q8Decoder:
         unsharded model."""
         c = self.cfg
         d = c.d_model
+        if c.kind == "gpt":
+            return [("Wqkv", d, ["Wq", "Wk", "Wv"]), ("Wo", d, ["Wo"]), ("W1", d, ["W1"]), ("W2", c.d_ff, ["W2"])]
         if c.kind == "llama":
             plan = [("Wqkv", d, ["Wq", "Wk", "Wv"]), ("Wo", d, ["Wo"])]
         else:

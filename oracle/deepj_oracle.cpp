@@ -674,12 +674,11 @@ void fillSynth(uint64_t seed, uint64_t& ordinal, std::vector<float>& w, size_t n
 // initMode 1: counter-based generator above, one ordinal per matrix in the same order.
 Model* buildModel(int kind, int V, int maxSeq, int d, int H, int L, int F, int qRank, int kvRank,
                   int64_t seed, int initMode, double std_, int nLayersBuilt) {
-    if (kind == GPT) throw std::runtime_error("GPT family is not built in the oracle yet");
     auto* m = new Model();
     m->kind = kind; m->V = V; m->maxSeq = maxSeq; m->d = d; m->H = H; m->L = L; m->F = F; m->qRank = qRank; m->kvRank = kvRank;
     int built = nLayersBuilt > 0 ? std::min(nLayersBuilt, L) : L;
     uint64_t ord = 0;
-    JRandom rEmb(seed), rStack(seed), rHead(seed + 1);
+    JRandom rEmb(seed), rStack(seed), rHead(seed + 1), rPos(seed + 2);
     auto fill = [&](JRandom& r, std::vector<float>& w, size_t n) {
         if (initMode == 0) fillJava(r, w, n, std_); else fillSynth((uint64_t)seed, ord, w, n, (float)std_);
     };
@@ -688,6 +687,16 @@ Model* buildModel(int kind, int V, int maxSeq, int d, int H, int L, int F, int q
     for (int l = 0; l < built; l++) {
         Block& b = m->blocks[l];
         b.g1.assign(d, 1.0f); b.g2.assign(d, 1.0f);
+        if (kind == GPT) {
+            // blocks/GPTTransformerBlock.java:61-64: ln1, ln2 (no draws), attention, then FNN's two Linear layers
+            // (layers/FNN.java:56-61; biases are zeros).  Wg / bg hold the hidden layer, Wd / bd the output layer.
+            b.b1n.assign(d, 0.0f); b.b2n.assign(d, 0.0f);
+            fill(rStack, b.Wq, (size_t)d * d); fill(rStack, b.Wk, (size_t)d * d);
+            fill(rStack, b.Wv, (size_t)d * d); fill(rStack, b.Wo, (size_t)d * d);
+            fill(rStack, b.Wg, (size_t)d * F); b.bg.assign(F, 0.0f);
+            fill(rStack, b.Wd, (size_t)F * d); b.bd.assign(d, 0.0f);
+            continue;
+        }
         if (kind == LLAMA) {
             fill(rStack, b.Wq, (size_t)d * d); fill(rStack, b.Wk, (size_t)d * d);
             fill(rStack, b.Wv, (size_t)d * d); fill(rStack, b.Wo, (size_t)d * d);
@@ -702,9 +711,25 @@ Model* buildModel(int kind, int V, int maxSeq, int d, int H, int L, int F, int q
     }
     // Skipped layers still consume their ordinals so that the LM head is the same
     // tensor whether or not every layer is materialised (synthetic mode only).
-    if (initMode == 1) ord += (uint64_t)(L - built) * (kind == LLAMA ? 7 : 9);
+    if (initMode == 1) ord += (uint64_t)(L - built) * (kind == LLAMA ? 7 : (kind == GPT ? 6 : 9));
     m->gF.assign(d, 1.0f);
     fill(rHead, m->Wlm, (size_t)d * V); m->blm.assign(V, 0.0f);
+    if (kind == GPT) {
+        // models/gpt/GPTModel.java:31-46: position table from Random(seed + 2), drawn after the LM head; then every
+        // parameter, gains included, is multiplied by initScale (GPTConfig's default 0.2f; :78-83).  In synthetic mode
+        // the table takes the ordinal after the LM head and nothing is rescaled (std is given directly).
+        m->bF.assign(d, 0.0f);
+        fill(rPos, m->pos, (size_t)maxSeq * d);
+        if (initMode == 0) {
+            const float f = 0.2f;
+            auto sc = [&](std::vector<float>& w) { for (auto& v : w) v = v * f; };
+            sc(m->emb); sc(m->pos); sc(m->gF); sc(m->bF); sc(m->Wlm); sc(m->blm);
+            for (auto& b : m->blocks) {
+                sc(b.g1); sc(b.b1n); sc(b.g2); sc(b.b2n); sc(b.Wq); sc(b.Wk); sc(b.Wv); sc(b.Wo);
+                sc(b.Wg); sc(b.bg); sc(b.Wd); sc(b.bd);
+            }
+        }
+    }
     int hd = d / H;
     m->cosT.resize((size_t)maxSeq * (hd / 2)); m->sinT.resize((size_t)maxSeq * (hd / 2));
     ropeTables(hd, maxSeq, m->cosT.data(), m->sinT.data());
@@ -713,6 +738,7 @@ Model* buildModel(int kind, int V, int maxSeq, int d, int H, int L, int F, int q
 
 // transformer/embeddings/RotaryEmbedding.java:112-122 on one row of headDim floats
 inline void ropeRow(const Model& m, float* row, int pos, int hd) {
+    if (m.kind == GPT) return;                      // plain MultiHeadSelfAttention: transformQueryKey is the identity
     int half = hd / 2;
     for (int i = 0; i < half; i++) {
         float c = m.cosT[(size_t)pos * half + i], s = m.sinT[(size_t)pos * half + i];
@@ -773,10 +799,12 @@ void forwardFull(Model& m, const int* ids, int seq, float* logits, int lastRowOn
         std::memcpy(&x.d[(size_t)i * d], &m.emb[(size_t)ids[i] * d], d * 4);
     }
     if (seq > m.maxSeq) throw std::runtime_error("seqLen " + std::to_string(seq) + " exceeds maxSeqLen " + std::to_string(m.maxSeq));
+    if (m.kind == GPT)      // GPTModel.embed: tokEmb.forward(ids).add(posEmb.forward(seq)) (embeddings/PositionalEmbedding.java:26-33)
+        for (int i = 0; i < seq; i++) for (int c = 0; c < d; c++) x.d[(size_t)i * d + c] = x.d[(size_t)i * d + c] + m.pos[(size_t)i * d + c];
     for (auto& b : m.blocks) {
         Mat n1, Q, K, V, merged, att;
-        rmsNorm(x, b.g1, n1);
-        if (m.kind == LLAMA) {
+        if (m.kind == GPT) layerNorm(x, b.g1, b.b1n, n1); else rmsNorm(x, b.g1, n1);
+        if (m.kind == LLAMA || m.kind == GPT) {
             linear(n1, b.Wq.data(), nullptr, d, d, Q);
             linear(n1, b.Wk.data(), nullptr, d, d, K);
             linear(n1, b.Wv.data(), nullptr, d, d, V);
@@ -793,10 +821,16 @@ void forwardFull(Model& m, const int* ids, int seq, float* logits, int lastRowOn
         Mat x2(seq, d);
         for (size_t i = 0; i < x2.d.size(); i++) x2.d[i] = x.d[i] + att.d[i];
         Mat n2, g, u, dn;
-        rmsNorm(x2, b.g2, n2);
-        linear(n2, b.Wg.data(), b.bg.data(), d, m.F, g);
-        linear(n2, b.Wu.data(), b.bu.data(), d, m.F, u);
-        for (size_t i = 0; i < g.d.size(); i++) { float sg = fSigmoid(g.d[i]); float si = g.d[i] * sg; g.d[i] = si * u.d[i]; }
+        if (m.kind == GPT) {        // blocks/GPTTransformerBlock.java:66-74, layers/FNN.java:70-88: Linear → GELU → Linear
+            layerNorm(x2, b.g2, b.b2n, n2);
+            linear(n2, b.Wg.data(), b.bg.data(), d, m.F, g);
+            for (size_t i = 0; i < g.d.size(); i++) g.d[i] = geluScalar(g.d[i]);
+        } else {
+            rmsNorm(x2, b.g2, n2);
+            linear(n2, b.Wg.data(), b.bg.data(), d, m.F, g);
+            linear(n2, b.Wu.data(), b.bu.data(), d, m.F, u);
+            for (size_t i = 0; i < g.d.size(); i++) { float sg = fSigmoid(g.d[i]); float si = g.d[i] * sg; g.d[i] = si * u.d[i]; }
+        }
         linear(g, b.Wd.data(), b.bd.data(), m.F, d, dn);
         for (size_t i = 0; i < x.d.size(); i++) x.d[i] = x2.d[i] + dn.d[i];
     }
@@ -804,11 +838,11 @@ void forwardFull(Model& m, const int* ids, int seq, float* logits, int lastRowOn
     if (lastRowOnly) {
         Mat last(1, d);
         std::memcpy(last.d.data(), &x.d[(size_t)(seq - 1) * d], d * 4);
-        rmsNorm(last, m.gF, nf);
+        if (m.kind == GPT) layerNorm(last, m.gF, m.bF, nf); else rmsNorm(last, m.gF, nf);
         linear(nf, m.Wlm.data(), m.blm.data(), d, m.V, lg);
         std::memcpy(logits, lg.d.data(), (size_t)m.V * 4);
     } else {
-        rmsNorm(x, m.gF, nf);
+        if (m.kind == GPT) layerNorm(x, m.gF, m.bF, nf); else rmsNorm(x, m.gF, nf);
         linear(nf, m.Wlm.data(), m.blm.data(), d, m.V, lg);
         std::memcpy(logits, lg.d.data(), (size_t)seq * m.V * 4);
     }
@@ -827,11 +861,12 @@ void decodeStep(Model& m, int token, float* logits) {
     float scale = (float)(1.0 / std::sqrt((double)hd));
     Mat x(1, d);
     std::memcpy(x.d.data(), &m.emb[(size_t)token * d], d * 4);
+    if (m.kind == GPT) for (int c = 0; c < d; c++) x.d[c] = x.d[c] + m.pos[(size_t)pos * d + c];
     for (size_t l = 0; l < m.blocks.size(); l++) {
         Block& b = m.blocks[l];
         Mat n1, Q, K, V, att;
-        rmsNorm(x, b.g1, n1);
-        if (m.kind == LLAMA) {
+        if (m.kind == GPT) layerNorm(x, b.g1, b.b1n, n1); else rmsNorm(x, b.g1, n1);
+        if (m.kind == LLAMA || m.kind == GPT) {
             linear(n1, b.Wq.data(), nullptr, d, d, Q);
             linear(n1, b.Wk.data(), nullptr, d, d, K);
             linear(n1, b.Wv.data(), nullptr, d, d, V);
@@ -868,15 +903,21 @@ void decodeStep(Model& m, int token, float* logits) {
         Mat x2(1, d);
         for (int i = 0; i < d; i++) x2.d[i] = x.d[i] + att.d[i];
         Mat n2, g, u, dn;
-        rmsNorm(x2, b.g2, n2);
-        linear(n2, b.Wg.data(), b.bg.data(), d, m.F, g);
-        linear(n2, b.Wu.data(), b.bu.data(), d, m.F, u);
-        for (size_t i = 0; i < g.d.size(); i++) { float sg = fSigmoid(g.d[i]); float si = g.d[i] * sg; g.d[i] = si * u.d[i]; }
+        if (m.kind == GPT) {
+            layerNorm(x2, b.g2, b.b2n, n2);
+            linear(n2, b.Wg.data(), b.bg.data(), d, m.F, g);
+            for (size_t i = 0; i < g.d.size(); i++) g.d[i] = geluScalar(g.d[i]);
+        } else {
+            rmsNorm(x2, b.g2, n2);
+            linear(n2, b.Wg.data(), b.bg.data(), d, m.F, g);
+            linear(n2, b.Wu.data(), b.bu.data(), d, m.F, u);
+            for (size_t i = 0; i < g.d.size(); i++) { float sg = fSigmoid(g.d[i]); float si = g.d[i] * sg; g.d[i] = si * u.d[i]; }
+        }
         linear(g, b.Wd.data(), b.bd.data(), m.F, d, dn);
         for (int i = 0; i < d; i++) x.d[i] = x2.d[i] + dn.d[i];
     }
     Mat nf, lg;
-    rmsNorm(x, m.gF, nf);
+    if (m.kind == GPT) layerNorm(x, m.gF, m.bF, nf); else rmsNorm(x, m.gF, nf);
     linear(nf, m.Wlm.data(), m.blm.data(), d, m.V, lg);
     std::memcpy(logits, lg.d.data(), (size_t)m.V * 4);
     m.cachePos++;
@@ -902,11 +943,17 @@ int greedyPick(const float* logits, int n) {
 
 std::vector<float>* weightByName(Model& m, const std::string& name, int layer) {
     if (name == "emb") return &m.emb;
+    if (name == "pos" && m.kind == GPT) return &m.pos;
+    if (name == "bF" && m.kind == GPT) return &m.bF;
     if (name == "gF") return &m.gF;
     if (name == "Wlm") return &m.Wlm;
     if (name == "blm") return &m.blm;
     if (layer < 0 || layer >= (int)m.blocks.size()) return nullptr;
     Block& b = m.blocks[layer];
+    if (m.kind == GPT) {              // the names Q8Decoder and the checkpoint layout use for the GPT family
+        if (name == "b1") return &b.b1n; if (name == "b2") return &b.b2n;
+        if (name == "W1") return &b.Wg;  if (name == "c1") return &b.bg;  if (name == "W2") return &b.Wd;  if (name == "c2") return &b.bd;
+    }
     if (name == "g1") return &b.g1;   if (name == "g2") return &b.g2;
     if (name == "Wq") return &b.Wq;   if (name == "Wk") return &b.Wk;   if (name == "Wv") return &b.Wv;   if (name == "Wo") return &b.Wo;
     if (name == "Wdq") return &b.Wdq; if (name == "Wuq") return &b.Wuq; if (name == "Wdkv") return &b.Wdkv;

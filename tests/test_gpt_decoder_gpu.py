@@ -164,6 +164,39 @@ def test_gpt_checkpoint_import(tmp_path):
     assert np.array_equal(outs[0], outs[1])
 
 
+def test_gpt_decoder_matches_the_cpp_oracle_with_java_exact_weights():
+    """`new GPTModel(cfg, seed)` as the oracle builds it (java.util.Random draw order, initScale 0.2): Q8 codes bit-exact,
+    logits within 2e-3 of their range and the same greedy tokens over a 20-token prompt and 24 new tokens."""
+    from test_decoder_gpu import run_parity
+    cfg = DecoderConfig("gpt", 256, 64, 128, 4, 3, 352)
+    prompt = list(np.random.default_rng(12).integers(0, 256, size=20))
+    run_parity(cfg, seed=17, prompt=prompt, n_new=24)
+
+
+def test_gpt_synthetic_weights_match_the_oracle_generator():
+    """Device-generated synthetic GPT weights (token and position tables, the blocks' matrices) are the oracle's
+    generator bit for bit, and the model decodes to the oracle's logits."""
+    from test_decoder_gpu import check_q8_bit_exact
+    cfg = DecoderConfig("gpt", 384, 48, 256, 4, 2, 640)
+    om = oracle.OracleModel("gpt", 384, 48, 256, 4, 2, 640, seed=6, init_mode=1, std=0.05)
+    dec = Q8Decoder(cfg, batch=1)
+    try:
+        dec.load_synthetic(6, 0.05)
+        for name, dev_name, n in (("emb", "emb", 384 * 256), ("pos", "posemb", 48 * 256)):
+            got = dec._download(dec.ids[dev_name], n)
+            assert np.array_equal(got.view(np.uint32), om.weight(name).view(np.uint32)), name
+        check_q8_bit_exact(dec, om, cfg, 1)
+        om.apply_q8()
+        prompt = list(np.random.default_rng(1).integers(0, 384, size=16))
+        toks_o, logits_o = om.generate_greedy(prompt, 8, use_cache=True)
+        toks_g, logits_g = dec.generate_greedy(prompt, 8, keep_logits=True)
+        span = float(logits_o.max() - logits_o.min())
+        assert float(np.abs(logits_o - logits_g).max()) <= LOGIT_TOL * span
+        assert np.array_equal(toks_o, toks_g)
+    finally:
+        dec.close()
+
+
 def test_gpt_runs_on_one_gpu_only():
     with pytest.raises(ValueError):
         Q8Decoder(DecoderConfig("gpt", 64, 32, 64, 2, 1, 64), tp_rank=0, tp_world=2)
