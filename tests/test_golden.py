@@ -58,3 +58,44 @@ def test_cuda_decoder_reproduces_golden_tokens_and_q8_arrays():
         assert np.abs(logits[0, :8] - np.asarray(G["logits_q8_step0_head"], dtype=np.float32)).max() <= 2e-3 * G["logits_q8_range"]
     finally:
         dec.close()
+
+
+GG = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tiny_gpt.json")))
+
+
+def gpt_model():
+    c = GG["config"]
+    return oracle.OracleModel("gpt", c["vocab"], c["max_seq"], c["d_model"], c["heads"], c["layers"], c["d_ff"], seed=c["weight_seed"])
+
+
+def test_oracle_reproduces_gpt_golden_vectors():
+    om = gpt_model()
+    assert [float(x) for x in om.weight("pos")[:8]] == GG["first_weights_pos"]
+    c1, s1 = oracle.q8_quantize(om.weight("W1", 1).reshape(128, 512))
+    assert (sha(c1), sha(s1)) == (GG["q8_W1_1_codes_sha256"], GG["q8_W1_1_scales_sha256"])
+    toks, logits = om.generate_greedy(GG["prompt"], 32, use_cache=True)
+    assert [int(t) for t in toks] == GG["tokens_fp32"]
+    assert [float(x) for x in logits[0, :8]] == GG["logits_fp32_step0_head"]
+    toks_full, _ = om.generate_greedy(GG["prompt"], 4, use_cache=False)         # the reference's own loop: full re-forward
+    assert [int(t) for t in toks_full] == GG["tokens_fp32"][:4]
+    om.apply_q8()
+    toks, logits = om.generate_greedy(GG["prompt"], 32, use_cache=True)
+    assert [int(t) for t in toks] == GG["tokens_q8"] and sha(logits) == GG["logits_q8_sha256"]
+
+
+@pytest.mark.gpu
+def test_cuda_decoder_reproduces_gpt_golden_tokens():
+    from deepj_b200.decoder import DecoderConfig, Q8Decoder
+    from test_decoder_gpu import weight_getter
+    c = GG["config"]
+    cfg = DecoderConfig("gpt", c["vocab"], c["max_seq"], c["d_model"], c["heads"], c["layers"], c["d_ff"])
+    dec = Q8Decoder(cfg, batch=1)
+    try:
+        dec.load_weights(weight_getter(gpt_model(), cfg))
+        codes, scales = dec.q8_arrays("W1.1")
+        assert sha(codes) == GG["q8_W1_1_codes_sha256"] and sha(scales) == GG["q8_W1_1_scales_sha256"]
+        toks, logits = dec.generate_greedy(GG["prompt"], 32, keep_logits=True)
+        assert [int(t) for t in toks] == GG["tokens_q8"]
+        assert np.abs(logits[0, :8] - np.asarray(GG["logits_q8_step0_head"], dtype=np.float32)).max() <= 2e-3 * GG["logits_q8_range"]
+    finally:
+        dec.close()
