@@ -232,8 +232,12 @@ def main():
     room = w["max_seq"] - w["prompt"] - 1          # decode steps that fit behind the prompt
     if room < 8:
         raise SystemExit("the context window of this workload leaves no room to decode")
-    # exchange slots sized for a prompt chunk (rows x d partial sums per exchange), capped at 64 MB per slot
-    slot = max(B * cfg.d_model, B * cfg.vocab_size // world, min(B * min(w["prompt"], Q8Decoder.PREFILL_CHUNK) * cfg.d_model, 16 << 20))
+    # exchange slots sized for a prompt chunk (rows x d partial sums per exchange), capped at 64 MB per slot.  The chunked
+    # tensor-parallel prompt pass has been run on 2 GPUs only; larger worlds take one decode step per prompt position
+    # (measured on 4 and 8 GPUs) unless DEEPJ_BENCH_TP_CHUNKED=1 asks for chunks there too.
+    slot = max(B * cfg.d_model, B * cfg.vocab_size // world)
+    if world == 2 or os.environ.get("DEEPJ_BENCH_TP_CHUNKED") == "1":
+        slot = max(slot, min(B * min(w["prompt"], Q8Decoder.PREFILL_CHUNK) * cfg.d_model, 16 << 20))
     dec = Q8Decoder(cfg, batch=B, device=local_rank, tp_rank=rank, tp_world=world, tp_slot_floats=slot if world > 1 else 0)
     if world > 1:
         # weights are split by rows/columns over the ranks; [rows x d] partial sums and the logits
@@ -375,7 +379,7 @@ def main():
         "profile_ms": {"gemv": gemv_ms, "attention": attn_ms, "exchange": exch_ms, "all_ops": total_prof_ms},
         "setup_s": t_load,
         "prefill": {"tokens": int(B * w["prompt"]), "seconds": t_prefill, "tokens_per_s": B * w["prompt"] / max(t_prefill, 1e-9),
-                    "path": "chunked, many-row kernels" if w["prompt"] >= 32 else "one decode step per position"},
+                    "path": "chunked, many-row kernels" if w["prompt"] >= 32 and (world == 1 or slot >= 16 * B * cfg.d_model) else "one decode step per position"},
     }
     if not args.no_cpu_baseline and rank == 0:
         v, used, sample = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))
