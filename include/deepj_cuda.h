@@ -114,7 +114,9 @@ int deepj_cuda_kv_alloc(int32_t kv_id, int32_t layers, int32_t batch, int32_t he
 
 /* Tensor parallelism, one process per GPU of one node.  No counterpart in the reference
  * (DeepJ is single-device).  Every rank calls tp_create (allocates its exchange buffer:
- * 2 x world slots of slot_floats floats plus flags, returns a 64-byte CUDA IPC handle),
+ * 2 x world slots of slot_floats values, 8 bytes each, returns a 64-byte CUDA IPC handle; one exchange
+ * carries at most slot_floats values per rank: M x N of op 71, M x n_local of op 72 - batch x dModel for decode
+ * steps, rows x dModel for prompt chunks),
  * the host exchanges the handles by any means (the Python runner uses torch.distributed),
  * then every rank calls tp_connect with all handles in rank order.  After that op codes 71
  * and 72 may appear in streams; every rank must flush the same sequence of them.  Waits
