@@ -78,10 +78,12 @@ constexpr int kStageRounds = 3;             // rows of up to 3·256·16 = 12288 
 
 // GPT = true adds LayerNorm1D (norm/LayerNorm1D.java:34-71: mean, biased variance, (x − mean)/√(var + eps)·γ + β)
 // to the staging and GELU to the epilogue; the Llama / DeepSeek instantiation carries neither.
-template <bool SWIGLU, int DEPTH, bool GPT>
+// NM = 2 takes three or four activation rows in one pass over the weights: a second MMA per block whose eight
+// columns are the digits of rows 2 and 3.
+template <bool SWIGLU, int DEPTH, bool GPT, int NM>
 __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    // layout: rings [warps][DEPTH][kSlotBytes], digits int8 [3M][K+pad], block scales fp32 [M][K/32], partials [2][warps][16][8]
+    // layout: rings [warps][DEPTH][kSlotBytes], digits int8 [3M][K+pad], block scales fp32 [M][K/32], partials [2][warps][NM][16][8]
     const int ldxs = p.K + kXsPad;
     int8_t* xd = reinterpret_cast<int8_t*>(smem + (size_t)kWarps * DEPTH * kSlotBytes);
     float* xsc = reinterpret_cast<float*>(smem + (size_t)kWarps * DEPTH * kSlotBytes + (size_t)kColsPerRow * p.M * ldxs);
@@ -297,12 +299,19 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
     }
     if (tracing) p.trace[3] = gtime();
 
-    // lane (g,t) feeds MMA column g: activation row g/4, digit g%4 (digit 3 does not exist)
-    const bool hasCol = (g >> 2) < p.M && (g & 3) != 3;
-    const unsigned char* xcol = reinterpret_cast<const unsigned char*>(xd) + (size_t)(hasCol ? kColsPerRow * (g >> 2) + (g & 3) : 0) * ldxs + t * 8;
-    // the lane's two result columns 2t, 2t+1 belong to activation row t/2
-    const float* myxsc = xsc + (size_t)((t >> 1) < p.M ? (t >> 1) : 0) * nBlocks;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // lane (g,t) feeds column g of MMA q: activation row 2q + g/4, digit g%4 (digit 3 does not exist)
+    bool hasCol[NM]; const unsigned char* xcol[NM]; const float* myxsc[NM];
+    float acc[NM][4];
+#pragma unroll
+    for (int q = 0; q < NM; q++) {
+        const int mrow = 2 * q + (g >> 2);
+        hasCol[q] = mrow < p.M && (g & 3) != 3;
+        xcol[q] = reinterpret_cast<const unsigned char*>(xd) + (size_t)(hasCol[q] ? kColsPerRow * mrow + (g & 3) : 0) * ldxs + t * 8;
+        // the lane's two result columns 2t, 2t+1 belong to activation row 2q + t/2
+        const int rrow = 2 * q + (t >> 1);
+        myxsc[q] = xsc + (size_t)(rrow < p.M ? rrow : 0) * nBlocks;
+        acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.0f;
+    }
     int cslot = 0, buf = 0;
     int aoff[2];
 #pragma unroll
@@ -329,33 +338,39 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
                 const float s0 = *reinterpret_cast<const float*>(slot + soff + h * 4);
                 const float s1 = *reinterpret_cast<const float*>(slot + soff + 64 + h * 4);
                 const int blk = pi * 2 + h;
-                uint2 xb = make_uint2(0u, 0u);
-                if (hasCol) xb = *reinterpret_cast<const uint2*>(xcol + blk * 32);
-                int cc[4] = {0, 0, 0, 0};
-                mma_s8_16832(cc, a.x, d.x, a.y, d.y, xb.x, xb.y);
-                const float xs_ = blk < nBlocks ? myxsc[blk] : 0.0f;     // the empty half of an odd last pair adds nothing
-                const float f0 = s0 * xs_, f1 = s1 * xs_;
-                acc[0] = fmaf(f0, (float)cc[0], acc[0]);
-                acc[1] = fmaf(f0, (float)cc[1], acc[1]);
-                acc[2] = fmaf(f1, (float)cc[2], acc[2]);
-                acc[3] = fmaf(f1, (float)cc[3], acc[3]);
+#pragma unroll
+                for (int q = 0; q < NM; q++) {
+                    uint2 xb = make_uint2(0u, 0u);
+                    if (hasCol[q]) xb = *reinterpret_cast<const uint2*>(xcol[q] + blk * 32);
+                    int cc[4] = {0, 0, 0, 0};
+                    mma_s8_16832(cc, a.x, d.x, a.y, d.y, xb.x, xb.y);
+                    const float xs_ = blk < nBlocks ? myxsc[q][blk] : 0.0f;     // the empty half of an odd last pair adds nothing
+                    const float f0 = s0 * xs_, f1 = s1 * xs_;
+                    acc[q][0] = fmaf(f0, (float)cc[0], acc[q][0]);
+                    acc[q][1] = fmaf(f0, (float)cc[1], acc[q][1]);
+                    acc[q][2] = fmaf(f1, (float)cc[2], acc[q][2]);
+                    acc[q][3] = fmaf(f1, (float)cc[3], acc[q][3]);
+                }
             }
             __syncwarp();
             cslot = cslot + 1 == DEPTH ? 0 : cslot + 1;
         }
         if (tracing && tile == blockIdx.x) p.trace[4] = gtime();
         // ── tile epilogue: reduce the warps' column subsets, recombine the digits ──
-        float* part = s_part + (size_t)buf * kWarps * 128;
-        float* mine = part + warp * 128;
-        mine[g * 8 + 2 * t] = acc[0];       mine[g * 8 + 2 * t + 1] = acc[1];
-        mine[(g + 8) * 8 + 2 * t] = acc[2]; mine[(g + 8) * 8 + 2 * t + 1] = acc[3];
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+        float* part = s_part + (size_t)buf * kWarps * NM * 128;
+#pragma unroll
+        for (int q = 0; q < NM; q++) {
+            float* mine = part + (warp * NM + q) * 128;
+            mine[g * 8 + 2 * t] = acc[q][0];       mine[g * 8 + 2 * t + 1] = acc[q][1];
+            mine[(g + 8) * 8 + 2 * t] = acc[q][2]; mine[(g + 8) * 8 + 2 * t + 1] = acc[q][3];
+            acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.0f;
+        }
         __syncthreads();
         if (em < p.M && en < p.N) {
             float a2 = 0.0f, a1 = 0.0f, a0 = 0.0f, b2 = 0.0f, b1 = 0.0f, b0 = 0.0f;
 #pragma unroll
             for (int q = 0; q < kWarps; q++) {
-                const float* pr = part + q * 128 + er * 8 + 4 * em;      // MMA columns 4m .. 4m+2
+                const float* pr = part + (q * NM + (em >> 1)) * 128 + er * 8 + 4 * (em & 1);      // MMA em/2, columns 4(em%2) .. +2
                 a2 += pr[0]; a1 += pr[1]; a0 += pr[2];
                 if (SWIGLU) { b2 += pr[64]; b1 += pr[65]; b0 += pr[66]; }
             }
@@ -382,14 +397,14 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
 
 size_t i8_smem_bytes(int K, int M, int depth) {
     return (size_t)kWarps * depth * kSlotBytes + (size_t)kColsPerRow * M * (K + kXsPad) + (size_t)M * (K / 32) * 4 +
-           (size_t)2 * kWarps * 128 * 4;
+           (size_t)2 * kWarps * (M > 2 ? 2 : 1) * 128 * 4;
 }
 
-template <bool SWIGLU, int DEPTH, bool GPT>
+template <bool SWIGLU, int DEPTH, bool GPT, int NM>
 void launch_i8(const TmaParams& p, cudaStream_t s) {
     static bool attrSet = false;
     if (!attrSet) {
-        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemv_i8<SWIGLU, DEPTH, GPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
+        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemv_i8<SWIGLU, DEPTH, GPT, NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
         attrSet = true;
     }
     int rowsPerTile = SWIGLU ? 8 : 16;
@@ -401,19 +416,27 @@ void launch_i8(const TmaParams& p, cudaStream_t s) {
     int gx = (nTiles + rounds - 1) / rounds;
     static const bool evenGrid = getenv("DEEPJ_CUDA_GEMV_FULLGRID") == nullptr;
     if (!evenGrid) gx = nTiles < cap ? nTiles : cap;
-    launch_k(k_q8_gemv_i8<SWIGLU, DEPTH, GPT>, dim3(gx), dim3(kThreads), i8_smem_bytes(p.K, p.M, DEPTH), s, true, p);
+    launch_k(k_q8_gemv_i8<SWIGLU, DEPTH, GPT, NM>, dim3(gx), dim3(kThreads), i8_smem_bytes(p.K, p.M, DEPTH), s, true, p);
 }
 
 template <bool SWIGLU, bool GPT>
 void launch_i8_depth(const TmaParams& p, int depth, cudaStream_t s) {
+    if (p.M > 2) {      // two MMAs per block; the digits of four rows leave room for a ring of at most five items
+        switch (depth) {
+            case 3: launch_i8<SWIGLU, 3, GPT, 2>(p, s); break;
+            case 4: launch_i8<SWIGLU, 4, GPT, 2>(p, s); break;
+            default: launch_i8<SWIGLU, 5, GPT, 2>(p, s); break;
+        }
+        return;
+    }
     switch (depth) {
-        case 3: launch_i8<SWIGLU, 3, GPT>(p, s); break;
-        case 4: launch_i8<SWIGLU, 4, GPT>(p, s); break;
-        case 5: launch_i8<SWIGLU, 5, GPT>(p, s); break;
-        case 6: launch_i8<SWIGLU, 6, GPT>(p, s); break;
-        case 7: launch_i8<SWIGLU, 7, GPT>(p, s); break;
-        case 8: launch_i8<SWIGLU, 8, GPT>(p, s); break;
-        default: launch_i8<SWIGLU, 9, GPT>(p, s); break;
+        case 3: launch_i8<SWIGLU, 3, GPT, 1>(p, s); break;
+        case 4: launch_i8<SWIGLU, 4, GPT, 1>(p, s); break;
+        case 5: launch_i8<SWIGLU, 5, GPT, 1>(p, s); break;
+        case 6: launch_i8<SWIGLU, 6, GPT, 1>(p, s); break;
+        case 7: launch_i8<SWIGLU, 7, GPT, 1>(p, s); break;
+        case 8: launch_i8<SWIGLU, 8, GPT, 1>(p, s); break;
+        default: launch_i8<SWIGLU, 9, GPT, 1>(p, s); break;
     }
 }
 
@@ -438,11 +461,12 @@ bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s) {
     const size_t budget = 111 * 1024;
     if (i8_smem_bytes(K, 1, 3) > budget) return false;
     for (int m0 = 0; m0 < a.M;) {
-        int rows = a.M - m0 < 2 ? a.M - m0 : 2;      // 8 MMA columns = 2 activation rows × (3 digits + 1 unused)
+        static const int maxRows = getenv("DEEPJ_CUDA_GEMV_ROWS") ? atoi(getenv("DEEPJ_CUDA_GEMV_ROWS")) : 4;
+        int rows = a.M - m0 < maxRows ? a.M - m0 : maxRows;      // 8 MMA columns = 2 activation rows × (3 digits + 1 unused); 3-4 rows take a second MMA
         while (rows > 1 && i8_smem_bytes(K, rows, 3) > budget) rows--;
         static int wantDepth = 0;
         if (wantDepth == 0) { const char* e = getenv("DEEPJ_CUDA_GEMV_DEPTH"); wantDepth = e ? atoi(e) : 5; if (wantDepth < 3) wantDepth = 3; if (wantDepth > 9) wantDepth = 9; }
-        int depth = wantDepth;      // default: four items (4 KB) per warp in flight, 64 KB per SM
+        int depth = rows > 2 && wantDepth > 5 ? 5 : wantDepth;      // default: four items (4 KB) per warp in flight, 64 KB per SM
         while (depth > 3 && i8_smem_bytes(K, rows, depth) > budget) depth--;
         TmaParams p;
         p.x = a.x + (size_t)m0 * a.ldx; p.ldx = a.ldx; p.gamma = a.gamma; p.eps = a.eps;
