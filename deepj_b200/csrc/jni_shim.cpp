@@ -138,6 +138,34 @@ JNIEXPORT void JNICALL CUDA_NATIVE(nativeKvAlloc)(JNIEnv* env, jclass, jint kvId
     if (deepj_cuda_kv_alloc(kvId, layers, batch, heads, maxSeq, headDim) != 0) raise_last(env);
 }
 
+// ───────────── tensor parallelism: one JVM per GPU, the host exchanges the 64-byte handles ─────────────
+
+// Allocates this rank's exchange buffer and returns its CUDA IPC handle (64 bytes), or null with an exception pending.
+JNIEXPORT jbyteArray JNICALL CUDA_NATIVE(nativeTpCreate)(JNIEnv* env, jclass, jint rank, jint world, jlong slotFloats) {
+    jbyte handle[64];
+    if (deepj_cuda_tp_create(rank, world, slotFloats, handle) != 0) { raise_last(env); return nullptr; }
+    jbyteArray out = env->NewByteArray(64);
+    if (out == nullptr) { raise(env, "nativeTpCreate: could not allocate the handle array"); return nullptr; }
+    env->SetByteArrayRegion(out, 0, 64, handle);
+    return out;
+}
+
+// handles: world × 64 bytes in rank order.
+JNIEXPORT void JNICALL CUDA_NATIVE(nativeTpConnect)(JNIEnv* env, jclass, jbyteArray handles, jint world) {
+    if (handles == nullptr) { raise(env, "nativeTpConnect: null handles"); return; }
+    const jsize len = env->GetArrayLength(handles);
+    if (world < 1 || (jlong)len != (jlong)world * 64) { raise(env, "nativeTpConnect: expected world x 64 handle bytes"); return; }
+    jbyte* p = env->GetByteArrayElements(handles, nullptr);
+    if (p == nullptr) { raise(env, "nativeTpConnect: handles could not be read"); return; }
+    const int rc = deepj_cuda_tp_connect(p, world);
+    env->ReleaseByteArrayElements(handles, p, JNI_ABORT);
+    if (rc != 0) raise_last(env);
+}
+
+JNIEXPORT void JNICALL CUDA_NATIVE(nativeTpDestroy)(JNIEnv* env, jclass) {
+    if (deepj_cuda_tp_destroy() != 0) raise_last(env);
+}
+
 // Library counters (launches, graph replays, device error code, …) into out[0 .. out.length).
 JNIEXPORT void JNICALL CUDA_NATIVE(nativeStats)(JNIEnv* env, jclass, jlongArray outArr) {
     if (outArr == nullptr) { raise(env, "nativeStats: null array"); return; }

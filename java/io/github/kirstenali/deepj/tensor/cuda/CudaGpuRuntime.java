@@ -71,6 +71,20 @@ public final class CudaGpuRuntime implements GpuRuntime {
         CudaNative.nativeKvAlloc(kvId, layers, batch, heads, maxSeq, headDim);
     }
 
+    /** Step 1 of the tensor-parallel set-up: this rank's 64-byte handle, to be sent to every other rank. */
+    public byte[] tpCreate(int rank, int world, long slotFloats) {
+        return CudaNative.nativeTpCreate(rank, world, slotFloats);
+    }
+
+    /** Step 2: every rank's handle concatenated in rank order; afterwards op codes 71 / 72 may be recorded. */
+    public void tpConnect(byte[] handles, int world) {
+        CudaNative.nativeTpConnect(handles, world);
+    }
+
+    public void tpDestroy() {
+        CudaNative.nativeTpDestroy();
+    }
+
     public long[] stats() {
         long[] out = new long[8];
         CudaNative.nativeStats(out);

@@ -83,6 +83,14 @@ final class CudaNative {
     /** K and V planes of [layers][batch][heads][maxSeq][headDim] floats, zero-filled. */
     static native void nativeKvAlloc(int kvId, int layers, int batch, int heads, int maxSeq, int headDim);
 
+    /** Tensor parallelism, one JVM per GPU: allocates this rank's exchange buffer, returns its 64-byte IPC handle. */
+    static native byte[] nativeTpCreate(int rank, int world, long slotFloats);
+
+    /** All ranks' handles (world × 64 bytes, rank order), exchanged by the host's own means. */
+    static native void nativeTpConnect(byte[] handles, int world);
+
+    static native void nativeTpDestroy();
+
     /** Library counters into out (launches, graph replays, device-side error code at index 5, …). */
     static native void nativeStats(long[] out);
 }

@@ -31,6 +31,8 @@ static void fill(_jarray* a, const void* data, int n, size_t elem) {
 }
 JNIEXPORT void* fj_ints_new(const int32_t* data, int n) { auto* a = new _jintArray(); fill(a, data, n, 4); return a; }
 JNIEXPORT void* fj_floats_new(const float* data, int n) { auto* a = new _jfloatArray(); fill(a, data, n, 4); return a; }
+JNIEXPORT void* fj_bytes_new(const int8_t* data, int n) { auto* a = new _jbyteArray(); fill(a, data, n, 1); return a; }
+JNIEXPORT int fj_array_length(void* a) { return static_cast<_jarray*>(a)->length; }
 JNIEXPORT void* fj_longs_new(int n) { auto* a = new _jlongArray(); fill(a, nullptr, n, 8); return a; }
 JNIEXPORT void fj_array_read(void* a, void* out) {
     auto* arr = static_cast<_jarray*>(a);

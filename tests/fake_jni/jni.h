@@ -20,6 +20,7 @@ typedef int64_t jlong;
 typedef float jfloat;
 typedef jint jsize;
 typedef uint8_t jboolean;
+typedef int8_t jbyte;
 
 struct _jobject { virtual ~_jobject() {} };
 struct _jclass : _jobject { std::string name; };
@@ -31,12 +32,14 @@ struct _jarray : _jobject {
 struct _jintArray : _jarray {};
 struct _jfloatArray : _jarray {};
 struct _jlongArray : _jarray {};
+struct _jbyteArray : _jarray {};
 typedef _jobject* jobject;
 typedef _jclass* jclass;
 typedef _jarray* jarray;
 typedef _jintArray* jintArray;
 typedef _jfloatArray* jfloatArray;
 typedef _jlongArray* jlongArray;
+typedef _jbyteArray* jbyteArray;
 
 struct JNIEnv {
     struct Release { const void* array; int mode; };
@@ -48,6 +51,8 @@ struct JNIEnv {
     _jclass runtime_exception;
     // Elements handed out by Get<T>ArrayElements are copies, as a moving collector would make them.
     std::vector<std::vector<uint8_t>> copies;
+    std::vector<_jarray*> created;
+    ~JNIEnv() { for (auto* a : created) delete a; }
 
     void note() { if (in_critical) ++calls_in_critical; }
 
@@ -76,6 +81,31 @@ struct JNIEnv {
         in_critical = false;
         if (mode != JNI_COMMIT) --a->pins;
         releases.push_back({a, mode});
+    }
+    jbyte* GetByteArrayElements(jbyteArray a, jboolean* is_copy) {
+        note();
+        copies.emplace_back(a->bytes);
+        ++a->pins;
+        if (is_copy) *is_copy = 1;
+        return reinterpret_cast<jbyte*>(copies.back().data());
+    }
+    void ReleaseByteArrayElements(jbyteArray a, jbyte* p, jint mode) {
+        note();
+        if (mode != JNI_ABORT) std::memcpy(a->bytes.data(), p, a->bytes.size());
+        if (mode != JNI_COMMIT) --a->pins;
+        releases.push_back({a, mode});
+    }
+    jbyteArray NewByteArray(jsize n) {            // owned by the env, like a local reference
+        note();
+        auto* a = new _jbyteArray();
+        a->length = n;
+        a->bytes.resize(static_cast<size_t>(n));
+        created.push_back(a);
+        return a;
+    }
+    void SetByteArrayRegion(jbyteArray a, jsize start, jsize n, const jbyte* src) {
+        note();
+        std::memcpy(a->bytes.data() + start, src, static_cast<size_t>(n));
     }
     jclass FindClass(const char* name) {
         note();

@@ -21,7 +21,7 @@ PREFIX = "Java_io_github_kirstenali_deepj_tensor_cuda_CudaNative_"
 JNI_ABORT = 2
 NATIVES = ["nativeAllocBuffers", "nativeUploadBuffer", "nativeDownloadBuffer", "nativeReleaseBuffers", "nativeFlushOps",
            "nativeFlushOpsAsync", "nativeSynchronize", "nativeInit", "nativeShutdown", "nativeQ8Alloc",
-           "nativeQ8QuantizeInto", "nativeKvAlloc", "nativeStats"]
+           "nativeQ8QuantizeInto", "nativeKvAlloc", "nativeStats", "nativeTpCreate", "nativeTpConnect", "nativeTpDestroy"]
 
 
 @pytest.fixture(scope="module")
@@ -34,6 +34,9 @@ def shim(tmp_path_factory):
     res = subprocess.run(cmd, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr
     lib = ctypes.CDLL(out)
+    lib.fj_bytes_new.restype = ctypes.c_void_p
+    lib.fj_bytes_new.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.fj_array_length.argtypes = [ctypes.c_void_p]
     for name, restype in (("fj_env_new", ctypes.c_void_p), ("fj_ints_new", ctypes.c_void_p), ("fj_floats_new", ctypes.c_void_p),
                           ("fj_longs_new", ctypes.c_void_p), ("fj_thrown_class", ctypes.c_char_p),
                           ("fj_thrown_message", ctypes.c_char_p), ("fj_release_array", ctypes.c_void_p)):
@@ -70,6 +73,12 @@ class Jvm:
         self.arrays.append(h)
         return h
 
+    def bytes_(self, values):
+        a = np.ascontiguousarray(values, dtype=np.int8)
+        h = ctypes.c_void_p(self.lib.fj_bytes_new(a.ctypes.data, a.size))
+        self.arrays.append(h)
+        return h
+
     def longs(self, n):
         h = ctypes.c_void_p(self.lib.fj_longs_new(n))
         self.arrays.append(h)
@@ -80,11 +89,11 @@ class Jvm:
         self.lib.fj_array_read(handle, out.ctypes.data)
         return out
 
-    def call(self, name, *args):
+    def call(self, name, *args, restype=None):
         fn = getattr(self.lib, PREFIX + name)
-        fn.restype = None
-        conv = [a if isinstance(a, ctypes.c_void_p) else ctypes.c_int32(a) for a in args]
-        fn(self.env, None, *conv)
+        fn.restype = restype
+        conv = [a if isinstance(a, (ctypes.c_void_p, ctypes.c_int64)) else ctypes.c_int32(a) for a in args]
+        return fn(self.env, None, *conv)
 
     def exception(self):
         if not self.lib.fj_pending(self.env):
@@ -125,7 +134,7 @@ def test_natives_match_the_java_declarations():
     """java/…/CudaNative.java declares exactly the natives the shim defines."""
     import re
     src = open(os.path.join(ROOT, "java", "io", "github", "kirstenali", "deepj", "tensor", "cuda", "CudaNative.java")).read()
-    declared = re.findall(r"static native \w+ (\w+)\(", src)
+    declared = re.findall(r"static native [\w\[\]]+ (\w+)\(", src)
     assert sorted(declared) == sorted(NATIVES)
 
 
@@ -153,6 +162,15 @@ def test_null_arrays_raise(jvm):
         assert jvm.exception() is not None, name
 
 
+def test_tp_connect_checks_the_handle_array_before_touching_the_library(jvm):
+    jvm.call("nativeTpConnect", jvm.bytes_(np.zeros(100)), 2)
+    assert "world x 64" in jvm.exception()[1]
+    jvm.clear()
+    jvm.call("nativeTpConnect", ctypes.c_void_p(None), 2)
+    assert jvm.exception() is not None
+    jvm.check_unpinned()
+
+
 def _no_cuda_device():
     import torch
     return not torch.cuda.is_available()
@@ -166,6 +184,9 @@ def test_library_failure_becomes_a_runtime_exception_and_releases_the_arrays(jvm
     cls, msg = jvm.exception()
     assert cls == "java/lang/RuntimeException" and "CUDA" in msg
     assert jvm.releases() == [(cmd.value, JNI_ABORT)]
+    jvm.clear()
+    got = jvm.call("nativeTpCreate", 0, 2, ctypes.c_int64(1024), restype=ctypes.c_void_p)
+    assert got is None and jvm.exception() is not None               # no handle, an exception instead
     jvm.clear()
     out = jvm.floats(np.full(4, 5.0))
     jvm.call("nativeDownloadBuffer", 1, out)
@@ -254,3 +275,24 @@ def test_q8_and_kv_natives_build_a_projection(jvm):
     jvm.call("nativeReleaseBuffers", jvm.ints([w_id, x_id, y_id, q_id, kv_id]), 5)
     assert jvm.exception() is None
     jvm.check_unpinned()
+
+
+@pytest.mark.gpu
+def test_tp_natives_create_connect_destroy_on_one_rank(jvm):
+    """A world of one: the handle comes back as a 64-byte array, connecting it maps no peer, destroy frees the buffer."""
+    jvm.call("nativeInit", 0)
+    handle = jvm.call("nativeTpCreate", 0, 1, ctypes.c_int64(1024), restype=ctypes.c_void_p)
+    assert jvm.exception() is None and handle
+    handle = ctypes.c_void_p(handle)
+    assert jvm.lib.fj_array_length(handle) == 64
+    try:
+        jvm.call("nativeTpConnect", handle, 1)
+        assert jvm.exception() is None
+        assert [m for _, m in jvm.releases()][-1] == JNI_ABORT
+        jvm.clear()
+        jvm.call("nativeTpCreate", 0, 1, ctypes.c_int64(1024), restype=ctypes.c_void_p)      # a second buffer is refused
+        assert "already created" in jvm.exception()[1]
+        jvm.clear()
+    finally:
+        jvm.call("nativeTpDestroy")
+    assert jvm.exception() is None
