@@ -123,7 +123,7 @@ class ClockSampler:
 
 def cpu_decode_sample(w, threads: int):
     """CPU oracle, KV-cached decode of workload `w`: time one block + the LM head at a
-    short context and extrapolate to the full depth.  Returns (tok/s, description)."""
+    short context and extrapolate to the full depth.  Returns (tok/s, threads used, description, steps run)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle
     oracle.lib().oracle_set_threads(threads)
@@ -151,9 +151,10 @@ def cpu_decode_sample(w, threads: int):
     t_layer = max(t_layer_head - t_head, 1e-9)
     t_token = t_layer * w["layers"] + t_head
     sample = (f"C++ restatement of CpuBackend, KV-cached decode, fp32 weights: {n} steps of {built} of {w['layers']} blocks "
-              f"+ LM head at context <= 4, extrapolated x{w['layers']} blocks (block {t_layer * 1e3:.1f} ms, head {t_head * 1e3:.1f} ms); "
-              f"batch 1; the reference itself re-forwards the whole context per token and is slower still")
-    return 1.0 / t_token, used, sample
+              f"+ LM head at context <= 4, EXTRAPOLATED x{w['layers']} blocks (block {t_layer * 1e3:.1f} ms, head {t_head * 1e3:.1f} ms); "
+              f"batch 1; CPU attention over the timed GPU context ({w['prompt']}+ cached positions) is NOT included, which flatters the CPU; "
+              f"the reference itself re-forwards the whole context per token and is slower still")
+    return 1.0 / t_token, used, sample, n
 
 
 def cpu_full_reforward_sample(w, threads: int, n_new: int = 8):
@@ -170,6 +171,28 @@ def cpu_full_reforward_sample(w, threads: int, n_new: int = 8):
     return n_new / (time.perf_counter() - t0)
 
 
+def timing_context(w, steps, warmup):
+    """The cached context length the timed steps are centred on — what `measure_decode` arrives at: warm-up steps
+    behind the prompt (rewinding to the end of the prompt when the window is full), then `steps` steps."""
+    room = w["max_seq"] - w["prompt"] - 1
+    pos, done = w["prompt"], 0
+    while done < warmup:
+        if pos >= w["max_seq"] - 1:
+            pos = w["prompt"]
+        k = min(warmup - done, w["max_seq"] - 1 - pos)
+        pos += k
+        done += k
+    if pos + min(steps, room) > w["max_seq"] - 1:
+        pos = w["prompt"]
+    return min(pos + min(steps, room) // 2, w["max_seq"] - 3)
+
+
+def workload_config(name, w, world, kv_dtype, ctx=None):
+    """The `config` object of the JSON line; the reference arm prints the same keys and values."""
+    return {"workload": name, "batch": w["batch"], "prompt_len": w["prompt"], "context_at_timing": ctx,
+            "parallelism": f"tp{world}", "kv_cache": kv_dtype, "l2": "weights+KV per step exceed L2 (inputs larger than L2)"}
+
+
 def run_reference(args, w, name):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -177,21 +200,93 @@ def run_reference(args, w, name):
     threads = max(1, (os.cpu_count() or 2) - 1)      # DeepJExecutor default: cores - 1
     t0 = time.perf_counter()
     vals = []
-    used, sample = threads, ""
+    used, sample, ran = threads, "", 0
     for _ in range(max(1, min(args.steps, 2))):
-        v, used, sample = cpu_decode_sample(w, threads)
+        v, used, sample, n = cpu_decode_sample(w, threads)
         vals.append(v)
-    v = float(np.median(vals)) * w["batch"] / w["batch"]
+        ran += n
+    v = float(np.median(vals))
     line = {
         "impl": "reference", "metric": "q8_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "parallelism": "cpu"},
+        # the same keys and values as the GPU arm prints for this command line (the work is the same; it runs on the host cores)
+        "config": workload_config(name, w, args.gpus, args.kv, timing_context(w, args.steps, args.warmup)),
+        # value and ms_per_step are extrapolated from a bounded sample, not measured over `steps` full tokens
+        "extrapolated": True, "steps_run": ran, "steps_run_what": "decode steps of 1 block + LM head at context <= 4",
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": used, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t0,
     }
     print(json.dumps(line), flush=True)
+
+
+def measure_decode(dec, w, args, world, local_rank, tp, repeats):
+    """The timed regions of one decoder whose cache already holds the prompt: `repeats` device-resident regions of
+    exactly `steps` steps each (median reported, all kept), then the host-buffer loop over the same context range."""
+    import ctypes
+    from deepj_b200 import _lib
+    lib = dec.lib
+    B = dec.B
+    room = w["max_seq"] - w["prompt"] - 1
+
+    def run_device(n):
+        """n steps with device feedback; when the window fills up, rewind to the end of the prompt."""
+        done = 0
+        while done < n:
+            if dec.position >= w["max_seq"] - 1:
+                dec.set_position(w["prompt"])
+            k = min(n - done, w["max_seq"] - 1 - dec.position)
+            dec.step_device(k, sync=False)
+            done += k
+
+    run_device(args.warmup)
+    if dec.position + min(args.steps, room) > w["max_seq"] - 1:
+        dec.set_position(w["prompt"])
+    ctx0 = dec.position
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    sampler.wait_ready()
+    regions = []
+    launches = 0
+    for rep in range(repeats):
+        dec.set_position(ctx0)
+        _lib.check(lib.deepj_cuda_synchronize())
+        if world > 1:
+            tp.barrier()
+        st0 = dec.stats()
+        _lib.check(lib.deepj_cuda_timer_begin())
+        run_device(args.steps)
+        ms = ctypes.c_float(0)
+        _lib.check(lib.deepj_cuda_timer_end(ctypes.byref(ms)))
+        _lib.check(lib.deepj_cuda_synchronize())
+        if world > 1:
+            tp.barrier()
+        st1 = dec.stats()
+        regions.append(tp.max_over_ranks(ms.value) if world > 1 else ms.value)      # device time, max over ranks
+        launches = (st1["graph_replays"] - st0["graph_replays"]) * st1["kernels_per_replay"] + (st1["eager_launches"] - st0["eager_launches"])
+    clocks = sampler.stop()
+    per_step = sorted(r / args.steps for r in regions)
+    ms_per_step = float(np.median(per_step))
+
+    # host-buffer loop (e2e): same context range, token ids through host memory every step
+    tok = dec.next_tokens()
+    dec.set_position(ctx0)
+    for _ in range(3):
+        tok = dec.step(tok)
+    dec.set_position(ctx0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        if dec.position >= w["max_seq"] - 1:
+            dec.set_position(w["prompt"])
+        tok = dec.step(tok)
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        e2e_s = tp.max_over_ranks(e2e_s)
+    ctx = min(ctx0 + min(args.steps, room) // 2, w["max_seq"] - 3)
+    dec.set_position(ctx)
+    return {"ms_per_step": ms_per_step, "ms_per_step_regions": per_step, "value": B * 1e3 / ms_per_step,
+            "e2e": B * args.steps / e2e_s, "launches": int(launches), "clocks": clocks, "ctx": ctx, "dev_error": dec.stats()["device_error"]}
 
 
 def main():
@@ -202,7 +297,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_q8_decode_b1", choices=sorted(WORKLOADS))
     ap.add_argument("--prompt-len", type=int, default=0, help="override the prompt length (debugging)")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of `steps` steps each; the median is reported")
+    ap.add_argument("--kv", default="f32", choices=["f32"], help="dtype of the K/V cache")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the reduced-depth check against the CPU oracle")
+    ap.add_argument("--no-batch16", action="store_true", help="skip the 16-sequence sub-record of the 7B workload")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.prompt_len > 0:
@@ -217,10 +316,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.gpus != world:
-        if args.gpus == 1 and world == 1:
-            pass
-        else:
-            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
     from deepj_b200.decoder import DecoderConfig, Q8Decoder
     from deepj_b200 import tp
     if world > 1:
@@ -232,21 +328,32 @@ def main():
     room = w["max_seq"] - w["prompt"] - 1          # decode steps that fit behind the prompt
     if room < 8:
         raise SystemExit("the context window of this workload leaves no room to decode")
-    # exchange slots sized for a prompt chunk (rows x d partial sums per exchange), capped at 64 MB per slot.  The chunked
-    # tensor-parallel prompt pass has been run on 2 GPUs only; larger worlds take one decode step per prompt position
-    # (measured on 4 and 8 GPUs) unless DEEPJ_BENCH_TP_CHUNKED=1 asks for chunks there too.
-    slot = max(B * cfg.d_model, B * cfg.vocab_size // world)
-    if world == 2 or os.environ.get("DEEPJ_BENCH_TP_CHUNKED") == "1":
-        slot = max(slot, min(B * min(w["prompt"], Q8Decoder.PREFILL_CHUNK) * cfg.d_model, 16 << 20))
+    batch16 = args.workload == "llama7b_q8_decode_b1" and not args.no_batch16 and args.prompt_len == 0
+    # exchange slots hold a prompt chunk's partial sums (rows x dModel per exchange), capped at 2048 rows
+    slot = max((16 if batch16 else B) * cfg.d_model, (16 if batch16 else B) * cfg.vocab_size // world,
+               min(B * min(w["prompt"], Q8Decoder.PREFILL_CHUNK), 2048) * cfg.d_model)
     dec = Q8Decoder(cfg, batch=B, device=local_rank, tp_rank=rank, tp_world=world, tp_slot_floats=slot if world > 1 else 0)
     if world > 1:
         # weights are split by rows/columns over the ranks; [rows x d] partial sums and the logits
-        # shards cross NVLink through the library's own peer-memory exchange kernel
+        # shards cross NVLink through the library's own peer-memory exchange
         tp.connect(rank, world, slot)
+
+    # ── correctness first: the same architecture at full width, two blocks deep, against the CPU oracle ──
+    parity = None
+    if not args.no_parity:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        from parity_util import reduced_depth_parity
+        parity = reduced_depth_parity(w, layers=2, prompt_len=48, n_new=8, rank=rank, world=world, device=local_rank,
+                                      tp_slot_floats=slot if world > 1 else 0, check_codes=False, kv_dtype=args.kv)
+        if not (parity["tokens_equal"] and parity["max_err_over_range"] <= parity["tolerance"]):
+            if rank == 0:
+                print(json.dumps({"metric": "q8_decode_tokens_per_s", "error": "parity check failed", "parity": parity}), flush=True)
+            raise SystemExit(3)
+
     t_load = time.perf_counter()
     dec.load_synthetic(w["seed"], w["std"])
     if world > 1:
-        tp.barrier()          # the exchange kernel's wait for a peer is bounded: start stepping together
+        tp.barrier()          # the exchange's wait for a peer is bounded: start stepping together
     rng = np.random.default_rng(w["seed"] + 1000)
     prompts = rng.integers(0, w["vocab"], size=(B, w["prompt"]))
     dec.reset()
@@ -254,70 +361,16 @@ def main():
     t_prefill = time.perf_counter()
     nxt = dec.prefill(prompts)          # many-row path (tcgen05 GEMMs, chunk attention; partial sums exchanged per chunk under tensor parallelism)
     t_prefill = time.perf_counter() - t_prefill
+    prefill_chunked = w["prompt"] >= 32 and (world == 1 or slot // cfg.d_model // B >= 16)
 
-    lib = dec.lib
-    from deepj_b200 import _lib
-    import ctypes
-
-    def run_device(n):
-        """n steps with device feedback; when the window fills up, rewind to the end of the prompt."""
-        done = 0
-        while done < n:
-            if dec.position >= w["max_seq"] - 1:
-                dec.set_position(w["prompt"])
-            k = min(n - done, w["max_seq"] - 1 - dec.position)
-            dec.step_device(k, sync=False)
-            done += k
-
-    # ── device-resident loop (value) ──
     dec.set_tokens(nxt)
-    run_device(args.warmup)
-    if dec.position + min(args.steps, room) > w["max_seq"] - 1:
-        dec.set_position(w["prompt"])
-    ctx0 = dec.position
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    sampler.wait_ready()
-    _lib.check(lib.deepj_cuda_synchronize())
-    if world > 1:
-        tp.barrier()
-    st0 = dec.stats()
-    _lib.check(lib.deepj_cuda_timer_begin())
-    run_device(args.steps)
-    ms = ctypes.c_float(0)
-    _lib.check(lib.deepj_cuda_timer_end(ctypes.byref(ms)))
-    _lib.check(lib.deepj_cuda_synchronize())
-    if world > 1:
-        tp.barrier()
-    clocks = sampler.stop()
-    st1 = dec.stats()
-    elapsed_ms = tp.max_over_ranks(ms.value) if world > 1 else ms.value      # device time, max over ranks
-    ms_per_step = elapsed_ms / args.steps
-    value = B * 1e3 / ms_per_step
-    launches = (st1["graph_replays"] - st0["graph_replays"]) * st1["kernels_per_replay"] + (st1["eager_launches"] - st0["eager_launches"])
+    m = measure_decode(dec, w, args, world, local_rank, tp, max(1, args.repeats))
+    ms_per_step, value, ctx = m["ms_per_step"], m["value"], m["ctx"]
 
-    # ── host-buffer loop (e2e): same context range, token ids through host memory every step ──
-    tok = dec.next_tokens()
-    dec.set_position(ctx0)
-    for _ in range(3):
-        tok = dec.step(tok)
-    dec.set_position(ctx0)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        if dec.position >= w["max_seq"] - 1:
-            dec.set_position(w["prompt"])
-        tok = dec.step(tok)
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        e2e_s = tp.max_over_ranks(e2e_s)
-    e2e = B * args.steps / e2e_s
-    dec.set_position(min(ctx0 + min(args.steps, room) // 2, w["max_seq"] - 3))
-
-    # ── the GEMV kernel against the HBM roofline ──
+    # ── the dominant kernels against the HBM roofline ──
     peak, peak_kind = measured_peak_gbs()
     prof = dec.profile_step()
     prof = dec.profile_step()
-    shapes = {n: (k, n_) for n, k, n_ in cfg.matmul_shapes()}
 
     def q8b(k, n):
         return k * n + ((k + 31) // 32) * n * 4
@@ -348,20 +401,22 @@ def main():
         gemv_stream_ms = tp.max_over_ranks(gemv_stream_ms)
         attn_stream_ms = tp.max_over_ranks(attn_stream_ms)
     achieved = gemv_bytes / (gemv_stream_ms * 1e-3) / 1e9
-    ctx = min(ctx0 + min(args.steps, room) // 2, w["max_seq"] - 3)
-    step_bytes = cfg.q8_weight_bytes() + B * ctx * cfg.kv_bytes_per_position()      # whole job, all ranks
+    kv_pos_bytes = cfg.kv_bytes_per_position()
+    step_bytes = cfg.q8_weight_bytes() + B * ctx * kv_pos_bytes                      # whole job, all ranks
     step_achieved = step_bytes / world / (ms_per_step * 1e-3) / 1e9                  # per GPU
-    attn_bytes = B * ctx * cfg.kv_bytes_per_position() // world                      # this rank's heads
+    attn_bytes = B * ctx * kv_pos_bytes // world                                     # this rank's heads
 
     line = {
         "metric": "q8_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "q8 weights, f32 activations/accumulate", "data": "synthetic",
-        "config": {"workload": args.workload, "batch": B, "prompt_len": w["prompt"], "context_at_timing": ctx,
-                   "parallelism": f"tp{world}", "kv_cache": "f32", "l2": "weights+KV per step exceed L2 (inputs larger than L2)"},
-        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
-        "gpu_launches": int(launches),
-        "clocks": clocks,
+        "config": workload_config(args.workload, w, world, args.kv, ctx),
+        "timed_regions": {"count": len(m["ms_per_step_regions"]), "steps_each": args.steps, "ms_per_step_median": ms_per_step,
+                          "ms_per_step_min": m["ms_per_step_regions"][0], "ms_per_step_max": m["ms_per_step_regions"][-1]},
+        "e2e": {"value": m["e2e"], "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": m["launches"],
+        "clocks": m["clocks"],
+        "parity": parity,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # DRAM bytes per launch (read + write), scaled by K·N from the ncu capture of the K=4096, N=12288
                      # launch (56.869 MB measured against 56.69 MB algorithmic): the full-size step is too large to capture
@@ -377,13 +432,42 @@ def main():
         "roofline_step": {"bytes_per_token": step_bytes, "achieved_per_gpu": step_achieved, "frac": step_achieved / peak,
                           "roofline_tokens_per_s": B * world * peak * 1e9 / step_bytes},
         "profile_ms": {"gemv": gemv_ms, "attention": attn_ms, "exchange": exch_ms, "all_ops": total_prof_ms},
+        "device_error": m["dev_error"],
         "setup_s": t_load,
         "prefill": {"tokens": int(B * w["prompt"]), "seconds": t_prefill, "tokens_per_s": B * w["prompt"] / max(t_prefill, 1e-9),
-                    "path": "chunked, many-row kernels" if w["prompt"] >= 32 and (world == 1 or slot >= 16 * B * cfg.d_model) else "one decode step per position"},
+                    "path": "chunked, many-row kernels" if prefill_chunked else "one decode step per position"},
     }
+
+    # ── the same model at 16 concurrent sequences (BASELINE configs[4] asks for 1 and 16), sharing the weights ──
+    if batch16:
+        w16 = dict(WORKLOADS["llama7b_q8_decode_b16"])
+        dec16 = Q8Decoder(cfg, batch=16, device=local_rank, id_base=5 << 24, tp_rank=rank, tp_world=world,
+                          tp_slot_floats=slot if world > 1 else 0, share_weights=dec)
+        if world > 1:
+            tp.barrier()
+        p16 = np.random.default_rng(w16["seed"] + 1016).integers(0, w16["vocab"], size=(16, w16["prompt"]))
+        dec16.reset()
+        t16 = time.perf_counter()
+        nxt16 = dec16.prefill(p16)
+        t16 = time.perf_counter() - t16
+        dec16.set_tokens(nxt16)
+        m16 = measure_decode(dec16, w16, args, world, local_rank, tp, max(1, min(args.repeats, 3)))
+        bytes16 = cfg.q8_weight_bytes() + 16 * m16["ctx"] * kv_pos_bytes
+        ach16 = bytes16 / world / (m16["ms_per_step"] * 1e-3) / 1e9
+        line["batch16"] = {
+            "workload": "llama7b_q8_decode_b16", "value": m16["value"], "unit": "tokens/s", "ms_per_step": m16["ms_per_step"],
+            "ms_per_step_regions": m16["ms_per_step_regions"], "context_at_timing": m16["ctx"],
+            "e2e": {"value": m16["e2e"], "unit": "tokens/s", "h2d_bytes_per_step": 64, "d2h_bytes_per_step": 64},
+            "roofline_step": {"bytes_per_step": bytes16, "achieved_per_gpu": ach16, "frac": ach16 / peak,
+                              "roofline_tokens_per_s": 16 * world * peak * 1e9 / bytes16},
+            "gpu_launches": m16["launches"], "device_error": m16["dev_error"],
+            "prefill": {"tokens": 16 * w16["prompt"], "seconds": t16},
+        }
+        dec16.close()
+
     if not args.no_cpu_baseline and rank == 0:
-        v, used, sample = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))
-        line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": used, "kind": "port", "sample": sample}
+        v, used, sample, _ = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))
+        line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": used, "kind": "port", "sample": sample, "extrapolated": True}
         if w["d"] <= 256:      # the tiny configuration: also the reference-faithful loop, full re-forward per token
             line["cpu_baseline"]["full_reforward_tokens_per_s"] = cpu_full_reforward_sample(w, used)
     if rank == 0:

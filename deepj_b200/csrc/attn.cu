@@ -509,9 +509,13 @@ extern "C" int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t
         if (stream == nullptr) throw std::runtime_error("attn_decode_static: the library holds no buffers yet (nothing was allocated through it)");
         const int dev = runtime_device();
         if (dev < 0 || dev >= 64) throw std::runtime_error("attn_decode_static: device index out of range");
-        int cur = -1;
-        DJ_CUDA_CHECK(cudaGetDevice(&cur));
-        if (cur != dev) DJ_CUDA_CHECK(cudaSetDevice(dev));
+        // the library's device is made current for the length of this call and the caller's is put back on every way out
+        struct DeviceGuard {
+            int prev = -1; bool switched = false;
+            ~DeviceGuard() { if (switched) cudaSetDevice(prev); }
+        } guard;
+        DJ_CUDA_CHECK(cudaGetDevice(&guard.prev));
+        if (guard.prev != dev) { DJ_CUDA_CHECK(cudaSetDevice(dev)); guard.switched = true; }
         if (g_static_scratch_addr[dev] == nullptr) {
             // first call on this device: resolve the scratch array's device address
             float* p = nullptr;

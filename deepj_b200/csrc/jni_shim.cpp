@@ -73,6 +73,9 @@ JNIEXPORT void JNICALL CUDA_NATIVE(nativeUploadBuffer)(JNIEnv* env, jclass, jint
 JNIEXPORT void JNICALL CUDA_NATIVE(nativeDownloadBuffer)(JNIEnv* env, jclass, jint bufId, jfloatArray outArr) {
     if (outArr == nullptr) { raise(env, "nativeDownloadBuffer: null array"); return; }
     const jsize len = env->GetArrayLength(outArr);
+    // wait for the queued work BEFORE the array is pinned: a critical region must be short and must not block
+    // (it holds off the collector), so it covers the device-to-host copy only
+    if (deepj_cuda_synchronize() != 0) { raise_last(env); return; }
     void* p = env->GetPrimitiveArrayCritical(outArr, nullptr);
     if (p == nullptr) { raise(env, "nativeDownloadBuffer: array could not be pinned"); return; }
     const int rc = deepj_cuda_download_buffer(bufId, static_cast<float*>(p), len);

@@ -82,8 +82,8 @@ struct Q8LinearArgs {
     const float* beta = nullptr; int act = 0; float* ln_ws = nullptr;
 };
 void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s);
-bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s);
-bool q8_tma_fuses_gpt(const Q8LinearArgs& a);     // true when launch_q8_linear_tma can take beta / act itself
+bool launch_q8_gemv_i8(const Q8LinearArgs& a, cudaStream_t s);
+bool q8_gemv_i8_fuses_gpt(const Q8LinearArgs& a);     // true when launch_q8_gemv_i8 can take beta / act itself
 void launch_layernorm_rows(const float* x, int ldx, const float* gamma, const float* beta, float eps, float* out, int K, int M, cudaStream_t s);
 void launch_gelu_rows(float* buf, int ld, int N, int M, cudaStream_t s);
 bool launch_q8_linear_batch(const Q8LinearArgs& a, int m0, int rows, float* ws, int* tickets, cudaStream_t s);
@@ -119,7 +119,11 @@ void launch_embed_gather(const float* table, const float* ids, float* out, int r
 // scratch: 2·16·rows ints of partial (key, index) pairs, tickets: rows zeroed self-resetting counters (rows ≤ kArgmaxRowsMax)
 constexpr int kArgmaxRowsMax = 4096;
 void launch_argmax_rows(const float* in, float* out, int rows, int cols, int* scratch, int* tickets, cudaStream_t s);
-void launch_sample_topk(const float* logits, const float* r, float* out, int rows, int cols, int topK, float temperature, cudaStream_t s);
+// topK = 0 means the whole row (the reference's convention); more than 1024 candidates sort the row in `ws`
+// (sample_topk_ws_floats floats, 8-byte aligned).
+void launch_sample_topk(const float* logits, const float* r, float* out, int rows, int cols, int topK, float temperature, float* ws,
+                        cudaStream_t s);
+size_t sample_topk_ws_floats(int rows, int cols, int topK);
 void launch_add_scalar_inplace(float* buf, float v, int n, cudaStream_t s);
 void launch_copy(const float* src, float* dst, long long n, cudaStream_t s);
 void launch_synth_fill(float* out, unsigned long long seed, unsigned long long ordinal, float std_dev,
@@ -140,6 +144,9 @@ bool pool_kv(int id, PoolKV* out);
 // The library's stream and device; the stream is null until the library has been initialised.
 cudaStream_t runtime_stream();
 int runtime_device();
+// Drops every captured graph: called when addresses baked into kernel parameters (peer mappings, exchange
+// buffers) stop being valid, so that the next flush of a cached stream is captured afresh.
+void invalidate_graphs();
 void set_last_error(const std::string& msg);
 
 // Launch helper: plain <<<>>> or cudaLaunchKernelEx with the PDL attribute.

@@ -208,6 +208,64 @@ __global__ void __launch_bounds__(1024) k_sample_topk(const float* __restrict__ 
     }
 }
 
+// The same draw when more than kSampleMaxK candidates take part — topK above 1024, or the reference's topK = 0,
+// which means the whole vocabulary (models/TextGenerator.java:111-115).  One CTA per row sorts ALL (key, −index)
+// pairs of the row, descending, with a bitonic network in global scratch (P = cols rounded up to a power of two,
+// 8 bytes each), turns the first k into probabilities (4 bytes each, behind the pairs) and lets one thread run the
+// reference's two sequential float loops.  Not a hot path: a 32000-entry row takes a fraction of a millisecond.
+__global__ void __launch_bounds__(1024) k_sample_sorted(const float* __restrict__ logits, const float* __restrict__ rbuf,
+                                                         float* __restrict__ out, int cols, int k, int P, float temperature,
+                                                         unsigned long long* __restrict__ scratch) {
+    __shared__ float s_red[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x;
+    const float* d = logits + (size_t)blockIdx.x * cols;
+    unsigned long long* cand = scratch + (size_t)blockIdx.x * ((size_t)P + (size_t)(P + 1) / 2);
+    float* prob = reinterpret_cast<float*>(cand + P);
+    for (int c = tid; c < P; c += blockDim.x)
+        cand[c] = c < cols ? (((unsigned long long)((unsigned)order_key(d[c]) ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (unsigned)c)) : 0ull;
+    for (int size = 2; size <= P; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int t = tid; t < (P >> 1); t += blockDim.x) {
+                const int i = 2 * t - (t & (stride - 1)), j = i + stride;
+                const unsigned long long a = cand[i], b = cand[j];
+                const bool desc = (i & size) == 0;
+                if (desc ? a < b : a > b) { cand[i] = b; cand[j] = a; }
+            }
+        }
+    }
+    __syncthreads();
+    float mx = -INFINITY;
+    for (int i = tid; i < k; i += blockDim.x) {
+        const float v = d[(int)(0xFFFFFFFFu - (unsigned)(cand[i] & 0xFFFFFFFFull))] / temperature;
+        if (v == v) mx = fmaxf(mx, v);               // `if (v > max) max = v` never takes a NaN
+    }
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((tid & 31) == 0) s_red[tid >> 5] = mx;
+    __syncthreads();
+    mx = s_red[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) mx = fmaxf(mx, s_red[w]);
+    for (int i = tid; i < k; i += blockDim.x) {
+        const float v = d[(int)(0xFFFFFFFFu - (unsigned)(cand[i] & 0xFFFFFFFFull))] / temperature;
+        prob[i] = (float)exp((double)(v - mx));
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.0f;
+        for (int i = 0; i < k; i++) sum += prob[i];
+        const float r = rbuf[blockIdx.x];
+        float cum = 0.0f;
+        int pick = k - 1;
+        for (int i = 0; i < k; i++) {
+            cum += prob[i] / sum;
+            if (r <= cum) { pick = i; break; }
+        }
+        out[blockIdx.x] = (float)(int)(0xFFFFFFFFu - (unsigned)(cand[pick] & 0xFFFFFFFFull));
+    }
+}
+
 __global__ void k_add_scalar_inplace(float* __restrict__ buf, float v, int n) {
     pdl_wait();
     pdl_launch_dependents();
@@ -260,11 +318,26 @@ void launch_argmax_rows(const float* in, float* out, int rows, int cols, int* sc
     const int parts = (cols >= 4096 && rows <= kArgmaxRowsMax && scratch != nullptr) ? kArgmaxParts : 1;
     launch_k(k_argmax_rows, dim3(parts, rows), dim3(256), 0, s, true, in, out, rows, cols, scratch, tickets);
 }
-void launch_sample_topk(const float* logits, const float* r, float* out, int rows, int cols, int topK, float temperature, cudaStream_t s) {
+static int sample_pow2(int cols) { int P = 2; while (P < cols) P <<= 1; return P; }
+size_t sample_topk_ws_floats(int rows, int cols, int topK) {
+    const int k = (topK == 0 || topK > cols) ? cols : topK;
+    if (k <= kSampleMaxK) return 0;
+    const size_t P = (size_t)sample_pow2(cols);
+    return (size_t)rows * (P + (P + 1) / 2) * 2;          // pairs of 8 bytes, then the probabilities
+}
+void launch_sample_topk(const float* logits, const float* r, float* out, int rows, int cols, int topK, float temperature, float* ws,
+                        cudaStream_t s) {
     if (rows <= 0) return;
-    if (topK < 1 || topK > kSampleMaxK) throw std::runtime_error("sampleTopK: topK must be in 1.." + std::to_string(kSampleMaxK) + " on the device sampler");
+    if (topK < 0) throw std::runtime_error("sampleTopK: topK must be >= 0 (0 = the whole vocabulary)");
     if (!(temperature > 0.0f)) throw std::runtime_error("temperature must be > 0");
-    launch_k(k_sample_topk, dim3(rows), dim3(1024), 0, s, true, logits, r, out, rows, cols, topK, temperature);
+    const int k = (topK == 0 || topK > cols) ? cols : topK;      // models/TextGenerator.java:111-115
+    if (k <= kSampleMaxK) {
+        launch_k(k_sample_topk, dim3(rows), dim3(1024), 0, s, true, logits, r, out, rows, cols, k, temperature);
+        return;
+    }
+    if (ws == nullptr) throw std::runtime_error("sampleTopK: more than 1024 candidates need the workspace");
+    launch_k(k_sample_sorted, dim3(rows), dim3(1024), 0, s, true, logits, r, out, cols, k, sample_pow2(cols), temperature,
+             reinterpret_cast<unsigned long long*>(ws));
 }
 void launch_add_scalar_inplace(float* buf, float v, int n, cudaStream_t s) {
     if (n <= 0) return;

@@ -325,7 +325,7 @@ void launch_q8_linear(const Q8LinearArgs& a0, cudaStream_t s) {
     if (a0.beta == nullptr && a0.act == 0) { dispatch_q8_linear(a0, s); return; }
     // GPT blocks: up to four rows go through the GEMV, which takes LayerNorm and GELU itself; the many-row
     // kernels see already normalised rows and get the activation applied to their output afterwards
-    if (g_gemv_mode == 2 && a0.M < 5 && q8_tma_fuses_gpt(a0)) { dispatch_q8_linear(a0, s); return; }
+    if (g_gemv_mode == 2 && a0.M < 5 && q8_gemv_i8_fuses_gpt(a0)) { dispatch_q8_linear(a0, s); return; }
     Q8LinearArgs a = a0;
     if (a.beta != nullptr) {
         if (a.ln_ws == nullptr) throw std::runtime_error("Q8 linear: LayerNorm needs its workspace");
@@ -366,7 +366,7 @@ void dispatch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
         for (int m0 = 0; m0 < a.M && ok; m0 += 16) ok = launch_q8_linear_batch(a, m0, a.M - m0 < 16 ? a.M - m0 : 16, a.ws, a.tickets, s);
         if (ok) return;
     }
-    if (g_gemv_mode == 2 && launch_q8_linear_tma(a, s)) return;
+    if (g_gemv_mode == 2 && launch_q8_gemv_i8(a, s)) return;
     if (swiglu) launch_gemv_dispatch<true>(p, a.M, s);
     else launch_gemv_dispatch<false>(p, a.M, s);
 }

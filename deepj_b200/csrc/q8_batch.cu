@@ -2,21 +2,21 @@
 // several concurrent sequences, and the short-prompt end of the operator sweep.
 //
 // Still HBM-bound — every weight byte is read once per launch and used for all rows — so the
-// structure is the GEMV's: warp-private cp.async rings, int8 codes straight into
-// mma.sync m16n8k32, activations as three signed base-256 digit columns with a power-of-two
-// scale per 32-k block, fp32 accumulation of (weight scale × activation scale) · integer sum.
-// What changes is the shape of the work:
-//   * one MMA column group (n-tile) holds two activation rows, so a warp runs NT = ⌈M/2⌉
-//     MMAs per weight block against the same A fragment;
-//   * the digits of all rows no longer fit in shared memory for the whole reduction length,
-//     so K is cut into slices (1024 for 9–16 rows, 2048 below): a work item is (group of 8
-//     row tiles, slice), a CTA stages only its slice of the activations, and each warp owns
-//     one 16-row tile of the group;
+// streaming side is the GEMV's: warp-private cp.async rings of 16 weight rows × 64 codes (+ 32
+// scales) per item.  The arithmetic is fp16 mma.sync m16n8k16 with fp32 accumulation:
+//   * the int8 codes become fp16 exactly (sign flip, byte under the exponent 0x64, subtract
+//     1152 — five instructions per four codes) and are the A operand;
+//   * the activations are the B operand as fp16 hi + lo halves of x · 2^-e, e taken from the
+//     largest |x| of the 512-k slice a work item covers: two MMAs per 32-k block and group of
+//     eight rows, and `weight scale · block sum` is accumulated in fp32, so the per-block scale
+//     semantics of the format are kept;
+//   * K is cut into slices of 512: a work item is (group of 8 row tiles, slice), a CTA stages
+//     only its slice of the activations, and each warp owns one 16-row tile of the group;
 //   * partial sums of the slices meet in a global workspace: the WARP that arrives last at a
 //     row tile (a ticket counter per tile) adds the slices in slice order — deterministic —
 //     and runs the epilogue (RMSNorm scale, bias, residual, SiLU-gate).  No CTA-wide
 //     barrier after the activations are staged: warps drift apart freely.
-// RMSNorm: the digits are taken from x ⊙ γ and the row factor 1/rms is applied in the
+// RMSNorm: the halves are taken from x ⊙ γ and the row factor 1/rms is applied in the
 // epilogue; Σx² of every 512-chunk of a row is left in the workspace by the CTAs that stage it.
 #include "kernels.h"
 #include "q8_common.cuh"

@@ -18,20 +18,8 @@
 // order as an fp32 FMA chain.  One MMA covers exactly one 32-k block of 16 weight
 // rows, so the per-block scale semantics of the format are kept.  RMSNorm is fused
 // into the activation staging; bias, residual and SiLU-gate into the epilogue.
-//
-// Measured dead ends, kept out of the code: a producer warp feeding a shared ring
-// through mbarriers reached 1.0 TB/s with cp.async and 1.6 TB/s with 1-D
-// cp.async.bulk row segments of 1 KB (per-copy cost of the bulk engine); fp16
-// mma.sync with byte-permute dequant was no faster than the FMA kernel; bulk L2
-// prefetch (cp.async.bulk.prefetch.L2) of the tiles ahead of the ring, or of the next
-// kernel's first weights as a CTA retires, made every shape 5–50 % slower; running the
-// decode attention inside this kernel for the QKV projection (clusters of 8 CTAs per
-// head, cluster barrier, partials merged through distributed shared memory) was correct
-// but 2 % slower per token than the two launches, whose attention kernel already starts
-// its K/V stream before the projection has finished.
 #include "kernels.h"
 #include "q8_common.cuh"
-#include <cstdlib>
 
 namespace dj {
 
@@ -59,7 +47,7 @@ constexpr int kXsPad = 32;                  // bytes of padding per activation d
 constexpr int kPreMax = 2;                  // items a warp prefetches before it waits for the previous kernel
 constexpr int kColsPerRow = 3;              // digit columns per activation row in shared memory: d2, d1, d0
 
-struct TmaParams {
+struct GemvI8Params {
     const float* x; int ldx;
     const float* gamma; float eps;
     const float* beta; int act;     // GPT instantiation only: LayerNorm shift (null = RMSNorm / none) and 1 = GELU after the bias
@@ -81,7 +69,7 @@ constexpr int kStageRounds = 3;             // rows of up to 3·256·16 = 12288 
 // NM = 2 takes three or four activation rows in one pass over the weights: a second MMA per block whose eight
 // columns are the digits of rows 2 and 3.
 template <bool SWIGLU, int DEPTH, bool GPT, int NM>
-__global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const TmaParams p) {
+__global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const GemvI8Params p) {
     extern __shared__ __align__(128) unsigned char smem[];
     // layout: rings [warps][DEPTH][kSlotBytes], digits int8 [3M][K+pad], block scales fp32 [M][K/32], partials [2][warps][NM][16][8]
     const int ldxs = p.K + kXsPad;
@@ -401,7 +389,7 @@ size_t i8_smem_bytes(int K, int M, int depth) {
 }
 
 template <bool SWIGLU, int DEPTH, bool GPT, int NM>
-void launch_i8(const TmaParams& p, cudaStream_t s) {
+void launch_i8(const GemvI8Params& p, cudaStream_t s) {
     static bool attrSet = false;
     if (!attrSet) {
         DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemv_i8<SWIGLU, DEPTH, GPT, NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
@@ -414,13 +402,11 @@ void launch_i8(const TmaParams& p, cudaStream_t s) {
     int cap = 2 * g_num_sms;
     int rounds = (nTiles + cap - 1) / cap;
     int gx = (nTiles + rounds - 1) / rounds;
-    static const bool evenGrid = getenv("DEEPJ_CUDA_GEMV_FULLGRID") == nullptr;
-    if (!evenGrid) gx = nTiles < cap ? nTiles : cap;
     launch_k(k_q8_gemv_i8<SWIGLU, DEPTH, GPT, NM>, dim3(gx), dim3(kThreads), i8_smem_bytes(p.K, p.M, DEPTH), s, true, p);
 }
 
 template <bool SWIGLU, bool GPT>
-void launch_i8_depth(const TmaParams& p, int depth, cudaStream_t s) {
+void launch_i8_depth(const GemvI8Params& p, int depth, cudaStream_t s) {
     if (p.M > 2) {      // two MMAs per block; the digits of four rows leave room for a ring of at most five items
         switch (depth) {
             case 3: launch_i8<SWIGLU, 3, GPT, 2>(p, s); break;
@@ -432,11 +418,7 @@ void launch_i8_depth(const TmaParams& p, int depth, cudaStream_t s) {
     switch (depth) {
         case 3: launch_i8<SWIGLU, 3, GPT, 1>(p, s); break;
         case 4: launch_i8<SWIGLU, 4, GPT, 1>(p, s); break;
-        case 5: launch_i8<SWIGLU, 5, GPT, 1>(p, s); break;
-        case 6: launch_i8<SWIGLU, 6, GPT, 1>(p, s); break;
-        case 7: launch_i8<SWIGLU, 7, GPT, 1>(p, s); break;
-        case 8: launch_i8<SWIGLU, 8, GPT, 1>(p, s); break;
-        default: launch_i8<SWIGLU, 9, GPT, 1>(p, s); break;
+        default: launch_i8<SWIGLU, 5, GPT, 1>(p, s); break;
     }
 }
 
@@ -445,30 +427,28 @@ void launch_i8_depth(const TmaParams& p, int depth, cudaStream_t s) {
 // Returns false when the shape is outside this kernel's domain (the caller falls
 // back to the FMA kernel).  Two CTAs share an SM, so a CTA may use half of its
 // shared memory: the ring takes what the activation digits leave.
-bool q8_tma_fuses_gpt(const Q8LinearArgs& a) {
+bool q8_gemv_i8_fuses_gpt(const Q8LinearArgs& a) {
     const int K = a.w.K;
     if (K % 32 != 0 || a.w.Kp != K || a.w2.codes != nullptr) return false;
     if (i8_smem_bytes(K, 1, 3) > 111 * 1024) return false;
     return (K >> 4) <= kStageRounds * kThreads;      // LayerNorm lives in the register staging path only
 }
 
-bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s) {
+bool launch_q8_gemv_i8(const Q8LinearArgs& a, cudaStream_t s) {
     const int K = a.w.K;
     if (K % 32 != 0 || a.w.Kp != K) return false;
     const bool swiglu = a.w2.codes != nullptr;
     const bool gpt = a.beta != nullptr || a.act != 0;
-    if (gpt && !q8_tma_fuses_gpt(a)) return false;
+    if (gpt && !q8_gemv_i8_fuses_gpt(a)) return false;
     const size_t budget = 111 * 1024;
     if (i8_smem_bytes(K, 1, 3) > budget) return false;
     for (int m0 = 0; m0 < a.M;) {
-        static const int maxRows = getenv("DEEPJ_CUDA_GEMV_ROWS") ? atoi(getenv("DEEPJ_CUDA_GEMV_ROWS")) : 4;
+        constexpr int maxRows = 4;
         int rows = a.M - m0 < maxRows ? a.M - m0 : maxRows;      // 8 MMA columns = 2 activation rows × (3 digits + 1 unused); 3-4 rows take a second MMA
         while (rows > 1 && i8_smem_bytes(K, rows, 3) > budget) rows--;
-        static int wantDepth = 0;
-        if (wantDepth == 0) { const char* e = getenv("DEEPJ_CUDA_GEMV_DEPTH"); wantDepth = e ? atoi(e) : 5; if (wantDepth < 3) wantDepth = 3; if (wantDepth > 9) wantDepth = 9; }
-        int depth = rows > 2 && wantDepth > 5 ? 5 : wantDepth;      // default: four items (4 KB) per warp in flight, 64 KB per SM
+        int depth = 5;      // four items (4 KB) per warp in flight, 64 KB per SM
         while (depth > 3 && i8_smem_bytes(K, rows, depth) > budget) depth--;
-        TmaParams p;
+        GemvI8Params p;
         p.x = a.x + (size_t)m0 * a.ldx; p.ldx = a.ldx; p.gamma = a.gamma; p.eps = a.eps;
         p.beta = a.beta; p.act = a.act;
         p.codes = a.w.codes; p.scales = a.w.scales; p.bias = a.bias;
@@ -476,10 +456,8 @@ bool launch_q8_linear_tma(const Q8LinearArgs& a, cudaStream_t s) {
         p.residual = a.residual ? a.residual + (size_t)m0 * a.ldr : nullptr; p.ldr = a.ldr;
         p.out = a.out + (size_t)m0 * a.ldo; p.ldo = a.ldo;
         p.K = K; p.N = a.w.N; p.Kp = a.w.Kp; p.nb = a.w.nb; p.M = rows;
-        static const int pre = getenv("DEEPJ_CUDA_GEMV_PRE") ? atoi(getenv("DEEPJ_CUDA_GEMV_PRE")) : kPreMax;
-        p.pre = pre;
-        static const int mid = getenv("DEEPJ_CUDA_GEMV_MID") ? atoi(getenv("DEEPJ_CUDA_GEMV_MID")) : 4;
-        p.mid = mid;
+        p.pre = kPreMax;
+        p.mid = 4;
         p.trace = trace_slot();
         if (swiglu) launch_i8_depth<true, false>(p, depth, s);
         else if (gpt) launch_i8_depth<false, true>(p, depth, s);

@@ -486,11 +486,9 @@ bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s) {
     launch_k(k_x_to_f16_tiles, dim3((unsigned)(mPad / 8)), dim3(256), 0, s, true, a.x, a.ldx, a.gamma, a.eps, M, K, tiles, rowscale);
     // Two accumulators per CTA halve the conversion work per flop but also the number of CTAs, and a paired CTA
     // takes 1.55–1.7 × as long as a single one: pair when the rounds of CTAs over the SMs it saves outweigh that.
-    static const int pairEnv = getenv("DEEPJ_CUDA_TC_PAIR") ? atoi(getenv("DEEPJ_CUDA_TC_PAIR")) : -1;
     const long single = (long)nTiles * mTiles, paired = (long)nTiles * ((mTiles + 1) / 2);
     const long roundsSingle = (single + g_num_sms - 1) / g_num_sms, roundsPaired = (paired + g_num_sms - 1) / g_num_sms;
     bool pair = mTiles >= 2 && 1.7 * (double)roundsPaired < (double)roundsSingle;
-    if (pairEnv >= 0) pair = pairEnv != 0 && mTiles >= 2;
     const dim3 grid(nTiles, pair ? (mTiles + 1) / 2 : mTiles);
     TcParams p;
     p.xtiles = tiles; p.rowscale = rowscale;

@@ -111,6 +111,7 @@ struct Ctx {
     bool execute;
     cudaStream_t s;
     size_t ws_need = 0;
+    bool bounded_waits = false;        // the stream holds an op whose kernel waits on a peer (tensor-parallel exchange)
     std::vector<std::pair<int, unsigned long long>>* refs = nullptr;
 };
 
@@ -394,13 +395,15 @@ void do_op(Ctx& ctx, const int32_t* c) {
         case DEEPJ_OP_SAMPLE_TOPK: {     // [op, logits, r, out, rows, cols, topK, temperatureBits]
             int rows = c[4], cols = c[5], topK = c[6];
             require(rows >= 0 && cols >= 1, "sampleTopK", "bad dimension");
-            require(topK >= 1 && topK <= 1024, "sampleTopK", "topK must be in 1..1024 on the device sampler");
+            require(topK >= 0, "sampleTopK", "topK must be >= 0 (0 = the whole vocabulary)");
             const float temperature = bits_to_float(c[7]);
             require(temperature > 0.0f, "sampleTopK", "temperature must be > 0");
             const float* lg = f32(ctx, c[1], sz(rows, cols), "sampleTopK");
             const float* rr = f32(ctx, c[2], rows, "sampleTopK");
             float* o = f32(ctx, c[3], rows, "sampleTopK");
-            if (go) launch_sample_topk(lg, rr, o, rows, cols, topK, temperature, s);
+            const size_t need = sample_topk_ws_floats(rows, cols, topK);
+            if (need > ctx.ws_need) ctx.ws_need = need;
+            if (go) launch_sample_topk(lg, rr, o, rows, cols, topK, temperature, R.ws, s);
             break;
         }
         case DEEPJ_OP_ADD_SCALAR_INPLACE: {
@@ -422,6 +425,7 @@ void do_op(Ctx& ctx, const int32_t* c) {
             const float* bias = f32_opt(ctx, c[2], N, "tpAllReduce");
             const float* res = f32_opt(ctx, c[3], sz(M, N), "tpAllReduce");
             float* o = f32(ctx, c[4], sz(M, N), "tpAllReduce");
+            ctx.bounded_waits = true;
             if (go) launch_tp_exchange(in, bias, res, o, M, N, 0, s);
             break;
         }
@@ -430,6 +434,7 @@ void do_op(Ctx& ctx, const int32_t* c) {
             require(tp_ready(), "tpAllGather", "deepj_cuda_tp_connect has not been called");
             const float* in = f32(ctx, c[1], sz(M, nl), "tpAllGather");
             float* o = f32(ctx, c[2], sz(M, nl) * tp_world(), "tpAllGather");
+            ctx.bounded_waits = true;
             if (go) launch_tp_exchange(in, nullptr, nullptr, o, M, nl, 1, s);
             break;
         }
@@ -544,7 +549,19 @@ void flush(const int32_t* cmd, int len, bool sync) {
         walk(x, cmd, len);
         if (ge) ge->seen++;
     }
-    if (sync) DJ_CUDA_CHECK(cudaStreamSynchronize(R.stream));
+    if (sync) {
+        DJ_CUDA_CHECK(cudaStreamSynchronize(R.stream));
+        if (v.bounded_waits) {
+            // a wait on a peer that ran out leaves a code in the device error word; the results of this flush are
+            // then incomplete, which a synchronous caller learns here (an asynchronous one from deepj_cuda_stats)
+            int code = 0;
+            DJ_CUDA_CHECK(cudaMemcpy(&code, g_dev_error, sizeof(int), cudaMemcpyDeviceToHost));
+            if (code != 0)
+                throw std::runtime_error("a bounded wait inside a kernel expired (device error word " + std::to_string(code) +
+                                         (code >= 100 && code < 200 ? ": no data from tensor-parallel rank " + std::to_string(code - 100) : std::string()) +
+                                         "); the results of this flush are incomplete, the context stays usable");
+        }
+    }
 }
 
 }  // namespace
@@ -563,6 +580,7 @@ bool pool_kv(int id, PoolKV* out) {
     out->ptr = (float*)b.ptr; out->layers = b.layers; out->B = b.B; out->H = b.H; out->maxSeq = b.maxSeq; out->hd = b.hd;
     return true;
 }
+void invalidate_graphs() { R.epoch++; drop_graphs(); }
 cudaStream_t runtime_stream() { return R.inited ? R.stream : nullptr; }
 int runtime_device() { return R.device; }
 void set_last_error(const std::string& msg) { g_err = msg; }

@@ -14,13 +14,20 @@
 //   finish add the slots in rank order (+ residual + bias) — every rank computes the same
 //          bits — or place them side by side for the gather.
 // The cost is one NVLink one-way latency instead of store → system fence → flag.
-// Parity flips every exchange; a rank can be at most one exchange ahead of a peer (it needs
-// the peer's words to finish), so two parities are enough and a stale word (epoch − 2) can
-// never be taken for a fresh one.  Epochs live in device memory, which makes the kernels
-// replayable inside a captured CUDA graph.
+// Parity flips every exchange of a grid class; a rank can be at most one exchange ahead of a
+// peer (it needs the peer's words to finish), so two parities are enough and a stale word
+// (epoch − 2) can never be taken for a fresh one.  That argument holds per grid class only —
+// a decode-sized exchange directly after a chunk-sized one could share a parity with it —
+// so the two classes own separate slot regions of the buffer and never touch each other's
+// words.  Epochs live in device memory, which makes the kernels replayable inside a
+// captured CUDA graph.
+// Once a wait has expired (the device error word is non-zero) every later wait, in this
+// launch and in the following ones, gives up at once: a dead peer costs one bounded wait,
+// not one per word.
 #include "../../include/deepj_cuda.h"
 #include "kernels.h"
 
+#include <algorithm>
 #include <cstring>
 #include <vector>
 
@@ -33,12 +40,16 @@ constexpr int kTpCtas = 8;                    // CTAs of a decode-sized exchange
 constexpr int kTpCtasLarge = 296;             // CTAs of a chunk-sized exchange (a fixed number: the per-CTA counters depend on it)
 constexpr long kTpLargePairs = 1L << 16;      // messages above 2^17 floats take the large grid
 constexpr unsigned kTpSpinLimit = 1u << 21;   // polls of one word (≈ a second), then give up
+long g_large_pairs = kTpLargePairs;           // deepj_cuda_tp_configure; the same on every rank
 
 struct TpState {
     bool ready = false;
     int rank = 0, world = 1;
-    size_t slot_floats = 0;
-    // layout of one rank's buffer: words[2][world][slot_floats] of {bits, epoch} (8 bytes each), then the per-CTA exchange counters (u32; kTpCtas for the small grid, kTpCtasLarge for the large one; private to this rank)
+    size_t slot_floats = 0;         // values one exchange may carry per rank
+    size_t small_floats = 0;        // … of which the decode-sized class can see at most this many
+    // layout of one rank's buffer, {bits, epoch} words of 8 bytes: the decode-sized class's region
+    // words[2][world][small_floats], then the chunk-sized class's words[2][world][slot_floats], then the
+    // per-CTA exchange counters (u32; kTpCtas for the small grid, kTpCtasLarge for the large one; private to this rank)
     void* local = nullptr;
     size_t bytes = 0;
     float* peer_data[kMaxWorld] = {};
@@ -66,7 +77,7 @@ constexpr int kTpPairsPerThread = 1;      // 2 values per thread and pass: a 16 
 
 // mode 0: out[m][n] = residual[m][n] + bias[n] + Σ_r contribution_r[m][n]   (n_local == N)
 // mode 1: out[m][r·n_local + j] = contribution_r[m][j]
-__global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int world, size_t slot_floats, unsigned* epochs, unsigned tag,
+__global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int world, size_t region_words, size_t slot_floats, unsigned* epochs, unsigned tag,
                                                       const float* __restrict__ in, const float* __restrict__ bias,
                                                       const float* __restrict__ residual, float* __restrict__ out,
                                                       int M, int n_local, int mode, int* error) {
@@ -81,7 +92,8 @@ __global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int wor
     const unsigned parity = count & 1u;
     const int total = M * n_local;                       // floats this rank contributes
     const int pairs = (total + 1) >> 1;
-    const size_t slotWords = (size_t)parity * world * slot_floats;      // in 8-byte words
+    const size_t slotWords = region_words + (size_t)parity * world * slot_floats;      // in 8-byte words
+    bool gaveUp = false;                                  // a wait of this thread has expired, or the error word was already set
     for (int p0 = (cta * blockDim.x + tid) * kTpPairsPerThread; p0 < pairs; p0 += gridDim.x * blockDim.x * kTpPairsPerThread) {
         // push: my values of these pairs into my slot on every rank (myself included)
         uint4 w[kTpPairsPerThread];
@@ -107,11 +119,19 @@ __global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int wor
             for (int q = 0; q < kTpPairsPerThread; q++) {
                 if (p0 + q >= pairs) continue;
                 uint4 v = ld_volatile_v4(src + p0 + q);
-                for (unsigned it = 0; (v.y != epoch || v.w != epoch) && it < kTpSpinLimit; it++) {
-                    __nanosleep(32);
-                    v = ld_volatile_v4(src + p0 + q);
+                if (v.y != epoch || v.w != epoch) {
+                    // not there yet: poll, unless some wait has already run out (here or in an earlier launch)
+                    gaveUp = gaveUp || *reinterpret_cast<volatile int*>(error) != 0;
+                    for (unsigned it = 0; !gaveUp && (v.y != epoch || v.w != epoch) && it < kTpSpinLimit; it++) {
+                        __nanosleep(32);
+                        v = ld_volatile_v4(src + p0 + q);
+                        if ((it & 63u) == 63u) gaveUp = *reinterpret_cast<volatile int*>(error) != 0;
+                    }
+                    if (v.y != epoch || v.w != epoch) {
+                        if (!gaveUp) atomicCAS(error, 0, 100 + r);      // the first expiry names the rank
+                        gaveUp = true;
+                    }
                 }
-                if (v.y != epoch || v.w != epoch) atomicExch(error, 100 + r);
                 const float a = __uint_as_float(v.x), b = __uint_as_float(v.z);
                 const int i = 2 * (p0 + q);
                 if (mode == 0) { sa[q] += a; sb[q] += b; }
@@ -144,6 +164,12 @@ __global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int wor
 
 }  // namespace
 
+size_t tp_data_bytes() {
+    // a chunk-sized region only when a message can exceed the decode-sized class
+    const size_t largeFloats = T.slot_floats > T.small_floats ? T.slot_floats : 0;
+    return (size_t)2 * T.world * (T.small_floats + largeFloats) * 8;
+}
+
 bool tp_ready() { return T.ready; }
 int tp_world() { return T.ready ? T.world : 1; }
 
@@ -157,9 +183,10 @@ void launch_tp_exchange(const float* in, const float* bias, const float* residua
     for (int r = 0; r < kMaxWorld; r++) { P.data[r] = T.peer_data[r]; }
     // a decode step's message (16 KB … 256 KB) spreads over kTpCtas CTAs; a prompt chunk's megabytes over kTpCtasLarge
     const long pairs = ((long)M * n_local + 1) / 2;
-    static const long largePairs = getenv("DEEPJ_CUDA_TP_LARGE_PAIRS") ? atol(getenv("DEEPJ_CUDA_TP_LARGE_PAIRS")) : kTpLargePairs;   // same on every rank
-    const bool large = pairs > largePairs;
-    launch_k(k_tp_exchange, dim3(large ? kTpCtasLarge : kTpCtas), dim3(256), 0, s, true, P, T.rank, T.world, T.slot_floats,
+    const bool large = pairs > g_large_pairs;
+    const size_t smallRegionWords = (size_t)2 * T.world * T.small_floats;
+    launch_k(k_tp_exchange, dim3(large ? kTpCtasLarge : kTpCtas), dim3(256), 0, s, true, P, T.rank, T.world,
+             large ? smallRegionWords : (size_t)0, large ? T.slot_floats : T.small_floats,
              large ? T.epochs + kTpCtas : T.epochs, large ? 0x80000000u : 0u, in, bias, residual, out,
              M, n_local, mode, g_dev_error);
 }
@@ -170,6 +197,17 @@ using namespace dj;
 
 extern "C" {
 
+// The message size (in floats per rank) above which an exchange takes the chunk-sized grid and its own slot
+// region.  Call before tp_create, with the same value on every rank; 0 restores the default (2^17).
+int deepj_cuda_tp_configure(int64_t large_message_floats) {
+    try {
+        if (T.local) throw std::runtime_error("tp_configure: call before tp_create");
+        if (large_message_floats < 0) throw std::runtime_error("tp_configure: negative threshold");
+        g_large_pairs = large_message_floats == 0 ? kTpLargePairs : (long)((large_message_floats + 1) / 2);
+        return 0;
+    } catch (const std::exception& e) { set_last_error(e.what()); return 1; }
+}
+
 // Step 1: allocate this rank's communication buffer and return its IPC handle (64 bytes).
 int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void* handle_out64) {
     try {
@@ -178,7 +216,8 @@ int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void*
         if (slot_floats <= 0 || slot_floats % 4 != 0) throw std::runtime_error("tp_create: slot size must be a positive multiple of 4 floats");
         if (T.local) throw std::runtime_error("tp_create: already created");
         T.rank = rank; T.world = world; T.slot_floats = (size_t)slot_floats;
-        const size_t dataBytes = (size_t)2 * world * slot_floats * 8;       // {bits, epoch} per value
+        T.small_floats = std::min((size_t)slot_floats, (size_t)(2 * g_large_pairs + 3) / 4 * 4);
+        const size_t dataBytes = tp_data_bytes();       // {bits, epoch} per value, both regions
         T.bytes = dataBytes + (size_t)(kTpCtas + kTpCtasLarge) * sizeof(unsigned);
         DJ_CUDA_CHECK(cudaMalloc(&T.local, T.bytes));
         DJ_CUDA_CHECK(cudaMemset(T.local, 0, T.bytes));
@@ -195,7 +234,7 @@ int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void*
 int deepj_cuda_tp_connect(const void* handles, int32_t world) {
     try {
         if (!T.local || world != T.world) throw std::runtime_error("tp_connect: call tp_create first, with the same world size");
-        const size_t dataBytes = (size_t)2 * T.world * T.slot_floats * 8;
+        const size_t dataBytes = tp_data_bytes();
         for (int r = 0; r < T.world; r++) {
             void* base = T.local;
             if (r != T.rank && handles == nullptr) {
@@ -213,6 +252,7 @@ int deepj_cuda_tp_connect(const void* handles, int32_t world) {
         }
         T.epochs = (unsigned*)((char*)T.local + dataBytes);
         T.ready = true;
+        invalidate_graphs();        // a graph captured against an earlier connection holds its peer addresses
         return 0;
     } catch (const std::exception& e) { set_last_error(e.what()); return 1; }
 }
@@ -233,6 +273,7 @@ int deepj_cuda_tp_destroy(void) {
         for (int r = 0; r < kMaxWorld; r++) if (T.absent[r]) { cudaFree(T.absent[r]); T.absent[r] = nullptr; }
         if (T.local) cudaFree(T.local);
         T = TpState();
+        invalidate_graphs();        // captured exchanges point into the buffers just unmapped
         return 0;
     } catch (const std::exception& e) { set_last_error(e.what()); return 1; }
 }

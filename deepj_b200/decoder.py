@@ -143,9 +143,11 @@ class Q8Decoder:
     """
 
     def __init__(self, cfg: DecoderConfig, batch: int = 1, device: int = 0, id_base: int = 1 << 24,
-                 tp_rank: int = 0, tp_world: int = 1, tp_slot_floats: int = 0):
+                 tp_rank: int = 0, tp_world: int = 1, tp_slot_floats: int = 0, share_weights: Optional["Q8Decoder"] = None):
         """`tp_slot_floats`: the slot size the exchange buffer was (or will be) connected with (`tp.connect`); it
-        bounds the rows a tensor-parallel prompt chunk may have (rows × dModel floats per exchange)."""
+        bounds the rows a tensor-parallel prompt chunk may have (rows × dModel floats per exchange).
+        `share_weights`: another decoder of the same configuration and sharding whose device weights this one reads
+        (its own activations and KV cache, a different `id_base`); the other decoder must outlive this one."""
         self.cfg = cfg
         self.B = int(batch)
         self.tp_slot_floats = int(tp_slot_floats)
@@ -178,6 +180,14 @@ class Q8Decoder:
         self._prefill_streams: Dict[int, np.ndarray] = {}
         self.position = 0
         self._alloc_state()
+        if share_weights is not None:
+            o = share_weights
+            if o.cfg != cfg or (o.tp_rank, o.tp_world) != (self.tp_rank, self.tp_world) or not o.loaded:
+                raise ValueError("share_weights needs a loaded decoder of the same configuration and sharding")
+            for name, buf_id in o.ids.items():
+                if name not in self.ids:          # everything that is not per-decoder state: the weights
+                    self.ids[name] = buf_id
+            self.loaded = True
 
     # ── id / buffer helpers ──
     def _new_id(self) -> int:
@@ -636,14 +646,14 @@ class Q8Decoder:
     def generate(self, prompt, max_new_tokens: int, temperature: float = 1.0, top_k: int = 40, seed: int = 0) -> np.ndarray:
         """TextGenerator.generate for batch 1 (models/TextGenerator.java:66-151) with the draw on the device:
         temperature / top-k sampling, one `java.util.Random(seed).nextFloat()` per new token, the logits never
-        leave the GPU.  The device sampler takes topK in 1..1024 (the reference's 0 = whole vocabulary is not offered)."""
+        leave the GPU.  topK = 0 means the whole vocabulary, as in the reference (TextGenerator.java:111-115)."""
         from .jrandom import JavaRandom
         if max_new_tokens < 0:
             raise ValueError("maxNewTokens must be >= 0")
         if not temperature > 0.0:
             raise ValueError("temperature must be > 0")
-        if top_k < 1 or top_k > 1024:
-            raise ValueError("topK must be in 1..1024 on the device sampler")
+        if top_k < 0:
+            raise ValueError("topK must be >= 0")
         if self.B != 1:
             raise ValueError("generate drives one sequence")
         rnd = JavaRandom(seed)

@@ -46,9 +46,11 @@ def barrier() -> None:
     dist.barrier()
 
 
-def connect(rank: int, world: int, slot_floats: int) -> None:
-    """Create this rank's exchange buffer, swap IPC handles, map the peers."""
+def connect(rank: int, world: int, slot_floats: int, large_message_floats: int = 0) -> None:
+    """Create this rank's exchange buffer, swap IPC handles, map the peers.  `large_message_floats` (the same on
+    every rank; 0 = the library's default) is the message size above which an exchange takes the chunk-sized grid."""
     lib = _lib.load()
+    _lib.check(lib.deepj_cuda_tp_configure(int(large_message_floats)))
     slot_floats = (int(slot_floats) + 3) // 4 * 4
     handle = ctypes.create_string_buffer(64)
     _lib.check(lib.deepj_cuda_tp_create(rank, world, slot_floats, handle))

@@ -121,11 +121,17 @@ int deepj_cuda_kv_alloc(int32_t kv_id, int32_t layers, int32_t batch, int32_t he
  * then every rank calls tp_connect with all handles in rank order.  After that op codes 71
  * and 72 may appear in streams; every rank must flush the same sequence of them.  Waits
  * inside the exchange kernel are bounded; an expired wait sets stats counter [5] to
- * 100 + the rank whose data did not arrive, the kernel finishes and the context stays usable.
+ * 100 + the rank whose data did not arrive, the kernel finishes and the context stays usable; while the counter
+ * is non-zero every later wait gives up at once, and a synchronous flush whose stream held an exchange returns
+ * non-zero with a message naming the rank.  tp_connect and tp_destroy drop the cached CUDA graphs (they hold peer
+ * addresses).
  * tp_connect(NULL, world) maps every other rank to a private buffer that nobody fills: the
  * way to see the bounded wait expire (a peer that never shows up) without a second process.
  * deepj_cuda_clear_device_error() zeroes counter [5] again. */
 int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void* handle_out64);
+/* Optional, before tp_create and with the same value on every rank: the message size (floats per rank) above
+ * which an exchange takes the chunk-sized grid and its own slot region; 0 = the default of 2^17. */
+int deepj_cuda_tp_configure(int64_t large_message_floats);
 int deepj_cuda_tp_connect(const void* handles, int32_t world);
 int deepj_cuda_tp_destroy(void);
 int deepj_cuda_clear_device_error(void);
@@ -143,8 +149,11 @@ int deepj_cuda_clear_device_error(void);
  * offsets, strides and shapes; it returns when `out` is readable.
  * Limits: batch·heads·splits·(head_dim+2) <= 524288 floats and batch·heads <= 4096;
  * anything larger is rejected with a message naming both numbers.
- * The first call on a device resolves the array's device address (cudaGetSymbolAddress);
- * make that first call before any stream capture begins.  Every call shares the one
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress), and the
+ * first call for a given head dimension may make the CUDA runtime load that kernel's code, which can
+ * allocate inside the driver: make one warm-up call per head dimension at start-up, before any stream
+ * capture begins and before the section that must not allocate.  The caller's current device is left
+ * as it was found.  Every call shares the one
  * array: calls that overlap on the GPU race on it, so keep them on one thread, one after
  * the other (the call is synchronous, which does that for a single caller). */
 int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int32_t v_off, int32_t ld,
@@ -172,8 +181,10 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
  *                        a prompt chunk: row b*T + t is token pos[b] + t of sequence b; the chunk's k (rotated)
  *                        and v are appended first, then every row attends causally over 0..pos[b]+t
  *  74 SAMPLE_TOPK       [op, logits, r, out, rows, cols, topK, temperatureBits]
- *                        TextGenerator.sampleFromLogits per row (stable descending order, first topK <= 1024,
- *                        float softmax of logit/T, first index whose running sum reaches r[row]); r = Random.nextFloat()
+ *                        TextGenerator.sampleFromLogits per row (stable descending order, first topK — 0 = the whole
+ *                        row, models/TextGenerator.java:111-115 — float softmax of logit/T, first index whose running
+ *                        sum reaches r[row]); r = Random.nextFloat().  Up to 1024 candidates are selected and sorted in
+ *                        shared memory; more sort the whole row in the workspace
  *  75 Q8_LINEAR_LN      [op, x, x_off, ldx, gamma, beta, epsBits, w, bias, residual, res_off, ldr, out, out_off, ldo, M, act]
  *                        the GPT blocks' projection: out = act(layernorm(x; gamma, beta, eps) · W + bias) (+residual),
  *                        LayerNorm1D semantics (mean, biased variance); act 0 = none, 1 = GELU (tanh form);

@@ -20,6 +20,13 @@ def test_reference_arm_prints_one_contract_line():
     assert d["higher_is_better"] is True and d["n_gpus"] == 1 and d["value"] > 0
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
     assert d["e2e"] == {"value": d["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    # the figure is extrapolated from a bounded sample and the line says so, with the steps really run
+    assert d["extrapolated"] is True and d["steps_run"] >= 1
+    # the same `config` object as the GPU arm prints for the same command line
+    sys.path.insert(0, ROOT)
+    import bench
+    w = bench.WORKLOADS["tiny_llama_q8_decode_b1"]
+    assert d["config"] == bench.workload_config("tiny_llama_q8_decode_b1", w, 1, "f32", bench.timing_context(w, 1, 3))
 
 
 def test_reference_arm_is_silent_on_other_ranks():

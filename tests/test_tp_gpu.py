@@ -23,8 +23,9 @@ def test_sharded_decode_matches_oracle(kind):
     if n < 2:
         pytest.skip("needs two GPUs")
     world = 4 if n >= 4 else 2
-    # the prompt chunks' exchanges (12288 value pairs) take the chunk-sized grid, the decode steps' the small one
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", DEEPJ_CUDA_TP_LARGE_PAIRS="4096")
+    # the worker lowers the large-message threshold (deepj_cuda_tp_configure) so that the prompt chunks' exchanges
+    # (24576 values) take the chunk-sized grid and the decode steps' the small one
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", "29621", os.path.join(HERE, "tp_gpu_worker.py"), kind]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
