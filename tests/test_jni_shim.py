@@ -191,7 +191,7 @@ def test_library_failure_becomes_a_runtime_exception_and_releases_the_arrays(jvm
     out = jvm.floats(np.full(4, 5.0))
     jvm.call("nativeDownloadBuffer", 1, out)
     assert jvm.exception() is not None
-    assert jvm.releases() == [(out.value, JNI_ABORT)]              # nothing written → nothing committed
+    assert jvm.releases() == []                                      # the wait for the device comes before the array is pinned: never pinned, nothing committed
     np.testing.assert_array_equal(jvm.read(out, np.float32, 4), 5.0)
     jvm.check_unpinned()
 
