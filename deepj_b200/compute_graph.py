@@ -33,7 +33,7 @@ OP_SUM_SCALAR, OP_SCATTER_ADD_ROWS_ATOMIC = 41, 42
 OP_EMBED_GATHER, OP_Q8_LINEAR, OP_Q8_SWIGLU, OP_ATTN_DECODE = 64, 65, 66, 67
 OP_ARGMAX_ROWS, OP_ADD_SCALAR_INPLACE, OP_COPY = 68, 69, 70
 OP_TP_ALLREDUCE, OP_TP_ALLGATHER = 71, 72
-OP_ATTN_PREFILL, OP_SAMPLE_TOPK, OP_Q8_LINEAR_LN = 73, 74, 75
+OP_ATTN_PREFILL, OP_SAMPLE_TOPK, OP_Q8_LINEAR_LN, OP_DECODE_STEP = 73, 74, 75, 76
 
 # op → (stride, offsets of the slots that hold buffer ids); ComputeGraph.java:89-147
 OP_METADATA: Dict[int, tuple] = {}
@@ -68,6 +68,7 @@ OP_METADATA[OP_TP_ALLGATHER] = (5, (1, 2))
 OP_METADATA[OP_ATTN_PREFILL] = (18, (1, 6, 8, 9, 10, 11))
 OP_METADATA[OP_SAMPLE_TOPK] = (8, (1, 2, 3))
 OP_METADATA[OP_Q8_LINEAR_LN] = (17, (1, 4, 5, 7, 8, 9, 12))
+OP_METADATA[OP_DECODE_STEP] = (3, (1,))
 
 
 def float_bits(value: float) -> int:

@@ -141,6 +141,17 @@ JNIEXPORT void JNICALL CUDA_NATIVE(nativeKvAlloc)(JNIEnv* env, jclass, jint kvId
     if (deepj_cuda_kv_alloc(kvId, layers, batch, heads, maxSeq, headDim) != 0) raise_last(env);
 }
 
+// Decode plan behind op 76 (the whole-token kernel): desc as deepj_cuda_decode_plan documents it.
+JNIEXPORT void JNICALL CUDA_NATIVE(nativeDecodePlan)(JNIEnv* env, jclass, jint planId, jintArray descArr, jint len) {
+    int rc;
+    {
+        IntsIn desc(env, descArr);
+        rc = desc.ok(len) ? deepj_cuda_decode_plan(planId, reinterpret_cast<const int32_t*>(desc.p), len) : -1;
+    }
+    if (rc == -1) raise(env, "nativeDecodePlan: len exceeds the descriptor array");
+    else if (rc != 0) raise_last(env);
+}
+
 // ───────────── tensor parallelism: one JVM per GPU, the host exchanges the 64-byte handles ─────────────
 
 // Allocates this rank's exchange buffer and returns its CUDA IPC handle (64 bytes), or null with an exception pending.

@@ -5,6 +5,8 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <utility>
+#include <vector>
 
 #define DJ_CUDA_CHECK(expr)                                                                  \
     do {                                                                                     \
@@ -141,6 +143,16 @@ struct PoolF32 { float* ptr; size_t floats; };
 struct PoolKV { float* ptr; int layers, B, H, maxSeq, hd; };
 bool pool_f32(int id, PoolF32* out);
 bool pool_kv(int id, PoolKV* out);
+bool pool_q8(int id, Q8View* out);
+// Serial number of a pool object (0 when the id does not exist); a released and re-created id gets a new serial.
+unsigned long long pool_serial(int id);
+// Registers device memory owned by a decode plan under `id` in the pool (released with the other objects).
+void pool_add_plan(int id, void* dev_ptr, size_t bytes);
+
+// ── whole-token decode kernel (decode_step.cu) ──
+// Validates the plan object behind op 76 and appends the (id, serial) of everything it references to `refs`.
+void decode_step_check(int plan_id, std::vector<std::pair<int, unsigned long long>>* refs);
+void launch_decode_step(int plan_id, int feed_back, cudaStream_t s);
 // The library's stream and device; the stream is null until the library has been initialised.
 cudaStream_t runtime_stream();
 int runtime_device();

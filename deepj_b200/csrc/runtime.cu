@@ -26,7 +26,7 @@ using namespace dj;
 
 thread_local std::string g_err;
 
-enum BufKind { kF32 = 0, kQ8 = 1, kKV = 2 };
+enum BufKind { kF32 = 0, kQ8 = 1, kKV = 2, kPlan = 3 };
 struct Buf {
     BufKind kind = kF32;
     void* ptr = nullptr;
@@ -167,6 +167,7 @@ int op_stride(int op) {
         case DEEPJ_OP_COPY: return 6;
         case DEEPJ_OP_TP_ALLREDUCE: return 7;
         case DEEPJ_OP_TP_ALLGATHER: return 5;
+        case DEEPJ_OP_DECODE_STEP: return 3;
         default: return -1;
     }
 }
@@ -438,6 +439,14 @@ void do_op(Ctx& ctx, const int32_t* c) {
             if (go) launch_tp_exchange(in, nullptr, nullptr, o, M, nl, 1, s);
             break;
         }
+        case DEEPJ_OP_DECODE_STEP: {   // [op, plan, feed_back]
+            require(c[2] == 0 || c[2] == 1, "decodeStep", "feed_back must be 0 or 1");
+            find_buf(ctx, c[1], kPlan, "decodeStep");
+            decode_step_check(c[1], ctx.refs);
+            if (tp_world() > 1) ctx.bounded_waits = true;
+            if (go) launch_decode_step(c[1], c[2], s);
+            break;
+        }
         default:
             throw std::runtime_error("Unknown op code in command stream: " + std::to_string(op));
     }
@@ -581,6 +590,21 @@ bool pool_kv(int id, PoolKV* out) {
     return true;
 }
 void invalidate_graphs() { R.epoch++; drop_graphs(); }
+bool pool_q8(int id, Q8View* out) {
+    auto it = R.pool.find(id);
+    if (it == R.pool.end() || it->second.kind != kQ8 || it->second.ptr == nullptr) return false;
+    *out = q8view(it->second);
+    return true;
+}
+unsigned long long pool_serial(int id) {
+    auto it = R.pool.find(id);
+    return it == R.pool.end() ? 0ull : it->second.serial;
+}
+void pool_add_plan(int id, void* dev_ptr, size_t bytes) {
+    Buf b; b.kind = kPlan; b.ptr = dev_ptr; b.bytes = bytes;
+    b.serial = R.next_serial++;
+    R.pool[id] = b;
+}
 cudaStream_t runtime_stream() { return R.inited ? R.stream : nullptr; }
 int runtime_device() { return R.device; }
 void set_last_error(const std::string& msg) { g_err = msg; }

@@ -48,8 +48,10 @@ struct TpState {
     size_t slot_floats = 0;         // values one exchange may carry per rank
     size_t small_floats = 0;        // … of which the decode-sized class can see at most this many
     // layout of one rank's buffer, {bits, epoch} words of 8 bytes: the decode-sized class's region
-    // words[2][world][small_floats], then the chunk-sized class's words[2][world][slot_floats], then the
-    // per-CTA exchange counters (u32; kTpCtas for the small grid, kTpCtasLarge for the large one; private to this rank)
+    // words[2][world][small_floats], then the chunk-sized class's words[2][world][slot_floats], then the region of the
+    // whole-token decode kernel (decode_step.cu: words[2][world][small_floats] of partial sums + [world][2] pick pairs),
+    // then the exchange counters (u32; kTpCtas for the small grid, kTpCtasLarge for the large one, one tag counter of
+    // the decode kernel; private to this rank)
     void* local = nullptr;
     size_t bytes = 0;
     float* peer_data[kMaxWorld] = {};
@@ -164,11 +166,21 @@ __global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int wor
 
 }  // namespace
 
-size_t tp_data_bytes() {
+size_t tp_exchange_bytes() {
     // a chunk-sized region only when a message can exceed the decode-sized class
     const size_t largeFloats = T.slot_floats > T.small_floats ? T.slot_floats : 0;
     return (size_t)2 * T.world * (T.small_floats + largeFloats) * 8;
 }
+size_t tp_step_words_count() { return (size_t)2 * T.world * T.small_floats + 2 * (size_t)T.world + 8; }
+size_t tp_data_bytes() { return tp_exchange_bytes() + tp_step_words_count() * 8; }
+
+// The decode-step kernel's view of the connection: rank r's word region, the tag counter, the region's size in words.
+unsigned long long* tp_step_words(int r) {
+    return T.ready ? reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(T.peer_data[r]) + tp_exchange_bytes()) : nullptr;
+}
+unsigned* tp_step_epoch() { return T.ready ? T.epochs + kTpCtas + kTpCtasLarge : nullptr; }
+size_t tp_step_floats() { return T.ready ? tp_step_words_count() : 0; }
+int tp_rank() { return T.rank; }
 
 bool tp_ready() { return T.ready; }
 int tp_world() { return T.ready ? T.world : 1; }
@@ -218,7 +230,7 @@ int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void*
         T.rank = rank; T.world = world; T.slot_floats = (size_t)slot_floats;
         T.small_floats = std::min((size_t)slot_floats, (size_t)(2 * g_large_pairs + 3) / 4 * 4);
         const size_t dataBytes = tp_data_bytes();       // {bits, epoch} per value, both regions
-        T.bytes = dataBytes + (size_t)(kTpCtas + kTpCtasLarge) * sizeof(unsigned);
+        T.bytes = dataBytes + (size_t)(kTpCtas + kTpCtasLarge + 4) * sizeof(unsigned);
         DJ_CUDA_CHECK(cudaMalloc(&T.local, T.bytes));
         DJ_CUDA_CHECK(cudaMemset(T.local, 0, T.bytes));
         DJ_CUDA_CHECK(cudaDeviceSynchronize());

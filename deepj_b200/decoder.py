@@ -27,7 +27,7 @@ from typing import Tuple, Callable, Dict, List, Optional
 import numpy as np
 
 from . import _lib
-from .compute_graph import (OP_ADD, OP_Q8_LINEAR_LN, OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_ATTN_PREFILL, OP_COPY, OP_EMBED_GATHER, OP_SAMPLE_TOPK,
+from .compute_graph import (OP_ADD, OP_DECODE_STEP, OP_Q8_LINEAR_LN, OP_ADD_SCALAR_INPLACE, OP_ARGMAX_ROWS, OP_ATTN_DECODE, OP_ATTN_PREFILL, OP_COPY, OP_EMBED_GATHER, OP_SAMPLE_TOPK,
                             OP_Q8_LINEAR, OP_Q8_SWIGLU, OP_TP_ALLGATHER, OP_TP_ALLREDUCE, float_bits)
 
 RMS_EPS = 1e-6      # layers/transformer/norm/RMSNorm1D.java:30
@@ -143,11 +143,15 @@ class Q8Decoder:
     """
 
     def __init__(self, cfg: DecoderConfig, batch: int = 1, device: int = 0, id_base: int = 1 << 24,
-                 tp_rank: int = 0, tp_world: int = 1, tp_slot_floats: int = 0, share_weights: Optional["Q8Decoder"] = None):
+                 tp_rank: int = 0, tp_world: int = 1, tp_slot_floats: int = 0, share_weights: Optional["Q8Decoder"] = None,
+                 fused_step: Optional[bool] = None):
         """`tp_slot_floats`: the slot size the exchange buffer was (or will be) connected with (`tp.connect`); it
         bounds the rows a tensor-parallel prompt chunk may have (rows × dModel floats per exchange).
         `share_weights`: another decoder of the same configuration and sharding whose device weights this one reads
-        (its own activations and KV cache, a different `id_base`); the other decoder must outlive this one."""
+        (its own activations and KV cache, a different `id_base`); the other decoder must outlive this one.
+        `fused_step`: run a token step as ONE persistent kernel (op 76) instead of one kernel per operator; None = whenever
+        the model qualifies (a Llama-shaped model, one sequence, every reduction length a multiple of 32, head dim 32 / 64 /
+        128).  Under tensor parallelism the plan is made at the first step, after `tp.connect`."""
         self.cfg = cfg
         self.B = int(batch)
         self.tp_slot_floats = int(tp_slot_floats)
@@ -179,6 +183,10 @@ class Q8Decoder:
         self._prefill_cap = 0
         self._prefill_streams: Dict[int, np.ndarray] = {}
         self.position = 0
+        self._plan_id: Optional[int] = None
+        if fused_step and not self.fused_step_eligible(cfg, self.B, tp_world):
+            raise ValueError("this configuration does not qualify for the single-kernel token step")
+        self.fused_step = self.fused_step_eligible(cfg, self.B, tp_world) if fused_step is None else bool(fused_step)
         self._alloc_state()
         if share_weights is not None:
             o = share_weights
@@ -188,6 +196,14 @@ class Q8Decoder:
                 if name not in self.ids:          # everything that is not per-decoder state: the weights
                     self.ids[name] = buf_id
             self.loaded = True
+
+    @staticmethod
+    def fused_step_eligible(cfg: DecoderConfig, batch: int, tp_world: int = 1) -> bool:
+        """Whether op 76 covers this model: see `deepj_cuda_decode_plan` in include/deepj_cuda.h."""
+        if cfg.kind != "llama" or batch != 1 or cfg.head_dim not in (32, 64, 128):
+            return False
+        ks = (cfg.d_model, cfg.d_model // tp_world, cfg.d_ff // tp_world)
+        return all(k % 32 == 0 for k in ks) and max(ks) <= 16384
 
     # ── id / buffer helpers ──
     def _new_id(self) -> int:
@@ -448,9 +464,31 @@ class Q8Decoder:
         if not self.loaded:
             raise RuntimeError("weights are not loaded")
         if self._stream_host is None:
-            self._stream_dev = self._build(feed_back=True)
-            self._stream_host = self._build(feed_back=False)
+            if self.fused_step:
+                plan = self._decode_plan()
+                self._stream_dev = np.asarray([OP_DECODE_STEP, plan, 1], dtype=np.int32)
+                self._stream_host = np.asarray([OP_DECODE_STEP, plan, 0], dtype=np.int32)
+            else:
+                self._stream_dev = self._build(feed_back=True)
+                self._stream_host = self._build(feed_back=False)
         return self._stream_host, self._stream_dev
+
+    def _decode_plan(self) -> int:
+        """The plan object behind op 76: every buffer and weight of a token step, resolved once by the library."""
+        if self._plan_id is None:
+            c, I = self.cfg, self.ids
+            logits = I["logits_local"] if self.tp_world > 1 else I["logits"]
+            desc = [1, c.n_layers, self.h_local, c.head_dim, float_bits(RMS_EPS),
+                    I["tok"], I["pos"], I["emb"], I["cos"], I["sin"], I["kv"], I["x"], I["x2"], I["qkv"], I["att"], I["h"],
+                    logits, I["next"], I["gF"], I["Wlm"], I["blm"]]
+            for l in range(c.n_layers):
+                desc += [I[f"g1.{l}"], I[f"Wqkv.{l}"], I[f"Wo.{l}"], I[f"g2.{l}"], I[f"Wg.{l}"], I[f"bg.{l}"], I[f"Wu.{l}"], I[f"bu.{l}"],
+                         I[f"Wd.{l}"], I[f"bd.{l}"]]
+            arr = np.asarray(desc, dtype=np.int32)
+            plan = self._new_id()
+            _lib.check(self.lib.deepj_cuda_decode_plan(plan, arr.ctypes.data, arr.size))
+            self._plan_id = plan
+        return self._plan_id
 
     # ── stepping ──
     def reset(self) -> None:
@@ -515,6 +553,11 @@ class Q8Decoder:
             _lib.check(self.lib.deepj_cuda_synchronize())
 
     def logits(self) -> np.ndarray:
+        if self.fused_step and self.tp_world > 1:
+            # the single-kernel step leaves this rank's vocabulary columns; gather the ranks' shards (every rank calls this)
+            I = self.ids
+            g = np.asarray([OP_TP_ALLGATHER, I["logits_local"], I["logits"], self.B, self.v_local], dtype=np.int32)
+            _lib.check(self.lib.deepj_cuda_flush_ops(g.ctypes.data, g.size))
         return self._download(self.ids["logits"], self.B * self.cfg.vocab_size).reshape(self.B, self.cfg.vocab_size)
 
     def next_tokens(self) -> np.ndarray:

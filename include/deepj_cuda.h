@@ -112,6 +112,20 @@ int deepj_cuda_synth_fill(int32_t id, uint64_t seed, uint64_t ordinal, float std
 int deepj_cuda_kv_alloc(int32_t kv_id, int32_t layers, int32_t batch, int32_t heads,
                         int32_t max_seq, int32_t head_dim);
 
+/* Decode plan: everything one batch-1 token step of a Llama-shaped Q8 model touches, resolved once, for op 76
+ * (DECODE_STEP), which runs the whole step — embedding row, every block, final norm, LM head, greedy pick, position
+ * advance — as ONE persistent kernel.  No counterpart in the reference (its step is DecoderOnlyModel.forward over the
+ * whole context, models/DecoderOnlyModel.java:58-64).  The plan lives in the same id space as the buffers and is
+ * released with deepj_cuda_release_buffers; releasing anything it references makes later flushes of op 76 fail cleanly.
+ * desc = [1 (version), n_layers, heads on this rank, head_dim (32 | 64 | 128), epsBits,
+ *         tok, pos, emb, cos, sin, kv, x, x2, qkv, att, h, logits, next, gF, Wlm, blm,                 (buffer ids)
+ *         then per block: g1, Wqkv, Wo, g2, Wgate, bgate, Wup, bup, Wdown, bdown]
+ * Shapes are checked against the Q8 objects (every reduction length a multiple of 32).  With a tensor-parallel
+ * connection in place (tp_connect before this call) the plan is made for this rank's shard: Wo and down are row shards
+ * whose partial sums the kernel exchanges itself, `logits` holds this rank's vocabulary columns, and every rank ends up
+ * with the same pick. */
+int deepj_cuda_decode_plan(int32_t plan_id, const int32_t* desc, int32_t len);
+
 /* Tensor parallelism, one process per GPU of one node.  No counterpart in the reference
  * (DeepJ is single-device).  Every rank calls tp_create (allocates its exchange buffer:
  * 2 x world slots of slot_floats values, 8 bytes each, returns a 64-byte CUDA IPC handle; one exchange
@@ -185,6 +199,8 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
  *                        row, models/TextGenerator.java:111-115 — float softmax of logit/T, first index whose running
  *                        sum reaches r[row]); r = Random.nextFloat().  Up to 1024 candidates are selected and sorted in
  *                        shared memory; more sort the whole row in the workspace
+ *  76 DECODE_STEP       [op, plan, feed_back]   one whole batch-1 token step of the plan's model as one kernel:
+ *                        next = greedy pick of the logits at pos, pos += 1, and tok = next when feed_back = 1
  *  75 Q8_LINEAR_LN      [op, x, x_off, ldx, gamma, beta, epsBits, w, bias, residual, res_off, ldr, out, out_off, ldo, M, act]
  *                        the GPT blocks' projection: out = act(layernorm(x; gamma, beta, eps) · W + bias) (+residual),
  *                        LayerNorm1D semantics (mean, biased variance); act 0 = none, 1 = GELU (tanh form);
@@ -202,6 +218,7 @@ int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t k_off, int
 #define DEEPJ_OP_ATTN_PREFILL        73
 #define DEEPJ_OP_SAMPLE_TOPK         74
 #define DEEPJ_OP_Q8_LINEAR_LN       75
+#define DEEPJ_OP_DECODE_STEP        76
 
 #ifdef __cplusplus
 }

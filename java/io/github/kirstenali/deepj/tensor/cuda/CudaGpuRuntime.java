@@ -71,6 +71,11 @@ public final class CudaGpuRuntime implements GpuRuntime {
         CudaNative.nativeKvAlloc(kvId, layers, batch, heads, maxSeq, headDim);
     }
 
+    /** Everything one batch-1 token step touches, resolved once; afterwards the stream {@code [76, planId, feedBack]} runs the step. */
+    public void decodePlan(int planId, int[] desc) {
+        CudaNative.nativeDecodePlan(planId, desc, desc.length);
+    }
+
     /** Step 1 of the tensor-parallel set-up: this rank's 64-byte handle, to be sent to every other rank. */
     public byte[] tpCreate(int rank, int world, long slotFloats) {
         return CudaNative.nativeTpCreate(rank, world, slotFloats);

@@ -20,13 +20,14 @@ def main():
     rank, world = tp.init_process_group()
     local = int(os.environ.get("LOCAL_RANK", rank))
     kind = sys.argv[1] if len(sys.argv) > 1 else "llama"
+    batch = int(sys.argv[2]) if len(sys.argv) > 2 else 2          # 1: the decode steps run as the single whole-token kernel
     if kind == "llama":
         cfg = DecoderConfig("llama", 512, 64, 512, 8, 2, 1024)
     else:
         cfg = DecoderConfig("deepseek", 512, 64, 512, 8, 2, 1024, q_rank=256, kv_rank=128)
     om = oracle.OracleModel(cfg.kind, cfg.vocab_size, cfg.max_seq_len, cfg.d_model, cfg.n_heads, cfg.n_layers, cfg.d_ff,
                             cfg.q_rank, cfg.kv_rank, seed=21)
-    B, T = 2, 40
+    B, T = batch, 40
     # slots large enough for a 24-token chunk per sequence: the 40-token prompt goes through the many-row path in
     # two chunks (24 + 16 tokens, 48 and 32 rows per exchange), the steps after it through the decode path
     slot = max(B * 24 * cfg.d_model, B * cfg.vocab_size // world)
@@ -60,7 +61,7 @@ def main():
     dec.close()
     tp.disconnect()
     if rank == 0:
-        print(f"TP_GPU_OK world={world} kind={kind}", flush=True)
+        print(f"TP_GPU_OK world={world} kind={kind} batch={B} fused_step={dec.fused_step}", flush=True)
 
 
 if __name__ == "__main__":
