@@ -52,6 +52,12 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes (read + write) over algorithmic bytes of one k_decode_step launch, from the ncu capture of a reduced-depth
+# model of the same width (profiles/); None until a capture exists.  Traffic grows with the weights and K/V rows streamed.
+DECODE_STEP_DRAM_RATIO = None
+DECODE_STEP_DRAM_SOURCE = "no capture yet"
+
+
 def measured_peak_gbs():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -302,6 +308,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the reduced-depth check against the CPU oracle")
     ap.add_argument("--no-batch16", action="store_true", help="skip the 16-sequence sub-record of the 7B workload")
+    ap.add_argument("--fused-step", action="store_true", help="the single whole-token kernel (op 76) instead of one kernel per operator")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.prompt_len > 0:
@@ -332,7 +339,8 @@ def main():
     # exchange slots hold a prompt chunk's partial sums (rows x dModel per exchange), capped at 2048 rows
     slot = max((16 if batch16 else B) * cfg.d_model, (16 if batch16 else B) * cfg.vocab_size // world,
                min(B * min(w["prompt"], Q8Decoder.PREFILL_CHUNK), 2048) * cfg.d_model)
-    dec = Q8Decoder(cfg, batch=B, device=local_rank, tp_rank=rank, tp_world=world, tp_slot_floats=slot if world > 1 else 0)
+    dec = Q8Decoder(cfg, batch=B, device=local_rank, tp_rank=rank, tp_world=world, tp_slot_floats=slot if world > 1 else 0,
+                    fused_step=args.fused_step)
     if world > 1:
         # weights are split by rows/columns over the ranks; [rows x d] partial sums and the logits
         # shards cross NVLink through the library's own peer-memory exchange
@@ -344,7 +352,8 @@ def main():
         sys.path.insert(0, os.path.join(ROOT, "tests"))
         from parity_util import reduced_depth_parity
         parity = reduced_depth_parity(w, layers=2, prompt_len=48, n_new=8, rank=rank, world=world, device=local_rank,
-                                      tp_slot_floats=slot if world > 1 else 0, check_codes=False, kv_dtype=args.kv)
+                                      tp_slot_floats=slot if world > 1 else 0, check_codes=False, kv_dtype=args.kv,
+                                      fused_step=args.fused_step)
         if not (parity["tokens_equal"] and parity["max_err_over_range"] <= parity["tolerance"]):
             if rank == 0:
                 print(json.dumps({"metric": "q8_decode_tokens_per_s", "error": "parity check failed", "parity": parity}), flush=True)
@@ -417,7 +426,7 @@ def main():
         "gpu_launches": m["launches"],
         "clocks": m["clocks"],
         "parity": parity,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+        "roofline_gemv" if dec.fused_step else "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # DRAM bytes per launch (read + write), scaled by K·N from the ncu capture of the K=4096, N=12288
                      # launch (56.869 MB measured against 56.69 MB algorithmic): the full-size step is too large to capture
                      "traffic": (gemv_bytes / max(n_gemv, 1)) * (56.869 / 56.69), "traffic_unit": "bytes per launch (average)",
@@ -437,6 +446,18 @@ def main():
         "prefill": {"tokens": int(B * w["prompt"]), "seconds": t_prefill, "tokens_per_s": B * w["prompt"] / max(t_prefill, 1e-9),
                     "path": "chunked, many-row kernels" if prefill_chunked else "one decode step per position"},
     }
+
+    if dec.fused_step:
+        # the step is ONE launch of the whole-token kernel: its algorithmic bytes are this GPU's share of the Q8 weights and of
+        # the K/V rows of the timed context, its launch duration the device time per step (CUDA events over the timed regions)
+        line["roofline"] = {"bound": "hbm", "kernel": "k_decode_step", "launches_per_step": 1, "achieved": step_achieved, "peak": peak,
+                            "unit": "GB/s", "frac": step_achieved / peak, "peak_kind": peak_kind, "bytes_per_launch": step_bytes / world,
+                            "us_per_launch": 1e3 * ms_per_step,
+                            "traffic": (step_bytes / world) * DECODE_STEP_DRAM_RATIO if DECODE_STEP_DRAM_RATIO else None,
+                            "traffic_unit": "bytes per launch", "traffic_source": DECODE_STEP_DRAM_SOURCE}
+        line["step_kernel"] = "k_decode_step: one cooperative launch per token (op 76)"
+    else:
+        line["step_kernel"] = "one kernel per operator, CUDA-graph replay"
 
     # ── the same model at 16 concurrent sequences (BASELINE configs[4] asks for 1 and 16), sharing the weights ──
     if batch16:

@@ -10,11 +10,19 @@
 // Why one kernel: a batch-1 token is ≈ 160 dependent operators of 3–25 µs; launched one by one,
 // each pays ≈ 5 µs around its streaming phase (dependency release, activation staging, tail).
 // Here one cooperative grid of one 16-warp CTA per SM walks the phases and meets at device-side
-// barriers.  The Q8 weights of ALL phases form one static sequence of ring items per warp (16 weight
-// rows × 64 codes + 32 scales = 1152 bytes, cp.async into a warp-private shared-memory ring, 8
-// deep), and the producer side of a ring runs ahead of the consumer ACROSS phase boundaries: while a
-// CTA waits at a barrier, stages activations or runs attention, its rings fill with the next
-// projection's weights, so HBM keeps streaming through the dependency chain.
+// barriers.  The Q8 weights of ALL phases form one static sequence of ring items per warp, and the
+// producer side of a ring runs ahead of the consumer ACROSS phase boundaries: while a CTA waits at a
+// barrier, stages activations or runs attention, its rings fill with the next projection's weights,
+// so HBM keeps streaming through the dependency chain.
+//
+// The weights are read from a tile-major copy made once per plan (k_pack_phase): the 16 weight rows ×
+// 64 codes + 32 scales of a (tile, 64-k pair) are one contiguous 1152-byte image of what the MMA
+// fragments read from shared memory (32-byte halves already XOR-swizzled by row), and a warp's pairs
+// of a tile follow each other, so a ring item — two pairs, 2304 bytes — is ONE cp.async.bulk on an
+// mbarrier, issued by one lane.  With the canonical row-major layout every lane spent ≈ 100
+// instructions per item on copy addresses and group bookkeeping and the projection loop was
+// issue-bound at about two thirds of the HBM rate.  The copy costs the plan as much memory again as
+// the Q8 weights it covers.
 //
 // The arithmetic is the per-operator kernels' (q8_gemv_i8.cu, attn.cu), instruction for
 // instruction: int8 codes as the A operand of mma.sync m16n8k32, activations as three base-256
@@ -54,8 +62,10 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kHalfWarps = 8;                   // warps that share a weight-row tile
 constexpr int kRows = 16;
 constexpr int kRowStride = 64;
-constexpr int kSlotBytes = kRows * kRowStride + kRows * 2 * 4;      // 1152: 16 rows × 64 codes, then 32 scales
-constexpr int kDepth = 8;                       // ring slots per warp
+constexpr int kPairBytes = kRows * kRowStride + kRows * 2 * 4;      // 1152: 16 rows × 64 codes, then 32 scales
+constexpr int kItemPairs = 2;                   // 64-k pairs per ring item
+constexpr int kSlotBytes = kItemPairs * kPairBytes;
+constexpr int kDepth = 4;                       // ring slots per warp: three items (6.9 KB) in flight, one being read
 constexpr int kXsPad = 32;
 constexpr int kStageRounds = 2;                 // rows of up to 2·512·16 = 16384 values are staged from registers
 constexpr int kMaxSplits = 256;
@@ -65,17 +75,13 @@ constexpr unsigned kSpinLimit = 1u << 22;
 constexpr int kMaxWorld = 8;
 
 struct DsLayer {                // one block's device pointers (a table in global memory)
-    const float* g1; const int8_t* qkv_c; const float* qkv_s;
-    const int8_t* wo_c; const float* wo_s;
-    const float* g2; const int8_t* wg_c; const float* wg_s; const float* bg;
-    const int8_t* wu_c; const float* wu_s; const float* bu;
-    const int8_t* wd_c; const float* wd_s; const float* bd;
+    const float* g1; const float* g2; const float* bg; const float* bu; const float* bd;
+    const unsigned char* w[4];  // tile-major weight streams: Wq‖Wk‖Wv, Wo, gate‖up (8 + 8 rows per tile), down
     float* kcache; float* vcache;
 };
 
 struct DsPhase {                // a projection's weight stream as the ring producer sees it
-    const int8_t* codes; const float* scales; const int8_t* codes2; const float* scales2;
-    int K, N, swiglu, pad;
+    const unsigned char* packed; int K, N, swiglu, pad;
 };
 
 struct DsPeers { unsigned long long* words[kMaxWorld]; };
@@ -83,8 +89,8 @@ struct DsPeers { unsigned long long* words[kMaxWorld]; };
 struct DsParams {
     const DsLayer* layers; int n_layers;
     const float* emb; float* tok; float* pos; const float* cosT; const float* sinT;
-    float* x; float* x2; float* qkv; float* att; float* h; float* part; float* logits; float* next;
-    const float* gF; const int8_t* lm_c; const float* lm_s; const float* blm;
+    float* x; float* x2; float* qkv; float* att; float* h; float* logits; float* next;
+    const float* gF; const unsigned char* lm_w; const float* blm;      // lm_w: the LM head's tile-major stream
     int d, H, hd, F, V, vocab, maxSeq, splits, kmax;
     float eps, scale;
     float* attn_ws; int* tickets; unsigned* bar; int* pick; int* error;
@@ -93,6 +99,7 @@ struct DsParams {
     int rank, world;
     DsPeers peers;                      // every rank's exchange words (mine included)
     unsigned* epoch;                    // the last exchange tag handed out (device counter, advanced by CTA 0 at the end)
+    unsigned long long* trace;          // phase tracing (DEEPJ_CUDA_TRACE=1): CTA 0 stamps %globaltimer at the phase boundaries of block 1
 };
 
 // ── small device helpers ──
@@ -102,19 +109,34 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void cp_async_wait_dyn(int n) {
-    switch (n) {
-        case 0: cp_async_wait<0>(); break;
-        case 1: cp_async_wait<1>(); break;
-        case 2: cp_async_wait<2>(); break;
-        case 3: cp_async_wait<3>(); break;
-        case 4: cp_async_wait<4>(); break;
-        case 5: cp_async_wait<5>(); break;
-        case 6: cp_async_wait<6>(); break;
-        default: cp_async_wait<7>(); break;
-    }
+// Shared-memory loads by 32-bit shared address: the out-of-line phases get their pointers as plain arguments, so the
+// compiler cannot prove the address space and would otherwise emit (slower) generic loads.
+__device__ __forceinline__ uint2 lds_u2(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
 }
-static_assert(kDepth == 8, "cp_async_wait_dyn covers ring depths up to 8");
+__device__ __forceinline__ float lds_f(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void load16_cg(const float* src, float (&v)[16]) {       // rows written by other SMs in this launch: L2, never a stale L1 line
 #pragma unroll
     for (int j = 0; j < 4; j++) {
@@ -132,342 +154,396 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ void st_volatile_v2(void* p, uint2 v) {
     asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 
-template <int LPP>      // lanes per cached position = head dim / 16
-__global__ void __launch_bounds__(kThreads, 1) k_decode_step(const DsParams p) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    constexpr int HD = LPP * 16;
-    constexpr int PPW = 32 / LPP;
-    constexpr int G = kSubWarps * PPW;              // position groups of an attention group
-    // layout: rings [16][kDepth][1152] | activation digits (3 columns) + block scales, overlaid by the attention scratch |
-    //         tile partials [2 halves][2][8 warps][128] | phase descriptors [2 layers][4] | reductions
-    unsigned char* rings = smem;
-    unsigned char* actRegion = rings + (size_t)kWarps * kDepth * kSlotBytes;
-    const int actBytes = max(3 * (p.kmax + kXsPad) + (p.kmax >> 5) * 4, 4 * kAttnScratchFloats * 4);
-    float* s_part = reinterpret_cast<float*>(actRegion + ((actBytes + 127) & ~127));
-    DsPhase* s_desc = reinterpret_cast<DsPhase*>(s_part + 2 * 2 * kHalfWarps * 128);
-    float* s_red = reinterpret_cast<float*>(s_desc + 8);             // [16]
-    int* s_flags = reinterpret_cast<int*>(s_red + kWarps);           // [0] dead, [1..4] attention group "last" flags, [8..] pick scratch
-    int8_t* xd = reinterpret_cast<int8_t*>(actRegion);
+// ── shared-memory layout ──
+// rings [16 warps][kDepth][2304] | activation digits (3 columns) + block scales, overlaid by the attention scratch |
+// tile partials [2 halves][2][8 warps][128] | weight-phase descriptors [2 blocks][4] | block tables [2] | reductions | flags | peers
+struct DsSmem {
+    unsigned char* rings; unsigned char* act; float* part; DsPhase* desc; DsLayer* lay; float* red; int* flags;
+    unsigned long long** peers; unsigned long long* mbar;      // mbar: one per ring slot, [16 warps][kDepth]
+};
+__device__ __forceinline__ DsSmem ds_layout(unsigned char* smem, int kmax) {
+    DsSmem m;
+    m.rings = smem;
+    m.act = smem + (size_t)kWarps * kDepth * kSlotBytes;
+    const int actBytes = max(3 * (kmax + kXsPad) + (kmax >> 5) * 4, 4 * kAttnScratchFloats * 4);
+    m.part = reinterpret_cast<float*>(m.act + ((actBytes + 127) & ~127));
+    m.desc = reinterpret_cast<DsPhase*>(m.part + 2 * 2 * kHalfWarps * 128);
+    m.lay = reinterpret_cast<DsLayer*>(m.desc + 8);
+    m.red = reinterpret_cast<float*>(m.lay + 2);
+    m.flags = reinterpret_cast<int*>(m.red + kWarps);       // [0] dead, [1..4] attention groups' "last" flags, [5] barrier generation, [8..39] pick pairs
+    m.peers = reinterpret_cast<unsigned long long**>(m.flags + 48);
+    m.mbar = reinterpret_cast<unsigned long long*>(m.peers + kMaxWorld);
+    return m;
+}
 
+// Grid barrier over the cooperative launch, bounded: the generation lives in shared memory (flags[5]); a CTA whose wait
+// ran out, or that finds the error word set, marks itself dead (flags[0]) and stops waiting for the rest of the launch.
+__device__ __noinline__ void ds_grid_barrier(unsigned* bar, int* error, int* flags, int nCtas, int code) {
+    __syncthreads();
+    if (threadIdx.x == 0 && flags[0] == 0) {
+        const unsigned gen = (unsigned)flags[5] + 1u;
+        flags[5] = (int)gen;
+        const unsigned target = gen * (unsigned)nCtas;
+        __threadfence();
+        atomicAdd(bar, 1u);
+        unsigned it = 0;
+        while (ld_acquire(bar) < target) {
+            if (++it > kSpinLimit) { atomicCAS(error, 0, code); flags[0] = 1; break; }
+            if (it > 4096u) __nanosleep(64);
+            if ((it & 0xffffu) == 0u && *reinterpret_cast<volatile int*>(error) != 0) { flags[0] = 1; break; }
+        }
+        __threadfence();
+    }
+    __syncthreads();
+}
+
+// A warp's cursors over its static sequence of ring items (weight phase, tile, 64-k pair): the producer side runs up to
+// kDepth items ahead of the consumer side, across phase boundaries.  Warp-uniform; lives in the kernel's frame and is
+// handed to the out-of-line phases by reference.
+struct DsRing {
+    int wp, itile, ipi, islot, ahead, cslot;      // producer: phase / tile / first pair of the next item (index among this warp's pairs of the tile) / next slot; items in flight; consumer slot
+    unsigned par;                                 // bit s: the parity the consumer waits for on slot s next
+    int cl;                                       // the block the consumer is in (the producer may be one block ahead)
+    int bestKey, bestIdx;                         // running greedy pick of the LM-head outputs this thread finished
+};
+
+struct DsCtx {                                    // what every phase needs from the launch
+    unsigned char* smem; int kmax, nCtas, nWp;
+    int rank, world, d;
+    float eps;
+};
+
+// The producer: where the next item of this warp's sequence lies in the phase's tile-major stream, and the issue
+// loop.  Everything is warp-uniform; lane 0 arms the slot's mbarrier and issues the one bulk copy of an item.
+struct DsProducer {
+    uint32_t ring_s, mbar_s;
+    int vcta, nV, hw, lane;
+    int pnTiles, pnPairs, npw, warpOff;           // this phase: tiles, pairs per tile, this warp's pairs per tile, their byte offset in a tile
+    size_t tileBytes;
+    const unsigned char* base;
+    const DsPhase* desc; int nWp;
+
+    __device__ __forceinline__ void init(const DsSmem& m, int nCtas, int nWp_) {
+        const int tid = threadIdx.x, warp = tid >> 5;
+        lane = tid & 31; hw = warp & 7;
+        vcta = 2 * blockIdx.x + (warp >> 3); nV = 2 * nCtas;
+        desc = m.desc; nWp = nWp_;
+        ring_s = smem_u32(m.rings + (size_t)warp * kDepth * kSlotBytes);
+        mbar_s = smem_u32(m.mbar + warp * kDepth);
+    }
+    __device__ __forceinline__ void load_phase(int w) {
+        const DsPhase& d = desc[((w >> 2) & 1) * 4 + (w & 3)];
+        const int rpt = d.swiglu ? 8 : 16;
+        pnTiles = (d.N + rpt - 1) / rpt;
+        pnPairs = ((d.K >> 5) + 1) >> 1;
+        // pairs hw, hw+8, …: warps below (pnPairs mod 8) own one more; a tile stores the warps' pairs one warp after the other
+        const int q = pnPairs >> 3, rem = pnPairs & 7;
+        npw = q + (hw < rem ? 1 : 0);
+        warpOff = (hw * q + min(hw, rem)) * kPairBytes;
+        tileBytes = (size_t)pnPairs * kPairBytes;
+        base = d.packed;
+    }
+    __device__ __forceinline__ bool can_issue(DsRing& r) {
+        while (true) {
+            if (r.wp >= nWp) return false;
+            if (r.itile < pnTiles && r.ipi < npw) return true;
+            if (((r.wp + 1) >> 2) > r.cl + 1) return false;       // descriptors exist for the consumer's block and the next one
+            r.wp++;
+            r.itile = vcta; r.ipi = 0;
+            if (r.wp < nWp) load_phase(r.wp);
+        }
+    }
+    __device__ __forceinline__ void top_up(DsRing& r) {
+        while (r.ahead < kDepth && can_issue(r)) {
+            const int pairs = min(kItemPairs, npw - r.ipi);
+#ifndef DS_EXP
+#define DS_EXP 0
+#endif
+            if (lane == 0 && DS_EXP != 1 && DS_EXP != 4 && DS_EXP != 5 && DS_EXP != 6) {
+                const uint32_t bar = mbar_s + (uint32_t)r.islot * 8u;
+                const uint32_t bytes = (uint32_t)pairs * kPairBytes;
+                mbar_arrive_expect_tx(bar, bytes);
+                bulk_g2s(ring_s + (uint32_t)r.islot * kSlotBytes, base + (size_t)r.itile * tileBytes + warpOff + (size_t)r.ipi * kPairBytes, bytes, bar);
+            }
+            r.ipi += pairs;
+            if (r.ipi >= npw) { r.ipi = 0; r.itile += nV; }
+            r.islot = r.islot + 1 == kDepth ? 0 : r.islot + 1;
+            r.ahead++;
+        }
+    }
+};
+
+// Fill the rings as far as the descriptors allow (launch start).
+__device__ __noinline__ void ds_prefetch(const DsCtx c, DsRing& ring) {
+    const DsSmem m = ds_layout(c.smem, c.kmax);
+    DsProducer P;
+    P.init(m, c.nCtas, c.nWp);
+    DsRing r = ring;
+    P.load_phase(r.wp);
+    P.top_up(r);
+    ring = r;
+}
+
+// Activation staging: one row → three int8 digit columns + a power-of-two scale per 32-k block (RMSNorm fused).
+// The gain is a weight: its loads go out together with the row's.
+__device__ __noinline__ void ds_stage(const DsCtx c, const float* xrow, int nanRow, const float* gamma, int K) {
+    const DsSmem m = ds_layout(c.smem, c.kmax);
+    int8_t* xd = reinterpret_cast<int8_t*>(m.act);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ldxs = K + kXsPad;
+    float* xsc = reinterpret_cast<float*>(xd + (size_t)3 * ldxs);
+    const int nHalf = K >> 4;
+    const int rounds = (nHalf + kThreads - 1) / kThreads;
+    float xv[kStageRounds][16], gv[kStageRounds][16];
+#pragma unroll
+    for (int r = 0; r < kStageRounds; r++) {
+        const int hb = r * kThreads + tid;
+        const bool on = r < rounds && hb < nHalf;
+        if (on && !nanRow) load16_cg(xrow + hb * 16, xv[r]);
+        else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) xv[r][j] = (nanRow && on) ? NAN : 0.0f;
+        }
+        if (gamma != nullptr && on) load16(gamma + hb * 16, true, gv[r]);
+        else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) gv[r][j] = 1.0f;
+        }
+    }
+    float inv = 1.0f;
+    if (gamma) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kStageRounds; r++)
+#pragma unroll
+            for (int j = 0; j < 16; j++) ss = fmaf(xv[r][j], xv[r][j], ss);
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) m.red[warp] = ss;
+        __syncthreads();
+        ss = 0.0f;
+#pragma unroll
+        for (int q = 0; q < kWarps; q++) ss += m.red[q];
+        inv = __frcp_rn(sqrtf(ss * (1.0f / (float)K) + c.eps));      // RMSNorm1D.forward: x / rms · γ
+    }
+#pragma unroll
+    for (int r = 0; r < kStageRounds; r++) {
+        const int hb = r * kThreads + tid;
+        const bool on = r < rounds && hb < nHalf;
+        if (gamma) {
+#pragma unroll
+            for (int j = 0; j < 16; j++) xv[r][j] = (xv[r][j] * inv) * gv[r][j];
+        }
+        if (r < rounds) digits16(xv[r], on, xd, ldxs, hb, xsc);
+    }
+    __syncthreads();
+}
+
+struct DsGemv {
+    int cp, mode;                     // weight phase; 0: out = v (+bias) (+residual); 1: SiLU(gate + bias) ⊙ (up + bias2);
+                                      // 2: logits (+bias) and the running greedy pick; 3: partial sums pushed to every rank's exchange words
+    const float* bias; const float* bias2; const float* residual; int resNan; float* out;
+    unsigned long long wordBase; unsigned tag;
+};
+
+// One projection: this half's tiles of weight phase `cp` against the staged row.  Warp hw of a half owns the 64-k pairs
+// hw, hw+8, … of a tile; every 32-k block of 16 weight rows is ONE int8 MMA whose B operand holds the row's three digits.
+__device__ __noinline__ void ds_gemv(const DsCtx c, const DsGemv a, DsRing& ring, int* error) {
+    const DsSmem m = ds_layout(c.smem, c.kmax);
+    const int8_t* xd = reinterpret_cast<const int8_t*>(m.act);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int half = warp >> 3, hw = warp & 7, htid = tid & 255;
     const int g = lane >> 2, t = lane & 3;
-    const int nCtas = gridDim.x;
-    const int vcta = 2 * blockIdx.x + half, nV = 2 * nCtas;           // a half = one virtual CTA of the GEMV tiling
-    const int L = p.n_layers;
-    const int nWp = 4 * L + 1;                                         // weight phases: 4 per block, then the LM head
-    const bool tp = p.world > 1;
-
-    if (tid == 0) s_flags[0] = 0;
-    // token and position of this step (they change only at the very end of the launch)
-    const int tokId = (int)__ldcg(p.tok);
-    const bool tokOk = tokId >= 0 && tokId < p.vocab;
-    int pos = (int)__ldcg(p.pos);
-    pos = pos < 0 ? 0 : (pos >= p.maxSeq ? p.maxSeq - 1 : pos);
-    const float* embRow = p.emb + (size_t)(tokOk ? tokId : 0) * p.d;
-    // Exchange e of this launch (Wo of block l: 2l, down: 2l + 1, the pick: 2L) travels under tag epochBase + 1 + e.  All
-    // ranks run the same launches, so their counters agree; words of exchange e − 2 (same slot parity) carry an older tag.
-    const unsigned epochBase = tp ? ld_acquire(p.epoch) : 0u;
-
-    // ── phase descriptors ──
-    auto load_desc = [&](int layer) {          // threads 0..3 fill the four descriptors of `layer` (layer == L: the LM head)
-        if (tid < 4) {
-            DsPhase d; d.codes = nullptr; d.scales = nullptr; d.codes2 = nullptr; d.scales2 = nullptr; d.K = 32; d.N = 0; d.swiglu = 0; d.pad = 0;
-            if (layer < L) {
-                const DsLayer* ly = p.layers + layer;
-                const int dl = p.H * HD;
-                if (tid == 0) { d.codes = ly->qkv_c; d.scales = ly->qkv_s; d.K = p.d; d.N = 3 * dl; }
-                if (tid == 1) { d.codes = ly->wo_c; d.scales = ly->wo_s; d.K = dl; d.N = p.d; }
-                if (tid == 2) { d.codes = ly->wg_c; d.scales = ly->wg_s; d.codes2 = ly->wu_c; d.scales2 = ly->wu_s; d.K = p.d; d.N = p.F; d.swiglu = 1; }
-                if (tid == 3) { d.codes = ly->wd_c; d.scales = ly->wd_s; d.K = p.F; d.N = p.d; }
-            } else if (layer == L && tid == 0) {
-                d.codes = p.lm_c; d.scales = p.lm_s; d.K = p.d; d.N = p.V;
-            }
-            s_desc[(layer & 1) * 4 + tid] = d;
+    DsProducer P;
+    P.init(m, c.nCtas, c.nWp);
+    DsRing r = ring;
+    if (r.wp < a.cp) { r.wp = a.cp; r.itile = P.vcta; r.ipi = 0; }          // a warp without items in earlier phases catches up
+    P.load_phase(r.wp);
+    const uint32_t myring = smem_u32(m.rings + (size_t)warp * kDepth * kSlotBytes);
+    const DsPhase& d = m.desc[((a.cp >> 2) & 1) * 4 + (a.cp & 3)];
+    const int K = d.K, N = d.N;
+    const bool sw = d.swiglu != 0;
+    const int rowsPerTile = sw ? 8 : 16;
+    const int nTiles = (N + rowsPerTile - 1) / rowsPerTile;
+    const int nBlocks = K >> 5, nPairs = (nBlocks + 1) >> 1;
+    const int myPairs = (nPairs >> 3) + (hw < (nPairs & 7) ? 1 : 0);          // pairs hw, hw+8, … of a tile
+    const int ldxs = K + kXsPad;
+    const uint32_t xsc = smem_u32(xd + (size_t)3 * ldxs);
+    // lane (g,t) feeds MMA column g: digit g (g < 3) of the one activation row; columns 3..7 stay zero
+    const bool hasCol = g < 3;
+    const uint32_t xcol = smem_u32(xd) + (uint32_t)((hasCol ? g : 0) * ldxs + t * 8);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    int aoff[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) aoff[hh] = g * kRowStride + (hh ^ ((g >> 1) & 1)) * 32 + t * 8;
+    const int soff = kRows * kRowStride + g * 8;
+    float* partBase = m.part + (size_t)half * 2 * kHalfWarps * 128;
+    int buf = 0;
+    int bestKey = r.bestKey, bestIdx = r.bestIdx;
+    volatile int* dead = m.flags;
+    for (int tile = P.vcta; tile < nTiles; tile += P.nV) {
+        const int er = htid, en = tile * rowsPerTile + er;          // htid < rowsPerTile: the thread that finishes output en
+        float ebias = 0.0f, ebias2 = 0.0f, eres = 0.0f;
+        if (er < rowsPerTile && en < N) {
+            if (a.bias) ebias = a.bias[en];
+            if (sw && a.bias2) ebias2 = a.bias2[en];
+            if (a.residual) eres = a.resNan ? NAN : __ldcg(a.residual + en);
         }
-    };
-    load_desc(0);
-    load_desc(1);
-    __syncthreads();
-
-    // ── ring producer: this warp's static sequence of (phase, tile, 64-k pair) items ──
-    unsigned char* myring = rings + (size_t)warp * kDepth * kSlotBytes;
-    const uint32_t ring_s = smem_u32(myring);
-    uint32_t dstoff[2]; int rsel[2], pieceOff[2];
-#pragma unroll
-    for (int j = 0; j < 2; j++) {
-        const int q = lane + 32 * j, r = q >> 2, piece = q & 3;
-        dstoff[j] = (uint32_t)(r * kRowStride + ((piece ^ (((r >> 1) & 1) << 1)) * 16));
-        rsel[j] = r; pieceOff[j] = piece * 16;
-    }
-    const int srow = lane >> 1;
-    const uint32_t sdst = (uint32_t)(kRows * kRowStride + lane * 4);
-    int wp = 0, itile = 0, ipi = 0, islot = 0, ahead = 0, cslot = 0;
-    int cl = 0;                                   // the block the consumer side is in: the producer may be one block ahead
-    int pN = 0, pK = 0, pnb = 0, pnPairs = 0, pnTiles = 0, pnBlocks = 0, prpt = 16;
-    int rloc[2], sloc = 0;
-    const int8_t* cbase[2]; const float* sbase = nullptr;
-    const int8_t* csrc[2]; const float* ssrc = nullptr;
-    auto set_issue_tile = [&]() {
-#pragma unroll
-        for (int j = 0; j < 2; j++) csrc[j] = cbase[j] + (size_t)min(itile * prpt + rloc[j], pN - 1) * pK;
-        ssrc = sbase + (size_t)min(itile * prpt + sloc, pN - 1) * pnb;
-    };
-    auto set_phase = [&](int w) {
-        const DsPhase& d = s_desc[((w >> 2) & 1) * 4 + (w & 3)];
-        const bool sw = d.swiglu != 0;
-        prpt = sw ? 8 : 16; pN = d.N; pK = d.K; pnb = d.K >> 5; pnBlocks = d.K >> 5; pnPairs = (pnBlocks + 1) >> 1;
-        pnTiles = (pN + prpt - 1) / prpt;
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            rloc[j] = sw ? (rsel[j] & 7) : rsel[j];
-            cbase[j] = ((sw && rsel[j] >= 8) ? d.codes2 : d.codes) + pieceOff[j];
-        }
-        sloc = sw ? (srow & 7) : srow;
-        sbase = ((sw && srow >= 8) ? d.scales2 : d.scales) + (lane & 1);
-        itile = vcta; ipi = hw;
-        if (itile < pnTiles) set_issue_tile();
-    };
-    set_phase(0);
-    auto can_issue = [&]() -> bool {
-        while (true) {
-            if (wp >= nWp) return false;
-            if (itile < pnTiles && ipi < pnPairs) return true;
-            if (((wp + 1) >> 2) > cl + 1) return false;       // descriptors exist for the consumer's block and the next one
-            wp++;
-            if (wp < nWp) set_phase(wp);
-        }
-    };
-    auto top_up = [&]() {
-        while (ahead < kDepth && can_issue()) {
-            const uint32_t dst = ring_s + (uint32_t)islot * kSlotBytes;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + dstoff[0]), "l"(csrc[0] + ipi * 64) : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + dstoff[1]), "l"(csrc[1] + ipi * 64) : "memory");
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + sdst), "l"(ssrc + min(ipi * 2, pnBlocks - 1 - (lane & 1))) : "memory");
-            cp_async_commit();
-            ipi += kHalfWarps;
-            if (ipi >= pnPairs) { ipi = hw; itile += nV; if (itile < pnTiles) set_issue_tile(); }
-            islot = islot + 1 == kDepth ? 0 : islot + 1;
-            ahead++;
-        }
-    };
-    top_up();
-
-    // ── grid barrier (bounded) ──
-    unsigned barGen = 0;
-    auto grid_barrier = [&](int code) {
-        __syncthreads();
-        if (tid == 0 && s_flags[0] == 0) {
-            barGen++;
-            const unsigned target = barGen * (unsigned)nCtas;
-            __threadfence();
-            atomicAdd(p.bar, 1u);
-            unsigned it = 0;
-            while (ld_acquire(p.bar) < target) {
-                if (++it > kSpinLimit) { atomicCAS(p.error, 0, code); s_flags[0] = 1; break; }
-                if (it > 4096u) __nanosleep(64);
-                if ((it & 0xffffu) == 0u && *reinterpret_cast<volatile int*>(p.error) != 0) { s_flags[0] = 1; break; }
-            }
-            __threadfence();
-        }
-        __syncthreads();
-    };
-
-    // ── activation staging: one row → three int8 digit columns + a power-of-two scale per 32-k block (RMSNorm fused) ──
-    auto stage = [&](const float* xrow, bool nanRow, const float* gamma, int K) {
-        const int ldxs = K + kXsPad;
-        float* xsc = reinterpret_cast<float*>(xd + (size_t)3 * ldxs);
-        const int nHalf = K >> 4;
-        const int rounds = (nHalf + kThreads - 1) / kThreads;
-        float xv[kStageRounds][16];
-#pragma unroll
-        for (int r = 0; r < kStageRounds; r++) {
-            const int hb = r * kThreads + tid;
-            if (r < rounds && hb < nHalf && !nanRow) load16_cg(xrow + hb * 16, xv[r]);
-            else {
-#pragma unroll
-                for (int j = 0; j < 16; j++) xv[r][j] = (nanRow && r < rounds && hb < nHalf) ? NAN : 0.0f;
-            }
-        }
-        float inv = 1.0f;
-        if (gamma) {
-            float ss = 0.0f;
-#pragma unroll
-            for (int r = 0; r < kStageRounds; r++)
-#pragma unroll
-                for (int j = 0; j < 16; j++) ss = fmaf(xv[r][j], xv[r][j], ss);
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (lane == 0) s_red[warp] = ss;
-            __syncthreads();
-            ss = 0.0f;
-#pragma unroll
-            for (int q = 0; q < kWarps; q++) ss += s_red[q];
-            inv = __frcp_rn(sqrtf(ss * (1.0f / (float)K) + p.eps));      // RMSNorm1D.forward: x / rms · γ
-        }
-#pragma unroll
-        for (int r = 0; r < kStageRounds; r++) {
-            const int hb = r * kThreads + tid;
-            const bool on = r < rounds && hb < nHalf;
-            if (gamma) {
-                float gv[16];
-                if (on) load16(gamma + hb * 16, true, gv);
-                else {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) gv[j] = 1.0f;
+        for (int j0 = 0; j0 < myPairs; j0 += kItemPairs) {
+            P.top_up(r);
+            {
+                // the item's bytes have landed when its slot's mbarrier completes the phase armed for it (bounded wait)
+                const uint32_t bar = P.mbar_s + (uint32_t)r.cslot * 8u;
+                const uint32_t parity = (r.par >> r.cslot) & 1u;
+                if (lane == 0 && !mbar_try_wait(bar, parity) && !*dead) {          // one lane polls; the warp meets it below
+                    unsigned it = 0;
+                    while (!mbar_try_wait(bar, parity)) {
+                        if (++it > kSpinLimit) { atomicCAS(error, 0, 310); *dead = 1; break; }
+                        if ((it & 0xfffu) == 0u && *dead) break;
+                    }
                 }
-#pragma unroll
-                for (int j = 0; j < 16; j++) xv[r][j] = (xv[r][j] * inv) * gv[j];
-            }
-            if (r < rounds) digits16(xv[r], on, xd, ldxs, hb, xsc);
-        }
-        __syncthreads();
-    };
-
-    // ── one projection: this half's tiles of the current weight phase against the staged row ──
-    // mode 0: out = v (+bias) (+residual); 1: SiLU(gate + bias) ⊙ (up + bias2); 2: logits (+bias) and the running greedy pick;
-    // 3: partial sum pushed to every rank's exchange words (tensor parallelism)
-    int bestKey = INT_MIN, bestIdx = INT_MAX;
-    auto gemv = [&](int cp, int mode, const float* bias, const float* bias2, const float* residual, bool resNan, float* out,
-                    unsigned long long wordBase, unsigned tag) {
-        if (wp < cp) { wp = cp; set_phase(cp); }          // a warp without items in earlier phases catches up
-        const DsPhase& d = s_desc[((cp >> 2) & 1) * 4 + (cp & 3)];
-        const int K = d.K, N = d.N;
-        const bool sw = d.swiglu != 0;
-        const int rowsPerTile = sw ? 8 : 16;
-        const int nTiles = (N + rowsPerTile - 1) / rowsPerTile;
-        const int nBlocks = K >> 5, nPairs = (nBlocks + 1) >> 1;
-        const int ldxs = K + kXsPad;
-        const float* xsc = reinterpret_cast<const float*>(xd + (size_t)3 * ldxs);
-        // lane (g,t) feeds MMA column g: digit g (g < 3) of the one activation row; columns 3..7 stay zero
-        const bool hasCol = g < 3;
-        const unsigned char* xcol = reinterpret_cast<const unsigned char*>(xd) + (size_t)(hasCol ? g : 0) * ldxs + t * 8;
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        int aoff[2];
-#pragma unroll
-        for (int hh = 0; hh < 2; hh++) aoff[hh] = g * kRowStride + (hh ^ ((g >> 1) & 1)) * 32 + t * 8;
-        const int soff = kRows * kRowStride + g * 8;
-        float* partBase = s_part + (size_t)half * 2 * kHalfWarps * 128;
-        int buf = 0;
-        for (int tile = vcta; tile < nTiles; tile += nV) {
-            const int er = htid, en = tile * rowsPerTile + er;          // htid < rowsPerTile: the thread that finishes output en
-            float ebias = 0.0f, ebias2 = 0.0f, eres = 0.0f;
-            if (er < rowsPerTile && en < N) {
-                if (bias) ebias = bias[en];
-                if (sw && bias2) ebias2 = bias2[en];
-                if (residual) eres = resNan ? NAN : __ldcg(residual + en);
-            }
-            for (int pi = hw; pi < nPairs; pi += kHalfWarps) {
-                top_up();
-                cp_async_wait_dyn(ahead - 1);
                 __syncwarp();
-                const unsigned char* slot = myring + (size_t)cslot * kSlotBytes;
+                r.par ^= 1u << r.cslot;
+            }
+            const uint32_t slot = myring + (uint32_t)r.cslot * kSlotBytes;
+            const int pairsHere = min(kItemPairs, myPairs - j0);
+            // all fragments of the item first (independent shared-memory loads), then the MMAs, then the fp32 folds
+            uint2 av[2 * kItemPairs], dd[2 * kItemPairs], xb[2 * kItemPairs];
+            float s0[2 * kItemPairs], s1[2 * kItemPairs], xs[2 * kItemPairs];
 #pragma unroll
-                for (int hh = 0; hh < 2; hh++) {
-                    const uint2 a = *reinterpret_cast<const uint2*>(slot + aoff[hh]);
-                    const uint2 dd = *reinterpret_cast<const uint2*>(slot + aoff[hh] + 8 * kRowStride);
-                    const float s0 = *reinterpret_cast<const float*>(slot + soff + hh * 4);
-                    const float s1 = *reinterpret_cast<const float*>(slot + soff + 64 + hh * 4);
-                    const int blk = pi * 2 + hh;
-                    uint2 xb = make_uint2(0u, 0u);
-                    if (hasCol) xb = *reinterpret_cast<const uint2*>(xcol + blk * 32);
-                    int cc[4] = {0, 0, 0, 0};
-                    mma_s8_16832(cc, a.x, dd.x, a.y, dd.y, xb.x, xb.y);
-                    const float xs_ = blk < nBlocks ? xsc[blk] : 0.0f;
-                    const float f0 = s0 * xs_, f1 = s1 * xs_;
+            for (int q = 0; q < 2 * kItemPairs; q++) {
+                const int pp = q >> 1, hh = q & 1;
+                const uint32_t ps = slot + pp * kPairBytes;
+                const int blk = (hw + kHalfWarps * (j0 + pp)) * 2 + hh;
+                const bool on = pp < pairsHere && blk < nBlocks;      // a short last item, or the empty half of an odd last pair
+                av[q] = lds_u2(ps + aoff[hh]);
+                dd[q] = lds_u2(ps + aoff[hh] + 8 * kRowStride);
+                s0[q] = lds_f(ps + soff + hh * 4);
+                s1[q] = lds_f(ps + soff + 64 + hh * 4);
+                xb[q] = (hasCol && on) ? lds_u2(xcol + blk * 32) : make_uint2(0u, 0u);
+                xs[q] = on ? lds_f(xsc + blk * 4) : 0.0f;
+            }
+#pragma unroll
+            for (int q = 0; q < 2 * kItemPairs; q++) {
+                int cc[4] = {0, 0, 0, 0};
+                mma_s8_16832(cc, av[q].x, dd[q].x, av[q].y, dd[q].y, xb[q].x, xb[q].y);
+                // a pair that is not there was not copied either: its slot bytes are stale, its activation scale is 0, and
+                // 0 · (finite stale scale · integer) adds +0 — but stale bytes could be NaN patterns, so the fold is skipped
+                if ((q >> 1) < pairsHere) {
+                    const float f0 = s0[q] * xs[q], f1 = s1[q] * xs[q];
                     acc[0] = fmaf(f0, (float)cc[0], acc[0]);
                     acc[1] = fmaf(f0, (float)cc[1], acc[1]);
                     acc[2] = fmaf(f1, (float)cc[2], acc[2]);
                     acc[3] = fmaf(f1, (float)cc[3], acc[3]);
                 }
-                __syncwarp();
-                cslot = cslot + 1 == kDepth ? 0 : cslot + 1;
-                ahead--;
             }
-            // tile epilogue: reduce the half's warps, recombine the digits
-            float* part = partBase + (size_t)buf * kHalfWarps * 128;
-            float* mine = part + hw * 128;
-            mine[g * 8 + 2 * t] = acc[0];       mine[g * 8 + 2 * t + 1] = acc[1];
-            mine[(g + 8) * 8 + 2 * t] = acc[2]; mine[(g + 8) * 8 + 2 * t + 1] = acc[3];
-            acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
-            bar_sync(1 + half, 256);
-            if (er < rowsPerTile && en < N) {
-                float a2 = 0.0f, a1 = 0.0f, a0 = 0.0f, b2 = 0.0f, b1 = 0.0f, b0 = 0.0f;
+            __syncwarp();          // every lane has read the slot before lane 0 may aim the next copy at it
+            r.cslot = r.cslot + 1 == kDepth ? 0 : r.cslot + 1;
+            r.ahead--;
+        }
+        // tile epilogue: reduce the half's warps, recombine the digits
+        float* part = partBase + (size_t)buf * kHalfWarps * 128;
+        float* mine = part + hw * 128;
+        mine[g * 8 + 2 * t] = acc[0];       mine[g * 8 + 2 * t + 1] = acc[1];
+        mine[(g + 8) * 8 + 2 * t] = acc[2]; mine[(g + 8) * 8 + 2 * t + 1] = acc[3];
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+        bar_sync(1 + half, 256);
+        if (er < rowsPerTile && en < N) {
+            float a2 = 0.0f, a1 = 0.0f, a0 = 0.0f, b2 = 0.0f, b1 = 0.0f, b0 = 0.0f;
 #pragma unroll
-                for (int q = 0; q < kHalfWarps; q++) {
-                    const float* pr = part + q * 128 + er * 8;
-                    a2 += pr[0]; a1 += pr[1]; a0 += pr[2];
-                    if (sw) { b2 += pr[64]; b1 += pr[65]; b0 += pr[66]; }
-                }
-                float v = fmaf(a2, 65536.0f, fmaf(a1, 256.0f, a0));
-                if (mode == 1) {
-                    float u = fmaf(b2, 65536.0f, fmaf(b1, 256.0f, b0));
-                    if (bias) v += ebias;
-                    if (bias2) u += ebias2;
-                    const float sig = 1.0f / (1.0f + expf(-v));
-                    out[en] = (v * sig) * u;                 // SiLU(gate) ⊙ up
-                } else if (mode == 3) {
-                    // the partial sum travels with the launch's epoch in one 8-byte word, to every rank (this one included)
-                    const uint2 w = make_uint2(__float_as_uint(v), tag);
+            for (int q = 0; q < kHalfWarps; q++) {
+                const float* pr = part + q * 128 + er * 8;
+                a2 += pr[0]; a1 += pr[1]; a0 += pr[2];
+                if (sw) { b2 += pr[64]; b1 += pr[65]; b0 += pr[66]; }
+            }
+            float v = fmaf(a2, 65536.0f, fmaf(a1, 256.0f, a0));
+            if (a.mode == 1) {
+                float u = fmaf(b2, 65536.0f, fmaf(b1, 256.0f, b0));
+                if (a.bias) v += ebias;
+                if (a.bias2) u += ebias2;
+                const float sig = 1.0f / (1.0f + expf(-v));
+                a.out[en] = (v * sig) * u;                 // SiLU(gate) ⊙ up
+            } else if (a.mode == 3) {
+                // the partial sum travels with its exchange tag in one 8-byte word, to every rank (this one included)
+                const uint2 w = make_uint2(__float_as_uint(v), a.tag);
 #pragma unroll 1
-                    for (int r = 0; r < p.world; r++) st_volatile_v2(p.peers.words[r] + wordBase + (size_t)p.rank * p.d + en, w);
-                } else {
-                    if (bias) v += ebias;
-                    if (residual) v += eres;
-                    out[en] = v;
-                    if (mode == 2) {
-                        const int k = order_key(v);
-                        if (k > bestKey || (k == bestKey && en < bestIdx)) { bestKey = k; bestIdx = en; }
-                    }
+                for (int q = 0; q < c.world; q++) st_volatile_v2(m.peers[q] + a.wordBase + (size_t)c.rank * c.d + en, w);
+            } else {
+                if (a.bias) v += ebias;
+                if (a.residual) v += eres;
+                a.out[en] = v;
+                if (a.mode == 2) {
+                    const int k = order_key(v);
+                    if (k > bestKey || (k == bestKey && en < bestIdx)) { bestKey = k; bestIdx = en; }
                 }
             }
-            buf ^= 1;
         }
-        top_up();          // whatever the next phases allow: these copies run through the barrier that follows
-    };
+        buf ^= 1;
+    }
+    P.top_up(r);          // whatever the next phases allow: these copies run through the barrier that follows
+    r.bestKey = bestKey; r.bestIdx = bestIdx;
+    ring = r;
+}
 
-    // ── sum of the ranks' partial words for a slice of the row: out = residual + bias + Σ_r part_r, rank order ──
-    auto tp_reduce = [&](unsigned long long wordBase, unsigned epochNow, const float* bias, const float* residual, bool resNan, float* out) {
-        // two values (16 bytes) per thread; CTA c takes pairs c·512 + tid, …
-        const int pairs = p.d >> 1;
-        for (int pr = blockIdx.x * kThreads + tid; pr < pairs; pr += nCtas * kThreads) {
-            float sa = 0.0f, sb = 0.0f;
-            bool gaveUp = s_flags[0] != 0;
-            for (int r = 0; r < p.world; r++) {
-                const unsigned long long* src = p.peers.words[p.rank] + wordBase + (size_t)r * p.d + 2 * pr;
-                uint4 v = ld_volatile_v4(src);
-                if (v.y != epochNow || v.w != epochNow) {
-                    gaveUp = gaveUp || *reinterpret_cast<volatile int*>(p.error) != 0;
-                    for (unsigned it = 0; !gaveUp && (v.y != epochNow || v.w != epochNow) && it < kSpinLimit; it++) {
-                        if (it > 1024u) __nanosleep(32);
-                        v = ld_volatile_v4(src);
-                        if ((it & 1023u) == 1023u) gaveUp = *reinterpret_cast<volatile int*>(p.error) != 0;
-                    }
-                    if (v.y != epochNow || v.w != epochNow) {
-                        if (!gaveUp) atomicCAS(p.error, 0, 100 + r);
-                        gaveUp = true;
-                    }
+// Sum of the ranks' partial words for a slice of the row: out = residual + bias + Σ_r part_r, in rank order.
+__device__ __noinline__ void ds_tp_reduce(const DsCtx c, unsigned long long wordBase, unsigned tag, const float* bias, const float* residual,
+                                          int resNan, float* out, int* error) {
+    const DsSmem m = ds_layout(c.smem, c.kmax);
+    const int tid = threadIdx.x;
+    const int pairs = c.d >> 1;          // two values (16 bytes) per thread; CTA b takes pairs b·512 + tid, …
+    for (int pr = blockIdx.x * kThreads + tid; pr < pairs; pr += c.nCtas * kThreads) {
+        float sa = 0.0f, sb = 0.0f;
+        bool gaveUp = m.flags[0] != 0;
+        for (int q = 0; q < c.world; q++) {
+            const unsigned long long* src = m.peers[c.rank] + wordBase + (size_t)q * c.d + 2 * pr;
+            uint4 v = ld_volatile_v4(src);
+            if (v.y != tag || v.w != tag) {
+                gaveUp = gaveUp || *reinterpret_cast<volatile int*>(error) != 0;
+                for (unsigned it = 0; !gaveUp && (v.y != tag || v.w != tag) && it < kSpinLimit; it++) {
+                    if (it > 1024u) __nanosleep(32);
+                    v = ld_volatile_v4(src);
+                    if ((it & 1023u) == 1023u) gaveUp = *reinterpret_cast<volatile int*>(error) != 0;
                 }
-                sa += __uint_as_float(v.x); sb += __uint_as_float(v.z);
+                if (v.y != tag || v.w != tag) {
+                    if (!gaveUp) atomicCAS(error, 0, 100 + q);
+                    gaveUp = true;
+                }
             }
-            float ra = 0.0f, rb = 0.0f;
-            if (residual) { if (resNan) { ra = NAN; rb = NAN; } else { const float2 rr = __ldcg(reinterpret_cast<const float2*>(residual) + pr); ra = rr.x; rb = rr.y; } }
-            if (bias) { ra += bias[2 * pr]; rb += bias[2 * pr + 1]; }
-            out[2 * pr] = ra + sa;
-            out[2 * pr + 1] = rb + sb;
-            if (gaveUp) s_flags[0] = 1;          // the CTA stops waiting at barriers too
+            sa += __uint_as_float(v.x); sb += __uint_as_float(v.z);
         }
-    };
+        float ra = 0.0f, rb = 0.0f;
+        if (residual) {
+            if (resNan) { ra = NAN; rb = NAN; }
+            else { const float2 rr = __ldcg(reinterpret_cast<const float2*>(residual) + pr); ra = rr.x; rb = rr.y; }
+        }
+        if (bias) { ra += bias[2 * pr]; rb += bias[2 * pr + 1]; }
+        out[2 * pr] = ra + sa;
+        out[2 * pr + 1] = rb + sb;
+        if (gaveUp) m.flags[0] = 1;          // the CTA stops waiting at barriers too
+    }
+}
 
-    // ── attention of one block: 4-warp groups take (head, split) items ──
+struct DsAttn {
+    const float* qkv; float* att; float* ws; int* tickets; const float* cosT; const float* sinT;
+    float* kcache; float* vcache; unsigned* bar; int* error; float* scratch; int* flags;
+    int pos, maxSeq, H, splits, nCtas; float scale;
+};
+
+// Attention of one block for the one new token: 4-warp groups of the CTA take (head, split) items.  The cached rows
+// below `pos` do not depend on this launch, so a group requests its first rows BEFORE the grid barrier that publishes
+// q, k and v, then rotates q, folds its slice of the cache in (the group that meets `pos` takes k and v from the
+// projections, rotates k and appends both), and the last group of a head to finish merges the split partials.
+template <int LPP>
+__device__ __noinline__ void ds_attention(const DsAttn p) {
+    constexpr int HD = LPP * 16;
+    constexpr int PPW = 32 / LPP;
+    constexpr int G = kSubWarps * PPW;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nCtas = p.nCtas, pos = p.pos;
+    int* s_flags = p.flags;
     const int sub = warp >> 2, w4 = warp & 3, st = tid & 127;
     const int group = lane / LPP, gl = lane % LPP;
     const int item = sub * nCtas + blockIdx.x;
@@ -477,14 +553,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_decode_step(const DsParams p) {
     const int achunk = (seq + p.splits - 1) / p.splits;
     const int astart = asplit * achunk, aend = min(seq, astart + achunk);
     const int halfHd = HD >> 1;
-    float* s_acc = reinterpret_cast<float*>(actRegion) + (size_t)sub * kAttnScratchFloats;      // [G][HD]
-    float* s_m = s_acc + 2048;                                                                    // [G], then s_l [G]
+    float* s_acc = p.scratch + (size_t)sub * kAttnScratchFloats;      // [G][HD]
+    float* s_m = s_acc + 2048;                                        // [G], then s_l [G]
     float* s_l = s_m + G;
+    float* kbase = p.kcache + (size_t)ah * p.maxSeq * HD + gl * 16;
+    float* vbase = p.vcache + (size_t)ah * p.maxSeq * HD + gl * 16;
 
-    auto fetch_cached = [&](const float* kb, const float* vb, int pp, bool valid, float (&kx)[16], float (&vx)[16]) {
+    auto fetch_cached = [&](int pp, bool valid, float (&kx)[16], float (&vx)[16]) {
         if (valid) {
-            const float4* kp = reinterpret_cast<const float4*>(kb + (size_t)pp * HD);
-            const float4* vp = reinterpret_cast<const float4*>(vb + (size_t)pp * HD);
+            const float4* kp = reinterpret_cast<const float4*>(kbase + (size_t)pp * HD);
+            const float4* vp = reinterpret_cast<const float4*>(vbase + (size_t)pp * HD);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const float4 a = __ldcs(kp + j), c = __ldcs(vp + j);
@@ -496,208 +574,300 @@ __global__ void __launch_bounds__(kThreads, 1) k_decode_step(const DsParams p) {
             for (int j = 0; j < 16; j++) { kx[j] = 0.0f; vx[j] = 0.0f; }
         }
     };
+    // rotate 8 interleaved pairs by the table row of the current position; the row is fetched where it is used
+    // (twice per launch and lane, cache hits) rather than kept live through the loop
+    auto rotate = [&](float (&v)[16]) {
+        const float4* cp4 = reinterpret_cast<const float4*>(p.cosT + (size_t)pos * halfHd + gl * 8);
+        const float4* sp4 = reinterpret_cast<const float4*>(p.sinT + (size_t)pos * halfHd + gl * 8);
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const float4 c4 = cp4[j], s4 = sp4[j];
+            const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float x0 = v[8 * j + 2 * i], x1 = v[8 * j + 2 * i + 1];
+                v[8 * j + 2 * i] = x0 * cs[i] - x1 * sn[i];
+                v[8 * j + 2 * i + 1] = x0 * sn[i] + x1 * cs[i];
+            }
+        }
+    };
+
+    float kf[16], vf[16];
+    if (attnOn) {
+        const int p0 = astart + w4 * PPW + group;
+        fetch_cached(p0, p0 < aend && p0 != pos, kf, vf);
+    }
+    ds_grid_barrier(p.bar, p.error, s_flags, nCtas, 300);
+    if (!attnOn) return;
+
+    const int dl = p.H * HD;
+    float q[16];
+    load16_cg(p.qkv + ah * HD + gl * 16, q);
+    rotate(q);
+    auto fetch = [&](int pp, bool valid, float (&kx)[16], float (&vx)[16]) {
+        if (valid && pp == pos) {
+            // the new token: k and v come from the projections; rotate k, append both to the cache
+            load16_cg(p.qkv + dl + ah * HD + gl * 16, kx);
+            load16_cg(p.qkv + 2 * dl + ah * HD + gl * 16, vx);
+            rotate(kx);
+            float4* kd = reinterpret_cast<float4*>(kbase + (size_t)pp * HD);
+            float4* vd = reinterpret_cast<float4*>(vbase + (size_t)pp * HD);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                kd[j] = make_float4(kx[4 * j], kx[4 * j + 1], kx[4 * j + 2], kx[4 * j + 3]);
+                vd[j] = make_float4(vx[4 * j], vx[4 * j + 1], vx[4 * j + 2], vx[4 * j + 3]);
+            }
+        } else fetch_cached(pp, valid, kx, vx);
+    };
+    float mx = -INFINITY, lsum = 0.0f, acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) acc[j] = 0.0f;
+    int base = astart + w4 * PPW;
+    if (base < aend) {
+        const int p0 = base + group;
+        if (p0 == pos && p0 < aend) fetch(p0, true, kf, vf);
+    }
+    float kn[16], vn[16];
+    for (; base < aend; base += G) {
+        const bool valid = base + group < aend;
+        const int nbase = base + G;
+        if (nbase < aend) fetch(nbase + group, nbase + group < aend, kn, vn);
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; j++) dot = fmaf(q[j], kf[j], dot);
+#pragma unroll
+        for (int o = LPP / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (valid) {
+            const float s = dot * p.scale;
+            const float mn = fmaxf(mx, s);
+            const float corr = expf(mx - mn);
+            const float pe = expf(s - mn);
+            lsum = lsum * corr + pe;
+#pragma unroll
+            for (int j = 0; j < 16; j++) acc[j] = fmaf(pe, vf[j], acc[j] * corr);
+            mx = mn;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++) { kf[j] = kn[j]; vf[j] = vn[j]; }
+    }
+    const int gg0 = w4 * PPW + group;
+#pragma unroll
+    for (int j = 0; j < 16; j++) s_acc[gg0 * HD + gl * 16 + j] = acc[j];
+    if (gl == 0) { s_m[gg0] = mx; s_l[gg0] = lsum; }
+    bar_sync(3 + sub, 128);
+    float* mine = p.ws + ((size_t)ah * p.splits + asplit) * (HD + 2);
+    for (int j = st; j < HD; j += 128) {
+        float M = -INFINITY;
+        for (int gg = 0; gg < G; gg++) M = fmaxf(M, s_m[gg]);
+        float a = 0.0f, Ls = 0.0f;
+        if (M > -INFINITY) {
+            for (int gg = 0; gg < G; gg++) {
+                const float e = expf(s_m[gg] - M);
+                a = fmaf(s_acc[gg * HD + j], e, a);
+                Ls = fmaf(s_l[gg], e, Ls);
+            }
+        }
+        mine[j] = a;
+        if (j == 0) { mine[HD] = M; mine[HD + 1] = Ls; }
+    }
+    if (p.splits == 1) {
+        bar_sync(3 + sub, 128);
+        for (int j = st; j < HD; j += 128) p.att[ah * HD + j] = mine[j] / mine[HD + 1];
+        return;
+    }
+    // the last group of this head merges the split partials
+    __threadfence();
+    bar_sync(3 + sub, 128);
+    if (st == 0) {
+        const int ticket = atomicAdd(&p.tickets[ah], 1);
+        const int last = ticket == p.splits - 1;
+        s_flags[1 + sub] = last;
+        if (last) p.tickets[ah] = 0;
+    }
+    bar_sync(3 + sub, 128);
+    if (!s_flags[1 + sub]) return;
+    __threadfence();
+    const float* pbase = p.ws + (size_t)ah * p.splits * (HD + 2);
+    float* s_m2 = s_acc;
+    float* s_l2 = s_m2 + kMaxSplits;
+    for (int sp = st; sp < p.splits; sp += 128) {
+        s_m2[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD);
+        s_l2[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD + 1);
+    }
+    constexpr int kBatch = 24;
+    const int j0 = st;
+    float first[kBatch];
+#pragma unroll
+    for (int q2 = 0; q2 < kBatch; q2++) first[q2] = (j0 < HD && q2 < p.splits) ? __ldcg(pbase + (size_t)q2 * (HD + 2) + j0) : 0.0f;
+    bar_sync(3 + sub, 128);
+    float M = -INFINITY;
+    for (int sp = 0; sp < p.splits; sp++) M = fmaxf(M, s_m2[sp]);
+    float Lt = 0.0f;
+    for (int sp = 0; sp < p.splits; sp++) Lt = fmaf(s_l2[sp], expf(s_m2[sp] - M), Lt);
+    bar_sync(3 + sub, 128);
+    for (int sp = st; sp < p.splits; sp += 128) s_m2[sp] = expf(s_m2[sp] - M);
+    bar_sync(3 + sub, 128);
+    for (int j = st; j < HD; j += 128) {
+        float a = 0.0f;
+        for (int s0 = 0; s0 < p.splits; s0 += kBatch) {
+            float part[kBatch];
+            if (j == j0 && s0 == 0) {
+#pragma unroll
+                for (int q2 = 0; q2 < kBatch; q2++) part[q2] = first[q2];
+            } else {
+#pragma unroll
+                for (int q2 = 0; q2 < kBatch; q2++) part[q2] = s0 + q2 < p.splits ? __ldcg(pbase + (size_t)(s0 + q2) * (HD + 2) + j) : 0.0f;
+            }
+#pragma unroll
+            for (int q2 = 0; q2 < kBatch; q2++) if (s0 + q2 < p.splits) a = fmaf(part[q2], s_m2[s0 + q2], a);
+        }
+        p.att[ah * HD + j] = a / Lt;
+    }
+}
+
+template <int LPP>      // lanes per cached position = head dim / 16
+__global__ void __launch_bounds__(kThreads, 1) k_decode_step(const DsParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const DsSmem m = ds_layout(smem, p.kmax);
+    int* s_flags = m.flags;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nCtas = gridDim.x;
+    const int L = p.n_layers;
+    const bool tp = p.world > 1;
+    DsCtx c;
+    c.smem = smem; c.kmax = p.kmax; c.nCtas = nCtas; c.nWp = 4 * L + 1;      // weight phases: 4 per block, then the LM head
+    c.rank = p.rank; c.world = p.world; c.d = p.d; c.eps = p.eps;
+
+    if (tid < 8) s_flags[tid] = 0;
+    if (tid < kMaxWorld) m.peers[tid] = p.peers.words[tid];
+    if (tid < kWarps * kDepth) mbar_init(smem_u32(m.mbar + tid), 1);          // one arrival (the issuing lane's, with the byte count) per use
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // token and position of this step (they change only at the very end of the launch)
+    const int tokId = (int)__ldcg(p.tok);
+    const bool tokOk = tokId >= 0 && tokId < p.vocab;
+    int pos = (int)__ldcg(p.pos);
+    pos = pos < 0 ? 0 : (pos >= p.maxSeq ? p.maxSeq - 1 : pos);
+    const float* embRow = p.emb + (size_t)(tokOk ? tokId : 0) * p.d;
+    // Exchange e of this launch (Wo of block l: 2l, down: 2l + 1, the pick: 2L) travels under tag epochBase + 1 + e.  All
+    // ranks run the same launches, so their counters agree; words of exchange e − 2 (same slot parity) carry an older tag.
+    const unsigned epochBase = tp ? ld_acquire(p.epoch) : 0u;
+
+    // ── block tables and weight-phase descriptors of two blocks at a time (block == L: the LM head) ──
+    auto load_block = [&](int layer) {
+        // the table entry: a handful of pointers, one per thread
+        if (layer < L && tid < (int)(sizeof(DsLayer) / sizeof(void*)))
+            reinterpret_cast<const void**>(m.lay + (layer & 1))[tid] = reinterpret_cast<const void* const*>(p.layers + layer)[tid];
+        if (tid >= 32 && tid < 36) {
+            const int ph = tid - 32;
+            DsPhase d; d.packed = nullptr; d.K = 32; d.N = 0; d.swiglu = 0; d.pad = 0;
+            if (layer < L) {
+                const DsLayer* ly = p.layers + layer;
+                const int dl = p.H * LPP * 16;
+                d.packed = ly->w[ph];
+                if (ph == 0) { d.K = p.d; d.N = 3 * dl; }
+                if (ph == 1) { d.K = dl; d.N = p.d; }
+                if (ph == 2) { d.K = p.d; d.N = p.F; d.swiglu = 1; }
+                if (ph == 3) { d.K = p.F; d.N = p.d; }
+            } else if (layer == L && ph == 0) {
+                d.packed = p.lm_w; d.K = p.d; d.N = p.V;
+            }
+            m.desc[(layer & 1) * 4 + ph] = d;
+        }
+    };
+    load_block(0);
+    load_block(1);
+    __syncthreads();
+
+    DsRing ring;
+    ring.wp = 0; ring.itile = 2 * blockIdx.x + (warp >> 3); ring.ipi = 0; ring.islot = 0; ring.ahead = 0; ring.cslot = 0; ring.cl = 0; ring.par = 0u;
+    ring.bestKey = INT_MIN; ring.bestIdx = INT_MAX;
+    ds_prefetch(c, ring);
+
+    auto grid_barrier = [&](int code) { ds_grid_barrier(p.bar, p.error, s_flags, nCtas, code); };
+    int stampAt = 0;
+    auto stamp = [&](int l) {
+        if (p.trace != nullptr && blockIdx.x == 0 && tid == 0 && l == (L > 1 ? 1 : 0) && stampAt < 32) p.trace[stampAt++] = gtime();
+    };
+    auto gemv = [&](int cp, int mode, const float* bias, const float* bias2, const float* residual, bool resNan, float* out,
+                    unsigned long long wordBase, unsigned tag) {
+        DsGemv a;
+        a.cp = cp; a.mode = mode; a.bias = bias; a.bias2 = bias2; a.residual = residual; a.resNan = resNan ? 1 : 0; a.out = out;
+        a.wordBase = wordBase; a.tag = tag;
+        ds_gemv(c, a, ring, p.error);
+    };
 
     for (int l = 0; l < L; l++) {
-        const DsLayer* ly = p.layers + l;
-        if (l > 0) load_desc(l + 1);        // into the slot block l−1 used; nobody reads it any more (visible after the staging barriers)
-        cl = l;
+        const DsLayer* ly = m.lay + (l & 1);          // this block's table, in shared memory since the block before
+        stamp(l);
+        if (l > 0) load_block(l + 1);                 // into the slots block l−1 used; nobody reads them any more (visible after the staging barriers)
+        ring.cl = l;
         const float* xin = l == 0 ? embRow : p.x;
         const bool xinNan = l == 0 && !tokOk;
 
         // ── RMSNorm → QKV projection ──
-        stage(xin, xinNan, ly->g1, p.d);
+        ds_stage(c, xin, xinNan, ly->g1, p.d);
+        stamp(l);
         gemv(4 * l, 0, nullptr, nullptr, nullptr, false, p.qkv, 0ull, 0u);
+        stamp(l);
 
-        // ── attention: the cached rows below `pos` do not depend on this launch, so the first group is requested
-        //    before the barrier that publishes q, k, v ──
-        float* kbase = ly->kcache + (size_t)ah * p.maxSeq * HD + gl * 16;
-        float* vbase = ly->vcache + (size_t)ah * p.maxSeq * HD + gl * 16;
-        float kf[16], vf[16];
-        float cs[8], sn[8];
-        if (attnOn) {
-            const int p0 = astart + w4 * PPW + group;
-            fetch_cached(kbase, vbase, p0, p0 < aend && p0 != pos, kf, vf);
-            const float4* cp4 = reinterpret_cast<const float4*>(p.cosT + (size_t)pos * halfHd + gl * 8);
-            const float4* sp4 = reinterpret_cast<const float4*>(p.sinT + (size_t)pos * halfHd + gl * 8);
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const float4 c4 = cp4[j], s4 = sp4[j];
-                cs[4 * j] = c4.x; cs[4 * j + 1] = c4.y; cs[4 * j + 2] = c4.z; cs[4 * j + 3] = c4.w;
-                sn[4 * j] = s4.x; sn[4 * j + 1] = s4.y; sn[4 * j + 2] = s4.z; sn[4 * j + 3] = s4.w;
-            }
+        // ── attention (RoPE, KV append, split-KV softmax attention, ticket merge; it holds the barrier that publishes q, k, v) ──
+        {
+            DsAttn aa;
+            aa.qkv = p.qkv; aa.att = p.att; aa.ws = p.attn_ws; aa.tickets = p.tickets; aa.cosT = p.cosT; aa.sinT = p.sinT;
+            aa.kcache = ly->kcache; aa.vcache = ly->vcache; aa.bar = p.bar; aa.error = p.error;
+            aa.scratch = reinterpret_cast<float*>(m.act); aa.flags = s_flags;
+            aa.pos = pos; aa.maxSeq = p.maxSeq; aa.H = p.H; aa.splits = p.splits; aa.nCtas = nCtas; aa.scale = p.scale;
+            ds_attention<LPP>(aa);
         }
-        grid_barrier(300 + 0);
-        if (attnOn) {
-            const int dl = p.H * HD;
-            float q[16];
-            load16_cg(p.qkv + ah * HD + gl * 16, q);
-            auto rotate = [&](float (&v)[16]) {
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const float x0 = v[2 * i], x1 = v[2 * i + 1];
-                    v[2 * i] = x0 * cs[i] - x1 * sn[i];
-                    v[2 * i + 1] = x0 * sn[i] + x1 * cs[i];
-                }
-            };
-            rotate(q);
-            auto fetch = [&](int pp, bool valid, float (&kx)[16], float (&vx)[16]) {
-                if (valid && pp == pos) {
-                    // the new token: k and v come from the projections; rotate k, append both to the cache
-                    load16_cg(p.qkv + dl + ah * HD + gl * 16, kx);
-                    load16_cg(p.qkv + 2 * dl + ah * HD + gl * 16, vx);
-                    rotate(kx);
-                    float4* kd = reinterpret_cast<float4*>(kbase + (size_t)pp * HD);
-                    float4* vd = reinterpret_cast<float4*>(vbase + (size_t)pp * HD);
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        kd[j] = make_float4(kx[4 * j], kx[4 * j + 1], kx[4 * j + 2], kx[4 * j + 3]);
-                        vd[j] = make_float4(vx[4 * j], vx[4 * j + 1], vx[4 * j + 2], vx[4 * j + 3]);
-                    }
-                } else fetch_cached(kbase, vbase, pp, valid, kx, vx);
-            };
-            float m = -INFINITY, lsum = 0.0f, acc[16];
-#pragma unroll
-            for (int j = 0; j < 16; j++) acc[j] = 0.0f;
-            int base = astart + w4 * PPW;
-            if (base < aend) {
-                const int p0 = base + group;
-                if (p0 == pos && p0 < aend) fetch(p0, true, kf, vf);
-            }
-            float kn[16], vn[16];
-            for (; base < aend; base += G) {
-                const bool valid = base + group < aend;
-                const int nbase = base + G;
-                if (nbase < aend) fetch(nbase + group, nbase + group < aend, kn, vn);
-                float dot = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 16; j++) dot = fmaf(q[j], kf[j], dot);
-#pragma unroll
-                for (int o = LPP / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                if (valid) {
-                    const float s = dot * p.scale;
-                    const float mn = fmaxf(m, s);
-                    const float corr = expf(m - mn);
-                    const float pe = expf(s - mn);
-                    lsum = lsum * corr + pe;
-#pragma unroll
-                    for (int j = 0; j < 16; j++) acc[j] = fmaf(pe, vf[j], acc[j] * corr);
-                    m = mn;
-                }
-#pragma unroll
-                for (int j = 0; j < 16; j++) { kf[j] = kn[j]; vf[j] = vn[j]; }
-            }
-            const int gg0 = w4 * PPW + group;
-#pragma unroll
-            for (int j = 0; j < 16; j++) s_acc[gg0 * HD + gl * 16 + j] = acc[j];
-            if (gl == 0) { s_m[gg0] = m; s_l[gg0] = lsum; }
-            bar_sync(3 + sub, 128);
-            float* mine = p.attn_ws + ((size_t)ah * p.splits + asplit) * (HD + 2);
-            for (int j = st; j < HD; j += 128) {
-                float M = -INFINITY;
-                for (int gg = 0; gg < G; gg++) M = fmaxf(M, s_m[gg]);
-                float a = 0.0f, Ls = 0.0f;
-                if (M > -INFINITY) {
-                    for (int gg = 0; gg < G; gg++) {
-                        const float e = expf(s_m[gg] - M);
-                        a = fmaf(s_acc[gg * HD + j], e, a);
-                        Ls = fmaf(s_l[gg], e, Ls);
-                    }
-                }
-                mine[j] = a;
-                if (j == 0) { mine[HD] = M; mine[HD + 1] = Ls; }
-            }
-            if (p.splits == 1) {
-                bar_sync(3 + sub, 128);
-                for (int j = st; j < HD; j += 128) p.att[ah * HD + j] = mine[j] / mine[HD + 1];
-            } else {
-                // the last group of this head merges the split partials
-                __threadfence();
-                bar_sync(3 + sub, 128);
-                if (st == 0) {
-                    const int ticket = atomicAdd(&p.tickets[ah], 1);
-                    const int last = ticket == p.splits - 1;
-                    s_flags[1 + sub] = last;
-                    if (last) p.tickets[ah] = 0;
-                }
-                bar_sync(3 + sub, 128);
-                if (s_flags[1 + sub]) {
-                    __threadfence();
-                    const float* pbase = p.attn_ws + (size_t)ah * p.splits * (HD + 2);
-                    float* s_m2 = s_acc;
-                    float* s_l2 = s_m2 + kMaxSplits;
-                    for (int sp = st; sp < p.splits; sp += 128) {
-                        s_m2[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD);
-                        s_l2[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD + 1);
-                    }
-                    constexpr int kBatch = 24;
-                    const int j0 = st;
-                    float first[kBatch];
-#pragma unroll
-                    for (int q2 = 0; q2 < kBatch; q2++) first[q2] = (j0 < HD && q2 < p.splits) ? __ldcg(pbase + (size_t)q2 * (HD + 2) + j0) : 0.0f;
-                    bar_sync(3 + sub, 128);
-                    float M = -INFINITY;
-                    for (int sp = 0; sp < p.splits; sp++) M = fmaxf(M, s_m2[sp]);
-                    float Lt = 0.0f;
-                    for (int sp = 0; sp < p.splits; sp++) Lt = fmaf(s_l2[sp], expf(s_m2[sp] - M), Lt);
-                    bar_sync(3 + sub, 128);
-                    for (int sp = st; sp < p.splits; sp += 128) s_m2[sp] = expf(s_m2[sp] - M);
-                    bar_sync(3 + sub, 128);
-                    for (int j = st; j < HD; j += 128) {
-                        float a = 0.0f;
-                        for (int s0 = 0; s0 < p.splits; s0 += kBatch) {
-                            float part[kBatch];
-                            if (j == j0 && s0 == 0) {
-#pragma unroll
-                                for (int q2 = 0; q2 < kBatch; q2++) part[q2] = first[q2];
-                            } else {
-#pragma unroll
-                                for (int q2 = 0; q2 < kBatch; q2++) part[q2] = s0 + q2 < p.splits ? __ldcg(pbase + (size_t)(s0 + q2) * (HD + 2) + j) : 0.0f;
-                            }
-#pragma unroll
-                            for (int q2 = 0; q2 < kBatch; q2++) if (s0 + q2 < p.splits) a = fmaf(part[q2], s_m2[s0 + q2], a);
-                        }
-                        p.att[ah * HD + j] = a / Lt;
-                    }
-                }
-            }
-        }
+        stamp(l);
         grid_barrier(300 + 1);
+        stamp(l);
 
         // ── Wo + residual ──
-        stage(p.att, false, nullptr, p.H * HD);
+        ds_stage(c, p.att, 0, nullptr, p.H * LPP * 16);
+        stamp(l);
         if (!tp) {
             gemv(4 * l + 1, 0, nullptr, nullptr, xin, xinNan, p.x2, 0ull, 0u);
+            stamp(l);
             grid_barrier(300 + 2);
         } else {
             const unsigned long long wb = 0ull;                                            // even exchanges: slot parity 0
             gemv(4 * l + 1, 3, nullptr, nullptr, nullptr, false, nullptr, wb, epochBase + 1u + 2u * l);
-            tp_reduce(wb, epochBase + 1u + 2u * l, nullptr, xin, xinNan, p.x2);
+            ds_tp_reduce(c, wb, epochBase + 1u + 2u * l, nullptr, xin, xinNan, p.x2, p.error);
             grid_barrier(300 + 2);
         }
 
         // ── RMSNorm → SwiGLU ──
-        stage(p.x2, false, ly->g2, p.d);
+        stamp(l);
+        ds_stage(c, p.x2, 0, ly->g2, p.d);
+        stamp(l);
         gemv(4 * l + 2, 1, ly->bg, ly->bu, nullptr, false, p.h, 0ull, 0u);
+        stamp(l);
         grid_barrier(300 + 3);
+        stamp(l);
 
         // ── down + bias + residual ──
-        stage(p.h, false, nullptr, p.F);
+        ds_stage(c, p.h, 0, nullptr, p.F);
+        stamp(l);
         if (!tp) {
             gemv(4 * l + 3, 0, ly->bd, nullptr, p.x2, false, p.x, 0ull, 0u);
+            stamp(l);
             grid_barrier(300 + 4);
+            stamp(l);
         } else {
             const unsigned long long wb = (unsigned long long)p.world * p.d;               // odd exchanges: slot parity 1
             gemv(4 * l + 3, 3, nullptr, nullptr, nullptr, false, nullptr, wb, epochBase + 2u + 2u * l);
-            tp_reduce(wb, epochBase + 2u + 2u * l, ly->bd, p.x2, false, p.x);
+            ds_tp_reduce(c, wb, epochBase + 2u + 2u * l, ly->bd, p.x2, 0, p.x, p.error);
             grid_barrier(300 + 4);
         }
     }
 
     // ── final RMSNorm → LM head → greedy pick ──
-    cl = L;
-    stage(L == 0 ? embRow : p.x, L == 0 && !tokOk, p.gF, p.d);
+    ring.cl = L;
+    ds_stage(c, L == 0 ? embRow : p.x, L == 0 && !tokOk, p.gF, p.d);
     gemv(4 * L, 2, p.blm, nullptr, nullptr, false, p.logits, 0ull, 0u);
-    cp_async_wait<0>();
+    // nothing lies behind the LM head in a warp's sequence, so no copy of this launch is in flight any more
+    int bestKey = ring.bestKey, bestIdx = ring.bestIdx;
     {
         // CTA-wide best (key, index) of the outputs this CTA finished; lowest index among equal keys
         for (int o = 16; o > 0; o >>= 1) {
@@ -725,8 +895,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_decode_step(const DsParams p) {
     grid_barrier(300 + 5);
     if (blockIdx.x == 0 && warp == 0) {
         bestKey = INT_MIN; bestIdx = INT_MAX;
-        for (int c = lane; c < nCtas; c += 32) {
-            const int k2 = __ldcg(p.pick + 2 * c), i2 = __ldcg(p.pick + 2 * c + 1);
+        for (int cc = lane; cc < nCtas; cc += 32) {
+            const int k2 = __ldcg(p.pick + 2 * cc), i2 = __ldcg(p.pick + 2 * cc + 1);
             if (k2 > bestKey || (k2 == bestKey && i2 < bestIdx)) { bestKey = k2; bestIdx = i2; }
         }
         for (int o = 16; o > 0; o >>= 1) {
@@ -771,6 +941,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_decode_step(const DsParams p) {
             if (tp) *p.epoch = epochBase + 2u * (unsigned)L + 2u;
         }
     }
+    // A CTA that gave up a wait may still have copies in flight (it stopped waiting for them): give them time to land
+    // before its shared memory is handed on.  A healthy CTA has consumed every item it issued.
+    if (s_flags[0] != 0) {
+        for (int i = 0; i < 100; i++) __nanosleep(2000);
+    }
     // the last CTA out re-arms the barrier counter for the next launch
     __syncthreads();
     if (tid == 0) {
@@ -778,6 +953,53 @@ __global__ void __launch_bounds__(kThreads, 1) k_decode_step(const DsParams p) {
         const unsigned done = atomicAdd(p.bar + 1, 1u);
         if (done == (unsigned)nCtas - 1u) { p.bar[0] = 0u; p.bar[1] = 0u; __threadfence(); }
     }
+}
+
+// ───────────── tile-major weight stream ─────────────
+// One CTA per (tile, 64-k pair): 72 threads move 16 bytes each — 64 code pieces (row r, 16-byte piece c at
+// r·64 + (c ^ ((r>>1 & 1)·2))·16, the swizzle the MMA fragment reads expect) and 8 × 4 scales (row r, block b at
+// 1024 + (2r + b)·4).  Rows past N repeat the last row (their results are never written); the missing second block
+// of an odd last pair is zeros with scale 0.  With codes2 != null a tile is 8 gate rows then 8 up rows.
+__global__ void k_pack_phase(const int8_t* __restrict__ codes, const float* __restrict__ scales, const int8_t* __restrict__ codes2,
+                             const float* __restrict__ scales2, int K, int N, unsigned char* __restrict__ out) {
+    const int nBlocks = K >> 5, nPairs = (nBlocks + 1) >> 1, nb = nBlocks;
+    const int tile = blockIdx.y, pi = blockIdx.x, i = threadIdx.x;
+    const bool sw = codes2 != nullptr;
+    const int rpt = sw ? 8 : 16;
+    const int hw = pi & 7, j = pi >> 3;
+    const int q = nPairs >> 3, rem = nPairs & 7;
+    const size_t dstPair = (size_t)tile * nPairs * kPairBytes + (size_t)(hw * q + min(hw, rem) + j) * kPairBytes;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (i < 64) {
+        const int r = i >> 2, c = i & 3;
+        const int row = min(tile * rpt + (sw ? (r & 7) : r), N - 1);
+        const int8_t* src = (sw && r >= 8) ? codes2 : codes;
+        if (pi * 2 + (c >> 1) < nBlocks) v = *reinterpret_cast<const uint4*>(src + (size_t)row * K + pi * 64 + c * 16);
+        *reinterpret_cast<uint4*>(out + dstPair + r * kRowStride + ((c ^ (((r >> 1) & 1) << 1)) * 16)) = v;
+    } else if (i < 72) {
+        float f[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int idx = (i - 64) * 4 + e, r = idx >> 1, b = idx & 1;
+            const int row = min(tile * rpt + (sw ? (r & 7) : r), N - 1);
+            const float* src = (sw && r >= 8) ? scales2 : scales;
+            f[e] = pi * 2 + b < nBlocks ? src[(size_t)row * nb + pi * 2 + b] : 0.0f;
+        }
+        *reinterpret_cast<float4*>(out + dstPair + kRows * kRowStride + (i - 64) * 16) = make_float4(f[0], f[1], f[2], f[3]);
+    }
+}
+
+size_t packed_bytes(int K, int N, bool swiglu) {
+    const int rpt = swiglu ? 8 : 16;
+    const size_t nTiles = (size_t)(N + rpt - 1) / rpt, nPairs = (size_t)((K >> 5) + 1) >> 1;
+    return nTiles * nPairs * kPairBytes;
+}
+
+void pack_phase(const Q8View& w, const Q8View* w2, unsigned char* out, cudaStream_t s) {
+    const int rpt = w2 ? 8 : 16;
+    const dim3 grid((unsigned)(((w.K >> 5) + 1) >> 1), (unsigned)((w.N + rpt - 1) / rpt));
+    k_pack_phase<<<grid, 96, 0, s>>>(w.codes, w.scales, w2 ? w2->codes : nullptr, w2 ? w2->scales : nullptr, w.K, w.N, out);
+    DJ_CUDA_CHECK(cudaGetLastError());
 }
 
 // ───────────── host side: plans ─────────────
@@ -795,7 +1017,7 @@ std::unordered_map<int, Plan> g_plans;
 size_t ds_smem_bytes(int kmax) {
     const size_t act = std::max<size_t>((size_t)3 * (kmax + kXsPad) + (size_t)(kmax >> 5) * 4, (size_t)4 * kAttnScratchFloats * 4);
     return (size_t)kWarps * kDepth * kSlotBytes + ((act + 127) & ~(size_t)127) + (size_t)2 * 2 * kHalfWarps * 128 * 4 + 8 * sizeof(DsPhase) +
-           kWarps * 4 + (8 + 2 * kWarps) * 4;
+           2 * sizeof(DsLayer) + kWarps * 4 + 48 * 4 + kMaxWorld * sizeof(void*) + (size_t)kWarps * kDepth * 8;
 }
 
 }  // namespace
@@ -823,6 +1045,8 @@ void launch_decode_step(int plan_id, int feed_back, cudaStream_t s) {
     Plan& pl = g_plans.at(plan_id);
     DsParams prm = pl.prm;
     prm.feed_back = feed_back;
+    prm.trace = g_trace;                 // null unless DEEPJ_CUDA_TRACE=1; the stamps of the last launch stay in the first 32 slots
+    if (g_trace && g_trace_launches < 4) g_trace_launches = 4;
     if (pl.uses_tp) {
         for (int r = 0; r < prm.world; r++) prm.peers.words[r] = tp_step_words(r);
         prm.epoch = tp_step_epoch();
@@ -885,7 +1109,7 @@ extern "C" int deepj_cuda_decode_plan(int32_t plan_id, const int32_t* desc, int3
         const int d = lm.K, V = lm.N;
         if (d != dl * world) throw std::runtime_error("decode_plan: dModel must equal heads x head_dim x tensor-parallel ranks");
         if (d % 32 != 0 || d % 2 != 0) throw std::runtime_error("decode_plan: dModel must be a multiple of 32");
-        P.d = d; P.V = V; P.lm_c = lm.codes; P.lm_s = lm.scales;
+        P.d = d; P.V = V;
         PoolKV kv;
         if (!pool_kv(desc[10], &kv)) throw std::runtime_error("decode_plan: missing KV cache");
         pl.refs.push_back({desc[10], pool_serial(desc[10])});
@@ -902,23 +1126,28 @@ extern "C" int deepj_cuda_decode_plan(int32_t plan_id, const int32_t* desc, int3
         P.gF = f32(desc[18], d, "final norm gain"); P.blm = f32(desc[20], V, "LM head bias");
         int F = 0;
         std::vector<DsLayer> table(L);
+        struct Src { Q8View w, w2; bool sw; };
+        std::vector<Src> srcs;                       // 4 per block in phase order, then the LM head
         const size_t plane = (size_t)kv.layers * kv.B * kv.H * kv.maxSeq * kv.hd;
         for (int l = 0; l < L; l++) {
             const int32_t* e = desc + kHead + l * kPerLayer;
             DsLayer& y = table[l];
             y.g1 = f32(e[0], d, "norm gain 1");
-            Q8View w = q8(e[1], d, 3 * dl, "Wqkv"); y.qkv_c = w.codes; y.qkv_s = w.scales;
-            w = q8(e[2], dl, d, "Wo"); y.wo_c = w.codes; y.wo_s = w.scales;
+            const Q8View wqkv = q8(e[1], d, 3 * dl, "Wqkv");
+            const Q8View wo = q8(e[2], dl, d, "Wo");
             y.g2 = f32(e[3], d, "norm gain 2");
-            w = q8(e[4], d, F, "gate"); if (l == 0) F = w.N; y.wg_c = w.codes; y.wg_s = w.scales;
+            const Q8View wg = q8(e[4], d, F, "gate");
+            if (l == 0) F = wg.N;
             y.bg = f32(e[5], F, "gate bias");
-            w = q8(e[6], d, F, "up"); y.wu_c = w.codes; y.wu_s = w.scales;
+            const Q8View wu = q8(e[6], d, F, "up");
             y.bu = f32(e[7], F, "up bias");
-            w = q8(e[8], F, d, "down"); y.wd_c = w.codes; y.wd_s = w.scales;
+            const Q8View wd = q8(e[8], F, d, "down");
             y.bd = f32(e[9], d, "down bias");
+            srcs.push_back({wqkv, {}, false}); srcs.push_back({wo, {}, false}); srcs.push_back({wg, wu, true}); srcs.push_back({wd, {}, false});
             const size_t layerOff = (size_t)l * kv.B * kv.H * kv.maxSeq * kv.hd;
             y.kcache = kv.ptr + layerOff; y.vcache = kv.ptr + plane + layerOff;
         }
+        srcs.push_back({lm, {}, false});
         if (L > 0 && F < 32) throw std::runtime_error("decode_plan: dFF must be at least 32");
         P.F = F;
         P.h = f32(desc[15], std::max(F, 1), "h");
@@ -939,13 +1168,26 @@ extern "C" int deepj_cuda_decode_plan(int32_t plan_id, const int32_t* desc, int3
         pl.lpp = hd / 16;
         pl.smem = ds_smem_bytes(P.kmax);
         if (pl.smem > 227 * 1024) throw std::runtime_error("decode_plan: the model's rows do not fit the kernel's shared memory");
-        // one device block: the layer table, then scratch (attention partials, tickets, barrier words, pick pairs)
+        // one device block: the layer table, scratch (attention partials, tickets, barrier words, pick pairs), then the
+        // tile-major copies of every weight the step streams (as many bytes again as the Q8 objects they are made from)
         const size_t tableBytes = ((size_t)L * sizeof(DsLayer) + 255) & ~(size_t)255;
         const size_t wsFloats = (size_t)H * P.splits * (hd + 2);
-        const size_t scratchBytes = wsFloats * 4 + (size_t)H * 4 + 16 * 4 + (size_t)2 * g_num_sms * 4 + 256;
+        const size_t scratchBytes = (wsFloats * 4 + (size_t)H * 4 + 16 * 4 + (size_t)2 * g_num_sms * 4 + 511) & ~(size_t)255;
+        std::vector<size_t> wOff(srcs.size());
+        size_t weightBytes = 0;
+        for (size_t i = 0; i < srcs.size(); i++) {
+            wOff[i] = weightBytes;
+            weightBytes += (packed_bytes(srcs[i].w.K, srcs[i].w.N, srcs[i].sw) + 255) & ~(size_t)255;
+        }
         char* block = nullptr;
-        DJ_CUDA_CHECK(cudaMalloc((void**)&block, tableBytes + scratchBytes));
+        DJ_CUDA_CHECK(cudaMalloc((void**)&block, tableBytes + scratchBytes + weightBytes));
         DJ_CUDA_CHECK(cudaMemset(block, 0, tableBytes + scratchBytes));
+        unsigned char* wbase = reinterpret_cast<unsigned char*>(block + tableBytes + scratchBytes);
+        for (size_t i = 0; i < srcs.size(); i++) pack_phase(srcs[i].w, srcs[i].sw ? &srcs[i].w2 : nullptr, wbase + wOff[i], runtime_stream());
+        for (int l = 0; l < L; l++)
+            for (int ph = 0; ph < 4; ph++) table[l].w[ph] = wbase + wOff[(size_t)4 * l + ph];
+        P.lm_w = wbase + wOff[(size_t)4 * L];
+        DJ_CUDA_CHECK(cudaStreamSynchronize(runtime_stream()));
         if (L > 0) DJ_CUDA_CHECK(cudaMemcpy(block, table.data(), (size_t)L * sizeof(DsLayer), cudaMemcpyHostToDevice));
         P.layers = reinterpret_cast<const DsLayer*>(block);
         P.attn_ws = reinterpret_cast<float*>(block + tableBytes);
@@ -961,7 +1203,7 @@ extern "C" int deepj_cuda_decode_plan(int32_t plan_id, const int32_t* desc, int3
             else DJ_CUDA_CHECK(cudaFuncSetAttribute(k_decode_step<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
             attrSet[ai] = true;
         }
-        pool_add_plan(plan_id, block, tableBytes + scratchBytes);
+        pool_add_plan(plan_id, block, tableBytes + scratchBytes + weightBytes);
         pl.serial = pool_serial(plan_id);
         g_plans[plan_id] = std::move(pl);
         return 0;

@@ -149,9 +149,9 @@ class Q8Decoder:
         bounds the rows a tensor-parallel prompt chunk may have (rows × dModel floats per exchange).
         `share_weights`: another decoder of the same configuration and sharding whose device weights this one reads
         (its own activations and KV cache, a different `id_base`); the other decoder must outlive this one.
-        `fused_step`: run a token step as ONE persistent kernel (op 76) instead of one kernel per operator; None = whenever
-        the model qualifies (a Llama-shaped model, one sequence, every reduction length a multiple of 32, head dim 32 / 64 /
-        128).  Under tensor parallelism the plan is made at the first step, after `tp.connect`."""
+        `fused_step`: run a token step as ONE persistent kernel (op 76) instead of one kernel per operator; the model must
+        qualify (a Llama-shaped model, one sequence, every reduction length a multiple of 32, head dim 32 / 64 / 128).
+        Under tensor parallelism the plan is made at the first step, after `tp.connect`."""
         self.cfg = cfg
         self.B = int(batch)
         self.tp_slot_floats = int(tp_slot_floats)
@@ -186,7 +186,7 @@ class Q8Decoder:
         self._plan_id: Optional[int] = None
         if fused_step and not self.fused_step_eligible(cfg, self.B, tp_world):
             raise ValueError("this configuration does not qualify for the single-kernel token step")
-        self.fused_step = self.fused_step_eligible(cfg, self.B, tp_world) if fused_step is None else bool(fused_step)
+        self.fused_step = bool(fused_step)          # opt-in: measured slower than the per-operator stream on one GPU so far
         self._alloc_state()
         if share_weights is not None:
             o = share_weights
@@ -739,12 +739,14 @@ class Q8Decoder:
         return (np.asarray(out, dtype=np.int64), np.stack(rows) if rows else None) if keep_logits else np.asarray(out, dtype=np.int64)
 
     def profile_step(self):
-        """Device time of every op of one token step, run op by op: [(label, ms)]."""
-        host, _ = self._streams()
+        """Device time of every op of one token step, run op by op as the per-operator stream (also when the
+        decoder itself steps with the single-kernel op): [(label, ms)]."""
+        if not self.loaded:
+            raise RuntimeError("weights are not loaded")
+        host = self._build(feed_back=False)
         n = len(self._op_labels) + 1
         ms = np.zeros(n, dtype=np.float32)
         cnt = ctypes.c_int32(0)
-        self._build(feed_back=False)
         _lib.check(self.lib.deepj_cuda_profile_ops(host.ctypes.data, host.size, ms.ctypes.data, n, ctypes.byref(cnt)))
         self.position += 1
         return list(zip(self._op_labels, ms[: cnt.value].tolist()))

@@ -1,5 +1,7 @@
-"""Operator benchmark: `python -m deepj_b200.opbench --m 1 --k 4096 --n 11008` (Q8 matmul) or
-`python -m deepj_b200.opbench --attn-prefill --heads 32 --head-dim 128 --tokens 1024 --pos0 1024` (prompt-chunk attention).
+"""Operator benchmark: `python -m deepj_b200.opbench --m 1 --k 4096 --n 11008` (Q8 matmul),
+`python -m deepj_b200.opbench --attn-prefill --heads 32 --head-dim 128 --tokens 1024 --pos0 1024` (prompt-chunk attention) or
+`python -m deepj_b200.opbench --decode-step --d 4096 --heads 32 --d-ff 11008 --vocab 32000 --layers 4 --context 2048`
+(token steps of a reduced-depth Llama-shaped model: the whole-token kernel, or with --per-op one kernel per operator).
 
 Times the fused Q8 linear op (y = x·W, W quantized to Q8) through the C ABI.  The
 weights of one GEMV (19-51 MB) fit in the B200's L2, so the stream cycles through
@@ -143,6 +145,46 @@ def run_attn_prefill(heads: int, hd: int, tokens: int, pos0: int, batch: int, it
     return res
 
 
+def run_decode_step(d: int, heads: int, d_ff: int, vocab: int, layers: int, context: int, iters: int, warmup: int, per_op: bool,
+                    device: int = 0, seed: int = 9):
+    """Times greedy token steps (token fed back on the device) of a Llama-shaped Q8 model with synthetic weights, the
+    cache positioned at `context` (its rows hold zeros below that: the attention still streams them).  Algorithmic bytes per
+    step = Q8 weight bytes + K/V rows of the context."""
+    from .decoder import DecoderConfig, Q8Decoder
+    steps = warmup + iters
+    cfg = DecoderConfig("llama", vocab, context + steps + 8, d, heads, layers, d_ff)
+    dec = Q8Decoder(cfg, batch=1, device=device, fused_step=not per_op)
+    dec.load_synthetic(seed, 0.02)
+    dec.reset()
+    dec.set_position(context)
+    dec.set_tokens([1])
+    dec.step_device(max(warmup, 3))
+    _lib.check(dec.lib.deepj_cuda_timer_begin())
+    dec.step_device(iters, sync=False)
+    ms = ctypes.c_float(0)
+    _lib.check(dec.lib.deepj_cuda_timer_end(ctypes.byref(ms)))
+    us = ms.value * 1e3 / iters
+    ctx = context + max(warmup, 3) + iters // 2
+    step_bytes = cfg.q8_weight_bytes() + ctx * cfg.kv_bytes_per_position()
+    st = dec.stats()
+    res = {"op": "decode_step", "kernel": "k_decode_step" if dec.fused_step else "one kernel per operator", "d": d, "heads": heads, "d_ff": d_ff,
+           "vocab": vocab, "layers": layers, "context": ctx, "us_per_step": us, "algorithmic_bytes": step_bytes,
+           "gb_per_s": step_bytes / (us * 1e-6) / 1e9, "device_error": st["device_error"], "graph_replays": st["graph_replays"]}
+    import os
+    if os.environ.get("DEEPJ_CUDA_TRACE") == "1" and dec.fused_step:
+        # CTA 0's %globaltimer stamps at the phase boundaries of block 1 (last launch): differences in ns
+        tr = np.zeros((4, 8), dtype=np.uint64)
+        cnt = ctypes.c_int32(0)
+        _lib.check(dec.lib.deepj_cuda_trace_read(tr.ctypes.data, 4, ctypes.byref(cnt)))
+        t = tr.reshape(-1).astype(np.int64)
+        names = ["stage_qkv", "gemv_qkv", "barrier", "attention", "barrier", "stage_att", "gemv_wo", "barrier", "(gap)", "stage_x2",
+                 "gemv_swiglu", "barrier", "stage_h", "gemv_down", "barrier"]
+        t = t[t > 0]
+        res["trace_ns"] = [[names[i] if i < len(names) else str(i), int(t[i + 1] - t[i])] for i in range(len(t) - 1)]
+    dec.close()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int, default=1)
@@ -159,7 +201,17 @@ def main():
     ap.add_argument("--tokens", type=int, default=1024)
     ap.add_argument("--pos0", type=int, default=1024)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--decode-step", action="store_true", help="time token steps of a reduced-depth model: --d --d-ff --vocab --layers --context")
+    ap.add_argument("--per-op", action="store_true", help="with --decode-step: one kernel per operator instead of the whole-token kernel")
+    ap.add_argument("--d", type=int, default=4096)
+    ap.add_argument("--d-ff", type=int, default=11008)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--context", type=int, default=2048)
     a = ap.parse_args()
+    if a.decode_step:
+        print(json.dumps(run_decode_step(a.d, a.heads, a.d_ff, a.vocab, a.layers, a.context, a.iters, a.warmup, a.per_op)))
+        return
     if a.attn_prefill:
         print(json.dumps(run_attn_prefill(a.heads, a.head_dim, a.tokens, a.pos0, a.batch, a.iters, a.warmup)))
         return

@@ -41,7 +41,7 @@ def check_q8_codes(dec: Q8Decoder, om, cfg: DecoderConfig, layer: int) -> None:
 
 def reduced_depth_parity(w: dict, layers: int = 2, prompt_len: int = 48, n_new: int = 8, rank: int = 0, world: int = 1,
                          device: int = 0, tp_slot_floats: int = 0, id_base: int = 3 << 24, check_codes: bool = True,
-                         kv_dtype: str = "f32") -> dict:
+                         kv_dtype: str = "f32", fused_step=None) -> dict:
     """Runs the check and returns {"max_err_over_range", "tokens_equal", "checked", "seconds"}.  Under tensor
     parallelism (world > 1) the exchange buffers must already be connected (`deepj_b200.tp.connect`) with slots of
     at least prompt_len × dModel floats."""
@@ -49,7 +49,7 @@ def reduced_depth_parity(w: dict, layers: int = 2, prompt_len: int = 48, n_new: 
     max_seq = prompt_len + n_new + 8
     cfg = reduced_config(w, layers, max_seq)
     dec = Q8Decoder(cfg, batch=1, device=device, id_base=id_base, tp_rank=rank, tp_world=world, tp_slot_floats=tp_slot_floats,
-                    **({"kv_dtype": kv_dtype} if kv_dtype != "f32" else {}))
+                    fused_step=fused_step, **({"kv_dtype": kv_dtype} if kv_dtype != "f32" else {}))
     try:
         dec.load_synthetic(w["seed"], w["std"])
         prompt = np.random.default_rng(w["seed"] + 1000).integers(0, w["vocab"], size=prompt_len)
@@ -82,7 +82,7 @@ def reduced_depth_parity(w: dict, layers: int = 2, prompt_len: int = 48, n_new: 
         what = (f"{cfg.kind} d={cfg.d_model} heads={cfg.n_heads} dFF={cfg.d_ff} vocab={cfg.vocab_size}"
                 + (f" qRank={cfg.q_rank} kvRank={cfg.kv_rank}" if cfg.kind == "deepseek" else "")
                 + f", {layers} of {w['layers']} blocks, synthetic weights seed {w['seed']}, {prompt_len}-token prompt through prefill"
-                + f" + {n_new} greedy steps, tp{world}, kv {kv_dtype}: logits of every new token and the tokens vs the CPU oracle"
+                + f" + {n_new} greedy steps ({'one whole-token kernel per step' if dec.fused_step else 'one kernel per operator'}), tp{world}, kv {kv_dtype}: logits of every new token and the tokens vs the CPU oracle"
                 + " with dequantized Q8 weights" + ("; Q8 codes and scales of one block bit-exact" if check_codes and world == 1 else ""))
         return {"max_err_over_range": err_over_range, "tokens_equal": bool(equal), "tolerance": LOGIT_TOL, "checked": what,
                 "seconds": time.perf_counter() - t_start}

@@ -31,7 +31,7 @@ def main():
     # slots large enough for a 24-token chunk per sequence: the 40-token prompt goes through the many-row path in
     # two chunks (24 + 16 tokens, 48 and 32 rows per exchange), the steps after it through the decode path
     slot = max(B * 24 * cfg.d_model, B * cfg.vocab_size // world)
-    dec = Q8Decoder(cfg, batch=B, device=local, tp_rank=rank, tp_world=world, tp_slot_floats=slot)
+    dec = Q8Decoder(cfg, batch=B, device=local, tp_rank=rank, tp_world=world, tp_slot_floats=slot, fused_step=(B == 1))
     tp.connect(rank, world, slot, large_message_floats=8192)      # both exchange grids and both slot regions get used
     dec.load_weights(weight_getter(om, cfg))
     om.apply_q8()
