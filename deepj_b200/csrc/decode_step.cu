@@ -17,12 +17,13 @@
 //
 // The weights are read from a tile-major copy made once per plan (k_pack_phase): the 16 weight rows ×
 // 64 codes + 32 scales of a (tile, 64-k pair) are one contiguous 1152-byte image of what the MMA
-// fragments read from shared memory (32-byte halves already XOR-swizzled by row), and a warp's pairs
-// of a tile follow each other, so a ring item — two pairs, 2304 bytes — is ONE cp.async.bulk on an
-// mbarrier, issued by one lane.  With the canonical row-major layout every lane spent ≈ 100
-// instructions per item on copy addresses and group bookkeeping and the projection loop was
-// issue-bound at about two thirds of the HBM rate.  The copy costs the plan as much memory again as
-// the Q8 weights it covers.
+// fragments read from shared memory (32-byte halves already XOR-swizzled by row), and a tile's pairs
+// follow each other, so a ring item — 16 pairs, two for each of the eight warps that share a tile,
+// 18 KB — is ONE cp.async.bulk on an mbarrier, issued by one lane of the half (full / empty
+// barriers per slot, as in any bulk-copy pipeline).  With the canonical row-major layout every lane
+// spent ≈ 100 instructions per 1152 bytes on copy addresses and group bookkeeping, and with one
+// small bulk copy per warp the issuing warp stalled ≈ 450 cycles per copy.  The tile-major copy
+// costs the plan as much memory again as the Q8 weights it covers.
 //
 // The arithmetic is the per-operator kernels' (q8_gemv_i8.cu, attn.cu), instruction for
 // instruction: int8 codes as the A operand of mma.sync m16n8k32, activations as three base-256
@@ -63,9 +64,12 @@ constexpr int kHalfWarps = 8;                   // warps that share a weight-row
 constexpr int kRows = 16;
 constexpr int kRowStride = 64;
 constexpr int kPairBytes = kRows * kRowStride + kRows * 2 * 4;      // 1152: 16 rows × 64 codes, then 32 scales
-constexpr int kItemPairs = 2;                   // 64-k pairs per ring item
+constexpr int kWarpPairs = 2;                   // 64-k pairs of one warp in a ring item
+constexpr int kItemPairs = 8 * kWarpPairs;      // a ring item: 16 consecutive pairs of a tile, two for each warp of the half (18 KB)
 constexpr int kSlotBytes = kItemPairs * kPairBytes;
-constexpr int kDepth = 4;                       // ring slots per warp: three items (6.9 KB) in flight, one being read
+constexpr int kDepth = 4;                       // ring slots per half: three items (55 KB) in flight, one being read
+constexpr int kPartBufs = 4;                    // tile partial buffers per half: a warp may run this many tiles ahead of the slowest
+constexpr int kPartFloats = 48;                 // 16 weight rows × 3 digit sums per warp and tile
 constexpr int kXsPad = 32;
 constexpr int kStageRounds = 2;                 // rows of up to 2·512·16 = 16384 values are staged from registers
 constexpr int kMaxSplits = 256;
@@ -124,6 +128,9 @@ __device__ __forceinline__ float lds_f(uint32_t a) {
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -159,23 +166,24 @@ __device__ __forceinline__ void st_volatile_v2(void* p, uint2 v) {
 }
 
 // ── shared-memory layout ──
-// rings [16 warps][kDepth][2304] | activation digits (3 columns) + block scales, overlaid by the attention scratch |
-// tile partials [2 halves][2][8 warps][128] | weight-phase descriptors [2 blocks][4] | block tables [2] | reductions | flags | peers
+// rings [2 halves][kDepth][18432] | activation digits (3 columns) + block scales, overlaid by the attention scratch |
+// tile partials [2 halves][4][8 warps][16 rows × 3 digits] | weight-phase descriptors [2 blocks][4] | block tables [2] | reductions | flags | peers
 struct DsSmem {
     unsigned char* rings; unsigned char* act; float* part; DsPhase* desc; DsLayer* lay; float* red; int* flags;
-    unsigned long long** peers; unsigned long long* mbar;      // mbar: one per ring slot, [16 warps][kDepth]
+    unsigned long long** peers; unsigned long long* mbar;      // mbar: [2 halves][full | empty][kDepth]
 };
 __device__ __forceinline__ DsSmem ds_layout(unsigned char* smem, int kmax) {
     DsSmem m;
     m.rings = smem;
-    m.act = smem + (size_t)kWarps * kDepth * kSlotBytes;
+    m.act = smem + (size_t)2 * kDepth * kSlotBytes;
     const int actBytes = max(3 * (kmax + kXsPad) + (kmax >> 5) * 4, 4 * kAttnScratchFloats * 4);
     m.part = reinterpret_cast<float*>(m.act + ((actBytes + 127) & ~127));
-    m.desc = reinterpret_cast<DsPhase*>(m.part + 2 * 2 * kHalfWarps * 128);
+    m.desc = reinterpret_cast<DsPhase*>(m.part + 2 * kPartBufs * kHalfWarps * kPartFloats);
     m.lay = reinterpret_cast<DsLayer*>(m.desc + 8);
     m.red = reinterpret_cast<float*>(m.lay + 2);
-    m.flags = reinterpret_cast<int*>(m.red + kWarps);       // [0] dead, [1..4] attention groups' "last" flags, [5] barrier generation, [8..39] pick pairs
-    m.peers = reinterpret_cast<unsigned long long**>(m.flags + 48);
+    m.flags = reinterpret_cast<int*>(m.red + kWarps);       // [0] dead, [1..4] attention groups' "last" flags, [5] barrier generation, [8..39] pick pairs,
+                                                            // [40..47] tile arrivals [half][buffer], [48..55] tile reductions done [half][buffer]
+    m.peers = reinterpret_cast<unsigned long long**>(m.flags + 64);
     m.mbar = reinterpret_cast<unsigned long long*>(m.peers + kMaxWorld);
     return m;
 }
@@ -205,8 +213,10 @@ __device__ __noinline__ void ds_grid_barrier(unsigned* bar, int* error, int* fla
 // kDepth items ahead of the consumer side, across phase boundaries.  Warp-uniform; lives in the kernel's frame and is
 // handed to the out-of-line phases by reference.
 struct DsRing {
-    int wp, itile, ipi, islot, ahead, cslot;      // producer: phase / tile / first pair of the next item (index among this warp's pairs of the tile) / next slot; items in flight; consumer slot
-    unsigned par;                                 // bit s: the parity the consumer waits for on slot s next
+    int wp, itile, ipi, islot, ahead, cslot;      // producer (warp 0 of a half): phase / tile / next item of the tile / next slot; items issued and not yet consumed; consumer slot
+    unsigned par;                                 // bit s: the parity a consumer waits for on full[s] next; bit 16+s: the parity the producer waits for on empty[s] next
+    unsigned used;                                // bit s: slot s has been filled before (its empty barrier must complete before the next fill)
+    unsigned tileSeq;                             // tiles this half has finished so far (the same in its eight warps)
     int cl;                                       // the block the consumer is in (the producer may be one block ahead)
     int bestKey, bestIdx;                         // running greedy pick of the LM-head outputs this thread finished
 };
@@ -217,60 +227,75 @@ struct DsCtx {                                    // what every phase needs from
     float eps;
 };
 
-// The producer: where the next item of this warp's sequence lies in the phase's tile-major stream, and the issue
-// loop.  Everything is warp-uniform; lane 0 arms the slot's mbarrier and issues the one bulk copy of an item.
+// The producer of a half's ring — lane 0 of the half's first warp: where the next item of the half's static sequence lies in
+// the phase's tile-major stream, and the issue loop.  A slot is refilled once all eight warps have released its previous
+// content (its empty barrier); the wait for that is taken only when the producer's own warp has nothing left to consume.
 struct DsProducer {
-    uint32_t ring_s, mbar_s;
+    uint32_t ring_s, full_s, empty_s;
     int vcta, nV, hw, lane;
-    int pnTiles, pnPairs, npw, warpOff;           // this phase: tiles, pairs per tile, this warp's pairs per tile, their byte offset in a tile
+    int pnTiles, pnPairs, pnItems;                // this phase: tiles, pairs per tile, items per tile
     size_t tileBytes;
     const unsigned char* base;
     const DsPhase* desc; int nWp;
+    volatile int* dead; int* error;
 
-    __device__ __forceinline__ void init(const DsSmem& m, int nCtas, int nWp_) {
-        const int tid = threadIdx.x, warp = tid >> 5;
+    __device__ __forceinline__ void init(const DsSmem& m, int nCtas, int nWp_, int* error_) {
+        const int tid = threadIdx.x, warp = tid >> 5, half = warp >> 3;
         lane = tid & 31; hw = warp & 7;
-        vcta = 2 * blockIdx.x + (warp >> 3); nV = 2 * nCtas;
+        vcta = 2 * blockIdx.x + half; nV = 2 * nCtas;
         desc = m.desc; nWp = nWp_;
-        ring_s = smem_u32(m.rings + (size_t)warp * kDepth * kSlotBytes);
-        mbar_s = smem_u32(m.mbar + warp * kDepth);
+        ring_s = smem_u32(m.rings + (size_t)half * kDepth * kSlotBytes);
+        full_s = smem_u32(m.mbar + half * 2 * kDepth);
+        empty_s = full_s + kDepth * 8u;
+        dead = m.flags; error = error_;
     }
     __device__ __forceinline__ void load_phase(int w) {
         const DsPhase& d = desc[((w >> 2) & 1) * 4 + (w & 3)];
         const int rpt = d.swiglu ? 8 : 16;
         pnTiles = (d.N + rpt - 1) / rpt;
         pnPairs = ((d.K >> 5) + 1) >> 1;
-        // pairs hw, hw+8, …: warps below (pnPairs mod 8) own one more; a tile stores the warps' pairs one warp after the other
-        const int q = pnPairs >> 3, rem = pnPairs & 7;
-        npw = q + (hw < rem ? 1 : 0);
-        warpOff = (hw * q + min(hw, rem)) * kPairBytes;
+        pnItems = (pnPairs + kItemPairs - 1) / kItemPairs;
         tileBytes = (size_t)pnPairs * kPairBytes;
         base = d.packed;
     }
     __device__ __forceinline__ bool can_issue(DsRing& r) {
         while (true) {
             if (r.wp >= nWp) return false;
-            if (r.itile < pnTiles && r.ipi < npw) return true;
+            if (r.itile < pnTiles && r.ipi < pnItems) return true;
             if (((r.wp + 1) >> 2) > r.cl + 1) return false;       // descriptors exist for the consumer's block and the next one
             r.wp++;
             r.itile = vcta; r.ipi = 0;
             if (r.wp < nWp) load_phase(r.wp);
         }
     }
+    // only the producer warp (hw == 0) calls this; warp-uniform
     __device__ __forceinline__ void top_up(DsRing& r) {
         while (r.ahead < kDepth && can_issue(r)) {
-            const int pairs = min(kItemPairs, npw - r.ipi);
-#ifndef DS_EXP
-#define DS_EXP 0
-#endif
-            if (lane == 0 && DS_EXP != 1 && DS_EXP != 4 && DS_EXP != 5 && DS_EXP != 6) {
-                const uint32_t bar = mbar_s + (uint32_t)r.islot * 8u;
+            const uint32_t ebar = empty_s + (uint32_t)r.islot * 8u;
+            if ((r.used >> r.islot) & 1u) {
+                // the slot's previous content must have been released by all eight warps
+                const uint32_t eparity = (r.par >> (16 + r.islot)) & 1u;
+                bool ok = mbar_try_wait(ebar, eparity);
+                if (!ok) {
+                    if (r.ahead > 0) return;                 // this warp still has items to consume: come back later
+                    unsigned it = 0;
+                    while (!(ok = mbar_try_wait(ebar, eparity))) {
+                        if (*dead) break;
+                        if (++it > kSpinLimit) { atomicCAS(error, 0, 312); *dead = 1; break; }
+                    }
+                }
+                r.par ^= 1u << (16 + r.islot);
+            }
+            r.used |= 1u << r.islot;
+            const int pairs = min(kItemPairs, pnPairs - r.ipi * kItemPairs);
+            if (lane == 0) {
+                const uint32_t bar = full_s + (uint32_t)r.islot * 8u;
                 const uint32_t bytes = (uint32_t)pairs * kPairBytes;
                 mbar_arrive_expect_tx(bar, bytes);
-                bulk_g2s(ring_s + (uint32_t)r.islot * kSlotBytes, base + (size_t)r.itile * tileBytes + warpOff + (size_t)r.ipi * kPairBytes, bytes, bar);
+                bulk_g2s(ring_s + (uint32_t)r.islot * kSlotBytes, base + (size_t)r.itile * tileBytes + (size_t)r.ipi * kSlotBytes, bytes, bar);
             }
-            r.ipi += pairs;
-            if (r.ipi >= npw) { r.ipi = 0; r.itile += nV; }
+            r.ipi++;
+            if (r.ipi >= pnItems) { r.ipi = 0; r.itile += nV; }
             r.islot = r.islot + 1 == kDepth ? 0 : r.islot + 1;
             r.ahead++;
         }
@@ -278,10 +303,11 @@ struct DsProducer {
 };
 
 // Fill the rings as far as the descriptors allow (launch start).
-__device__ __noinline__ void ds_prefetch(const DsCtx c, DsRing& ring) {
+__device__ __noinline__ void ds_prefetch(const DsCtx c, DsRing& ring, int* error) {
     const DsSmem m = ds_layout(c.smem, c.kmax);
     DsProducer P;
-    P.init(m, c.nCtas, c.nWp);
+    P.init(m, c.nCtas, c.nWp, error);
+    if (P.hw != 0) return;
     DsRing r = ring;
     P.load_phase(r.wp);
     P.top_up(r);
@@ -355,21 +381,22 @@ __device__ __noinline__ void ds_gemv(const DsCtx c, const DsGemv a, DsRing& ring
     const DsSmem m = ds_layout(c.smem, c.kmax);
     const int8_t* xd = reinterpret_cast<const int8_t*>(m.act);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int half = warp >> 3, hw = warp & 7, htid = tid & 255;
+    const int half = warp >> 3, hw = warp & 7;
     const int g = lane >> 2, t = lane & 3;
     DsProducer P;
-    P.init(m, c.nCtas, c.nWp);
+    P.init(m, c.nCtas, c.nWp, error);
+    const bool producer = hw == 0;                                           // this warp also feeds the half's ring
     DsRing r = ring;
-    if (r.wp < a.cp) { r.wp = a.cp; r.itile = P.vcta; r.ipi = 0; }          // a warp without items in earlier phases catches up
+    if (r.wp < a.cp) { r.wp = a.cp; r.itile = P.vcta; r.ipi = 0; }          // a half without items in earlier phases catches up
     P.load_phase(r.wp);
-    const uint32_t myring = smem_u32(m.rings + (size_t)warp * kDepth * kSlotBytes);
+    const uint32_t myring = P.ring_s + (uint32_t)hw * kPairBytes;            // this warp's first pair inside a slot; its second lies 8 pairs on
     const DsPhase& d = m.desc[((a.cp >> 2) & 1) * 4 + (a.cp & 3)];
     const int K = d.K, N = d.N;
     const bool sw = d.swiglu != 0;
     const int rowsPerTile = sw ? 8 : 16;
     const int nTiles = (N + rowsPerTile - 1) / rowsPerTile;
     const int nBlocks = K >> 5, nPairs = (nBlocks + 1) >> 1;
-    const int myPairs = (nPairs >> 3) + (hw < (nPairs & 7) ? 1 : 0);          // pairs hw, hw+8, … of a tile
+    const int nItems = (nPairs + kItemPairs - 1) / kItemPairs;               // ring items of a tile; pairs hw, hw+8, … are this warp's
     const int ldxs = K + kXsPad;
     const uint32_t xsc = smem_u32(xd + (size_t)3 * ldxs);
     // lane (g,t) feeds MMA column g: digit g (g < 3) of the one activation row; columns 3..7 stay zero
@@ -380,45 +407,47 @@ __device__ __noinline__ void ds_gemv(const DsCtx c, const DsGemv a, DsRing& ring
 #pragma unroll
     for (int hh = 0; hh < 2; hh++) aoff[hh] = g * kRowStride + (hh ^ ((g >> 1) & 1)) * 32 + t * 8;
     const int soff = kRows * kRowStride + g * 8;
-    float* partBase = m.part + (size_t)half * 2 * kHalfWarps * 128;
-    int buf = 0;
+    float* partBase = m.part + (size_t)half * kPartBufs * kHalfWarps * kPartFloats;
+    volatile int* arrivals = m.flags + 40 + half * kPartBufs;
+    volatile int* reduced = m.flags + 48 + half * kPartBufs;
     int bestKey = r.bestKey, bestIdx = r.bestIdx;
     volatile int* dead = m.flags;
     for (int tile = P.vcta; tile < nTiles; tile += P.nV) {
-        const int er = htid, en = tile * rowsPerTile + er;          // htid < rowsPerTile: the thread that finishes output en
+        // epilogue operands of output row `lane` of the tile, in every warp: whichever arrives last finishes the tile
+        const int er = lane, en = tile * rowsPerTile + er;
         float ebias = 0.0f, ebias2 = 0.0f, eres = 0.0f;
         if (er < rowsPerTile && en < N) {
             if (a.bias) ebias = a.bias[en];
             if (sw && a.bias2) ebias2 = a.bias2[en];
             if (a.residual) eres = a.resNan ? NAN : __ldcg(a.residual + en);
         }
-        for (int j0 = 0; j0 < myPairs; j0 += kItemPairs) {
-            P.top_up(r);
+        for (int it_ = 0; it_ < nItems; it_++) {
+            if (producer) P.top_up(r);
+            const uint32_t fbar = P.full_s + (uint32_t)r.cslot * 8u;
             {
-                // the item's bytes have landed when its slot's mbarrier completes the phase armed for it (bounded wait)
-                const uint32_t bar = P.mbar_s + (uint32_t)r.cslot * 8u;
+                // the item's bytes have landed when its slot's full barrier completes the phase armed for it (bounded wait)
                 const uint32_t parity = (r.par >> r.cslot) & 1u;
-                if (lane == 0 && !mbar_try_wait(bar, parity) && !*dead) {          // one lane polls; the warp meets it below
+                if (!mbar_try_wait(fbar, parity) && !*dead) {
                     unsigned it = 0;
-                    while (!mbar_try_wait(bar, parity)) {
+                    while (!mbar_try_wait(fbar, parity)) {
                         if (++it > kSpinLimit) { atomicCAS(error, 0, 310); *dead = 1; break; }
                         if ((it & 0xfffu) == 0u && *dead) break;
                     }
                 }
-                __syncwarp();
                 r.par ^= 1u << r.cslot;
             }
             const uint32_t slot = myring + (uint32_t)r.cslot * kSlotBytes;
-            const int pairsHere = min(kItemPairs, myPairs - j0);
-            // all fragments of the item first (independent shared-memory loads), then the MMAs, then the fp32 folds
-            uint2 av[2 * kItemPairs], dd[2 * kItemPairs], xb[2 * kItemPairs];
-            float s0[2 * kItemPairs], s1[2 * kItemPairs], xs[2 * kItemPairs];
+            // this warp's pairs of the item: hw + 16·it_ and hw + 16·it_ + 8, where they exist
+            const int pi0 = it_ * kItemPairs + hw;
+            // all fragments first (independent shared-memory loads), then the MMAs, then the fp32 folds
+            uint2 av[2 * kWarpPairs], dd[2 * kWarpPairs], xb[2 * kWarpPairs];
+            float s0[2 * kWarpPairs], s1[2 * kWarpPairs], xs[2 * kWarpPairs];
 #pragma unroll
-            for (int q = 0; q < 2 * kItemPairs; q++) {
+            for (int q = 0; q < 2 * kWarpPairs; q++) {
                 const int pp = q >> 1, hh = q & 1;
-                const uint32_t ps = slot + pp * kPairBytes;
-                const int blk = (hw + kHalfWarps * (j0 + pp)) * 2 + hh;
-                const bool on = pp < pairsHere && blk < nBlocks;      // a short last item, or the empty half of an odd last pair
+                const uint32_t ps = slot + pp * (kHalfWarps * kPairBytes);
+                const int pi = pi0 + kHalfWarps * pp, blk = pi * 2 + hh;
+                const bool on = pi < nPairs && blk < nBlocks;      // a short last item, or the empty half of an odd last pair
                 av[q] = lds_u2(ps + aoff[hh]);
                 dd[q] = lds_u2(ps + aoff[hh] + 8 * kRowStride);
                 s0[q] = lds_f(ps + soff + hh * 4);
@@ -426,64 +455,93 @@ __device__ __noinline__ void ds_gemv(const DsCtx c, const DsGemv a, DsRing& ring
                 xb[q] = (hasCol && on) ? lds_u2(xcol + blk * 32) : make_uint2(0u, 0u);
                 xs[q] = on ? lds_f(xsc + blk * 4) : 0.0f;
             }
-#pragma unroll
-            for (int q = 0; q < 2 * kItemPairs; q++) {
-                int cc[4] = {0, 0, 0, 0};
-                mma_s8_16832(cc, av[q].x, dd[q].x, av[q].y, dd[q].y, xb[q].x, xb[q].y);
-                // a pair that is not there was not copied either: its slot bytes are stale, its activation scale is 0, and
-                // 0 · (finite stale scale · integer) adds +0 — but stale bytes could be NaN patterns, so the fold is skipped
-                if ((q >> 1) < pairsHere) {
-                    const float f0 = s0[q] * xs[q], f1 = s1[q] * xs[q];
-                    acc[0] = fmaf(f0, (float)cc[0], acc[0]);
-                    acc[1] = fmaf(f0, (float)cc[1], acc[1]);
-                    acc[2] = fmaf(f1, (float)cc[2], acc[2]);
-                    acc[3] = fmaf(f1, (float)cc[3], acc[3]);
-                }
-            }
-            __syncwarp();          // every lane has read the slot before lane 0 may aim the next copy at it
+            __syncwarp();          // every lane has its fragments: this warp releases the slot
+            if (lane == 0) mbar_arrive(P.empty_s + (uint32_t)r.cslot * 8u);
             r.cslot = r.cslot + 1 == kDepth ? 0 : r.cslot + 1;
             r.ahead--;
-        }
-        // tile epilogue: reduce the half's warps, recombine the digits
-        float* part = partBase + (size_t)buf * kHalfWarps * 128;
-        float* mine = part + hw * 128;
-        mine[g * 8 + 2 * t] = acc[0];       mine[g * 8 + 2 * t + 1] = acc[1];
-        mine[(g + 8) * 8 + 2 * t] = acc[2]; mine[(g + 8) * 8 + 2 * t + 1] = acc[3];
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
-        bar_sync(1 + half, 256);
-        if (er < rowsPerTile && en < N) {
-            float a2 = 0.0f, a1 = 0.0f, a0 = 0.0f, b2 = 0.0f, b1 = 0.0f, b0 = 0.0f;
 #pragma unroll
-            for (int q = 0; q < kHalfWarps; q++) {
-                const float* pr = part + q * 128 + er * 8;
-                a2 += pr[0]; a1 += pr[1]; a0 += pr[2];
-                if (sw) { b2 += pr[64]; b1 += pr[65]; b0 += pr[66]; }
-            }
-            float v = fmaf(a2, 65536.0f, fmaf(a1, 256.0f, a0));
-            if (a.mode == 1) {
-                float u = fmaf(b2, 65536.0f, fmaf(b1, 256.0f, b0));
-                if (a.bias) v += ebias;
-                if (a.bias2) u += ebias2;
-                const float sig = 1.0f / (1.0f + expf(-v));
-                a.out[en] = (v * sig) * u;                 // SiLU(gate) ⊙ up
-            } else if (a.mode == 3) {
-                // the partial sum travels with its exchange tag in one 8-byte word, to every rank (this one included)
-                const uint2 w = make_uint2(__float_as_uint(v), a.tag);
-#pragma unroll 1
-                for (int q = 0; q < c.world; q++) st_volatile_v2(m.peers[q] + a.wordBase + (size_t)c.rank * c.d + en, w);
-            } else {
-                if (a.bias) v += ebias;
-                if (a.residual) v += eres;
-                a.out[en] = v;
-                if (a.mode == 2) {
-                    const int k = order_key(v);
-                    if (k > bestKey || (k == bestKey && en < bestIdx)) { bestKey = k; bestIdx = en; }
+            for (int q = 0; q < 2 * kWarpPairs; q++) {
+                int cc[4] = {0, 0, 0, 0};
+                mma_s8_16832(cc, av[q].x, dd[q].x, av[q].y, dd[q].y, xb[q].x, xb[q].y);
+                // a pair that is not there was not copied either: its slot bytes are stale (possibly NaN patterns), so its fold is skipped
+                if (pi0 + kHalfWarps * (q >> 1) < nPairs) {
+                    const float f0 = s0[q] * xs[q], f1 = s1[q] * xs[q];
+                    // |block sum| ≤ 32·127·128 < 2^22: the integer drops exactly into the mantissa of 1.5·2^23 (one add instead of a convert)
+                    acc[0] = fmaf(f0, __int_as_float(0x4B400000 + cc[0]) - 12582912.0f, acc[0]);
+                    acc[1] = fmaf(f0, __int_as_float(0x4B400000 + cc[1]) - 12582912.0f, acc[1]);
+                    acc[2] = fmaf(f1, __int_as_float(0x4B400000 + cc[2]) - 12582912.0f, acc[2]);
+                    acc[3] = fmaf(f1, __int_as_float(0x4B400000 + cc[3]) - 12582912.0f, acc[3]);
                 }
             }
         }
-        buf ^= 1;
+        // ── tile epilogue without a barrier: every warp leaves its 16 × 3 digit sums and moves on; the warp that arrives
+        //    last adds the eight in warp order (deterministic) and finishes the outputs ──
+        const unsigned useNo = r.tileSeq / kPartBufs;
+        const int pbuf = (int)(r.tileSeq % kPartBufs);
+        r.tileSeq++;
+        if ((unsigned)reduced[pbuf] < useNo && !*dead) {          // the buffer's previous tile has not been reduced yet (a warp ran four tiles ahead)
+            unsigned it = 0;
+            while ((unsigned)reduced[pbuf] < useNo) {
+                if (++it > kSpinLimit) { atomicCAS(error, 0, 311); *dead = 1; break; }
+                if ((it & 0xfffu) == 0u && *dead) break;
+            }
+        }
+        float* part = partBase + (size_t)pbuf * kHalfWarps * kPartFloats;
+        float* mine = part + hw * kPartFloats;
+        if (t == 0) {
+            mine[g * 3] = acc[0]; mine[g * 3 + 1] = acc[1];
+            mine[(g + 8) * 3] = acc[2]; mine[(g + 8) * 3 + 1] = acc[3];
+        } else if (t == 1) {
+            mine[g * 3 + 2] = acc[0];
+            mine[(g + 8) * 3 + 2] = acc[2];
+        }
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+            __threadfence_block();
+            const int old = atomicAdd(const_cast<int*>(arrivals + pbuf), 1);
+            last = ((old + 1) % kHalfWarps) == 0;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            __threadfence_block();
+            if (er < rowsPerTile && en < N) {
+                float a2 = 0.0f, a1 = 0.0f, a0 = 0.0f, b2 = 0.0f, b1 = 0.0f, b0 = 0.0f;
+                const volatile float* vp = part;
+#pragma unroll
+                for (int q = 0; q < kHalfWarps; q++) {
+                    const volatile float* pr = vp + q * kPartFloats + er * 3;
+                    a2 += pr[0]; a1 += pr[1]; a0 += pr[2];
+                    if (sw) { b2 += pr[24]; b1 += pr[25]; b0 += pr[26]; }
+                }
+                float v = fmaf(a2, 65536.0f, fmaf(a1, 256.0f, a0));
+                if (a.mode == 1) {
+                    float u = fmaf(b2, 65536.0f, fmaf(b1, 256.0f, b0));
+                    if (a.bias) v += ebias;
+                    if (a.bias2) u += ebias2;
+                    const float sig = 1.0f / (1.0f + expf(-v));
+                    a.out[en] = (v * sig) * u;                 // SiLU(gate) ⊙ up
+                } else if (a.mode == 3) {
+                    // the partial sum travels with its exchange tag in one 8-byte word, to every rank (this one included)
+                    const uint2 w = make_uint2(__float_as_uint(v), a.tag);
+#pragma unroll 1
+                    for (int q = 0; q < c.world; q++) st_volatile_v2(m.peers[q] + a.wordBase + (size_t)c.rank * c.d + en, w);
+                } else {
+                    if (a.bias) v += ebias;
+                    if (a.residual) v += eres;
+                    a.out[en] = v;
+                    if (a.mode == 2) {
+                        const int k = order_key(v);
+                        if (k > bestKey || (k == bestKey && en < bestIdx)) { bestKey = k; bestIdx = en; }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) { __threadfence_block(); reduced[pbuf] = (int)useNo + 1; }
+        }
     }
-    P.top_up(r);          // whatever the next phases allow: these copies run through the barrier that follows
+    if (producer) P.top_up(r);          // whatever the next phases allow: these copies run through the barrier that follows
     r.bestKey = bestKey; r.bestIdx = bestIdx;
     ring = r;
 }
@@ -738,9 +796,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_decode_step(const DsParams p) {
     c.smem = smem; c.kmax = p.kmax; c.nCtas = nCtas; c.nWp = 4 * L + 1;      // weight phases: 4 per block, then the LM head
     c.rank = p.rank; c.world = p.world; c.d = p.d; c.eps = p.eps;
 
-    if (tid < 8) s_flags[tid] = 0;
+    if (tid < 64 && (tid < 8 || tid >= 40)) s_flags[tid] = 0;
     if (tid < kMaxWorld) m.peers[tid] = p.peers.words[tid];
-    if (tid < kWarps * kDepth) mbar_init(smem_u32(m.mbar + tid), 1);          // one arrival (the issuing lane's, with the byte count) per use
+    // full barriers: one arrival (the issuing lane's, with the byte count) per use; empty barriers: one arrival per warp of the half
+    if (tid < 2 * 2 * kDepth) mbar_init(smem_u32(m.mbar + tid), ((tid / kDepth) & 1) ? kHalfWarps : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     // token and position of this step (they change only at the very end of the launch)
     const int tokId = (int)__ldcg(p.tok);
@@ -779,9 +838,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_decode_step(const DsParams p) {
     __syncthreads();
 
     DsRing ring;
-    ring.wp = 0; ring.itile = 2 * blockIdx.x + (warp >> 3); ring.ipi = 0; ring.islot = 0; ring.ahead = 0; ring.cslot = 0; ring.cl = 0; ring.par = 0u;
+    ring.wp = 0; ring.itile = 2 * blockIdx.x + (warp >> 3); ring.ipi = 0; ring.islot = 0; ring.ahead = 0; ring.cslot = 0; ring.cl = 0; ring.par = 0u; ring.used = 0u; ring.tileSeq = 0u;
     ring.bestKey = INT_MIN; ring.bestIdx = INT_MAX;
-    ds_prefetch(c, ring);
+    ds_prefetch(c, ring, p.error);
 
     auto grid_barrier = [&](int code) { ds_grid_barrier(p.bar, p.error, s_flags, nCtas, code); };
     int stampAt = 0;
@@ -966,9 +1025,7 @@ __global__ void k_pack_phase(const int8_t* __restrict__ codes, const float* __re
     const int tile = blockIdx.y, pi = blockIdx.x, i = threadIdx.x;
     const bool sw = codes2 != nullptr;
     const int rpt = sw ? 8 : 16;
-    const int hw = pi & 7, j = pi >> 3;
-    const int q = nPairs >> 3, rem = nPairs & 7;
-    const size_t dstPair = (size_t)tile * nPairs * kPairBytes + (size_t)(hw * q + min(hw, rem) + j) * kPairBytes;
+    const size_t dstPair = ((size_t)tile * nPairs + pi) * kPairBytes;          // a tile's pairs in order: 16 consecutive ones are a ring item
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (i < 64) {
         const int r = i >> 2, c = i & 3;
@@ -1016,8 +1073,8 @@ std::unordered_map<int, Plan> g_plans;
 
 size_t ds_smem_bytes(int kmax) {
     const size_t act = std::max<size_t>((size_t)3 * (kmax + kXsPad) + (size_t)(kmax >> 5) * 4, (size_t)4 * kAttnScratchFloats * 4);
-    return (size_t)kWarps * kDepth * kSlotBytes + ((act + 127) & ~(size_t)127) + (size_t)2 * 2 * kHalfWarps * 128 * 4 + 8 * sizeof(DsPhase) +
-           2 * sizeof(DsLayer) + kWarps * 4 + 48 * 4 + kMaxWorld * sizeof(void*) + (size_t)kWarps * kDepth * 8;
+    return (size_t)2 * kDepth * kSlotBytes + ((act + 127) & ~(size_t)127) + (size_t)2 * kPartBufs * kHalfWarps * kPartFloats * 4 + 8 * sizeof(DsPhase) +
+           2 * sizeof(DsLayer) + kWarps * 4 + 64 * 4 + kMaxWorld * sizeof(void*) + (size_t)2 * 2 * kDepth * 8;
 }
 
 }  // namespace
