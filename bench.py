@@ -304,7 +304,8 @@ def main():
     ap.add_argument("--workload", default="llama7b_q8_decode_b1", choices=sorted(WORKLOADS))
     ap.add_argument("--prompt-len", type=int, default=0, help="override the prompt length (debugging)")
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of `steps` steps each; the median is reported")
-    ap.add_argument("--kv", default="f32", choices=["f32"], help="dtype of the K/V cache")
+    ap.add_argument("--kv", default="f32", choices=["f32", "f16"], help="dtype of the K/V cache of the headline run (fp32 = the reference's precision)")
+    ap.add_argument("--no-kv16", action="store_true", help="skip the fp16-K/V sub-record")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the reduced-depth check against the CPU oracle")
     ap.add_argument("--no-batch16", action="store_true", help="skip the 16-sequence sub-record of the 7B workload")
@@ -340,7 +341,8 @@ def main():
     slot = max((16 if batch16 else B) * cfg.d_model, (16 if batch16 else B) * cfg.vocab_size // world,
                min(B * min(w["prompt"], Q8Decoder.PREFILL_CHUNK), 2048) * cfg.d_model)
     dec = Q8Decoder(cfg, batch=B, device=local_rank, tp_rank=rank, tp_world=world, tp_slot_floats=slot if world > 1 else 0,
-                    fused_step=args.fused_step)
+                    fused_step=args.fused_step, kv_dtype=args.kv)
+    kv16 = not args.no_kv16 and args.kv == "f32" and not args.fused_step and args.prompt_len == 0
     if world > 1:
         # weights are split by rows/columns over the ranks; [rows x d] partial sums and the logits
         # shards cross NVLink through the library's own peer-memory exchange
@@ -350,10 +352,14 @@ def main():
     parity = None
     if not args.no_parity:
         sys.path.insert(0, os.path.join(ROOT, "tests"))
-        from parity_util import reduced_depth_parity
-        parity = reduced_depth_parity(w, layers=2, prompt_len=48, n_new=8, rank=rank, world=world, device=local_rank,
-                                      tp_slot_floats=slot if world > 1 else 0, check_codes=False, kv_dtype=args.kv,
-                                      fused_step=args.fused_step)
+        from parity_util import reduced_depth_parity_variants
+        variants = [dict(kv_dtype=args.kv, fused_step=args.fused_step)] + ([dict(kv_dtype="f16")] if kv16 else [])
+        checks = reduced_depth_parity_variants(w, variants, layers=2, prompt_len=48, n_new=8, rank=rank, world=world, device=local_rank,
+                                               tp_slot_floats=slot if world > 1 else 0, check_codes=False)
+        parity = checks[0]
+        parity16 = checks[1] if kv16 else None
+        if kv16 and not (parity16["tokens_equal"] and parity16["max_err_over_range"] <= parity16["tolerance"]):
+            kv16 = False          # the option does not pass its gate on this configuration: it is reported as failed, not timed
         if not (parity["tokens_equal"] and parity["max_err_over_range"] <= parity["tolerance"]):
             if rank == 0:
                 print(json.dumps({"metric": "q8_decode_tokens_per_s", "error": "parity check failed", "parity": parity}), flush=True)
@@ -410,7 +416,7 @@ def main():
         gemv_stream_ms = tp.max_over_ranks(gemv_stream_ms)
         attn_stream_ms = tp.max_over_ranks(attn_stream_ms)
     achieved = gemv_bytes / (gemv_stream_ms * 1e-3) / 1e9
-    kv_pos_bytes = cfg.kv_bytes_per_position()
+    kv_pos_bytes = cfg.kv_bytes_per_position(args.kv)
     step_bytes = cfg.q8_weight_bytes() + B * ctx * kv_pos_bytes                      # whole job, all ranks
     step_achieved = step_bytes / world / (ms_per_step * 1e-3) / 1e9                  # per GPU
     attn_bytes = B * ctx * kv_pos_bytes // world                                     # this rank's heads
@@ -459,6 +465,27 @@ def main():
     else:
         line["step_kernel"] = "one kernel per operator, CUDA-graph replay"
 
+    # ── the same step with the K/V cache in fp16 (an option behind the same parity gate; the headline stays at the reference's fp32) ──
+    if not args.no_parity and not args.no_kv16 and args.kv == "f32" and not args.fused_step and args.prompt_len == 0:
+        line["kv_f16"] = {"parity": parity16}
+    if kv16 and not args.no_parity:
+        d16 = Q8Decoder(cfg, batch=B, device=local_rank, id_base=6 << 24, tp_rank=rank, tp_world=world,
+                        tp_slot_floats=slot if world > 1 else 0, share_weights=dec, kv_dtype="f16")
+        if world > 1:
+            tp.barrier()
+        d16.reset()
+        nx = d16.prefill(prompts)
+        d16.set_tokens(nx)
+        mk = measure_decode(d16, w, args, world, local_rank, tp, max(1, min(args.repeats, 3)))
+        bk = cfg.q8_weight_bytes() + B * mk["ctx"] * cfg.kv_bytes_per_position("f16")
+        ak = bk / world / (mk["ms_per_step"] * 1e-3) / 1e9
+        line["kv_f16"].update({"value": mk["value"], "unit": "tokens/s", "ms_per_step": mk["ms_per_step"], "ms_per_step_regions": mk["ms_per_step_regions"],
+                               "e2e": {"value": mk["e2e"], "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+                               "roofline_step": {"bytes_per_token": bk, "achieved_per_gpu": ak, "frac": ak / peak,
+                                                 "roofline_tokens_per_s": B * world * peak * 1e9 / bk},
+                               "device_error": mk["dev_error"]})
+        d16.close()
+
     # ── the same model at 16 concurrent sequences (BASELINE configs[4] asks for 1 and 16), sharing the weights ──
     if batch16:
         w16 = dict(WORKLOADS["llama7b_q8_decode_b16"])
@@ -485,6 +512,24 @@ def main():
             "prefill": {"tokens": 16 * w16["prompt"], "seconds": t16},
         }
         dec16.close()
+        if kv16 and not args.no_parity:
+            # … and with the fp16 K/V cache (16 sequences read 16 caches per step: the K/V rows are most of the bytes)
+            dec16h = Q8Decoder(cfg, batch=16, device=local_rank, id_base=7 << 24, tp_rank=rank, tp_world=world,
+                               tp_slot_floats=slot if world > 1 else 0, share_weights=dec, kv_dtype="f16")
+            if world > 1:
+                tp.barrier()
+            dec16h.reset()
+            nxt16 = dec16h.prefill(p16)
+            dec16h.set_tokens(nxt16)
+            m16h = measure_decode(dec16h, w16, args, world, local_rank, tp, max(1, min(args.repeats, 3)))
+            b16h = cfg.q8_weight_bytes() + 16 * m16h["ctx"] * cfg.kv_bytes_per_position("f16")
+            a16h = b16h / world / (m16h["ms_per_step"] * 1e-3) / 1e9
+            line["batch16"]["kv_f16"] = {"value": m16h["value"], "unit": "tokens/s", "ms_per_step": m16h["ms_per_step"],
+                                         "e2e": {"value": m16h["e2e"], "unit": "tokens/s", "h2d_bytes_per_step": 64, "d2h_bytes_per_step": 64},
+                                         "roofline_step": {"bytes_per_step": b16h, "achieved_per_gpu": a16h, "frac": a16h / peak,
+                                                           "roofline_tokens_per_s": 16 * world * peak * 1e9 / b16h},
+                                         "device_error": m16h["dev_error"]}
+            dec16h.close()
 
     if not args.no_cpu_baseline and rank == 0:
         v, used, sample, _ = cpu_decode_sample(w, max(1, (os.cpu_count() or 2) - 1))

@@ -41,6 +41,7 @@ SIGNATURES = {
     "deepj_cuda_q8_download": (ctypes.c_int, [ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
     "deepj_cuda_synth_fill": (ctypes.c_int, [ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, ctypes.c_int64, ctypes.c_int64]),
     "deepj_cuda_kv_alloc": (ctypes.c_int, [ctypes.c_int32] * 6),
+    "deepj_cuda_kv_alloc_f16": (ctypes.c_int, [ctypes.c_int32] * 6),
     "deepj_cuda_tp_create": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p]),
     "deepj_cuda_decode_plan": (ctypes.c_int, [ctypes.c_int32, ctypes.c_void_p, ctypes.c_int32]),
     "deepj_cuda_tp_configure": (ctypes.c_int, [ctypes.c_int64]),

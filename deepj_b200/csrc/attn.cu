@@ -15,6 +15,7 @@
 // is needed.  HBM-bound: the algorithmic traffic is the K and V rows of 0..pos.
 #include "../../include/deepj_cuda.h"
 #include "kernels.h"
+#include "kv_cache.cuh"
 #include <cmath>
 #include <cstdlib>
 
@@ -30,8 +31,9 @@ constexpr int kMaxSplits = 256;             // split partials a head can have (t
 
 // Prompt chunk: row z = (sequence b, token t) of the projection buffer holds k and v of position pos[b] + t.
 // One thread per interleaved pair: rotate k (x0·c − x1·s, x0·s + x1·c — RotaryEmbedding.java:81-122), copy v.
-__global__ void k_kv_append(const float* __restrict__ qkv, int k_off, int v_off, int ld, float* __restrict__ kcache,
-                            float* __restrict__ vcache, int maxSeq, const float* __restrict__ posbuf,
+template <typename KT>
+__global__ void k_kv_append(const float* __restrict__ qkv, int k_off, int v_off, int ld, KT* __restrict__ kcache,
+                            KT* __restrict__ vcache, int maxSeq, const float* __restrict__ posbuf,
                             const float* __restrict__ cosT, const float* __restrict__ sinT, int H, int hd, int T) {
     pdl_wait();
     pdl_launch_dependents();
@@ -44,14 +46,14 @@ __global__ void k_kv_append(const float* __restrict__ qkv, int k_off, int v_off,
     const float2 v2 = *reinterpret_cast<const float2*>(row + v_off + h * hd + 2 * i);
     const float c = cosT[(size_t)p * (hd >> 1) + i], s = sinT[(size_t)p * (hd >> 1) + i];
     const size_t dst = (((size_t)b * H + h) * maxSeq + p) * hd + 2 * i;
-    *reinterpret_cast<float2*>(kcache + dst) = make_float2(k2.x * c - k2.y * s, k2.x * s + k2.y * c);
-    *reinterpret_cast<float2*>(vcache + dst) = v2;
+    KvIo<KT>::st2(kcache + dst, k2.x * c - k2.y * s, k2.x * s + k2.y * c);
+    KvIo<KT>::st2(vcache + dst, v2.x, v2.y);
 }
 
-template <int LPP>   // lanes per position = hd / 16
+template <int LPP, typename KT>   // lanes per position = hd / 16; cache element type
 __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
         const float* __restrict__ qkv, int q_off, int k_off, int v_off, int ld,
-        float* __restrict__ kcache, float* __restrict__ vcache, int maxSeq,
+        KT* __restrict__ kcache, KT* __restrict__ vcache, int maxSeq,
         const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
         float* __restrict__ ws, int* __restrict__ tickets, float* __restrict__ out, int ldo, int H, float scale,
         int T, int append) {
@@ -82,19 +84,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
     int chunk = (seq + splits - 1) / splits;
     int start = split * chunk;
     int end = min(seq, start + chunk);
-    float* kbase = kcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
-    float* vbase = vcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
+    KT* kbase = kcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
+    KT* vbase = vcache + ((size_t)b * H + h) * maxSeq * HD + gl * 16;
     float kf[16], vf[16], kn[16], vn[16];
     auto fetch_cached = [&](int p, bool valid, float (&kx)[16], float (&vx)[16]) {
         if (valid) {
-            const float4* kp = reinterpret_cast<const float4*>(kbase + (size_t)p * HD);
-            const float4* vp = reinterpret_cast<const float4*>(vbase + (size_t)p * HD);
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float4 a = __ldcs(kp + j), c = __ldcs(vp + j);
-                kx[4 * j] = a.x; kx[4 * j + 1] = a.y; kx[4 * j + 2] = a.z; kx[4 * j + 3] = a.w;
-                vx[4 * j] = c.x; vx[4 * j + 1] = c.y; vx[4 * j + 2] = c.z; vx[4 * j + 3] = c.w;
-            }
+            KvIo<KT>::ld16_stream(kbase + (size_t)p * HD, kx);
+            KvIo<KT>::ld16_stream(vbase + (size_t)p * HD, vx);
         } else {
 #pragma unroll
             for (int j = 0; j < 16; j++) { kx[j] = 0.0f; vx[j] = 0.0f; }
@@ -161,22 +157,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
             float ck[8], sk[8];              // fetched again here (a cache hit) rather than kept live through the loop
             load_tables(ck, sk);
             rotate(kf, ck, sk);
-            float4* kd = reinterpret_cast<float4*>(kbase + (size_t)p * HD);
-            float4* vd = reinterpret_cast<float4*>(vbase + (size_t)p * HD);
+            KvIo<KT>::st16(kbase + (size_t)p * HD, kf);
+            KvIo<KT>::st16(vbase + (size_t)p * HD, vf);
+            // this step attends to what later steps will read back (the rounded values of an fp16 cache)
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                kd[j] = make_float4(kf[4 * j], kf[4 * j + 1], kf[4 * j + 2], kf[4 * j + 3]);
-                vd[j] = make_float4(vf[4 * j], vf[4 * j + 1], vf[4 * j + 2], vf[4 * j + 3]);
-            }
+            for (int j = 0; j < 16; j++) { kf[j] = KvIo<KT>::stored(kf[j]); vf[j] = KvIo<KT>::stored(vf[j]); }
         } else if (valid) {
-            const float4* kp = reinterpret_cast<const float4*>(kbase + (size_t)p * HD);
-            const float4* vp = reinterpret_cast<const float4*>(vbase + (size_t)p * HD);
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float4 a = __ldcs(kp + j), c = __ldcs(vp + j);
-                kf[4 * j] = a.x; kf[4 * j + 1] = a.y; kf[4 * j + 2] = a.z; kf[4 * j + 3] = a.w;
-                vf[4 * j] = c.x; vf[4 * j + 1] = c.y; vf[4 * j + 2] = c.z; vf[4 * j + 3] = c.w;
-            }
+            KvIo<KT>::ld16_stream(kbase + (size_t)p * HD, kf);
+            KvIo<KT>::ld16_stream(vbase + (size_t)p * HD, vf);
         } else {
 #pragma unroll
             for (int j = 0; j < 16; j++) { kf[j] = 0.0f; vf[j] = 0.0f; }
@@ -303,9 +291,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
 // the 16 lanes of a row pair are contiguous, row reductions are half-warp shuffles.
 constexpr int kPQ = 32, kPK = 64;
 
-template <int HD>
+template <int HD, typename KT>
 __global__ void __launch_bounds__(256, 2) k_attn_prefill_tiled(
-        const float* __restrict__ qkv, int q_off, int ld, const float* __restrict__ kcache, const float* __restrict__ vcache,
+        const float* __restrict__ qkv, int q_off, int ld, const KT* __restrict__ kcache, const KT* __restrict__ vcache,
         int maxSeq, const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
         float* __restrict__ out, int ldo, int H, float scale, int T) {
     extern __shared__ __align__(16) float sm[];
@@ -336,8 +324,8 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tiled(
         Qs[r * HD + 2 * pr] = x0;
         Qs[r * HD + 2 * pr + 1] = x1;
     }
-    const float* kb = kcache + ((size_t)b * H + h) * maxSeq * HD;
-    const float* vb = vcache + ((size_t)b * H + h) * maxSeq * HD;
+    const KT* kb = kcache + ((size_t)b * H + h) * maxSeq * HD;
+    const KT* vb = vcache + ((size_t)b * H + h) * maxSeq * HD;
     const int lastKey = min(maxSeq - 1, pos0 + min(T, t0 + kPQ) - 1);       // newest key any row of this tile may see
     const int r0 = 2 * rg, r1 = 2 * rg + 1;
     const int lim0 = pos0 + t0 + r0, lim1 = pos0 + t0 + r1;                  // row r attends to keys ≤ lim
@@ -353,8 +341,8 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tiled(
             const int key = i / (HD / 4), d4 = i % (HD / 4);
             float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
             if (k0 + key <= lastKey) {
-                kv = __ldg(reinterpret_cast<const float4*>(kb + (size_t)(k0 + key) * HD) + d4);
-                vv = __ldg(reinterpret_cast<const float4*>(vb + (size_t)(k0 + key) * HD) + d4);
+                kv = KvIo<KT>::ld4(kb + (size_t)(k0 + key) * HD + 4 * d4);
+                vv = KvIo<KT>::ld4(vb + (size_t)(k0 + key) * HD + 4 * d4);
             }
             *reinterpret_cast<float4*>(Ks + key * HD + 4 * (d4 ^ ((key >> 2) & 7))) = kv;
             *reinterpret_cast<float4*>(Vs + key * HD + 4 * d4) = vv;
@@ -440,7 +428,10 @@ size_t attn_decode_ws_floats(int B, int H, int hd, int splits) {
     return (size_t)B * H * splits * (hd + 2);
 }
 
-void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s) {
+namespace {
+
+template <typename KT>
+void launch_attn_decode_t(const AttnDecodeArgs& a, cudaStream_t s) {
     int lpp = a.hd / 16;
     if (a.hd % 16 != 0 || (lpp != 1 && lpp != 2 && lpp != 4 && lpp != 8 && lpp != 16 && lpp != 32))
         throw std::runtime_error("attention: head dim " + std::to_string(a.hd) + " is not one of 16,32,64,128,256,512");
@@ -449,10 +440,12 @@ void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s) {
     if (rows > 65535) throw std::runtime_error("attention: more than 65535 rows in one launch");
     dim3 grid(a.splits, a.H, (unsigned)rows), block(kAttnWarps * 32);
     if (a.splits > 1 && rows * a.H > kAttnTickets / 2) throw std::runtime_error("attention: rows × heads exceeds " + std::to_string(kAttnTickets / 2));
+    KT* kc = static_cast<KT*>(a.kcache);
+    KT* vc = static_cast<KT*>(a.vcache);
     if (T > 1) {
         // the chunk's keys (rotated) and values go into the cache first; the attention kernel then only reads
         dim3 ag(a.H, (unsigned)rows);
-        launch_k(k_kv_append, ag, dim3(a.hd / 2), 0, s, true, (const float*)a.qkv, a.k_off, a.v_off, a.ld, a.kcache, a.vcache, a.maxSeq,
+        launch_k(k_kv_append<KT>, ag, dim3(a.hd / 2), 0, s, true, (const float*)a.qkv, a.k_off, a.v_off, a.ld, kc, vc, a.maxSeq,
                  a.pos, a.cosT, a.sinT, a.H, a.hd, T);
     }
     static const bool noTiled = getenv("DEEPJ_CUDA_NO_TILED_PREFILL") != nullptr;
@@ -462,26 +455,33 @@ void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s) {
         dim3 tg((T + kPQ - 1) / kPQ, a.H, a.B);
         if (a.hd == 128) {
             static bool attr = false;
-            if (!attr) { DJ_CUDA_CHECK(cudaFuncSetAttribute(k_attn_prefill_tiled<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_tiled_smem<128>())); attr = true; }
-            launch_k(k_attn_prefill_tiled<128>, tg, dim3(256), prefill_tiled_smem<128>(), s, true, (const float*)a.qkv, a.q_off, a.ld,
-                     (const float*)a.kcache, (const float*)a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.out, a.ldo, a.H, a.scale, T);
+            if (!attr) { DJ_CUDA_CHECK(cudaFuncSetAttribute(k_attn_prefill_tiled<128, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_tiled_smem<128>())); attr = true; }
+            launch_k(k_attn_prefill_tiled<128, KT>, tg, dim3(256), prefill_tiled_smem<128>(), s, true, (const float*)a.qkv, a.q_off, a.ld,
+                     (const KT*)kc, (const KT*)vc, a.maxSeq, a.pos, a.cosT, a.sinT, a.out, a.ldo, a.H, a.scale, T);
         } else {
             static bool attr = false;
-            if (!attr) { DJ_CUDA_CHECK(cudaFuncSetAttribute(k_attn_prefill_tiled<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_tiled_smem<64>())); attr = true; }
-            launch_k(k_attn_prefill_tiled<64>, tg, dim3(256), prefill_tiled_smem<64>(), s, true, (const float*)a.qkv, a.q_off, a.ld,
-                     (const float*)a.kcache, (const float*)a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.out, a.ldo, a.H, a.scale, T);
+            if (!attr) { DJ_CUDA_CHECK(cudaFuncSetAttribute(k_attn_prefill_tiled<64, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_tiled_smem<64>())); attr = true; }
+            launch_k(k_attn_prefill_tiled<64, KT>, tg, dim3(256), prefill_tiled_smem<64>(), s, true, (const float*)a.qkv, a.q_off, a.ld,
+                     (const KT*)kc, (const KT*)vc, a.maxSeq, a.pos, a.cosT, a.sinT, a.out, a.ldo, a.H, a.scale, T);
         }
         return;
     }
     const int append = T == 1 ? 1 : 0;
     int* tickets = a.tickets;
 #define DJ_ATTN_CASE(L)                                                                                              \
-    case L: launch_k(k_attn_decode<L>, grid, block, 0, s, true, (const float*)a.qkv, a.q_off, a.k_off, a.v_off, a.ld, \
-                     a.kcache, a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.ws, tickets, a.out, a.ldo, a.H, a.scale, T, append); break;
+    case L: launch_k(k_attn_decode<L, KT>, grid, block, 0, s, true, (const float*)a.qkv, a.q_off, a.k_off, a.v_off, a.ld, \
+                     kc, vc, a.maxSeq, a.pos, a.cosT, a.sinT, a.ws, tickets, a.out, a.ldo, a.H, a.scale, T, append); break;
     switch (lpp) {
         DJ_ATTN_CASE(1) DJ_ATTN_CASE(2) DJ_ATTN_CASE(4) DJ_ATTN_CASE(8) DJ_ATTN_CASE(16) DJ_ATTN_CASE(32)
     }
 #undef DJ_ATTN_CASE
+}
+
+}  // namespace
+
+void launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t s) {
+    if (a.kvHalf) launch_attn_decode_t<__half>(a, s);
+    else launch_attn_decode_t<float>(a, s);
 }
 
 }  // namespace dj
@@ -550,9 +550,11 @@ extern "C" int deepj_cuda_attn_decode_static(int32_t qkv, int32_t q_off, int32_t
         DJ_CUDA_CHECK(cudaMemsetAsync(tickets, 0, (size_t)B * H * sizeof(int), stream));
         AttnDecodeArgs a = {};
         a.qkv = bq.ptr; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.ld = ld;
+        const size_t esz = kvb.half ? 2 : 4;
         const size_t plane = (size_t)kvb.layers * kvb.B * kvb.H * kvb.maxSeq * kvb.hd;
         const size_t layerOff = (size_t)layer * kvb.B * kvb.H * kvb.maxSeq * kvb.hd;
-        a.kcache = kvb.ptr + layerOff; a.vcache = kvb.ptr + plane + layerOff; a.maxSeq = kvb.maxSeq;
+        a.kcache = static_cast<char*>(kvb.ptr) + layerOff * esz; a.vcache = static_cast<char*>(kvb.ptr) + (plane + layerOff) * esz;
+        a.maxSeq = kvb.maxSeq; a.kvHalf = kvb.half;
         a.pos = bp.ptr; a.cosT = bc.ptr; a.sinT = bs.ptr;
         a.out = bo.ptr + out_off; a.ldo = ldo; a.B = B; a.H = H; a.hd = hd;
         a.scale = (float)(1.0 / std::sqrt((double)hd));

@@ -21,6 +21,7 @@
 // applyAttentionToValues (layers/transformer/attention/HeadOps.java:90-140, activations/Softmax.java:16-19);
 // masked terms contribute exactly 0, as exp(−1e9 − max) does in fp32.
 #include "kernels.h"
+#include "kv_cache.cuh"
 #include "q8_common.cuh"
 #include <cuda_fp16.h>
 
@@ -51,9 +52,9 @@ __device__ __forceinline__ void split2(float x0, float x1, uint32_t& hi, uint32_
     lo = pack_h2(__float2half_rn(x0 - __half2float(h0)), __float2half_rn(x1 - __half2float(h1)));
 }
 
-template <int HD>
+template <int HD, typename KT>
 __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
-        const float* __restrict__ qkv, int q_off, int ld, const float* __restrict__ kcache, const float* __restrict__ vcache,
+        const float* __restrict__ qkv, int q_off, int ld, const KT* __restrict__ kcache, const KT* __restrict__ vcache,
         int maxSeq, const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
         float* __restrict__ out, int ldo, int H, float scale, int T) {
     constexpr int LDS = HD + 8;                     // halves per shared-memory row
@@ -91,8 +92,8 @@ __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
         *reinterpret_cast<uint32_t*>(Qh + r * LDS + 2 * pr) = hi;
         *reinterpret_cast<uint32_t*>(Ql + r * LDS + 2 * pr) = lo;
     }
-    const float* kb = kcache + ((size_t)b * H + h) * maxSeq * HD;
-    const float* vb = vcache + ((size_t)b * H + h) * maxSeq * HD;
+    const KT* kb = kcache + ((size_t)b * H + h) * maxSeq * HD;
+    const KT* vb = vcache + ((size_t)b * H + h) * maxSeq * HD;
     const int lastKey = min(maxSeq - 1, pos0 + min(T, t0 + kMQ) - 1);       // newest key any row of this tile may see
     const int row0 = warp * 16 + g, row1 = row0 + 8;                         // this lane's two query rows within the tile
     const int lim0 = pos0 + t0 + row0, lim1 = pos0 + t0 + row1;              // row r attends to keys ≤ lim
@@ -112,13 +113,13 @@ __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
     // A thread's share of one 32-key tile of K (or of V): kPer float4 pieces, piece u = tid + 128·u.
     constexpr int kPer = kMK * (HD / 4) / 128;
     float4 pre[kPer];
-    auto fetch = [&](const float* base, int k0) {
+    auto fetch = [&](const KT* base, int k0) {
 #pragma unroll
         for (int u = 0; u < kPer; u++) {
             const int i = tid + u * 128;
             const int key = i / (HD / 4), d4 = i % (HD / 4);
             pre[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (k0 + key <= lastKey) pre[u] = __ldg(reinterpret_cast<const float4*>(base + (size_t)(k0 + key) * HD) + d4);
+            if (k0 + key <= lastKey) pre[u] = KvIo<KT>::ld4(base + (size_t)(k0 + key) * HD + 4 * d4);
         }
     };
     auto put = [&](__half* hiT, __half* loT) {      // split what `fetch` brought and lay it down as fp16 [key][dim]
@@ -250,16 +251,16 @@ __global__ void __launch_bounds__(128, 2) k_attn_prefill_mma(
 
 template <int HD> constexpr size_t prefill_mma_smem() { return (size_t)(2 * kMQ + 2 * 4 * kMK) * (HD + 8) * sizeof(__half); }
 
-template <int HD>
+template <int HD, typename KT>
 void launch_mma(const AttnDecodeArgs& a, int T, cudaStream_t s) {
     static bool attr = false;
     if (!attr) {
-        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_attn_prefill_mma<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_mma_smem<HD>()));
+        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_attn_prefill_mma<HD, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_mma_smem<HD>()));
         attr = true;
     }
     dim3 grid((T + kMQ - 1) / kMQ, a.H, a.B);
-    launch_k(k_attn_prefill_mma<HD>, grid, dim3(128), prefill_mma_smem<HD>(), s, true, (const float*)a.qkv, a.q_off, a.ld,
-             (const float*)a.kcache, (const float*)a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.out, a.ldo, a.H, a.scale, T);
+    launch_k(k_attn_prefill_mma<HD, KT>, grid, dim3(128), prefill_mma_smem<HD>(), s, true, (const float*)a.qkv, a.q_off, a.ld,
+             (const KT*)a.kcache, (const KT*)a.vcache, a.maxSeq, a.pos, a.cosT, a.sinT, a.out, a.ldo, a.H, a.scale, T);
 }
 
 }  // namespace
@@ -269,9 +270,10 @@ void launch_mma(const AttnDecodeArgs& a, int T, cudaStream_t s) {
 bool launch_attn_prefill_mma(const AttnDecodeArgs& a, cudaStream_t s) {
     const int T = a.T < 1 ? 1 : a.T;
     if (a.ldo % 2 != 0 || (reinterpret_cast<uintptr_t>(a.out) & 7) != 0) return false;      // float2 stores
-    if (a.hd == 128) { launch_mma<128>(a, T, s); return true; }
-    if (a.hd == 64) { launch_mma<64>(a, T, s); return true; }
-    return false;
+    if (a.hd != 128 && a.hd != 64) return false;
+    if (a.kvHalf) { if (a.hd == 128) launch_mma<128, __half>(a, T, s); else launch_mma<64, __half>(a, T, s); }
+    else { if (a.hd == 128) launch_mma<128, float>(a, T, s); else launch_mma<64, float>(a, T, s); }
+    return true;
 }
 
 }  // namespace dj

@@ -1171,6 +1171,7 @@ extern "C" int deepj_cuda_decode_plan(int32_t plan_id, const int32_t* desc, int3
         if (!pool_kv(desc[10], &kv)) throw std::runtime_error("decode_plan: missing KV cache");
         pl.refs.push_back({desc[10], pool_serial(desc[10])});
         if (kv.layers < L || kv.H != H || kv.hd != hd || kv.B < 1) throw std::runtime_error("decode_plan: the KV cache does not match the model");
+        if (kv.half) throw std::runtime_error("decode_plan: the whole-token kernel reads an fp32 KV cache");
         P.maxSeq = kv.maxSeq;
         P.tok = f32(desc[5], 1, "token"); P.pos = f32(desc[6], 1, "position");
         PoolF32 emb;
@@ -1202,7 +1203,7 @@ extern "C" int deepj_cuda_decode_plan(int32_t plan_id, const int32_t* desc, int3
             y.bd = f32(e[9], d, "down bias");
             srcs.push_back({wqkv, {}, false}); srcs.push_back({wo, {}, false}); srcs.push_back({wg, wu, true}); srcs.push_back({wd, {}, false});
             const size_t layerOff = (size_t)l * kv.B * kv.H * kv.maxSeq * kv.hd;
-            y.kcache = kv.ptr + layerOff; y.vcache = kv.ptr + plane + layerOff;
+            y.kcache = static_cast<float*>(kv.ptr) + layerOff; y.vcache = static_cast<float*>(kv.ptr) + plane + layerOff;
         }
         srcs.push_back({lm, {}, false});
         if (L > 0 && F < 32) throw std::runtime_error("decode_plan: dFF must be at least 32");

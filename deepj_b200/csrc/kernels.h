@@ -98,7 +98,7 @@ constexpr int kTcMinRows = 17;            // from this many activation rows on, 
 // ── decode attention ──
 struct AttnDecodeArgs {
     float* qkv; int q_off, k_off, v_off, ld;   // current token's projections, one row per sequence
-    float* kcache; float* vcache;              // this layer's planes [B][H][maxSeq][hd]
+    void* kcache; void* vcache;                // this layer's planes [B][H][maxSeq][hd], fp32 or (kvHalf) fp16
     int maxSeq;
     const float* pos;                          // [B] floats holding the write position
     const float* cosT; const float* sinT;      // [maxSeq × hd/2]
@@ -107,6 +107,7 @@ struct AttnDecodeArgs {
     float scale;
     float* ws;                                 // split partials: [B][H][splits][hd + 2]
     int* tickets;                              // [B·H] zero-initialised, self-resetting counters
+    int kvHalf = 0;                            // 1: the cache holds fp16 (keys rounded after the rotation, values rounded; fp32 arithmetic)
     int T = 1;                                 // tokens per sequence in this call: 1 = decode step, > 1 = prompt chunk (rows b·T + t)
     int splits;
 };
@@ -140,7 +141,7 @@ void launch_tp_exchange(const float* in, const float* bias, const float* residua
 
 // Read-only views of the runtime's buffer pool for entry points that live beside their kernels.
 struct PoolF32 { float* ptr; size_t floats; };
-struct PoolKV { float* ptr; int layers, B, H, maxSeq, hd; };
+struct PoolKV { void* ptr; int layers, B, H, maxSeq, hd, half; };
 bool pool_f32(int id, PoolF32* out);
 bool pool_kv(int id, PoolKV* out);
 bool pool_q8(int id, Q8View* out);

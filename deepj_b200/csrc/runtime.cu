@@ -33,7 +33,7 @@ struct Buf {
     size_t bytes = 0;
     size_t floats = 0;                 // kF32
     int K = 0, N = 0, Kp = 0, nb = 0;  // kQ8
-    int layers = 0, B = 0, H = 0, maxSeq = 0, hd = 0;   // kKV
+    int layers = 0, B = 0, H = 0, maxSeq = 0, hd = 0, kvHalf = 0;   // kKV (kvHalf: fp16 elements)
     unsigned long long serial = 0;
 };
 
@@ -372,8 +372,9 @@ void do_op(Ctx& ctx, const int32_t* c) {
             a.qkv = f32(ctx, c[1], sz(rows - 1, ld) + maxOff + d, "attnDecode"); a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.ld = ld;
             size_t plane = (size_t)kv.layers * kv.B * kv.H * kv.maxSeq * kv.hd;
             size_t layerOff = (size_t)layer * kv.B * kv.H * kv.maxSeq * kv.hd;
-            a.kcache = (float*)kv.ptr + layerOff; a.vcache = (float*)kv.ptr + plane + layerOff;
-            a.maxSeq = kv.maxSeq;
+            const size_t esz = kv.kvHalf ? 2 : 4;
+            a.kcache = (char*)kv.ptr + layerOff * esz; a.vcache = (char*)kv.ptr + (plane + layerOff) * esz;
+            a.maxSeq = kv.maxSeq; a.kvHalf = kv.kvHalf;
             a.pos = f32(ctx, c[8], B, "attnDecode");
             a.cosT = f32(ctx, c[9], sz(kv.maxSeq, hd / 2), "attnDecode"); a.sinT = f32(ctx, c[10], sz(kv.maxSeq, hd / 2), "attnDecode");
             a.out = f32(ctx, c[11], (size_t)out_off + sz(rows - 1, ldo) + d, "attnDecode") + out_off; a.ldo = ldo;
@@ -586,7 +587,7 @@ bool pool_kv(int id, PoolKV* out) {
     auto it = R.pool.find(id);
     if (it == R.pool.end() || it->second.kind != kKV || it->second.ptr == nullptr) return false;
     const Buf& b = it->second;
-    out->ptr = (float*)b.ptr; out->layers = b.layers; out->B = b.B; out->H = b.H; out->maxSeq = b.maxSeq; out->hd = b.hd;
+    out->ptr = b.ptr; out->layers = b.layers; out->B = b.B; out->H = b.H; out->maxSeq = b.maxSeq; out->hd = b.hd; out->half = b.kvHalf;
     return true;
 }
 void invalidate_graphs() { R.epoch++; drop_graphs(); }
@@ -827,19 +828,28 @@ int deepj_cuda_synth_fill(int32_t id, uint64_t seed, uint64_t ordinal, float std
     DJ_CATCH
 }
 
-int deepj_cuda_kv_alloc(int32_t id, int32_t layers, int32_t batch, int32_t heads, int32_t max_seq, int32_t head_dim) {
+static int kv_alloc_impl(int32_t id, int32_t layers, int32_t batch, int32_t heads, int32_t max_seq, int32_t head_dim, int half) {
     DJ_TRY
     ensure_init();
     if (layers <= 0 || batch <= 0 || heads <= 0 || max_seq <= 0 || head_dim <= 0) throw std::runtime_error("kv_alloc: dimensions must be positive");
     if (R.pool.count(id)) throw std::runtime_error("kv_alloc: id " + std::to_string(id) + " already exists");
     Buf b; b.kind = kKV; b.layers = layers; b.B = batch; b.H = heads; b.maxSeq = max_seq; b.hd = head_dim;
     size_t plane = (size_t)layers * batch * heads * max_seq * head_dim;
-    b.bytes = plane * 2 * 4;
+    b.kvHalf = half;
+    if (half && head_dim % 16 != 0) throw std::runtime_error("kv_alloc: an fp16 cache needs a head dim that is a multiple of 16");
+    b.bytes = plane * 2 * (half ? 2 : 4);
     DJ_CUDA_CHECK(cudaMalloc(&b.ptr, b.bytes));
     DJ_CUDA_CHECK(cudaMemsetAsync(b.ptr, 0, b.bytes, R.stream));
     b.serial = R.next_serial++;
     R.pool[id] = b;
     DJ_CATCH
+}
+
+int deepj_cuda_kv_alloc(int32_t id, int32_t layers, int32_t batch, int32_t heads, int32_t max_seq, int32_t head_dim) {
+    return kv_alloc_impl(id, layers, batch, heads, max_seq, head_dim, 0);
+}
+int deepj_cuda_kv_alloc_f16(int32_t id, int32_t layers, int32_t batch, int32_t heads, int32_t max_seq, int32_t head_dim) {
+    return kv_alloc_impl(id, layers, batch, heads, max_seq, head_dim, 1);
 }
 
 }  // extern "C"

@@ -87,9 +87,9 @@ class DecoderConfig:
         per_layer = sum(q8(k, n) for _, k, n in self.matmul_shapes())
         return per_layer * self.n_layers + q8(self.d_model, self.vocab_size)
 
-    def kv_bytes_per_position(self) -> int:
-        """fp32 K and V rows of one cached position, all layers."""
-        return 2 * self.n_layers * self.d_model * 4
+    def kv_bytes_per_position(self, kv_dtype: str = "f32") -> int:
+        """K and V rows of one cached position, all layers (fp32, or fp16 with kv_dtype "f16")."""
+        return 2 * self.n_layers * self.d_model * (2 if kv_dtype == "f16" else 4)
 
 
 def rope_tables(head_dim: int, max_seq: int):
@@ -144,16 +144,23 @@ class Q8Decoder:
 
     def __init__(self, cfg: DecoderConfig, batch: int = 1, device: int = 0, id_base: int = 1 << 24,
                  tp_rank: int = 0, tp_world: int = 1, tp_slot_floats: int = 0, share_weights: Optional["Q8Decoder"] = None,
-                 fused_step: Optional[bool] = None):
+                 fused_step: Optional[bool] = None, kv_dtype: str = "f32"):
         """`tp_slot_floats`: the slot size the exchange buffer was (or will be) connected with (`tp.connect`); it
         bounds the rows a tensor-parallel prompt chunk may have (rows × dModel floats per exchange).
         `share_weights`: another decoder of the same configuration and sharding whose device weights this one reads
         (its own activations and KV cache, a different `id_base`); the other decoder must outlive this one.
         `fused_step`: run a token step as ONE persistent kernel (op 76) instead of one kernel per operator; the model must
         qualify (a Llama-shaped model, one sequence, every reduction length a multiple of 32, head dim 32 / 64 / 128).
-        Under tensor parallelism the plan is made at the first step, after `tp.connect`."""
+        Under tensor parallelism the plan is made at the first step, after `tp.connect`.
+        `kv_dtype`: "f32" (the reference's precision) or "f16" — keys rounded after the rotation, values rounded, fp32
+        arithmetic; half the bytes a step's attention reads."""
         self.cfg = cfg
         self.B = int(batch)
+        if kv_dtype not in ("f32", "f16"):
+            raise ValueError("kv_dtype must be 'f32' or 'f16'")
+        if kv_dtype == "f16" and (fused_step or cfg.head_dim % 16 != 0):
+            raise ValueError("an fp16 KV cache needs a head dim that is a multiple of 16 and the per-operator step")
+        self.kv_dtype = kv_dtype
         self.tp_slot_floats = int(tp_slot_floats)
         if tp_world < 1 or not (0 <= tp_rank < tp_world):
             raise ValueError("bad tensor-parallel rank / world size")
@@ -267,7 +274,8 @@ class Q8Decoder:
         if c.kind == "deepseek":
             self._f32("lat", B * (c.q_rank + c.kv_rank))
         kv = self._new_id()
-        _lib.check(self.lib.deepj_cuda_kv_alloc(kv, c.n_layers, B, self.h_local, c.max_seq_len, c.head_dim))
+        alloc = self.lib.deepj_cuda_kv_alloc_f16 if self.kv_dtype == "f16" else self.lib.deepj_cuda_kv_alloc
+        _lib.check(alloc(kv, c.n_layers, B, self.h_local, c.max_seq_len, c.head_dim))
         self.ids["kv"] = kv
 
     # ── weights ──

@@ -111,6 +111,13 @@ int deepj_cuda_synth_fill(int32_t id, uint64_t seed, uint64_t ordinal, float std
  * floats, zero-filled. */
 int deepj_cuda_kv_alloc(int32_t kv_id, int32_t layers, int32_t batch, int32_t heads,
                         int32_t max_seq, int32_t head_dim);
+/* The same object with fp16 elements (half the bytes a token's attention reads).  Keys are rotated in fp32 and
+ * rounded to nearest-even when appended, values are rounded when appended; scores, softmax and the weighted sum
+ * stay fp32.  The reference keeps everything in fp32 (tensor/cpu/CpuBackend.java), so this is an option that has to
+ * pass the same logit and token gates against the oracle; head_dim must be a multiple of 16.  Ops 67 and 73 and
+ * deepj_cuda_attn_decode_static take either kind; decode plans (op 76) take the fp32 kind only. */
+int deepj_cuda_kv_alloc_f16(int32_t kv_id, int32_t layers, int32_t batch, int32_t heads,
+                            int32_t max_seq, int32_t head_dim);
 
 /* Decode plan: everything one batch-1 token step of a Llama-shaped Q8 model touches, resolved once, for op 76
  * (DECODE_STEP), which runs the whole step — embedding row, every block, final norm, LM head, greedy pick, position

@@ -7,13 +7,14 @@ the CPU side to seconds; the sampled columns see every kernel the dispatcher pic
 
 C3 / C4 / C5 (Llama-1B, DeepSeek and Llama-7B shapes) at reduced depth: 2 blocks, full width, synthetic weights
 that the oracle generates bit-identically; a 48-token prompt through the chunked prefill path, then 8 greedy
-decode steps; Q8 codes bit-exact on one block, logits within 2e-3 of the logit range, identical tokens."""
+decode steps; Q8 codes bit-exact on one block, logits within 2e-3 of the logit range, identical tokens — for the
+fp32 and the fp16 K/V cache, and (Llama shapes) for the whole-token kernel."""
 import numpy as np
 import pytest
 
 import oracle
 from deepj_b200.compute_graph import OP_Q8_LINEAR
-from parity_util import LOGIT_TOL, reduced_depth_parity
+from parity_util import LOGIT_TOL, reduced_depth_parity_variants
 from test_q8_gpu import Dev, close
 
 pytestmark = pytest.mark.gpu
@@ -65,6 +66,10 @@ def test_operator_sweep_shapes_match_oracle(dev, sweep_weights, M, N):
 
 @pytest.mark.parametrize("name", ["llama1b", "deepseek", "llama7b"])
 def test_reduced_depth_baseline_config_matches_oracle(name):
-    res = reduced_depth_parity(BASELINE_SHAPES[name], layers=2, prompt_len=48, n_new=8)
-    assert res["tokens_equal"], res
-    assert res["max_err_over_range"] <= LOGIT_TOL, res
+    # the per-operator step with the fp32 and the fp16 K/V cache; Llama shapes also as the single whole-token kernel
+    variants = [dict(kv_dtype="f32"), dict(kv_dtype="f16")]
+    if BASELINE_SHAPES[name]["kind"] == "llama":
+        variants.append(dict(kv_dtype="f32", fused_step=True))
+    for res in reduced_depth_parity_variants(BASELINE_SHAPES[name], variants, layers=2, prompt_len=48, n_new=8):
+        assert res["tokens_equal"], res
+        assert res["max_err_over_range"] <= LOGIT_TOL, res

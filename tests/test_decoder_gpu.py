@@ -39,10 +39,10 @@ def check_q8_bit_exact(dec, om, cfg, layer):
             col += n
 
 
-def run_parity(cfg, seed, prompt, n_new, std=0.1):
+def run_parity(cfg, seed, prompt, n_new, std=0.1, kv_dtype="f32"):
     om = oracle.OracleModel(cfg.kind, cfg.vocab_size, cfg.max_seq_len, cfg.d_model, cfg.n_heads, cfg.n_layers,
                             cfg.d_ff, cfg.q_rank, cfg.kv_rank, seed=seed, init_mode=0, std=std)
-    dec = Q8Decoder(cfg, batch=1)
+    dec = Q8Decoder(cfg, batch=1, kv_dtype=kv_dtype)
     try:
         dec.load_weights(weight_getter(om, cfg))
         check_q8_bit_exact(dec, om, cfg, 0)
@@ -71,6 +71,20 @@ def test_tiny_llama_greedy_matches_oracle():
     r = oracle.JRandom(7)
     prompt = [r.next_int(256) for _ in range(32)]
     run_parity(cfg, 42, prompt, 64)
+
+
+def test_fp16_kv_cache_passes_the_same_gates():
+    """The fp16 K/V cache option (keys rounded after the rotation, values rounded, fp32 arithmetic) against the fp32
+    oracle: logits within 2e-3 of the logit range and the same greedy tokens — on the tiny reference configuration
+    (head dim 32, short prompt: one decode step per position), on head dim 128, and behind a chunked prompt pass (head
+    dim 64, the tensor-core chunk attention reading the fp16 cache)."""
+    r = oracle.JRandom(7)
+    prompt = [r.next_int(256) for _ in range(32)]
+    e1 = run_parity(DecoderConfig("llama", 256, 256, 256, 8, 4, 688), 42, prompt[:20], 64, kv_dtype="f16")
+    e2 = run_parity(DecoderConfig("llama", 256, 64, 256, 2, 2, 512), 23, list(np.random.default_rng(3).integers(0, 256, size=24)), 16, kv_dtype="f16")
+    e3 = run_parity(DecoderConfig("llama", 256, 128, 256, 4, 2, 512), 29, list(np.random.default_rng(4).integers(0, 256, size=70)), 16, kv_dtype="f16")
+    e4 = run_parity(DecoderConfig("deepseek", 256, 128, 256, 8, 2, 688, q_rank=128, kv_rank=64), 5, prompt[:24], 24, kv_dtype="f16")
+    assert max(e1, e2, e3, e4) <= LOGIT_TOL
 
 
 def test_tiny_deepseek_greedy_matches_oracle():
