@@ -16,15 +16,14 @@
 #include "../../include/deepj_cuda.h"
 #include "kernels.h"
 #include "kv_cache.cuh"
+#include "q8_common.cuh"
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 
 namespace dj {
 
 namespace {
-
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 constexpr int kAttnWarps = 4;
 constexpr int kMaxSplits = 256;             // split partials a head can have (the merge keeps their weights in shared memory)
@@ -52,6 +51,268 @@ __global__ void k_kv_append(const float* __restrict__ qkv, int k_off, int v_off,
 
 template <int LPP, typename KT>   // lanes per position = hd / 16; cache element type
 __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
+        const float* __restrict__ qkv, int q_off, int k_off, int v_off, int ld,
+        KT* __restrict__ kcache, KT* __restrict__ vcache, int maxSeq,
+        const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
+        float* __restrict__ ws, int* __restrict__ tickets, float* __restrict__ out, int ldo, int H, float scale,
+        int T, int append) {
+    constexpr int HD = LPP * 16;
+    constexpr int PPW = 32 / LPP;                 // positions per warp iteration
+    constexpr int G = kAttnWarps * PPW;           // position groups per CTA
+    constexpr int kStages = 3;                    // ring stages per warp: two groups of positions in flight, one being folded in
+    constexpr int kStageElems = 2 * PPW * HD;     // a stage: K rows of PPW consecutive positions, then their V rows (1024 elements)
+    // dynamic shared memory: warp-private K/V rings [warps][kStages][kStageElems] of the cache type while the slice
+    // streams; afterwards the same bytes hold the CTA's partial rows (s_acc [G][HD], s_m [G], s_l [G])
+    extern __shared__ __align__(16) unsigned char dynsm[];
+    float (*s_acc)[HD] = reinterpret_cast<float (*)[HD]>(dynsm);
+    float* s_m = reinterpret_cast<float*>(dynsm) + G * HD;
+    float* s_l = s_m + G;
+    __shared__ int s_last;
+
+    // row z of the projection / output buffers is token t of sequence b: T = 1 (and append) for a decode step;
+    // T > 1 for a prompt chunk, whose k/v rows the append kernel has already written
+    const int split = blockIdx.x, splits = gridDim.x, h = blockIdx.y, z = blockIdx.z;
+    const int b = z / T, tok = z - b * T;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int group = lane / LPP, gl = lane % LPP;
+    // The cache rows below the current position were written by earlier steps, not by the kernel this one depends
+    // on, so the first two groups of K/V rows are requested BEFORE the wait and stream in while the projection kernel
+    // drains.  The position read here is re-read after the wait; in the (never observed) case that it moved, the
+    // speculative rows are dropped and requested again.
+    const int half = HD >> 1;
+    auto read_pos = [&]() {
+        int v = (int)__ldcg(posbuf + b) + tok;
+        return v < 0 ? 0 : (v >= maxSeq ? maxSeq - 1 : v);
+    };
+    int pos = read_pos();
+    int seq = pos + 1;
+    int chunk = (seq + splits - 1) / splits;
+    int start = split * chunk;
+    int end = min(seq, start + chunk);
+    KT* khead = kcache + ((size_t)b * H + h) * maxSeq * HD;      // this head's rows [maxSeq][HD]
+    KT* vhead = vcache + ((size_t)b * H + h) * maxSeq * HD;
+    KT* kbase = khead + gl * 16;
+    KT* vbase = vhead + gl * 16;
+    KT* ring = reinterpret_cast<KT*>(dynsm) + (size_t)warp * kStages * kStageElems;
+    // Stage `st` ← the K and V rows of positions pb … pb+PPW−1 (consecutive rows are contiguous): 16-byte pieces, lane by
+    // lane.  Rows past the end of the cache are clamped to its last row (their lanes are masked out below).
+    constexpr int kPieces = PPW * HD * (int)sizeof(KT) / 16;       // per plane: 128 (fp32) or 64 (fp16)
+    constexpr int kPerRow = HD * (int)sizeof(KT) / 16;
+    auto issue = [&](int st, int pb) {
+        KT* dst = ring + (size_t)st * kStageElems;
+#pragma unroll
+        for (int c0 = 0; c0 < kPieces; c0 += 32) {
+            const int c = c0 + lane;
+            const int prow = min(pb + c / kPerRow, maxSeq - 1);
+            const size_t src = (size_t)prow * HD + (size_t)(c % kPerRow) * (16 / sizeof(KT));
+            cp_async16(reinterpret_cast<unsigned char*>(dst) + (size_t)c * 16, khead + src);
+            cp_async16(reinterpret_cast<unsigned char*>(dst + PPW * HD) + (size_t)c * 16, vhead + src);
+        }
+    };
+    // iteration `it` of this warp covers positions start + warp·PPW + it·G … + PPW − 1
+    int nIter = 0;
+    auto count_iters = [&]() { const int first = start + warp * PPW; nIter = first < end ? (end - first + G - 1) / G : 0; };
+    count_iters();
+    const bool spec = T == 1;                     // a chunk's own rows were written by the kernel before this one: no early requests
+    if (spec) {
+#pragma unroll
+        for (int i = 0; i < kStages - 1; i++) {
+            if (i < nIter) issue(i, start + warp * PPW + i * G);
+            cp_async_commit();
+        }
+    }
+    // the rotation tables are constants: the row of the speculative position is fetched before the wait too
+    float cs[8], sn[8];
+    auto load_tables = [&](float (&cs)[8], float (&sn)[8]) {
+        const float4* cp = reinterpret_cast<const float4*>(cosT + (size_t)pos * half + gl * 8);
+        const float4* sp = reinterpret_cast<const float4*>(sinT + (size_t)pos * half + gl * 8);
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const float4 c4 = cp[j], s4 = sp[j];
+            cs[4 * j] = c4.x; cs[4 * j + 1] = c4.y; cs[4 * j + 2] = c4.z; cs[4 * j + 3] = c4.w;
+            sn[4 * j] = s4.x; sn[4 * j + 1] = s4.y; sn[4 * j + 2] = s4.z; sn[4 * j + 3] = s4.w;
+        }
+    };
+    load_tables(cs, sn);
+    const int specPos = pos;
+    pdl_wait();
+    pdl_launch_dependents();
+    // the query row does not depend on the position: its loads go out together with the position's
+    const float* rowp = qkv + (size_t)z * ld;
+    float q[16];
+    {
+        const float4* qp = reinterpret_cast<const float4*>(rowp + q_off + h * HD + gl * 16);
+#pragma unroll
+        for (int j = 0; j < 4; j++) { float4 v = qp[j]; q[4 * j] = v.x; q[4 * j + 1] = v.y; q[4 * j + 2] = v.z; q[4 * j + 3] = v.w; }
+    }
+    pos = read_pos();
+    if (pos != specPos || !spec) {
+        if (pos != specPos) load_tables(cs, sn);
+        seq = pos + 1;
+        chunk = (seq + splits - 1) / splits;
+        start = split * chunk;
+        end = min(seq, start + chunk);
+        cp_async_wait<0>();                       // whatever was requested for the old position is dropped
+        __syncwarp();
+        count_iters();
+#pragma unroll
+        for (int i = 0; i < kStages - 1; i++) {
+            if (i < nIter) issue(i, start + warp * PPW + i * G);
+            cp_async_commit();
+        }
+    }
+
+    // rotate 8 interleaved pairs held in v[16] by the table row of the current position (cs, sn)
+    auto rotate = [&](float (&v)[16], const float (&cs)[8], const float (&sn)[8]) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float x0 = v[2 * i], x1 = v[2 * i + 1];
+            v[2 * i] = x0 * cs[i] - x1 * sn[i];
+            v[2 * i + 1] = x0 * sn[i] + x1 * cs[i];
+        }
+    };
+    rotate(q, cs, sn);
+
+    float m = -INFINITY, l = 0.0f, acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) acc[j] = 0.0f;
+    for (int it = 0; it < nIter; it++) {
+        // keep two groups in flight: the stage freed by the previous iteration takes the group two ahead
+        if (it + kStages - 1 < nIter) issue((it + kStages - 1) % kStages, start + warp * PPW + (it + kStages - 1) * G);
+        cp_async_commit();
+        cp_async_wait<kStages - 1>();
+        __syncwarp();
+        const int p = start + warp * PPW + it * G + group;
+        const bool valid = p < end;
+        float kf[16], vf[16];
+        if (valid && p == pos && append) {
+            // the new token: k and v come from the projections; rotate k, append both to the cache
+            const float4* kp = reinterpret_cast<const float4*>(rowp + k_off + h * HD + gl * 16);
+            const float4* vp = reinterpret_cast<const float4*>(rowp + v_off + h * HD + gl * 16);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float4 a = kp[j], c = vp[j];
+                kf[4 * j] = a.x; kf[4 * j + 1] = a.y; kf[4 * j + 2] = a.z; kf[4 * j + 3] = a.w;
+                vf[4 * j] = c.x; vf[4 * j + 1] = c.y; vf[4 * j + 2] = c.z; vf[4 * j + 3] = c.w;
+            }
+            float ck[8], sk[8];              // fetched again here (a cache hit) rather than kept live through the loop
+            load_tables(ck, sk);
+            rotate(kf, ck, sk);
+            KvIo<KT>::st16(kbase + (size_t)p * HD, kf);
+            KvIo<KT>::st16(vbase + (size_t)p * HD, vf);
+            // this step attends to what later steps will read back (the rounded values of an fp16 cache)
+#pragma unroll
+            for (int j = 0; j < 16; j++) { kf[j] = KvIo<KT>::stored(kf[j]); vf[j] = KvIo<KT>::stored(vf[j]); }
+        } else if (valid) {
+            const KT* st = ring + (size_t)(it % kStages) * kStageElems + group * HD + gl * 16;
+            KvIo<KT>::ld16_shared(st, kf);
+            KvIo<KT>::ld16_shared(st + PPW * HD, vf);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) { kf[j] = 0.0f; vf[j] = 0.0f; }
+        }
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; j++) dot = fmaf(q[j], kf[j], dot);
+#pragma unroll
+        for (int o = LPP / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (valid) {
+            const float s = dot * scale;
+            const float mn = fmaxf(m, s);
+            const float corr = expf(m - mn);
+            const float pe = expf(s - mn);
+            l = l * corr + pe;
+#pragma unroll
+            for (int j = 0; j < 16; j++) acc[j] = fmaf(pe, vf[j], acc[j] * corr);
+            m = mn;
+        }
+        __syncwarp();                             // the stage is read out before a later request may overwrite it
+    }
+    cp_async_wait<0>();
+    __syncthreads();                              // every warp is done with its ring: the bytes become the partial rows
+    const int g = warp * PPW + group;
+#pragma unroll
+    for (int j = 0; j < 16; j++) s_acc[g][gl * 16 + j] = acc[j];
+    if (gl == 0) { s_m[g] = m; s_l[g] = l; }
+    __syncthreads();
+    float* mine = ws + (((size_t)z * H + h) * splits + split) * (HD + 2);
+    for (int j = threadIdx.x; j < HD; j += blockDim.x) {
+        float M = -INFINITY;
+        for (int gg = 0; gg < G; gg++) M = fmaxf(M, s_m[gg]);
+        float a = 0.0f, L = 0.0f;
+        if (M > -INFINITY) {
+            for (int gg = 0; gg < G; gg++) {
+                const float e = expf(s_m[gg] - M);
+                a = fmaf(s_acc[gg][j], e, a);
+                L = fmaf(s_l[gg], e, L);
+            }
+        }
+        mine[j] = a;
+        if (j == 0) { mine[HD] = M; mine[HD + 1] = L; }
+    }
+    if (splits == 1) {
+        // nothing to merge
+        __syncthreads();
+        for (int j = threadIdx.x; j < HD; j += blockDim.x) out[(size_t)z * ldo + h * HD + j] = mine[j] / mine[HD + 1];
+        return;
+    }
+    // ── the last CTA of this head merges the split partials ──
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(&tickets[z * H + h], 1);
+        s_last = ticket == splits - 1;
+        if (s_last) tickets[z * H + h] = 0;          // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // Every thread requests its own column of up to 24 split partials together with the (m, l) pairs, so the
+    // merge costs one load round trip (more splits: further rounds of 24).
+    const float* pbase = ws + ((size_t)z * H + h) * splits * (HD + 2);
+    float* s_m2 = &s_acc[0][0];                 // reused: the CTA's own partial has been written out
+    float* s_l2 = s_m2 + kMaxSplits;
+    for (int sp = threadIdx.x; sp < splits; sp += blockDim.x) {
+        s_m2[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD);
+        s_l2[sp] = __ldcg(pbase + (size_t)sp * (HD + 2) + HD + 1);
+    }
+    constexpr int kBatch = 24;
+    const int j0 = threadIdx.x;                 // HD ≤ 512 = 4 columns per thread at most; the first one is prefetched here
+    float first[kBatch];
+#pragma unroll
+    for (int q = 0; q < kBatch; q++) first[q] = (j0 < HD && q < splits) ? __ldcg(pbase + (size_t)q * (HD + 2) + j0) : 0.0f;
+    __syncthreads();
+    float M = -INFINITY;
+    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, s_m2[sp]);
+    float L = 0.0f;
+    for (int sp = 0; sp < splits; sp++) L = fmaf(s_l2[sp], expf(s_m2[sp] - M), L);
+    __syncthreads();
+    for (int sp = threadIdx.x; sp < splits; sp += blockDim.x) s_m2[sp] = expf(s_m2[sp] - M);
+    __syncthreads();
+    for (int j = threadIdx.x; j < HD; j += blockDim.x) {
+        float a = 0.0f;
+        for (int s0 = 0; s0 < splits; s0 += kBatch) {
+            float part[kBatch];
+            if (j == j0 && s0 == 0) {
+#pragma unroll
+                for (int q = 0; q < kBatch; q++) part[q] = first[q];
+            } else {
+#pragma unroll
+                for (int q = 0; q < kBatch; q++) part[q] = s0 + q < splits ? __ldcg(pbase + (size_t)(s0 + q) * (HD + 2) + j) : 0.0f;
+            }
+#pragma unroll
+            for (int q = 0; q < kBatch; q++) if (s0 + q < splits) a = fmaf(part[q], s_m2[s0 + q], a);
+        }
+        out[(size_t)z * ldo + h * HD + j] = a / L;
+    }
+}
+
+
+// The same step with the K/V rows travelling through registers, one group of positions ahead: the form the fp32 cache
+// keeps — its 48 KB of rings per CTA would leave no room for this kernel's CTAs to move in beside the projection kernel
+// they follow, and measured slower (0.55 against 0.51 ms per 7B token at context 2063).
+template <int LPP, typename KT>   // lanes per position = hd / 16; cache element type
+__global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode_regs(
         const float* __restrict__ qkv, int q_off, int k_off, int v_off, int ld,
         KT* __restrict__ kcache, KT* __restrict__ vcache, int maxSeq,
         const float* __restrict__ posbuf, const float* __restrict__ cosT, const float* __restrict__ sinT,
@@ -281,6 +542,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode(
 }
 
 
+
 // ───────────── prompt chunks: tiled causal attention ─────────────
 // Row-wise decode attention re-reads every key once per query row.  For a chunk of T ≥ 32 tokens this kernel
 // lets 32 consecutive query rows of one head share each 64-key tile of K and V through shared memory (fp32 on the
@@ -468,9 +730,20 @@ void launch_attn_decode_t(const AttnDecodeArgs& a, cudaStream_t s) {
     }
     const int append = T == 1 ? 1 : 0;
     int* tickets = a.tickets;
+    // fp16 cache: K/V stream through warp-private rings in dynamic shared memory (3 stages × 1024 elements each, reused for
+    // the partial rows afterwards); fp32 cache: through registers (k_attn_decode_regs)
+    const size_t smem = std::max<size_t>((size_t)kAttnWarps * 3 * 1024 * sizeof(KT), (size_t)(4 * 512 + 2 * 4 * 32) * sizeof(float));
 #define DJ_ATTN_CASE(L)                                                                                              \
-    case L: launch_k(k_attn_decode<L, KT>, grid, block, 0, s, true, (const float*)a.qkv, a.q_off, a.k_off, a.v_off, a.ld, \
-                     kc, vc, a.maxSeq, a.pos, a.cosT, a.sinT, a.ws, tickets, a.out, a.ldo, a.H, a.scale, T, append); break;
+    case L: {                                                                                                        \
+        static bool attr = false;                                                                                    \
+        if (!attr) { DJ_CUDA_CHECK(cudaFuncSetAttribute(k_attn_decode<L, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024)); attr = true; } \
+        if (sizeof(KT) == 2)                                                                                         \
+            launch_k(k_attn_decode<L, KT>, grid, block, smem, s, true, (const float*)a.qkv, a.q_off, a.k_off, a.v_off, a.ld, \
+                     kc, vc, a.maxSeq, a.pos, a.cosT, a.sinT, a.ws, tickets, a.out, a.ldo, a.H, a.scale, T, append); \
+        else                                                                                                         \
+            launch_k(k_attn_decode_regs<L, KT>, grid, block, 0, s, true, (const float*)a.qkv, a.q_off, a.k_off, a.v_off, a.ld, \
+                     kc, vc, a.maxSeq, a.pos, a.cosT, a.sinT, a.ws, tickets, a.out, a.ldo, a.H, a.scale, T, append); \
+    } break;
     switch (lpp) {
         DJ_ATTN_CASE(1) DJ_ATTN_CASE(2) DJ_ATTN_CASE(4) DJ_ATTN_CASE(8) DJ_ATTN_CASE(16) DJ_ATTN_CASE(32)
     }

@@ -21,6 +21,13 @@ template <> struct KvIo<float> {
             v[4 * j] = a.x; v[4 * j + 1] = a.y; v[4 * j + 2] = a.z; v[4 * j + 3] = a.w;
         }
     }
+    static __device__ __forceinline__ void ld16_shared(const float* p, float (&v)[16]) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float4 a = reinterpret_cast<const float4*>(p)[j];
+            v[4 * j] = a.x; v[4 * j + 1] = a.y; v[4 * j + 2] = a.z; v[4 * j + 3] = a.w;
+        }
+    }
     static __device__ __forceinline__ void st16(float* p, const float (&v)[16]) {
 #pragma unroll
         for (int j = 0; j < 4; j++) reinterpret_cast<float4*>(p)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -39,6 +46,18 @@ template <> struct KvIo<__half> {
 #pragma unroll
         for (int j = 0; j < 2; j++) {
             const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p) + j);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[q]));
+                v[8 * j + 2 * q] = f.x; v[8 * j + 2 * q + 1] = f.y;
+            }
+        }
+    }
+    static __device__ __forceinline__ void ld16_shared(const __half* p, float (&v)[16]) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const uint4 u = reinterpret_cast<const uint4*>(p)[j];
             const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
             for (int q = 0; q < 4; q++) {
