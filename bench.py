@@ -500,6 +500,11 @@ def main():
         t16 = time.perf_counter() - t16
         dec16.set_tokens(nxt16)
         m16 = measure_decode(dec16, w16, args, world, local_rank, tp, max(1, min(args.repeats, 3)))
+        prof16 = dec16.profile_step()
+        prof16 = dec16.profile_step()
+        by_label = {}
+        for lbl, t in prof16:
+            by_label[lbl] = by_label.get(lbl, 0.0) + t
         bytes16 = cfg.q8_weight_bytes() + 16 * m16["ctx"] * kv_pos_bytes
         ach16 = bytes16 / world / (m16["ms_per_step"] * 1e-3) / 1e9
         line["batch16"] = {
@@ -510,6 +515,7 @@ def main():
                               "roofline_tokens_per_s": 16 * world * peak * 1e9 / bytes16},
             "gpu_launches": m16["launches"], "device_error": m16["dev_error"],
             "prefill": {"tokens": 16 * w16["prompt"], "seconds": t16},
+            "profile_ms_op_by_op": by_label,
         }
         dec16.close()
         if kv16 and not args.no_parity:

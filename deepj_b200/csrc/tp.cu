@@ -36,7 +36,7 @@ namespace dj {
 namespace {
 
 constexpr int kMaxWorld = 8;
-constexpr int kTpCtas = 8;                    // CTAs of a decode-sized exchange
+constexpr int kTpCtas = 32;                   // CTAs of a decode-sized exchange (one pass for one sequence, eight for sixteen)
 constexpr int kTpCtasLarge = 296;             // CTAs of a chunk-sized exchange (a fixed number: the per-CTA counters depend on it)
 constexpr long kTpLargePairs = 1L << 16;      // messages above 2^17 floats take the large grid
 constexpr unsigned kTpSpinLimit = 1u << 21;   // polls of one word (≈ a second), then give up
@@ -75,7 +75,6 @@ __device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
     asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-constexpr int kTpPairsPerThread = 1;      // 2 values per thread and pass: a 16 KB message spreads over all 2048 threads
 
 // mode 0: out[m][n] = residual[m][n] + bias[n] + Σ_r contribution_r[m][n]   (n_local == N)
 // mode 1: out[m][r·n_local + j] = contribution_r[m][j]
@@ -96,67 +95,55 @@ __global__ void __launch_bounds__(256) k_tp_exchange(TpPtrs P, int rank, int wor
     const int pairs = (total + 1) >> 1;
     const size_t slotWords = region_words + (size_t)parity * world * slot_floats;      // in 8-byte words
     bool gaveUp = false;                                  // a wait of this thread has expired, or the error word was already set
-    for (int p0 = (cta * blockDim.x + tid) * kTpPairsPerThread; p0 < pairs; p0 += gridDim.x * blockDim.x * kTpPairsPerThread) {
-        // push: my values of these pairs into my slot on every rank (myself included)
-        uint4 w[kTpPairsPerThread];
-#pragma unroll
-        for (int q = 0; q < kTpPairsPerThread; q++) {
-            const int i = 2 * (p0 + q);
-            const float a = i < total ? in[i] : 0.0f, b = i + 1 < total ? in[i + 1] : 0.0f;
-            w[q] = make_uint4(__float_as_uint(a), epoch, __float_as_uint(b), epoch);
-        }
+    // push first, for ALL of this thread's pairs: my values into my slot on every rank (myself included).  Only then wait —
+    // a thread with several passes (16 sequences, a prompt chunk) pays one NVLink latency, not one per pass.
+    const int stride = gridDim.x * blockDim.x;
+    for (int p0 = cta * blockDim.x + tid; p0 < pairs; p0 += stride) {
+        const int i = 2 * p0;
+        const float a = i < total ? in[i] : 0.0f, b = i + 1 < total ? in[i + 1] : 0.0f;
+        const uint4 w = make_uint4(__float_as_uint(a), epoch, __float_as_uint(b), epoch);
         for (int r = 0; r < world; r++) {
             uint4* dst = reinterpret_cast<uint4*>(P.data[r]) + (slotWords + (size_t)rank * slot_floats) / 2;
-#pragma unroll
-            for (int q = 0; q < kTpPairsPerThread; q++)
-                if (p0 + q < pairs) st_volatile_v4(dst + p0 + q, w[q]);
+            st_volatile_v4(dst + p0, w);
         }
-        // wait + finish: the same pairs from every rank's slot in my own buffer, in rank order
-        float sa[kTpPairsPerThread], sb[kTpPairsPerThread];
-#pragma unroll
-        for (int q = 0; q < kTpPairsPerThread; q++) { sa[q] = 0.0f; sb[q] = 0.0f; }
+    }
+    // wait + finish: the same pairs from every rank's slot in my own buffer, in rank order
+    for (int p0 = cta * blockDim.x + tid; p0 < pairs; p0 += stride) {
+        float sa = 0.0f, sb = 0.0f;
+        const int i = 2 * p0;
         for (int r = 0; r < world; r++) {
             const uint4* src = reinterpret_cast<const uint4*>(P.data[rank]) + (slotWords + (size_t)r * slot_floats) / 2;
-#pragma unroll
-            for (int q = 0; q < kTpPairsPerThread; q++) {
-                if (p0 + q >= pairs) continue;
-                uint4 v = ld_volatile_v4(src + p0 + q);
+            uint4 v = ld_volatile_v4(src + p0);
+            if (v.y != epoch || v.w != epoch) {
+                // not there yet: poll, unless some wait has already run out (here or in an earlier launch)
+                gaveUp = gaveUp || *reinterpret_cast<volatile int*>(error) != 0;
+                for (unsigned it = 0; !gaveUp && (v.y != epoch || v.w != epoch) && it < kTpSpinLimit; it++) {
+                    __nanosleep(32);
+                    v = ld_volatile_v4(src + p0);
+                    if ((it & 63u) == 63u) gaveUp = *reinterpret_cast<volatile int*>(error) != 0;
+                }
                 if (v.y != epoch || v.w != epoch) {
-                    // not there yet: poll, unless some wait has already run out (here or in an earlier launch)
-                    gaveUp = gaveUp || *reinterpret_cast<volatile int*>(error) != 0;
-                    for (unsigned it = 0; !gaveUp && (v.y != epoch || v.w != epoch) && it < kTpSpinLimit; it++) {
-                        __nanosleep(32);
-                        v = ld_volatile_v4(src + p0 + q);
-                        if ((it & 63u) == 63u) gaveUp = *reinterpret_cast<volatile int*>(error) != 0;
-                    }
-                    if (v.y != epoch || v.w != epoch) {
-                        if (!gaveUp) atomicCAS(error, 0, 100 + r);      // the first expiry names the rank
-                        gaveUp = true;
-                    }
+                    if (!gaveUp) atomicCAS(error, 0, 100 + r);      // the first expiry names the rank
+                    gaveUp = true;
                 }
-                const float a = __uint_as_float(v.x), b = __uint_as_float(v.z);
-                const int i = 2 * (p0 + q);
-                if (mode == 0) { sa[q] += a; sb[q] += b; }
-                else {
-                    if (i < total) out[(size_t)(i / n_local) * n_local * world + (size_t)r * n_local + i % n_local] = a;
-                    if (i + 1 < total) out[(size_t)((i + 1) / n_local) * n_local * world + (size_t)r * n_local + (i + 1) % n_local] = b;
-                }
+            }
+            const float a = __uint_as_float(v.x), b = __uint_as_float(v.z);
+            if (mode == 0) { sa += a; sb += b; }
+            else {
+                if (i < total) out[(size_t)(i / n_local) * n_local * world + (size_t)r * n_local + i % n_local] = a;
+                if (i + 1 < total) out[(size_t)((i + 1) / n_local) * n_local * world + (size_t)r * n_local + (i + 1) % n_local] = b;
             }
         }
         if (mode == 0) {
-#pragma unroll
-            for (int q = 0; q < kTpPairsPerThread; q++) {
-                const int i = 2 * (p0 + q);
-                if (i < total) {
-                    float v = residual ? residual[i] : 0.0f;
-                    if (bias) v += bias[i % n_local];
-                    out[i] = v + sa[q];
-                }
-                if (i + 1 < total) {
-                    float v = residual ? residual[i + 1] : 0.0f;
-                    if (bias) v += bias[(i + 1) % n_local];
-                    out[i + 1] = v + sb[q];
-                }
+            if (i < total) {
+                float v = residual ? residual[i] : 0.0f;
+                if (bias) v += bias[i % n_local];
+                out[i] = v + sa;
+            }
+            if (i + 1 < total) {
+                float v = residual ? residual[i + 1] : 0.0f;
+                if (bias) v += bias[(i + 1) % n_local];
+                out[i + 1] = v + sb;
             }
         }
     }
