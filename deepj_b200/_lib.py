@@ -45,6 +45,7 @@ SIGNATURES = {
     "deepj_cuda_tp_create": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p]),
     "deepj_cuda_decode_plan": (ctypes.c_int, [ctypes.c_int32, ctypes.c_void_p, ctypes.c_int32]),
     "deepj_cuda_tp_configure": (ctypes.c_int, [ctypes.c_int64]),
+    "deepj_cuda_tc_configure": (ctypes.c_int, [ctypes.c_int32]),
     "deepj_cuda_tp_connect": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32]),
     "deepj_cuda_clear_device_error": (ctypes.c_int, []),
     "deepj_cuda_tp_destroy": (ctypes.c_int, []),

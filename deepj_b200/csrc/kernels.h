@@ -27,6 +27,7 @@ extern bool g_use_pdl;
 // Q8 GEMV kernel choice (environment DEEPJ_CUDA_GEMV = tma | mma | fma); shapes outside a
 // kernel's domain fall through to the next one.
 extern int g_gemv_mode;
+extern int g_tc_terms;      // deepj_cuda_tc_configure
 // Device int set non-zero when a bounded wait inside a kernel expired.
 extern int* g_dev_error;
 // Phase-trace ring (null unless tracing is on) and the number of traced launches so far.

@@ -203,6 +203,7 @@ struct TcParams {
     int mTiles;             // 128-row activation tiles
     int pair;               // 1: a CTA takes tiles 2·blockIdx.y and 2·blockIdx.y + 1 (the second may not exist), two accumulators; 0: tile blockIdx.y
     int mode;               // 0: out = acc + bias (+ residual);  1: out = SiLU(out) · (acc + bias)   (SwiGLU's second GEMM)
+    int terms;              // correction products on top of x_hi · w_hi: bit 0 adds x_lo · w_hi, bit 1 adds x_hi · w_lo
     int* error;
     unsigned long long* trace;      // optional: thread 0 of CTA (0,0) sums the time it spends waiting / converting / fencing
 };
@@ -277,6 +278,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
         issue_group(0);
         const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0;
         unsigned long long tWait = 0, tConv = 0, tFence = 0, tStart = tracing ? gtime() : 0;
+        const bool wantLo = (p.terms & 2) != 0;              // without the x_hi · w_lo product the low halves are never read
         for (int G = 0; G < nG; G++) {
             uint4 cur4[2][2][2]; float scl4[2][2];            // [own k-tile of the group][row][16-byte half]
             mbar_wait(bar_rawFull, G & 1, &s_abort, p.error, 206);
@@ -335,17 +337,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
                             for (int e = 0; e < 2; e++) {
                                 const __half2 c = *reinterpret_cast<const __half2*>(e == 0 ? &c01 : &c23);
                                 const __half2 wh = __hmul2(c, sh);
-                                const __half2 er = __hfma2(c, sh, __hneg2(wh));
-                                const __half2 wl = __hfma2(c, sl, er);
                                 hi[2 * q + e] = *reinterpret_cast<const uint32_t*>(&wh);
-                                lo[2 * q + e] = *reinterpret_cast<const uint32_t*>(&wl);
+                                if (wantLo) {
+                                    const __half2 er = __hfma2(c, sh, __hneg2(wh));
+                                    const __half2 wl = __hfma2(c, sl, er);
+                                    lo[2 * q + e] = *reinterpret_cast<const uint32_t*>(&wl);
+                                }
                             }
                         }
                         const int o0 = swz_off(row, 2 * j), o1 = swz_off(row, 2 * j + 1);
                         *reinterpret_cast<uint4*>(bhi + o0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                         *reinterpret_cast<uint4*>(bhi + o1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-                        *reinterpret_cast<uint4*>(blo + o0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                        *reinterpret_cast<uint4*>(blo + o1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                        if (wantLo) {
+                            *reinterpret_cast<uint4*>(blo + o0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                            *reinterpret_cast<uint4*>(blo + o1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                        }
                     }
                 }
                 unsigned long long t2 = tracing ? gtime() : 0;
@@ -416,6 +422,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
         // ── MMA issue: one thread ──
         if (lane == 0) {
             bool ok = true;
+            const bool xLo = (p.terms & 1) != 0, wLo = (p.terms & 2) != 0;
             for (int kt = 0; kt < nK && ok; kt++) {
                 const int sa = kt % nStA, sb = kt % kStagesB;
                 ok = mbar_wait(bar_fullA(sa), (kt / nStA) & 1, &s_abort, p.error, 204) &&
@@ -428,12 +435,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
                 for (int ks = 0; ks < kTileK / 16; ks++) {
                     const uint32_t off = ks * 32;          // 16 halves along K inside the swizzled row
                     umma_f16(tmem_base, umma_desc(a_hi + off), umma_desc(b_hi + off), kIdesc, (kt | ks) != 0);
-                    umma_f16(tmem_base, umma_desc(a_lo + off), umma_desc(b_hi + off), kIdesc, 1);
-                    umma_f16(tmem_base, umma_desc(a_hi + off), umma_desc(b_lo + off), kIdesc, 1);
+                    if (xLo) umma_f16(tmem_base, umma_desc(a_lo + off), umma_desc(b_hi + off), kIdesc, 1);
+                    if (wLo) umma_f16(tmem_base, umma_desc(a_hi + off), umma_desc(b_lo + off), kIdesc, 1);
                     if (has1) {                            // the same weight tile against the second 128 rows → accumulator 2
                         umma_f16(tmem_base + kTileN, umma_desc(a_hi + kAImageBytes + off), umma_desc(b_hi + off), kIdesc, (kt | ks) != 0);
-                        umma_f16(tmem_base + kTileN, umma_desc(a_lo + kAImageBytes + off), umma_desc(b_hi + off), kIdesc, 1);
-                        umma_f16(tmem_base + kTileN, umma_desc(a_hi + kAImageBytes + off), umma_desc(b_lo + off), kIdesc, 1);
+                        if (xLo) umma_f16(tmem_base + kTileN, umma_desc(a_lo + kAImageBytes + off), umma_desc(b_hi + off), kIdesc, 1);
+                        if (wLo) umma_f16(tmem_base + kTileN, umma_desc(a_hi + kAImageBytes + off), umma_desc(b_lo + off), kIdesc, 1);
                     }
                 }
                 umma_commit(bar_emptyA(sa));               // both arrive when the MMAs above have finished reading the stages
@@ -454,6 +461,8 @@ constexpr size_t kTcSmem = (size_t)kARegionBytes + (size_t)kStagesB * kStageBByt
 // Rough duration of launch_q8_linear_tc in µs, for the choice between this path and passes of the 16-row kernel
 // when M is small: a CTA needs ≈ 0.75 µs per 32-k tile (1.2 µs when it carries two accumulators), CTAs run in
 // rounds over the SMs, and the activation pre-pass costs a few µs.
+int g_tc_terms = 3;
+
 double q8_tc_estimate_us(int M, int K, int N) {
     const long mTiles = (M + kTileM - 1) / kTileM, nTiles = (N + kTileN - 1) / kTileN;
     const long single = nTiles * mTiles, paired = nTiles * ((mTiles + 1) / 2);
@@ -496,7 +505,7 @@ bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s) {
     p.residual = a.residual; p.ldr = a.ldr;
     p.out = a.out; p.ldo = a.ldo;
     p.M = M; p.N = N; p.K = K; p.Kp = a.w.Kp; p.nb = a.w.nb; p.mTiles = mTiles; p.pair = pair ? 1 : 0;
-    p.mode = 0; p.error = g_dev_error; p.trace = trace_slot();
+    p.mode = 0; p.terms = g_tc_terms; p.error = g_dev_error; p.trace = trace_slot();
     launch_k(k_q8_gemm_tc, grid, dim3(kTcThreads), kTcSmem, s, true, p);
     if (a.w2.codes != nullptr) {
         // SwiGLU: the gate projection is in `out`; the up projection's epilogue multiplies SiLU(gate) into it
@@ -507,3 +516,12 @@ bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s) {
 }
 
 }  // namespace dj
+
+// Which of the two fp16 correction products the tensor-core GEMM issues on top of x_hi · w_hi: bit 0 = x_lo · w_hi,
+// bit 1 = x_hi · w_lo.  3 (the default) carries ≈ 22 bits of both operands; 1, 2 and 0 trade bits for tensor-pipe time
+// (and, without bit 1, for half of the dequantisation stores).  Drops the cached CUDA graphs, which hold the old value.
+extern "C" int deepj_cuda_tc_configure(int32_t correction_terms) {
+    if (correction_terms < 0 || correction_terms > 3) { dj::set_last_error("tc_configure: correction_terms must be 0..3"); return 1; }
+    if (dj::g_tc_terms != correction_terms) { dj::g_tc_terms = correction_terms; dj::invalidate_graphs(); }
+    return 0;
+}

@@ -157,6 +157,13 @@ int deepj_cuda_tp_connect(const void* handles, int32_t world);
 int deepj_cuda_tp_destroy(void);
 int deepj_cuda_clear_device_error(void);
 
+/* Precision of the many-row (tcgen05) Q8 projection, which multiplies fp16 halves x = x_hi + x_lo and
+ * w = w_hi + w_lo: x_hi * w_hi is always issued; bit 0 of correction_terms adds x_lo * w_hi, bit 1 adds x_hi * w_lo.
+ * 3 is the default (both operands at about 22 bits); fewer products are faster and coarser (11 bits in the dropped
+ * operand).  Takes effect on the next flush; cached CUDA graphs are dropped.  No counterpart in the reference, whose
+ * Q8 matmul is fp32 throughout (native/deepj_metal_jni.mm:828-889). */
+int deepj_cuda_tc_configure(int32_t correction_terms);
+
 /* Decode attention for callers that must not allocate.  No counterpart in the reference.
  *
  * Some hosts of this library cannot let a call reach cudaMalloc: a JVM thread inside a

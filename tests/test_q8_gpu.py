@@ -190,3 +190,28 @@ def test_q8_linear_strided_windows(dev):
     expected = oracle.matmul(np.ascontiguousarray(xw[:, 100:164]), oracle.q8_dequantize(*oracle.q8_quantize(W)))
     close(expected, got[:, 32:80])
     assert np.array_equal(got[:, :32], out0[:, :32]) and np.array_equal(got[:, 80:], out0[:, 80:])
+
+
+def test_tc_correction_terms_trade_bits_for_products(dev):
+    """deepj_cuda_tc_configure: the many-row kernel with both correction products (the default) sits at fp32-like error;
+    each dropped product leaves an operand at 11 bits and the error rises by orders of magnitude; the setting is
+    validated, takes effect on the next flush and is restored."""
+    M, K, N = 512, 2048, 256
+    rng = np.random.default_rng(99)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    Wq = oracle.q8_dequantize(*oracle.q8_quantize(W))
+    expected = (x.astype(np.float64) @ Wq.astype(np.float64))
+    q, xb, ob = dev.q8(W), dev.buf(M * K, x), dev.buf(M * N)
+    errs = {}
+    try:
+        for terms in (3, 1, 2, 0):
+            _lib.check(dev.lib.deepj_cuda_tc_configure(terms))
+            dev.flush([OP_Q8_LINEAR, xb, 0, K, -1, 0, q, -1, -1, 0, 0, ob, 0, N, M])
+            errs[terms] = float(np.abs(dev.get(ob, M * N).reshape(M, N) - expected).max() / np.abs(expected).max())
+        assert dev.lib.deepj_cuda_tc_configure(4) != 0 and "correction_terms" in dev.lib.deepj_cuda_last_error().decode()
+    finally:
+        _lib.check(dev.lib.deepj_cuda_tc_configure(3))
+    assert errs[3] < 2e-5, errs
+    assert all(errs[t] > 8 * errs[3] for t in (1, 2, 0)), errs
+    assert errs[0] < 2e-3, errs
