@@ -24,7 +24,7 @@ extern int g_num_sms;
 // When true, launchers attach the programmatic-dependent-launch attribute so that
 // a kernel's weight prefetch overlaps the tail of its predecessor.
 extern bool g_use_pdl;
-// Q8 GEMV kernel choice (environment DEEPJ_CUDA_GEMV = tma | mma | fma); shapes outside a
+// Q8 GEMV kernel choice (environment DEEPJ_CUDA_GEMV = cpasync | fma to step down); shapes outside a
 // kernel's domain fall through to the next one.
 extern int g_gemv_mode;
 extern int g_tc_terms;      // deepj_cuda_tc_configure
@@ -86,6 +86,7 @@ struct Q8LinearArgs {
 };
 void launch_q8_linear(const Q8LinearArgs& a, cudaStream_t s);
 bool launch_q8_gemv_i8(const Q8LinearArgs& a, cudaStream_t s);
+bool launch_q8_gemv_tma(const Q8LinearArgs& a, cudaStream_t s);     // K a multiple of 128; false = outside its domain
 bool q8_gemv_i8_fuses_gpt(const Q8LinearArgs& a);     // true when launch_q8_gemv_i8 can take beta / act itself
 void launch_layernorm_rows(const float* x, int ldx, const float* gamma, const float* beta, float eps, float* out, int K, int M, cudaStream_t s);
 void launch_gelu_rows(float* buf, int ld, int N, int M, cudaStream_t s);

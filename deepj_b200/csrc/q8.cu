@@ -18,7 +18,7 @@
 
 namespace dj {
 
-int g_gemv_mode = 2;   // 2: tensor-pipe kernels (GEMV, batched, tcgen05) with the FMA kernel as the fallback, 0: FMA kernel only
+int g_gemv_mode = 2;   // 2: tensor-pipe kernels (TMA GEMV, cp.async GEMV, batched, tcgen05) with the FMA kernel as the fallback, 1: the same without the TMA GEMV, 0: FMA kernel only
 
 namespace {
 
@@ -325,7 +325,7 @@ void launch_q8_linear(const Q8LinearArgs& a0, cudaStream_t s) {
     if (a0.beta == nullptr && a0.act == 0) { dispatch_q8_linear(a0, s); return; }
     // GPT blocks: up to four rows go through the GEMV, which takes LayerNorm and GELU itself; the many-row
     // kernels see already normalised rows and get the activation applied to their output afterwards
-    if (g_gemv_mode == 2 && a0.M < 5 && q8_gemv_i8_fuses_gpt(a0)) { dispatch_q8_linear(a0, s); return; }
+    if (g_gemv_mode >= 1 && a0.M < 5 && q8_gemv_i8_fuses_gpt(a0)) { dispatch_q8_linear(a0, s); return; }
     Q8LinearArgs a = a0;
     if (a.beta != nullptr) {
         if (a.ln_ws == nullptr) throw std::runtime_error("Q8 linear: LayerNorm needs its workspace");
@@ -351,7 +351,7 @@ void dispatch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
     p.K = a.w.K; p.N = a.w.N; p.Kp = a.w.Kp; p.nb = a.w.nb;
     const bool swiglu = a.w2.codes != nullptr;
     static const bool noTc = getenv("DEEPJ_CUDA_NO_TC") != nullptr;
-    const bool batchOk = g_gemv_mode == 2 && a.M >= 5 && a.ws != nullptr && a.w.K % 32 == 0 && a.w.Kp == a.w.K;
+    const bool batchOk = g_gemv_mode >= 1 && a.M >= 5 && a.ws != nullptr && a.w.K % 32 == 0 && a.w.Kp == a.w.K;
     // A few dozen rows leave most SMs without a 128 × 256 tile: passes of the 16-row kernel (≈ 0.9 ps per weight and
     // pass, measured) win until the tensor-core grid fills up.
     bool preferBatch = false;
@@ -359,14 +359,15 @@ void dispatch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
         const double batchUs = (double)((a.M + 15) / 16) * 0.9e-6 * (double)a.w.K * (double)a.w.N;
         preferBatch = batchUs < q8_tc_estimate_us(a.M, a.w.K, a.w.N);
     }
-    if (g_gemv_mode == 2 && !noTc && !preferBatch && a.M >= kTcMinRows && a.ws != nullptr && launch_q8_linear_tc(a, a.ws, s)) return;
+    if (g_gemv_mode >= 1 && !noTc && !preferBatch && a.M >= kTcMinRows && a.ws != nullptr && launch_q8_linear_tc(a, a.ws, s)) return;
     if (batchOk) {
         // five or more rows share one pass over the weights, 16 at a time (up to four are two GEMV passes, which is as fast)
         bool ok = true;
         for (int m0 = 0; m0 < a.M && ok; m0 += 16) ok = launch_q8_linear_batch(a, m0, a.M - m0 < 16 ? a.M - m0 : 16, a.ws, a.tickets, s);
         if (ok) return;
     }
-    if (g_gemv_mode == 2 && launch_q8_gemv_i8(a, s)) return;
+    if (g_gemv_mode == 2 && launch_q8_gemv_tma(a, s)) return;
+    if (g_gemv_mode >= 1 && launch_q8_gemv_i8(a, s)) return;
     if (swiglu) launch_gemv_dispatch<true>(p, a.M, s);
     else launch_gemv_dispatch<false>(p, a.M, s);
 }

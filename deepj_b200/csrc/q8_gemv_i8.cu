@@ -20,6 +20,7 @@
 // into the activation staging; bias, residual and SiLU-gate into the epilogue.
 #include "kernels.h"
 #include "q8_common.cuh"
+#include "q8_stage.cuh"
 
 namespace dj {
 
@@ -38,14 +39,14 @@ unsigned long long* trace_slot() {
 
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
+constexpr int kWarps = kGemvWarps;
+constexpr int kThreads = kGemvThreads;
 constexpr int kRows = 16;                   // weight rows per tile (MMA M)
 constexpr int kRowStride = 64;              // 64 code bytes per row per pair; 32-byte halves swizzled by row for conflict-free reads
 constexpr int kSlotBytes = kRows * kRowStride + kRows * 2 * 4;    // + 32 scales
-constexpr int kXsPad = 32;                  // bytes of padding per activation digit column
+constexpr int kXsPad = kGemvXsPad;
 constexpr int kPreMax = 2;                  // items a warp prefetches before it waits for the previous kernel
-constexpr int kColsPerRow = 3;              // digit columns per activation row in shared memory: d2, d1, d0
+constexpr int kColsPerRow = kGemvColsPerRow;
 
 struct GemvI8Params {
     const float* x; int ldx;
@@ -62,7 +63,7 @@ struct GemvI8Params {
 };
 
 
-constexpr int kStageRounds = 3;             // rows of up to 3·256·16 = 12288 values are staged from registers
+constexpr int kStageRounds = kGemvStageRounds;
 
 // GPT = true adds LayerNorm1D (norm/LayerNorm1D.java:34-71: mean, biased variance, (x − mean)/√(var + eps)·γ + β)
 // to the staging and GELU to the epilogue; the Llama / DeepSeek instantiation carries neither.
@@ -147,140 +148,13 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const GemvI8Params p
     pdl_wait();
     if (tracing) p.trace[2] = gtime();
 
-    // activations → three int8 digit columns + one power-of-two scale per 32-k block (RMSNorm
-    // fused).  A thread converts 16 consecutive values (half a block) per round; all rounds of a
-    // row are loaded before anything is converted, so a row costs one load round trip.
-    for (int m = 0; m < p.M; m++) {
-        const float* xrow = p.x + (size_t)m * p.ldx;
-        bool vec = ((reinterpret_cast<uintptr_t>(xrow) | (p.gamma ? reinterpret_cast<uintptr_t>(p.gamma) : 0)) & 15) == 0;
-        if (GPT && p.beta) vec = vec && (reinterpret_cast<uintptr_t>(p.beta) & 15) == 0;
-        int8_t* dcol = xd + (size_t)(kColsPerRow * m) * ldxs;
-        float* xscRow = xsc + (size_t)m * nBlocks;
-        if (rounds <= kStageRounds) {
-            float xv[kStageRounds][16];
-#pragma unroll
-            for (int r = 0; r < kStageRounds; r++) {
-                const int hb = r * kThreads + tid;
-                if (r < rounds && hb < nHalf) load16(xrow + hb * 16, vec, xv[r]);
-                else {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) xv[r][j] = 0.0f;
-                }
-            }
-            if (m == 0 && haveWork) {
-                for (int d = kPre; d < kMid; d++) issue_next();      // more of the ring behind the activation loads
-            }
-            float inv = 1.0f;
-            const bool layerNorm = GPT && p.gamma && p.beta;
-            if (layerNorm) {
-                // padding lanes hold zeros: they add nothing to the sum, and are masked out of the squared deviations
-                float sm = 0.0f;
-#pragma unroll
-                for (int r = 0; r < kStageRounds; r++)
-#pragma unroll
-                    for (int j = 0; j < 16; j++) sm += xv[r][j];
-                for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
-                __syncthreads();
-                if (lane == 0) s_red[warp] = sm;
-                __syncthreads();
-                sm = 0.0f;
-#pragma unroll
-                for (int q = 0; q < kWarps; q++) sm += s_red[q];
-                const float mean = sm * (1.0f / (float)p.K);
-                float ss = 0.0f;
-#pragma unroll
-                for (int r = 0; r < kStageRounds; r++) {
-                    const bool on = r < rounds && r * kThreads + tid < nHalf;
-#pragma unroll
-                    for (int j = 0; j < 16; j++) { xv[r][j] = on ? xv[r][j] - mean : 0.0f; ss = fmaf(xv[r][j], xv[r][j], ss); }
-                }
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                __syncthreads();
-                if (lane == 0) s_red[warp] = ss;
-                __syncthreads();
-                ss = 0.0f;
-#pragma unroll
-                for (int q = 0; q < kWarps; q++) ss += s_red[q];
-                inv = __frcp_rn(sqrtf(ss * (1.0f / (float)p.K) + p.eps));
-            } else if (p.gamma) {
-                float ss = 0.0f;
-#pragma unroll
-                for (int r = 0; r < kStageRounds; r++)
-#pragma unroll
-                    for (int j = 0; j < 16; j++) ss = fmaf(xv[r][j], xv[r][j], ss);
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                __syncthreads();
-                if (lane == 0) s_red[warp] = ss;
-                __syncthreads();
-                ss = 0.0f;
-#pragma unroll
-                for (int q = 0; q < kWarps; q++) ss += s_red[q];
-                inv = __frcp_rn(sqrtf(ss * (1.0f / (float)p.K) + p.eps));      // RMSNorm1D.forward: x / rms · γ
-            }
-#pragma unroll
-            for (int r = 0; r < kStageRounds; r++) {
-                const int hb = r * kThreads + tid;
-                const bool on = r < rounds && hb < nHalf;
-                if (p.gamma) {
-                    float gv[16];
-                    if (gammaEarly) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) gv[j] = gpre[j];
-                    } else if (on) load16(p.gamma + hb * 16, vec, gv);
-                    else {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) gv[j] = 1.0f;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; j++) xv[r][j] = (xv[r][j] * inv) * gv[j];
-                    if (layerNorm && on) {
-                        load16(p.beta + hb * 16, vec, gv);
-#pragma unroll
-                        for (int j = 0; j < 16; j++) xv[r][j] += gv[j];
-                    }
-                }
-                if (r < rounds) digits16(xv[r], on, dcol, ldxs, hb, xscRow);
-            }
-        } else {
-            // very wide rows: one pass for the sum of squares, then round by round
-            float inv = 1.0f;
-            if (p.gamma) {
-                float ss = 0.0f;
-                for (int k = tid; k < p.K; k += kThreads) { float v = xrow[k]; ss = fmaf(v, v, ss); }
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                __syncthreads();
-                if (lane == 0) s_red[warp] = ss;
-                __syncthreads();
-                ss = 0.0f;
-#pragma unroll
-                for (int q = 0; q < kWarps; q++) ss += s_red[q];
-                inv = __frcp_rn(sqrtf(ss * (1.0f / (float)p.K) + p.eps));
-            }
-            if (m == 0 && haveWork) {
-                for (int d = kPre; d < kMid; d++) issue_next();
-            }
-            for (int r = 0; r < rounds; r++) {
-                const int hb = r * kThreads + tid;
-                const bool on = hb < nHalf;
-                float xv[16], gv[16];
-                if (on) load16(xrow + hb * 16, vec, xv);
-                else {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) xv[j] = 0.0f;
-                }
-                if (p.gamma) {
-                    if (on) load16(p.gamma + hb * 16, vec, gv);
-                    else {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) gv[j] = 1.0f;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; j++) xv[j] = (xv[j] * inv) * gv[j];
-                }
-                digits16(xv, on, dcol, ldxs, hb, xscRow);
-            }
+    // activations → three int8 digit columns + one power-of-two scale per 32-k block (norm fused); more of the
+    // ring is queued behind the first row's loads
+    gemv_stage_rows<GPT, false>(p.x, p.ldx, p.gamma, p.beta, p.eps, p.K, p.M, xd, ldxs, xsc, s_red, gpre, gammaEarly, [&]() {
+        if (haveWork) {
+            for (int d = kPre; d < kMid; d++) issue_next();
         }
-    }
+    });
     __syncthreads();
     if (haveWork) {
         for (int d = kMid; d < DEPTH - 1; d++) issue_next();      // the rest of the ring: nothing latency-critical queues behind it now
@@ -307,13 +181,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const GemvI8Params p
     const int soff = kRows * kRowStride + g * 8;      // scales of row g: two floats; row g+8 is 64 bytes on
     for (int tile = blockIdx.x; tile < nTiles; tile += gridDim.x) {
         // epilogue operands are fetched now so that their latency hides behind the tile
-        const int er = tid % rowsPerTile, em = tid / rowsPerTile, en = tile * rowsPerTile + er;
-        float ebias = 0.0f, ebias2 = 0.0f, eres = 0.0f;
-        if (em < p.M && en < p.N) {
-            if (p.bias) ebias = p.bias[en];
-            if (SWIGLU && p.bias2) ebias2 = p.bias2[en];
-            if (!SWIGLU && p.residual) eres = p.residual[(size_t)em * p.ldr + en];
-        }
+        const GemvEpilogueOperands eo = gemv_epilogue_fetch<SWIGLU>(tile, p.M, p.N, p.bias, p.bias2, p.residual, p.ldr);
         for (int pi = warp; pi < nPairs; pi += kWarps) {
             issue_next();
             cp_async_wait<DEPTH - 1>();
@@ -345,37 +213,8 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const GemvI8Params p
         }
         if (tracing && tile == blockIdx.x) p.trace[4] = gtime();
         // ── tile epilogue: reduce the warps' column subsets, recombine the digits ──
-        float* part = s_part + (size_t)buf * kWarps * NM * 128;
-#pragma unroll
-        for (int q = 0; q < NM; q++) {
-            float* mine = part + (warp * NM + q) * 128;
-            mine[g * 8 + 2 * t] = acc[q][0];       mine[g * 8 + 2 * t + 1] = acc[q][1];
-            mine[(g + 8) * 8 + 2 * t] = acc[q][2]; mine[(g + 8) * 8 + 2 * t + 1] = acc[q][3];
-            acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.0f;
-        }
-        __syncthreads();
-        if (em < p.M && en < p.N) {
-            float a2 = 0.0f, a1 = 0.0f, a0 = 0.0f, b2 = 0.0f, b1 = 0.0f, b0 = 0.0f;
-#pragma unroll
-            for (int q = 0; q < kWarps; q++) {
-                const float* pr = part + (q * NM + (em >> 1)) * 128 + er * 8 + 4 * (em & 1);      // MMA em/2, columns 4(em%2) .. +2
-                a2 += pr[0]; a1 += pr[1]; a0 += pr[2];
-                if (SWIGLU) { b2 += pr[64]; b1 += pr[65]; b0 += pr[66]; }
-            }
-            float v = fmaf(a2, 65536.0f, fmaf(a1, 256.0f, a0));
-            if (SWIGLU) {
-                float u = fmaf(b2, 65536.0f, fmaf(b1, 256.0f, b0));
-                if (p.bias) v += ebias;
-                if (p.bias2) u += ebias2;
-                float sig = 1.0f / (1.0f + expf(-v));
-                p.out[(size_t)em * p.ldo + en] = (v * sig) * u;          // SiLU(gate) ⊙ up
-            } else {
-                if (p.bias) v += ebias;
-                if (GPT && p.act == 1) v = gelu_ref(v);
-                if (p.residual) v += eres;
-                p.out[(size_t)em * p.ldo + en] = v;
-            }
-        }
+        gemv_tile_epilogue<SWIGLU, GPT, NM>(acc, s_part + (size_t)buf * kWarps * NM * 128, tile, p.M, p.N, eo, p.bias != nullptr,
+                                            p.bias2 != nullptr, p.residual != nullptr, p.act, p.out, p.ldo);
         buf ^= 1;
     }
     cp_async_wait<0>();

@@ -1,0 +1,202 @@
+// Activation staging and tile epilogue shared by the two Q8 GEMV kernels (cp.async rings in q8_gemv_i8.cu,
+// TMA rings in q8_gemv_tma.cu): fp32 rows → three int8 digit columns + one power-of-two scale per 32-k block with
+// RMSNorm / LayerNorm fused, and the cross-warp reduction with bias / GELU / residual / SiLU-gate fused.
+#pragma once
+#include "q8_common.cuh"
+
+namespace dj {
+
+constexpr int kGemvWarps = 8;
+constexpr int kGemvThreads = kGemvWarps * 32;
+constexpr int kGemvStageRounds = 3;         // rows of up to 3·256·16 = 12288 values are staged from registers
+constexpr int kGemvXsPad = 32;              // bytes of padding per activation digit column
+constexpr int kGemvColsPerRow = 3;          // digit columns per activation row in shared memory: d2, d1, d0
+
+// Cross-warp sum of one value per thread (all threads of the CTA call it; s_red holds kGemvWarps floats).
+__device__ __forceinline__ float gemv_block_sum(float v, float* s_red, int lane, int warp) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    v = 0.0f;
+#pragma unroll
+    for (int q = 0; q < kGemvWarps; q++) v += s_red[q];
+    return v;
+}
+
+// M activation rows → digit columns xd [3M][ldxs] and block scales xsc [M][K/32].  A thread converts 16
+// consecutive values (half a block) per round; all rounds of a row are loaded before anything is converted, so a
+// row costs one load round trip.  `after_first_loads` runs once, behind the first row's loads (the callers queue
+// more weight copies there).  GPT adds LayerNorm1D (norm/LayerNorm1D.java:34-71: mean, biased variance,
+// (x − mean)/√(var + eps)·γ + β); otherwise gamma != nullptr means RMSNorm1D (x / rms · γ).
+// PERM stores every 32-k block in the order the standard int8 MMA fragment reads it (see digits16).
+template <bool GPT, bool PERM, class F>
+__device__ __forceinline__ void gemv_stage_rows(const float* x, int ldx, const float* gamma, const float* beta, float eps, int K, int M,
+                                                int8_t* xd, int ldxs, float* xsc, float* s_red, const float (&gpre)[16], bool gammaEarly,
+                                                F&& after_first_loads) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nBlocks = K >> 5, nHalf = K >> 4;
+    const int rounds = (nHalf + kGemvThreads - 1) / kGemvThreads;
+    for (int m = 0; m < M; m++) {
+        const float* xrow = x + (size_t)m * ldx;
+        bool vec = ((reinterpret_cast<uintptr_t>(xrow) | (gamma ? reinterpret_cast<uintptr_t>(gamma) : 0)) & 15) == 0;
+        if (GPT && beta) vec = vec && (reinterpret_cast<uintptr_t>(beta) & 15) == 0;
+        int8_t* dcol = xd + (size_t)(kGemvColsPerRow * m) * ldxs;
+        float* xscRow = xsc + (size_t)m * nBlocks;
+        if (rounds <= kGemvStageRounds) {
+            float xv[kGemvStageRounds][16];
+#pragma unroll
+            for (int r = 0; r < kGemvStageRounds; r++) {
+                const int hb = r * kGemvThreads + tid;
+                if (r < rounds && hb < nHalf) load16(xrow + hb * 16, vec, xv[r]);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) xv[r][j] = 0.0f;
+                }
+            }
+            if (m == 0) after_first_loads();
+            float inv = 1.0f;
+            const bool layerNorm = GPT && gamma && beta;
+            if (layerNorm) {
+                // padding lanes hold zeros: they add nothing to the sum, and are masked out of the squared deviations
+                float sm = 0.0f;
+#pragma unroll
+                for (int r = 0; r < kGemvStageRounds; r++)
+#pragma unroll
+                    for (int j = 0; j < 16; j++) sm += xv[r][j];
+                const float mean = gemv_block_sum(sm, s_red, lane, warp) * (1.0f / (float)K);
+                float ss = 0.0f;
+#pragma unroll
+                for (int r = 0; r < kGemvStageRounds; r++) {
+                    const bool on = r < rounds && r * kGemvThreads + tid < nHalf;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) { xv[r][j] = on ? xv[r][j] - mean : 0.0f; ss = fmaf(xv[r][j], xv[r][j], ss); }
+                }
+                ss = gemv_block_sum(ss, s_red, lane, warp);
+                inv = __frcp_rn(sqrtf(ss * (1.0f / (float)K) + eps));
+            } else if (gamma) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int r = 0; r < kGemvStageRounds; r++)
+#pragma unroll
+                    for (int j = 0; j < 16; j++) ss = fmaf(xv[r][j], xv[r][j], ss);
+                ss = gemv_block_sum(ss, s_red, lane, warp);
+                inv = __frcp_rn(sqrtf(ss * (1.0f / (float)K) + eps));      // RMSNorm1D.forward: x / rms · γ
+            }
+#pragma unroll
+            for (int r = 0; r < kGemvStageRounds; r++) {
+                const int hb = r * kGemvThreads + tid;
+                const bool on = r < rounds && hb < nHalf;
+                if (gamma) {
+                    float gv[16];
+                    if (gammaEarly) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) gv[j] = gpre[j];
+                    } else if (on) load16(gamma + hb * 16, vec, gv);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) gv[j] = 1.0f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; j++) xv[r][j] = (xv[r][j] * inv) * gv[j];
+                    if (layerNorm && on) {
+                        load16(beta + hb * 16, vec, gv);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) xv[r][j] += gv[j];
+                    }
+                }
+                if (r < rounds) digits16<PERM>(xv[r], on, dcol, ldxs, hb, xscRow);
+            }
+        } else {
+            // very wide rows: one pass for the sum of squares, then round by round
+            float inv = 1.0f;
+            if (gamma) {
+                float ss = 0.0f;
+                for (int k = tid; k < K; k += kGemvThreads) { float v = xrow[k]; ss = fmaf(v, v, ss); }
+                ss = gemv_block_sum(ss, s_red, lane, warp);
+                inv = __frcp_rn(sqrtf(ss * (1.0f / (float)K) + eps));
+            }
+            if (m == 0) after_first_loads();
+            for (int r = 0; r < rounds; r++) {
+                const int hb = r * kGemvThreads + tid;
+                const bool on = hb < nHalf;
+                float xv[16], gv[16];
+                if (on) load16(xrow + hb * 16, vec, xv);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) xv[j] = 0.0f;
+                }
+                if (gamma) {
+                    if (on) load16(gamma + hb * 16, vec, gv);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) gv[j] = 1.0f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; j++) xv[j] = (xv[j] * inv) * gv[j];
+                }
+                digits16<PERM>(xv, on, dcol, ldxs, hb, xscRow);
+            }
+        }
+    }
+}
+
+// Operands of a tile's epilogue, fetched before the tile so that their latency hides behind it: thread `tid`
+// finishes output (row em = tid / rowsPerTile of the activations, column en = tile·rowsPerTile + tid % rowsPerTile).
+struct GemvEpilogueOperands { float bias, bias2, res; };
+
+template <bool SWIGLU>
+__device__ __forceinline__ GemvEpilogueOperands gemv_epilogue_fetch(int tile, int M, int N, const float* bias, const float* bias2,
+                                                                    const float* residual, int ldr) {
+    constexpr int rowsPerTile = SWIGLU ? 8 : 16;
+    const int er = threadIdx.x % rowsPerTile, em = threadIdx.x / rowsPerTile, en = tile * rowsPerTile + er;
+    GemvEpilogueOperands o = {0.0f, 0.0f, 0.0f};
+    if (em < M && en < N) {
+        if (bias) o.bias = bias[en];
+        if (SWIGLU && bias2) o.bias2 = bias2[en];
+        if (!SWIGLU && residual) o.res = residual[(size_t)em * ldr + en];
+    }
+    return o;
+}
+
+// Reduces the warps' partial sums of one tile (part: [warps][NM][16 rows][8 columns], column 4(m%2) + d = digit
+// 2 − d of activation row m), recombines the digits and stores the fused result.  acc is zeroed for the next tile.
+template <bool SWIGLU, bool GPT, int NM>
+__device__ __forceinline__ void gemv_tile_epilogue(float (&acc)[NM][4], float* part, int tile, int M, int N, const GemvEpilogueOperands& o,
+                                                   bool hasBias, bool hasBias2, bool hasRes, int act, float* out, int ldo) {
+    constexpr int rowsPerTile = SWIGLU ? 8 : 16;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int er = tid % rowsPerTile, em = tid / rowsPerTile, en = tile * rowsPerTile + er;
+#pragma unroll
+    for (int q = 0; q < NM; q++) {
+        float* mine = part + (warp * NM + q) * 128;
+        mine[g * 8 + 2 * t] = acc[q][0];       mine[g * 8 + 2 * t + 1] = acc[q][1];
+        mine[(g + 8) * 8 + 2 * t] = acc[q][2]; mine[(g + 8) * 8 + 2 * t + 1] = acc[q][3];
+        acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.0f;
+    }
+    __syncthreads();
+    if (em < M && en < N) {
+        float a2 = 0.0f, a1 = 0.0f, a0 = 0.0f, b2 = 0.0f, b1 = 0.0f, b0 = 0.0f;
+#pragma unroll
+        for (int q = 0; q < kGemvWarps; q++) {
+            const float* pr = part + (q * NM + (em >> 1)) * 128 + er * 8 + 4 * (em & 1);      // MMA em/2, columns 4(em%2) .. +2
+            a2 += pr[0]; a1 += pr[1]; a0 += pr[2];
+            if (SWIGLU) { b2 += pr[64]; b1 += pr[65]; b0 += pr[66]; }
+        }
+        float v = fmaf(a2, 65536.0f, fmaf(a1, 256.0f, a0));
+        if (SWIGLU) {
+            float u = fmaf(b2, 65536.0f, fmaf(b1, 256.0f, b0));
+            if (hasBias) v += o.bias;
+            if (hasBias2) u += o.bias2;
+            float sig = 1.0f / (1.0f + expf(-v));
+            out[(size_t)em * ldo + en] = (v * sig) * u;          // SiLU(gate) ⊙ up
+        } else {
+            if (hasBias) v += o.bias;
+            if (GPT && act == 1) v = gelu_ref(v);
+            if (hasRes) v += o.res;
+            out[(size_t)em * ldo + en] = v;
+        }
+    }
+}
+
+}  // namespace dj
