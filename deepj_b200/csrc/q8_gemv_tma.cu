@@ -14,7 +14,8 @@
 // an integer add and a subtraction on the main pipes instead of a conversion-unit instruction.
 //
 // Two CTAs of 8 warps per SM as before (the next kernel's CTAs move in while this one drains); warp w owns the
-// 128-k groups w, w+8, … of every tile of its CTA; DEPTH−1 items (2304 bytes each) per warp in flight.
+// 128-k groups w, w+8, … of every tile of its CTA and stages exactly those groups of the activations itself;
+// two items (2304 bytes each) per warp in flight.
 #include <cuda.h>
 
 #include "kernels.h"
@@ -31,6 +32,10 @@ constexpr int kItemK = 128;                         // reduction length of one i
 constexpr int kCodeBytes = 16 * kItemK;             // 16 rows × 128 code bytes, two 1024-byte swizzle atoms
 constexpr int kScaleBytes = 16 * 16;                // 16 rows × 4 block scales
 constexpr int kItemBytes = kCodeBytes + kScaleBytes;
+// Three items per warp: a deeper ring measured no faster back to back (the kernel waits on the handoff and on the
+// activations, not on bytes in flight) and slower inside the decode step, where a CTA pair of 2 × 96 KB and more takes
+// the L1 capacity that the attention kernel beside it uses.
+constexpr int kDepth = 3;
 constexpr int kSpinLimit = 1 << 22;                 // polls of one item's barrier before the kernel gives up on it
 constexpr int kErrTmaWait = 330;                    // device error code: an item never arrived
 
@@ -78,6 +83,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_tma(const __grid_consta
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long s_bar[kWarps * DEPTH];
     __shared__ float s_red[kWarps];
+    __shared__ float s_ss[4 * kWarps];               // the warps' parts of Σx² per activation row (RMSNorm in the epilogue)
     // layout (from a 1024-byte boundary, which the swizzle pattern wants): code rings [warps][DEPTH][2048], scale rings
     // [warps][DEPTH][256], digits int8 [3M][K+pad], block scales fp32 [M][K/32], partials [2][warps][NM][16][8]
     const uint32_t raw_s = smem_u32(smem_raw);
@@ -134,19 +140,40 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_tma(const __grid_consta
     if (tracing) p.trace[1] = gtime();
     // the norm's gain is a weight as well: fetch it before the wait when one round covers the row
     const int nHalf = p.K >> 4;
-    const bool gammaEarly = p.gamma != nullptr && nHalf <= kThreads;
+    const bool gammaEarly = p.gamma != nullptr && (GPT ? nHalf <= kThreads : nGroups <= 4 * kWarps) &&
+                            (reinterpret_cast<uintptr_t>(p.gamma) & 15) == 0;
     float gpre[16];
+    float4 gpre4[4];
 #pragma unroll
     for (int j = 0; j < 16; j++) gpre[j] = 1.0f;
-    if (gammaEarly && tid < nHalf) load16(p.gamma + tid * 16, (reinterpret_cast<uintptr_t>(p.gamma) & 15) == 0, gpre);
+#pragma unroll
+    for (int j = 0; j < 4; j++) gpre4[j] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    if (GPT) {
+        if (gammaEarly && tid < nHalf) load16(p.gamma + tid * 16, true, gpre);
+    } else if (gammaEarly) {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (warp + kWarps * j < nGroups) gpre4[j] = gemv_load4(p.gamma + (warp + kWarps * j) * 128 + lane * 4, true);
+    }
     pdl_wait();
     if (tracing) p.trace[2] = gtime();
 
-    // activations → digit columns in the MMA fragment's order; the rest of the ring is queued behind the first row's loads
-    gemv_stage_rows<GPT, true>(p.x, p.ldx, p.gamma, p.beta, p.eps, p.K, p.M, xd, ldxs, xsc, s_red, gpre, gammaEarly, [&]() {
-        for (int d = kPre; d < DEPTH - 1; d++) issue_next();
-    });
-    __syncthreads();
+    // activations → digit columns in the MMA fragment's order; the rest of the ring is queued behind the first loads.
+    // Llama / DeepSeek: every warp converts the groups it consumes and goes on by itself, RMSNorm's 1/rms is applied
+    // in the epilogue.  GPT: LayerNorm needs the row's mean first, so the CTA stages the rows together.
+    if (GPT) {
+        gemv_stage_rows<GPT, true>(p.x, p.ldx, p.gamma, p.beta, p.eps, p.K, p.M, xd, ldxs, xsc, s_red, gpre, gammaEarly, [&]() {
+            for (int d = kPre; d < DEPTH - 1; d++) issue_next();
+        });
+        __syncthreads();
+    } else {
+        gemv_stage_warp_groups(p.x, p.ldx, p.gamma, p.K, p.M, xd, ldxs, xsc, s_ss, gpre4, gammaEarly, [&]() {
+            for (int d = kPre; d < DEPTH - 1; d++) issue_next();
+        });
+        if (warp >= nGroups) {                               // a warp without groups still owes the ring its issue slots
+            for (int d = kPre; d < DEPTH - 1; d++) issue_next();
+        }
+    }
     if (tracing) p.trace[3] = gtime();
 
     // lane (g,t) feeds column g of MMA q: activation row 2q + g/4, digit g%4 (digit 3 does not exist)
@@ -216,7 +243,8 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_tma(const __grid_consta
         }
         if (tracing && tile == blockIdx.x) p.trace[4] = gtime();
         gemv_tile_epilogue<SWIGLU, GPT, NM>(acc, s_part + (size_t)buf * kWarps * NM * 128, tile, p.M, p.N, eo, p.bias != nullptr,
-                                            p.bias2 != nullptr, p.residual != nullptr, p.act, p.out, p.ldo);
+                                            p.bias2 != nullptr, p.residual != nullptr, p.act, p.out, p.ldo,
+                                            (!GPT && p.gamma) ? s_ss : nullptr, p.eps, p.K);
         buf ^= 1;
     }
     if (tracing) p.trace[5] = gtime();
@@ -293,15 +321,6 @@ void launch_tma(const GemvTmaParams& p, cudaStream_t s) {
     launch_k(k_q8_gemv_tma<SWIGLU, DEPTH, GPT, NM>, dim3(gx), dim3(kThreads), tma_smem_bytes(p.K, p.M, DEPTH), s, true, p);
 }
 
-template <bool SWIGLU, bool GPT, int NM>
-void launch_tma_depth(const GemvTmaParams& p, int depth, cudaStream_t s) {
-    switch (depth) {
-        case 3: launch_tma<SWIGLU, 3, GPT, NM>(p, s); break;
-        case 4: launch_tma<SWIGLU, 4, GPT, NM>(p, s); break;
-        default: launch_tma<SWIGLU, 5, GPT, NM>(p, s); break;
-    }
-}
-
 }  // namespace
 
 // Returns false when the shape is outside this kernel's domain (K a multiple of 128, rows of at most 12288
@@ -314,7 +333,7 @@ bool launch_q8_gemv_tma(const Q8LinearArgs& a, cudaStream_t s) {
     const bool gpt = a.beta != nullptr || a.act != 0;
     if (gpt && (swiglu || (K >> 4) > kGemvStageRounds * kThreads)) return false;
     if (swiglu && (a.w2.K != K || a.w2.Kp != K || a.w2.N != a.w.N)) return false;
-    if (tma_smem_bytes(K, 1, 3) > kSmemBudget) return false;
+    if (tma_smem_bytes(K, 1, kDepth) > kSmemBudget) return false;
     GemvTmaParams p;
     if (!encode_weight_maps(a.w, &p.codes, &p.scales)) return false;
     if (swiglu) {
@@ -324,9 +343,7 @@ bool launch_q8_gemv_tma(const Q8LinearArgs& a, cudaStream_t s) {
     }
     for (int m0 = 0; m0 < a.M;) {
         int rows = a.M - m0 < 4 ? a.M - m0 : 4;      // 8 MMA columns = 2 activation rows × (3 digits + 1 unused); 3-4 rows take a second MMA
-        while (rows > 1 && tma_smem_bytes(K, rows, 3) > kSmemBudget) rows--;
-        int depth = 5;
-        while (depth > 3 && tma_smem_bytes(K, rows, depth) > kSmemBudget) depth--;
+        while (rows > 1 && tma_smem_bytes(K, rows, kDepth) > kSmemBudget) rows--;
         p.x = a.x + (size_t)m0 * a.ldx; p.ldx = a.ldx; p.gamma = a.gamma; p.eps = a.eps;
         p.beta = a.beta; p.act = a.act;
         p.bias = a.bias; p.bias2 = a.bias2;
@@ -334,18 +351,16 @@ bool launch_q8_gemv_tma(const Q8LinearArgs& a, cudaStream_t s) {
         p.out = a.out + (size_t)m0 * a.ldo; p.ldo = a.ldo;
         p.K = K; p.N = a.w.N; p.M = rows;
         p.pre = 2;
-        { const char* e = getenv("DEEPJ_CUDA_PRE"); if (e) p.pre = atoi(e); }
-        { const char* e = getenv("DEEPJ_CUDA_DEPTH"); if (e) depth = atoi(e); }
         p.error = g_dev_error;
         p.trace = trace_slot();
         if (rows > 2) {
-            if (swiglu) launch_tma_depth<true, false, 2>(p, depth, s);
-            else if (gpt) launch_tma_depth<false, true, 2>(p, depth, s);
-            else launch_tma_depth<false, false, 2>(p, depth, s);
+            if (swiglu) launch_tma<true, kDepth, false, 2>(p, s);
+            else if (gpt) launch_tma<false, kDepth, true, 2>(p, s);
+            else launch_tma<false, kDepth, false, 2>(p, s);
         } else {
-            if (swiglu) launch_tma_depth<true, false, 1>(p, depth, s);
-            else if (gpt) launch_tma_depth<false, true, 1>(p, depth, s);
-            else launch_tma_depth<false, false, 1>(p, depth, s);
+            if (swiglu) launch_tma<true, kDepth, false, 1>(p, s);
+            else if (gpt) launch_tma<false, kDepth, true, 1>(p, s);
+            else launch_tma<false, kDepth, false, 1>(p, s);
         }
         m0 += rows;
     }

@@ -141,6 +141,78 @@ __device__ __forceinline__ void gemv_stage_rows(const float* x, int ldx, const f
     }
 }
 
+__device__ __forceinline__ float4 gemv_load4(const float* src, bool vec) {
+    if (vec) return *reinterpret_cast<const float4*>(src);
+    return make_float4(src[0], src[1], src[2], src[3]);
+}
+
+// Staging for kernels whose warp w consumes only the 128-k groups w, w+8, … of the reduction: the warp converts exactly
+// those groups of every row into its own part of the digit columns, so nothing but the warp itself waits for it — no
+// block-wide barrier stands between the wait for the previous kernel and the first MMA.  RMSNorm is split: the gain
+// is folded into the digits (x·γ), the warp's part of Σx² goes to ss_part[m][warp], and the tile epilogue multiplies
+// the finished sums by 1/rms (Σ_k w_k·(x_k·γ_k)/rms = Σ_k w_k·(x_k/rms·γ_k)).  A lane converts four consecutive
+// values of a group; eight lanes share a 32-k block.  Digits are stored in the MMA fragment's order (digits16<true>).
+constexpr int kGemvWarpGroups = 12;         // groups a warp keeps in registers per load round trip: rows of up to 12288 values in one
+template <class F>
+__device__ __forceinline__ void gemv_stage_warp_groups(const float* x, int ldx, const float* gamma, int K, int M, int8_t* xd, int ldxs,
+                                                       float* xsc, float* ss_part, const float4 (&gpre)[4], bool gammaEarly,
+                                                       F&& after_first_loads) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nGroups = K >> 7, nBlocks = K >> 5;
+    const int j8 = lane & 7;
+    const int pos = j8 < 4 ? 8 * j8 : 8 * (j8 - 4) + 4;          // where the lane's four values sit inside the permuted block
+    for (int m = 0; m < M; m++) {
+        const float* xrow = x + (size_t)m * ldx;
+        const bool vec = ((reinterpret_cast<uintptr_t>(xrow) | (gamma ? reinterpret_cast<uintptr_t>(gamma) : 0)) & 15) == 0;
+        int8_t* dcol = xd + (size_t)(kGemvColsPerRow * m) * ldxs;
+        float* xscRow = xsc + (size_t)m * nBlocks;
+        float ss = 0.0f;
+        for (int g0 = warp; g0 < nGroups; g0 += kGemvWarps * kGemvWarpGroups) {
+            float4 xv[kGemvWarpGroups];
+#pragma unroll
+            for (int i = 0; i < kGemvWarpGroups; i++) {
+                const int grp = g0 + kGemvWarps * i;
+                xv[i] = grp < nGroups ? gemv_load4(xrow + grp * 128 + lane * 4, vec) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+            if (m == 0 && g0 == warp) after_first_loads();
+#pragma unroll
+            for (int i = 0; i < kGemvWarpGroups; i++) {
+                const int grp = g0 + kGemvWarps * i;
+                if (grp >= nGroups) break;                           // warp-uniform
+                float v[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
+                ss = fmaf(v[0], v[0], ss); ss = fmaf(v[1], v[1], ss); ss = fmaf(v[2], v[2], ss); ss = fmaf(v[3], v[3], ss);
+                if (gamma) {
+                    const float4 gv = (gammaEarly && g0 == warp && i < 4) ? gpre[i & 3] : gemv_load4(gamma + grp * 128 + lane * 4, vec);
+                    v[0] *= gv.x; v[1] *= gv.y; v[2] *= gv.z; v[3] *= gv.w;
+                }
+                float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                int sbits = 0x3f800000;                              // as digits16: s = 2^(exponent(amax)+2), q = rne(v·2^23/s)
+                if (amax > 0.0f && amax < 1e36f) sbits = (__float_as_int(amax) & 0x7f800000) + 0x01000000;
+                const float mul = __int_as_float(0x7f000000 - sbits) * 8388608.0f;
+                uint32_t u[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) u[e] = (uint32_t)(__float2int_rn(v[e] * mul) + 0x808080);
+                const uint32_t t0 = __byte_perm(u[0], u[1], 0x5140), t1 = __byte_perm(u[2], u[3], 0x5140);
+                const uint32_t t2 = __byte_perm(u[0], u[1], 0x7362), t3 = __byte_perm(u[2], u[3], 0x7362);
+                const int blk = grp * 4 + (lane >> 3);
+                int8_t* b = dcol + blk * 32 + pos;
+                *reinterpret_cast<uint32_t*>(b) = __byte_perm(t2, t3, 0x5410) ^ 0x80808080u;
+                *reinterpret_cast<uint32_t*>(b + ldxs) = __byte_perm(t0, t1, 0x7632) ^ 0x80808080u;
+                *reinterpret_cast<uint32_t*>(b + 2 * ldxs) = __byte_perm(t0, t1, 0x5410) ^ 0x80808080u;
+                if (j8 == 0) xscRow[blk] = __int_as_float(sbits) * (1.0f / 8388608.0f);
+            }
+        }
+        if (gamma) {
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) ss_part[m * kGemvWarps + warp] = ss;
+        }
+    }
+    __syncwarp();
+}
+
 // Operands of a tile's epilogue, fetched before the tile so that their latency hides behind it: thread `tid`
 // finishes output (row em = tid / rowsPerTile of the activations, column en = tile·rowsPerTile + tid % rowsPerTile).
 struct GemvEpilogueOperands { float bias, bias2, res; };
@@ -161,9 +233,11 @@ __device__ __forceinline__ GemvEpilogueOperands gemv_epilogue_fetch(int tile, in
 
 // Reduces the warps' partial sums of one tile (part: [warps][NM][16 rows][8 columns], column 4(m%2) + d = digit
 // 2 − d of activation row m), recombines the digits and stores the fused result.  acc is zeroed for the next tile.
+// ss_part != nullptr: the sums are of x·γ and get the row's 1/rms here.
 template <bool SWIGLU, bool GPT, int NM>
 __device__ __forceinline__ void gemv_tile_epilogue(float (&acc)[NM][4], float* part, int tile, int M, int N, const GemvEpilogueOperands& o,
-                                                   bool hasBias, bool hasBias2, bool hasRes, int act, float* out, int ldo) {
+                                                   bool hasBias, bool hasBias2, bool hasRes, int act, float* out, int ldo,
+                                                   const float* ss_part = nullptr, float eps = 0.0f, int K = 1) {
     constexpr int rowsPerTile = SWIGLU ? 8 : 16;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int er = tid % rowsPerTile, em = tid / rowsPerTile, en = tile * rowsPerTile + er;
@@ -184,8 +258,16 @@ __device__ __forceinline__ void gemv_tile_epilogue(float (&acc)[NM][4], float* p
             if (SWIGLU) { b2 += pr[64]; b1 += pr[65]; b0 += pr[66]; }
         }
         float v = fmaf(a2, 65536.0f, fmaf(a1, 256.0f, a0));
+        float inv = 1.0f;
+        if (ss_part) {                                   // RMSNorm left to the epilogue (gemv_stage_warp_groups): the warps' parts of Σx² in a fixed order
+            float ss = 0.0f;
+#pragma unroll
+            for (int q = 0; q < kGemvWarps; q++) ss += ss_part[em * kGemvWarps + q];
+            inv = __frcp_rn(sqrtf(ss * (1.0f / (float)K) + eps));
+            v *= inv;
+        }
         if (SWIGLU) {
-            float u = fmaf(b2, 65536.0f, fmaf(b1, 256.0f, b0));
+            float u = fmaf(b2, 65536.0f, fmaf(b1, 256.0f, b0)) * inv;
             if (hasBias) v += o.bias;
             if (hasBias2) u += o.bias2;
             float sig = 1.0f / (1.0f + expf(-v));

@@ -81,6 +81,7 @@ void ensure_init() {
     e = getenv("DEEPJ_CUDA_GEMV");
     if (e && std::string(e) == "fma") g_gemv_mode = 0;
     if (e && std::string(e) == "cpasync") g_gemv_mode = 1;
+    if (e && std::string(e) == "cpasync") g_gemv_mode = 1;
     e = getenv("DEEPJ_CUDA_TRACE");
     if (e && e[0] == '1') {
         DJ_CUDA_CHECK(cudaMalloc((void**)&g_trace, (size_t)kTraceSlots * 8 * sizeof(unsigned long long)));

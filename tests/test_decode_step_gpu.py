@@ -1,9 +1,10 @@
 """The whole-token decode kernel (op 76, `deepj_cuda_decode_plan`) against the per-operator stream.
 
-On one GPU the single kernel runs the per-operator kernels' arithmetic at the same tile, warp and split
-assignments, so logits and tokens must agree bit for bit with the per-operator path — which the other decoder
-tests pin to the CPU oracle (and, since eligible configurations take the single kernel by default, those tests
-check it against the oracle directly as well)."""
+The single kernel runs the arithmetic of the cp.async projection kernel and of the split attention kernel at the
+same tile, warp and split assignments.  The per-operator path takes the TMA projection kernel wherever the
+reduction length is a multiple of 128, which sums the 32-k blocks in another order and applies RMSNorm's 1/rms
+after the sums, so the two paths agree to fp32 rounding (a few 1e-6 of the logit range), not bit for bit; both
+are held to the CPU oracle at the tolerance of the other decoder tests, and the greedy tokens must be equal."""
 import ctypes
 
 import numpy as np
@@ -16,6 +17,8 @@ from deepj_b200.decoder import DecoderConfig, Q8Decoder
 from test_decoder_gpu import weight_getter
 
 pytestmark = pytest.mark.gpu
+
+PATH_TOL = 2e-5      # of the logit range: two fp32 summation orders of the same products
 
 
 def run_steps(cfg, get, prompt, n_new, fused, chunked_prompt):
@@ -42,7 +45,7 @@ def run_steps(cfg, get, prompt, n_new, fused, chunked_prompt):
     (128, 4, 352, 2, 256, 40),         # head dim 32; odd 32-block count (K = 352 → 11 blocks) in the down projection
     (512, 8, 1408, 2, 1000, 70),       # more tiles than virtual CTAs in no phase, more warps than 64-k pairs in none
 ])
-def test_single_kernel_step_equals_the_per_operator_stream_bit_for_bit(d, heads, d_ff, layers, vocab, prompt_len):
+def test_single_kernel_step_agrees_with_the_per_operator_stream(d, heads, d_ff, layers, vocab, prompt_len):
     cfg = DecoderConfig("llama", vocab, 128, d, heads, layers, d_ff)
     assert Q8Decoder.fused_step_eligible(cfg, 1)
     om = oracle.OracleModel("llama", vocab, 128, d, heads, layers, d_ff, seed=77 + d)
@@ -51,14 +54,15 @@ def test_single_kernel_step_equals_the_per_operator_stream_bit_for_bit(d, heads,
     # token by token from position 0: every step of the fused run is the single kernel
     tok_a, log_a, st_a = run_steps(cfg, get, prompt, 10, fused=False, chunked_prompt=False)
     tok_b, log_b, st_b = run_steps(cfg, get, prompt, 10, fused=True, chunked_prompt=False)
+    span_a = float(log_a.max() - log_a.min())
     assert np.array_equal(tok_a, tok_b)
-    assert np.array_equal(log_a.view(np.uint32), log_b.view(np.uint32)), float(np.abs(log_a - log_b).max())
+    assert float(np.abs(log_a - log_b).max()) <= PATH_TOL * span_a, float(np.abs(log_a - log_b).max()) / span_a
     # and behind a chunked prompt pass (prompts of 32 tokens or more), whose cache rows the many-row kernels wrote
     if prompt_len >= 32:
         tok_c, log_c, _ = run_steps(cfg, get, prompt, 10, fused=False, chunked_prompt=True)
         tok_d, log_d, _ = run_steps(cfg, get, prompt, 10, fused=True, chunked_prompt=True)
         assert np.array_equal(tok_c, tok_d)
-        assert np.array_equal(log_c[1:].view(np.uint32), log_d[1:].view(np.uint32))
+        assert float(np.abs(log_c[1:] - log_d[1:]).max()) <= PATH_TOL * span_a
     # the oracle agrees with both
     om.apply_q8()
     toks_o, logits_o = om.generate_greedy(prompt, 10, use_cache=True)
