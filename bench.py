@@ -487,6 +487,7 @@ def main():
         d16.close()
 
     # ── the same model at 16 concurrent sequences (BASELINE configs[4] asks for 1 and 16), sharing the weights ──
+    fail16 = False
     if batch16:
         w16 = dict(WORKLOADS["llama7b_q8_decode_b16"])
         dec16 = Q8Decoder(cfg, batch=16, device=local_rank, id_base=5 << 24, tp_rank=rank, tp_world=world,
@@ -498,6 +499,25 @@ def main():
         t16 = time.perf_counter()
         nxt16 = dec16.prefill(p16)
         t16 = time.perf_counter() - t16
+        par16 = None
+        if not args.no_parity:
+            # full-depth check of the several-row kernels: sequence 0 of the batch against the same prompt decoded alone
+            # (single-row kernels, themselves held to the oracle above), logits of the prompt's last token and of four
+            # teacher-forced steps
+            dec.reset()
+            n1 = dec.prefill(p16[:1])
+            rows1, rows16, toks1, toks16 = [dec.logits()[0].copy()], [dec16.logits()[0].copy()], [int(n1[0])], [int(nxt16[0])]
+            for _ in range(4):
+                fed = np.asarray(nxt16[:1]).copy()           # both decoders get the batch's own pick for sequence 0
+                nxt16 = dec16.step(nxt16)
+                n1 = dec.step(fed)
+                rows1.append(dec.logits()[0].copy()); rows16.append(dec16.logits()[0].copy())
+                toks1.append(int(n1[0])); toks16.append(int(nxt16[0]))
+            r1, r16 = np.stack(rows1), np.stack(rows16)
+            err16 = float(np.abs(r1 - r16).max()) / float(r1.max() - r1.min())
+            par16 = {"max_err_over_range": err16, "tokens_equal": toks1 == toks16, "tolerance": 2e-3,
+                     "checked": f"all {cfg.n_layers} blocks, 16 sequences at context {w16['prompt']}: sequence 0's logits after the prompt and after "
+                                "four steps vs the same prompt decoded alone (single-row kernels)"}
         dec16.set_tokens(nxt16)
         m16 = measure_decode(dec16, w16, args, world, local_rank, tp, max(1, min(args.repeats, 3)))
         prof16 = dec16.profile_step()
@@ -517,6 +537,11 @@ def main():
             "prefill": {"tokens": 16 * w16["prompt"], "seconds": t16},
             "profile_ms_op_by_op": by_label,
         }
+        if par16 is not None:
+            line["batch16"]["parity_vs_single_sequence"] = par16
+            if not (par16["tokens_equal"] and par16["max_err_over_range"] <= par16["tolerance"]):
+                line["batch16"]["error"] = "parity check failed: the timings of this sub-record do not count"
+                fail16 = True
         dec16.close()
         if kv16 and not args.no_parity:
             # … and with the fp16 K/V cache (16 sequences read 16 caches per step: the K/V rows are most of the bytes)
@@ -547,6 +572,8 @@ def main():
     dec.close()
     if world > 1:
         tp.disconnect()
+    if fail16:
+        raise SystemExit(3)
 
 
 if __name__ == "__main__":

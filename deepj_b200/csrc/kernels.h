@@ -92,6 +92,7 @@ bool q8_gemv_i8_fuses_gpt(const Q8LinearArgs& a);     // true when launch_q8_gem
 void launch_layernorm_rows(const float* x, int ldx, const float* gamma, const float* beta, float eps, float* out, int K, int M, cudaStream_t s);
 void launch_gelu_rows(float* buf, int ld, int N, int M, cudaStream_t s);
 bool launch_q8_linear_batch(const Q8LinearArgs& a, int m0, int rows, float* ws, int* tickets, cudaStream_t s);
+bool launch_q8_linear_batch_tma(const Q8LinearArgs& a, int m0, int rows, float* ws, int* tickets, cudaStream_t s);   // K a multiple of 128; same workspace
 size_t q8_batch_ws_floats(int K, int N, bool swiglu);
 bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s);
 size_t q8_tc_ws_floats(int M, int K);

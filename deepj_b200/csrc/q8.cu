@@ -363,7 +363,10 @@ void dispatch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
     if (batchOk) {
         // five or more rows share one pass over the weights, 16 at a time (up to four are two GEMV passes, which is as fast)
         bool ok = true;
-        for (int m0 = 0; m0 < a.M && ok; m0 += 16) ok = launch_q8_linear_batch(a, m0, a.M - m0 < 16 ? a.M - m0 : 16, a.ws, a.tickets, s);
+        for (int m0 = 0; m0 < a.M && ok; m0 += 16) {
+            const int rows = a.M - m0 < 16 ? a.M - m0 : 16;
+            ok = (g_gemv_mode == 2 && launch_q8_linear_batch_tma(a, m0, rows, a.ws, a.tickets, s)) || launch_q8_linear_batch(a, m0, rows, a.ws, a.tickets, s);
+        }
         if (ok) return;
     }
     if (g_gemv_mode == 2 && launch_q8_gemv_tma(a, s)) return;

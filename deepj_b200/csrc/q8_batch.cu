@@ -20,6 +20,7 @@
 // epilogue; Σx² of every 512-chunk of a row is left in the workspace by the CTAs that stage it.
 #include "kernels.h"
 #include "q8_common.cuh"
+#include "q8_batch_tail.cuh"
 #include <cuda_fp16.h>
 #include <cstdlib>
 
@@ -35,8 +36,8 @@ constexpr int kSlice = 512;                 // reduction length per work item = 
 constexpr int kLdx = kSlice * 2 + 64;       // bytes per fp16 activation column (64 mod 128: conflict-free 16-byte reads)
 constexpr int kDepth = 6;                   // ring slots per warp
 constexpr int kPre = 2;                     // of which fetched before the previous kernel has finished
-constexpr int kMaxRows = 16;                // activation rows per launch
-constexpr int kTileFloats = kMaxRows * 16;  // one (tile, slice) record: partial sums [16 activation rows][16 weight rows]
+constexpr int kMaxRows = kBatchMaxRows;
+constexpr int kTileFloats = kBatchTileFloats;
 
 struct BatchParams {
     const float* x; int ldx;
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemm_f16(const BatchParams p
     const int soff = kRows * kRowStride + g * 8;
     const int nChunksK = (p.K + kSlice - 1) / kSlice;
 
+    const BatchTail tail = {p.gamma, p.eps, p.bias, p.bias2, p.residual, p.ldr, p.out, p.ldo, p.K, p.N, p.M, p.nSlices, p.ws, p.ssq, p.tickets};
     int staged = -1, cslot = 0;
     for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
         const int slice = item % p.nSlices, grp = item / p.nSlices;
@@ -279,72 +281,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemm_f16(const BatchParams p
                 rec[m * 16 + g + 8] = (acc[j][2] + acc[j][3]) * up;
             }
         }
-        // ── the warp that arrives last at this tile adds the slices, in slice order, and finishes the outputs ──
-        __threadfence();
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) {
-            const int ticket = atomicAdd(&p.tickets[tile], 1);
-            last = ticket == p.nSlices - 1;
-            if (last) p.tickets[tile] = 0;                  // ready for the next launch
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (!last) continue;
-        __threadfence();
-        float inv = 1.0f;
-        if (p.gamma && lane < p.M) {
-            float ss = 0.0f;
-            for (int c = 0; c < nChunksK; c++) ss += __ldcg(p.ssq + c * kMaxRows + lane);
-            inv = __frcp_rn(sqrtf(ss * (1.0f / (float)p.K) + p.eps));
-        }
-        // every lane owns up to 8 outputs (SwiGLU: 4 gate/up pairs); the partials of 4 slices × all of them
-        // are requested before any is added, so a tile costs one load round trip per 4 slices
-        const float* base = p.ws + (size_t)tile * p.nSlices * kTileFloats;
-        const int nOut = p.M * rowsPerTile;
-        constexpr int kIdx = SWIGLU ? 4 : 8;
-        constexpr int kSliceBatch = 4;
-        float v[kIdx], u[kIdx];
-#pragma unroll
-        for (int i = 0; i < kIdx; i++) { v[i] = 0.0f; u[i] = 0.0f; }
-        for (int s0 = 0; s0 < p.nSlices; s0 += kSliceBatch) {
-            float tv[kIdx][kSliceBatch], tu[SWIGLU ? kIdx : 1][kSliceBatch];
-#pragma unroll
-            for (int i = 0; i < kIdx; i++) {
-                const int idx = lane + 32 * i;
-                const int m = idx / rowsPerTile, r = idx % rowsPerTile;
-#pragma unroll
-                for (int q = 0; q < kSliceBatch; q++) {
-                    const bool ok = idx < nOut && s0 + q < p.nSlices;
-                    const float* src = base + (size_t)(s0 + q) * kTileFloats + m * 16 + r;
-                    tv[i][q] = ok ? __ldcg(src) : 0.0f;
-                    if (SWIGLU) tu[i][q] = ok ? __ldcg(src + 8) : 0.0f;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < kIdx; i++)
-#pragma unroll
-                for (int q = 0; q < kSliceBatch; q++) { v[i] += tv[i][q]; if (SWIGLU) u[i] += tu[i][q]; }
-        }
-#pragma unroll
-        for (int i = 0; i < kIdx; i++) {
-            const int idx = lane + 32 * i;
-            const int m = idx / rowsPerTile, r = idx % rowsPerTile;
-            const float invm = __shfl_sync(0xffffffffu, inv, m & 31);
-            const int n = tile * rowsPerTile + r;
-            if (idx >= nOut || n >= p.N) continue;
-            float vv = v[i] * invm;
-            if (SWIGLU) {
-                float uu = u[i] * invm;
-                if (p.bias) vv += p.bias[n];
-                if (p.bias2) uu += p.bias2[n];
-                const float sig = 1.0f / (1.0f + expf(-vv));
-                p.out[(size_t)m * p.ldo + n] = (vv * sig) * uu;
-            } else {
-                if (p.bias) vv += p.bias[n];
-                if (p.residual) vv += p.residual[(size_t)m * p.ldr + n];
-                p.out[(size_t)m * p.ldo + n] = vv;
-            }
-        }
+        batch_finish_tile<SWIGLU>(tail, tile, nChunksK);
     }
     cp_async_wait<0>();
     if (tracing) p.trace[5] = gtime();

@@ -21,6 +21,7 @@
 #include "kernels.h"
 #include "q8_common.cuh"
 #include "q8_stage.cuh"
+#include "q8_tma.cuh"
 
 namespace dj {
 
@@ -28,7 +29,7 @@ namespace {
 
 constexpr int kWarps = kGemvWarps;
 constexpr int kThreads = kGemvThreads;
-constexpr int kItemK = 128;                         // reduction length of one item
+constexpr int kItemK = kTmaItemK;
 constexpr int kCodeBytes = 16 * kItemK;             // 16 rows × 128 code bytes, two 1024-byte swizzle atoms
 constexpr int kScaleBytes = 16 * 16;                // 16 rows × 4 block scales
 constexpr int kItemBytes = kCodeBytes + kScaleBytes;
@@ -52,30 +53,6 @@ struct GemvTmaParams {
     int* error;
     unsigned long long* trace;
 };
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// one box of a two-dimensional tensor map → shared memory; x counts elements of the inner dimension, y rows
-__device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
-}
-// exact for |v| < 2^22: the integer lands in the mantissa of 1.5 · 2^23
-__device__ __forceinline__ float int_to_float_exact(int v) { return __int_as_float(v + 0x4B400000) - 12582912.0f; }
 
 // NM = 2 takes three or four activation rows in one pass over the weights (a second MMA per block).
 template <bool SWIGLU, int DEPTH, bool GPT, int NM>
@@ -257,13 +234,32 @@ size_t tma_smem_bytes(int K, int M, int depth) {
 }
 constexpr size_t kSmemBudget = 112 * 1024;       // two CTAs per SM
 
+template <bool SWIGLU, int DEPTH, bool GPT, int NM>
+void launch_tma(const GemvTmaParams& p, cudaStream_t s) {
+    static bool attrSet = false;
+    if (!attrSet) {
+        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemv_tma<SWIGLU, DEPTH, GPT, NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+        attrSet = true;
+    }
+    const int rowsPerTile = SWIGLU ? 8 : 16;
+    const int nTiles = (p.N + rowsPerTile - 1) / rowsPerTile;
+    // every CTA gets the same number of tiles (±1 only in the last round): the grid is the smallest one that
+    // keeps the rounds of the full grid
+    const int cap = 2 * g_num_sms;
+    const int rounds = (nTiles + cap - 1) / cap;
+    const int gx = (nTiles + rounds - 1) / rounds;
+    launch_k(k_q8_gemv_tma<SWIGLU, DEPTH, GPT, NM>, dim3(gx), dim3(kThreads), tma_smem_bytes(p.K, p.M, DEPTH), s, true, p);
+}
+
+}  // namespace
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // The driver's tensor-map encoder, looked up through the runtime so that the library carries no link-time
 // dependency on the driver (it must load on machines without one).
-EncodeTiledFn encode_tiled_fn() {
+static EncodeTiledFn encode_tiled_fn() {
     static EncodeTiledFn fn = []() -> EncodeTiledFn {
         void* sym = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -278,7 +274,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 // Tensor maps over one Q8 weight: codes [N][Kp] bytes in boxes of 8 rows × 128 bytes (128-byte swizzle) and
 // scales [N][nb] floats in boxes of 8 rows × 4.
-bool encode_weight_maps(const Q8View& w, CUtensorMap* codes, CUtensorMap* scales) {
+bool q8_encode_weight_maps(const Q8View& w, CUtensorMap* codes, CUtensorMap* scales) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return false;
     if ((reinterpret_cast<uintptr_t>(w.codes) & 15) != 0 || (reinterpret_cast<uintptr_t>(w.scales) & 15) != 0) return false;
@@ -304,25 +300,6 @@ bool encode_weight_maps(const Q8View& w, CUtensorMap* codes, CUtensorMap* scales
     return true;
 }
 
-template <bool SWIGLU, int DEPTH, bool GPT, int NM>
-void launch_tma(const GemvTmaParams& p, cudaStream_t s) {
-    static bool attrSet = false;
-    if (!attrSet) {
-        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemv_tma<SWIGLU, DEPTH, GPT, NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-        attrSet = true;
-    }
-    const int rowsPerTile = SWIGLU ? 8 : 16;
-    const int nTiles = (p.N + rowsPerTile - 1) / rowsPerTile;
-    // every CTA gets the same number of tiles (±1 only in the last round): the grid is the smallest one that
-    // keeps the rounds of the full grid
-    const int cap = 2 * g_num_sms;
-    const int rounds = (nTiles + cap - 1) / cap;
-    const int gx = (nTiles + rounds - 1) / rounds;
-    launch_k(k_q8_gemv_tma<SWIGLU, DEPTH, GPT, NM>, dim3(gx), dim3(kThreads), tma_smem_bytes(p.K, p.M, DEPTH), s, true, p);
-}
-
-}  // namespace
-
 // Returns false when the shape is outside this kernel's domain (K a multiple of 128, rows of at most 12288
 // values when a LayerNorm is fused, a ring of at least three items beside the digits); the caller then takes
 // the cp.async kernel.
@@ -335,9 +312,9 @@ bool launch_q8_gemv_tma(const Q8LinearArgs& a, cudaStream_t s) {
     if (swiglu && (a.w2.K != K || a.w2.Kp != K || a.w2.N != a.w.N)) return false;
     if (tma_smem_bytes(K, 1, kDepth) > kSmemBudget) return false;
     GemvTmaParams p;
-    if (!encode_weight_maps(a.w, &p.codes, &p.scales)) return false;
+    if (!q8_encode_weight_maps(a.w, &p.codes, &p.scales)) return false;
     if (swiglu) {
-        if (!encode_weight_maps(a.w2, &p.codes2, &p.scales2)) return false;
+        if (!q8_encode_weight_maps(a.w2, &p.codes2, &p.scales2)) return false;
     } else {
         p.codes2 = p.codes; p.scales2 = p.scales;
     }

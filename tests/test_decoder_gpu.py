@@ -132,10 +132,10 @@ def test_batched_sequences_are_independent():
     perm = [2, 0, 5, 1, 3, 4]
     moved = batch_logits(perm)
     for b in range(6):
-        # five or more rows run on the batched kernel, whose summation order differs from the
-        # single-row kernel's: equal within the Q8 tolerance, and bit-identical wherever the row sits
+        # five or more rows run on the several-row kernel (16-bit fixed-point activations, another summation order):
+        # equal to the single-row path well inside the Q8 tolerance of 2e-3, and bit-identical wherever the row sits
         scale = float(np.abs(single[b]).max())
-        assert float(np.abs(got[b] - single[b]).max()) <= 1e-4 * scale
+        assert float(np.abs(got[b] - single[b]).max()) <= 5e-4 * scale
     for slot, b in enumerate(perm):
         assert np.array_equal(moved[slot].view(np.uint32), got[b].view(np.uint32))
 

@@ -12,11 +12,14 @@ from deepj_b200.compute_graph import OP_Q8_LINEAR, OP_Q8_SWIGLU, float_bits
 pytestmark = pytest.mark.gpu
 
 ATOL, RTOL = 1e-4, 1e-4      # the reference's GPU-vs-CPU comparator: |e-a| <= atol + rtol*|e|
+MANY_ROW_FLOOR = 1e-4        # of the largest |expected|, for five activation rows and more
 
 
 def close(expected, actual, atol=ATOL, rtol=RTOL, floor=0.0):
-    """|error| ≤ atol + rtol·|expected| + floor·max|expected|.  The floor term is for the many-row kernels,
-    whose tensor-core accumulation carries ≈ 2^-18 of the output scale (the stated Q8 tolerance is 2e-3 of it)."""
+    """|error| ≤ atol + rtol·|expected| + floor·max|expected|.  The floor term is for the several-row kernels: the
+    5 … 16-row kernel multiplies 16-bit fixed-point activations (an error of up to 2^-16 of a 32-k block's largest
+    value per element), the tensor-core GEMM accumulates fp16 products with ≈ 2^-18 of the output scale; the stated
+    Q8 tolerance is 2e-3 of the output scale."""
     err = np.abs(expected - actual)
     bound = atol + rtol * np.abs(expected) + floor * float(np.abs(expected).max())
     worst = np.unravel_index(np.argmax(err - bound), err.shape)
@@ -150,7 +153,7 @@ def test_q8_linear_matches_oracle(dev, M, K, N, fused):
         expected = (oracle.matmul(oracle_rmsnorm(x, gamma), Wq) + bias) + res
         gb, bb, rb = dev.buf(K, gamma), dev.buf(N, bias), dev.buf(M * N, res)
         dev.flush([OP_Q8_LINEAR, xb, 0, K, gb, float_bits(1e-6), q, bb, rb, 0, N, ob, 0, N, M])
-    close(expected, dev.get(ob, M * N).reshape(M, N), floor=2e-5 if M >= 5 else 0.0)
+    close(expected, dev.get(ob, M * N).reshape(M, N), floor=MANY_ROW_FLOOR if M >= 5 else 0.0)
 
 
 @pytest.mark.parametrize("M,K,F", [(1, 256, 688), (2, 256, 100), (1, 4096, 256), (1, 2048, 5632),
@@ -172,7 +175,7 @@ def test_q8_swiglu_matches_oracle(dev, M, K, F):
     qg, qu = dev.q8(Wg), dev.q8(Wu)
     xb, gb, bgb, bub, ob = dev.buf(M * K, x), dev.buf(K, gamma), dev.buf(F, bg), dev.buf(F, bu), dev.buf(M * F)
     dev.flush([OP_Q8_SWIGLU, xb, 0, K, gb, float_bits(1e-6), qg, bgb, qu, bub, ob, 0, F, M])
-    close(expected, dev.get(ob, M * F).reshape(M, F), floor=2e-5 if M >= 5 else 0.0)
+    close(expected, dev.get(ob, M * F).reshape(M, F), floor=MANY_ROW_FLOOR if M >= 5 else 0.0)
 
 
 def test_q8_linear_strided_windows(dev):
