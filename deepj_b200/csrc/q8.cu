@@ -352,12 +352,14 @@ void dispatch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
     const bool swiglu = a.w2.codes != nullptr;
     static const bool noTc = getenv("DEEPJ_CUDA_NO_TC") != nullptr;
     const bool batchOk = g_gemv_mode >= 1 && a.M >= 5 && a.ws != nullptr && a.w.K % 32 == 0 && a.w.Kp == a.w.K;
-    // A few dozen rows leave most SMs without a 128 × 256 tile: passes of the 16-row kernel (≈ 0.9 ps per weight and
-    // pass, measured) win until the tensor-core grid fills up.
+    // A few dozen rows leave most SMs without a 128 × 256 tile: passes of the 16-row kernel (≈ 3 µs + 0.5 ps per weight
+    // and pass with the TMA kernel, 0.9 ps with the cp.async one; measured on 4096 × 12288, 11008 × 4096 and 4096 × 4096)
+    // win until the tensor-core grid fills up.
     bool preferBatch = false;
     if (batchOk && a.M >= kTcMinRows && a.M <= 256) {
-        const double batchUs = (double)((a.M + 15) / 16) * 0.9e-6 * (double)a.w.K * (double)a.w.N;
-        preferBatch = batchUs < q8_tc_estimate_us(a.M, a.w.K, a.w.N);
+        const bool tmaKernel = g_gemv_mode == 2 && a.w.K % 128 == 0;
+        const double perPassUs = tmaKernel ? 3.0 + 0.5e-6 * (double)a.w.K * (double)a.w.N : 0.9e-6 * (double)a.w.K * (double)a.w.N;
+        preferBatch = (double)((a.M + 15) / 16) * perPassUs < q8_tc_estimate_us(a.M, a.w.K, a.w.N);
     }
     if (g_gemv_mode >= 1 && !noTc && !preferBatch && a.M >= kTcMinRows && a.ws != nullptr && launch_q8_linear_tc(a, a.ws, s)) return;
     if (batchOk) {
