@@ -54,8 +54,8 @@ WORKLOADS = {
 
 # DRAM bytes (read + write) over algorithmic bytes of one k_decode_step launch, from the ncu capture of a reduced-depth
 # model of the same width (profiles/); None until a capture exists.  Traffic grows with the weights and K/V rows streamed.
-DECODE_STEP_DRAM_RATIO = None
-DECODE_STEP_DRAM_SOURCE = "no capture yet"
+DECODE_STEP_DRAM_RATIO = (742.42 + 60.54) / 737.0
+DECODE_STEP_DRAM_SOURCE = "profiles/decode_step_2blocks_7bwidth_ncu.md (742.4 MB read + 60.5 MB written for 737 MB algorithmic on a 2-block model), scaled by algorithmic bytes"
 
 
 def measured_peak_gbs():
@@ -435,9 +435,9 @@ def main():
         "roofline_gemv" if dec.fused_step else "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # DRAM bytes per launch (read + write), scaled by K·N from the ncu capture of the K=4096, N=12288
                      # launch (56.869 MB measured against 56.69 MB algorithmic): the full-size step is too large to capture
-                     "traffic": (gemv_bytes / max(n_gemv, 1)) * (56.869 / 56.69), "traffic_unit": "bytes per launch (average)",
-                     "traffic_source": "profiles/q8_gemv_i8_k4096_n12288_ncu.md, scaled by algorithmic bytes",
-                     "peak_kind": peak_kind, "kernel": "k_q8_gemv", "launches_per_step": n_gemv,
+                     "traffic": (gemv_bytes / max(n_gemv, 1)) * (56.826 / 56.689), "traffic_unit": "bytes per launch (average)",
+                     "traffic_source": "profiles/q8_gemv_tma_k4096_n12288_ncu.md (56.709 MB read + 0.117 MB written per launch, mean of two, for 56.689 MB algorithmic), scaled by algorithmic bytes",
+                     "peak_kind": peak_kind, "kernel": "k_q8_gemv_tma", "launches_per_step": n_gemv,
                      "bytes_per_step": gemv_bytes, "us_per_launch": 1e3 * gemv_stream_ms / max(n_gemv_stream, 1),
                      "ms_per_step_back_to_back": gemv_stream_ms, "ms_per_step_op_by_op": gemv_ms},
         "roofline_attention": {"bound": "hbm", "kernel": "k_attn_decode", "launches_per_step": n_attn,

@@ -35,7 +35,10 @@ constexpr int kSlice = 512;                          // reduction length per wor
 constexpr int kCodeBytes = 16 * kTmaItemK;           // 16 rows × 128 code bytes, two 1024-byte swizzle atoms
 constexpr int kScaleBytes = 16 * 16;                 // 16 rows × 4 block scales
 constexpr int kItemBytes = kCodeBytes + kScaleBytes;
-constexpr int kDepth = 4;                            // ring slots per warp (three items in flight)
+// Ring slots per warp (two items in flight).  Measured in the 16-sequence decode step of the 7B model: 3 slots 8.75 ms,
+// 4 slots 8.83 ms, 5 slots 11.1 ms per step with identical times back to back — the shared memory a deeper ring takes is
+// L1 capacity that the attention kernel beside it (two thirds of that step) uses.
+constexpr int kRingDepth = 3;
 constexpr int kPre = 2;                              // of which fetched before the previous kernel has finished
 constexpr int kLdx = kSlice + 32;                    // bytes per activation byte column (32 mod 128: conflict-free 8-byte reads)
 constexpr int kCols = 2 * kBatchMaxRows;             // high-byte columns of rows 0..15, then low-byte columns
@@ -61,7 +64,7 @@ __device__ __forceinline__ void mma_s8u8_16832(int (&c)[4], uint32_t a0, uint32_
 }
 
 // NP = MMA pairs per block: activation rows 0..7 (NP = 1) or 0..15 (NP = 2)
-template <bool SWIGLU, int NP>
+template <bool SWIGLU, int NP, int kDepth>
 __global__ void __launch_bounds__(kThreads, 2) k_q8_gemm_i8(const __grid_constant__ BatchTmaParams p) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long s_bar[kWarps * kDepth];
@@ -188,7 +191,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemm_i8(const __grid_constan
                         whi[j] = __byte_perm(t0, t1, 0x7632);          // bits 8-15: the signed high byte
                     }
                     if (on[u]) {
-                        // permuted block order (digits16<true>): the lane's values 4j … 4j+3 sit at 8j + 4·(half of the block)
+                        // the block order of the MMA's B fragment (as gemv_stage_warp_groups): the lane's values 4j … 4j+3 sit at 8j + 4·(half of the block)
                         unsigned char* bh = xd + (size_t)m * kLdx + (lane >> 1) * 32 + (lane & 1) * 4;
                         unsigned char* bl = bh + (size_t)kBatchMaxRows * kLdx;
 #pragma unroll
@@ -337,22 +340,22 @@ __global__ void __launch_bounds__(256) k_q8_batch_reduce(const BatchTail t, int 
     }
 }
 
-constexpr size_t batch_tma_smem() {
+constexpr size_t batch_tma_smem(int kDepth) {
     return 1024 + (size_t)kWarps * kDepth * kItemBytes + (size_t)kCols * kLdx + (size_t)kBatchMaxRows * kXsLd * 4;
 }
 
-template <bool SWIGLU, int NP>
+template <bool SWIGLU, int NP, int kDepth>
 void launch_batch_tma(const BatchTmaParams& p, cudaStream_t s) {
     static bool attrSet = false;
     if (!attrSet) {
-        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemm_i8<SWIGLU, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)batch_tma_smem()));
+        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemm_i8<SWIGLU, NP, kDepth>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)batch_tma_smem(kDepth)));
         attrSet = true;
     }
     const int nItems = p.nGroups * p.nSlices;
     int cap = 2 * g_num_sms;
     if (p.nSlices <= cap) cap -= cap % p.nSlices;       // a CTA then keeps its slice from item to item
     const int gx = nItems < cap ? nItems : cap;
-    launch_k(k_q8_gemm_i8<SWIGLU, NP>, dim3(gx), dim3(kThreads), batch_tma_smem(), s, true, p);
+    launch_k(k_q8_gemm_i8<SWIGLU, NP, kDepth>, dim3(gx), dim3(kThreads), batch_tma_smem(kDepth), s, true, p);
     const int nChunksK = (p.K + kSlice - 1) / kSlice;
     launch_k(k_q8_batch_reduce<SWIGLU>, dim3(p.nTiles < 4 * g_num_sms ? p.nTiles : 4 * g_num_sms), dim3(256), 0, s, true, p.tail, p.nTiles, nChunksK);
 }
@@ -391,9 +394,9 @@ bool launch_q8_linear_batch_tma(const Q8LinearArgs& a, int m0, int rows, float* 
     p.error = g_dev_error;
     p.trace = trace_slot();
     if (swiglu) {
-        if (rows <= 8) launch_batch_tma<true, 1>(p, s); else launch_batch_tma<true, 2>(p, s);
+        if (rows <= 8) launch_batch_tma<true, 1, kRingDepth>(p, s); else launch_batch_tma<true, 2, kRingDepth>(p, s);
     } else {
-        if (rows <= 8) launch_batch_tma<false, 1>(p, s); else launch_batch_tma<false, 2>(p, s);
+        if (rows <= 8) launch_batch_tma<false, 1, kRingDepth>(p, s); else launch_batch_tma<false, 2, kRingDepth>(p, s);
     }
     return true;
 }

@@ -51,10 +51,6 @@ __device__ __forceinline__ void load16(const float* src, bool vec, float (&v)[16
 // block's power-of-two scale.  q = rne(v·2^23/s) with |q| ≤ 2^22; adding 128 at every digit turns
 // the balanced digits e2,e1,e0 ∈ [−128,127] into the plain bytes of q + 0x808080, and flipping each
 // top bit turns them back: one add per value, a 4×4 byte transpose per four values.
-// PERM = false stores a block's 32 values in k order.  PERM = true stores them in the order of the int8 MMA's B
-// fragment, so that lane t fetches both of its registers (k = 4t … 4t+3 and k = 16+4t … 16+4t+3) with one 8-byte
-// load at offset 8t: value k sits at 8·((k mod 16)/4) + 4·(k/16) + k mod 4.
-template <bool PERM = false>
 __device__ __forceinline__ void digits16(const float (&v)[16], bool on, int8_t* dcol, int ldxs, int hb, float* xscRow) {
     float amax = 0.0f;
 #pragma unroll
@@ -77,19 +73,9 @@ __device__ __forceinline__ void digits16(const float (&v)[16], bool on, int8_t* 
         w2[j] = __byte_perm(t2, t3, 0x5410) ^ 0x80808080u;
     }
     if (on) {
-        if (PERM) {
-            int8_t* b = dcol + (hb >> 1) * 32 + (hb & 1) * 4;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                *reinterpret_cast<uint32_t*>(b + 8 * j) = w2[j];
-                *reinterpret_cast<uint32_t*>(b + ldxs + 8 * j) = w1[j];
-                *reinterpret_cast<uint32_t*>(b + 2 * ldxs + 8 * j) = w0[j];
-            }
-        } else {
-            *reinterpret_cast<uint4*>(dcol + hb * 16) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
-            *reinterpret_cast<uint4*>(dcol + ldxs + hb * 16) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
-            *reinterpret_cast<uint4*>(dcol + 2 * ldxs + hb * 16) = make_uint4(w0[0], w0[1], w0[2], w0[3]);
-        }
+        *reinterpret_cast<uint4*>(dcol + hb * 16) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+        *reinterpret_cast<uint4*>(dcol + ldxs + hb * 16) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+        *reinterpret_cast<uint4*>(dcol + 2 * ldxs + hb * 16) = make_uint4(w0[0], w0[1], w0[2], w0[3]);
         if ((hb & 1) == 0) xscRow[hb >> 1] = __int_as_float(sbits) * (1.0f / 8388608.0f);
     }
 }

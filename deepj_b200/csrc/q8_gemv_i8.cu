@@ -1,5 +1,8 @@
-// Q8 GEMV on the integer tensor pipe with warp-private cp.async rings — the decode
-// hot kernel for up to two activation rows per pass.
+// Q8 GEMV on the integer tensor pipe with warp-private cp.async rings — up to four activation rows
+// per pass, for reduction lengths that are multiples of 32.  Reduction lengths that are multiples of 128
+// take the TMA kernel (q8_gemv_tma.cu, same arithmetic); this one serves the rest (tensor maps want
+// 16-byte row pitches, i.e. K/32 scales per row a multiple of 4) and row counts whose digits do not fit
+// beside the TMA kernel's ring.
 //
 // HBM-bound: 1.125 bytes per weight, read exactly once.  Two persistent CTAs of 8
 // warps per SM walk 16-row weight tiles (two, so that the next kernel's CTAs can move
@@ -150,7 +153,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_i8(const GemvI8Params p
 
     // activations → three int8 digit columns + one power-of-two scale per 32-k block (norm fused); more of the
     // ring is queued behind the first row's loads
-    gemv_stage_rows<GPT, false>(p.x, p.ldx, p.gamma, p.beta, p.eps, p.K, p.M, xd, ldxs, xsc, s_red, gpre, gammaEarly, [&]() {
+    gemv_stage_rows<GPT>(p.x, p.ldx, p.gamma, p.beta, p.eps, p.K, p.M, xd, ldxs, xsc, s_red, gpre, gammaEarly, [&]() {
         if (haveWork) {
             for (int d = kPre; d < kMid; d++) issue_next();
         }

@@ -15,7 +15,8 @@
 //
 // Two CTAs of 8 warps per SM as before (the next kernel's CTAs move in while this one drains); warp w owns the
 // 128-k groups w, w+8, … of every tile of its CTA and stages exactly those groups of the activations itself;
-// two items (2304 bytes each) per warp in flight.
+// two items (2304 bytes each) per warp in flight.  Projections with a fused LayerNorm or GELU (GPT blocks) stay on
+// the cp.async kernel.
 #include <cuda.h>
 
 #include "kernels.h"
@@ -44,7 +45,6 @@ struct GemvTmaParams {
     CUtensorMap codes, scales, codes2, scales2;     // boxes of 8 rows; the second pair is the SwiGLU up projection
     const float* x; int ldx;
     const float* gamma; float eps;
-    const float* beta; int act;
     const float* bias; const float* bias2;
     const float* residual; int ldr;
     float* out; int ldo;
@@ -55,11 +55,10 @@ struct GemvTmaParams {
 };
 
 // NM = 2 takes three or four activation rows in one pass over the weights (a second MMA per block).
-template <bool SWIGLU, int DEPTH, bool GPT, int NM>
+template <bool SWIGLU, int DEPTH, int NM>
 __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_tma(const __grid_constant__ GemvTmaParams p) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long s_bar[kWarps * DEPTH];
-    __shared__ float s_red[kWarps];
     __shared__ float s_ss[4 * kWarps];               // the warps' parts of Σx² per activation row (RMSNorm in the epilogue)
     // layout (from a 1024-byte boundary, which the swizzle pattern wants): code rings [warps][DEPTH][2048], scale rings
     // [warps][DEPTH][256], digits int8 [3M][K+pad], block scales fp32 [M][K/32], partials [2][warps][NM][16][8]
@@ -115,19 +114,12 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_tma(const __grid_consta
     for (int d = 0; d < kPre; d++) issue_next();
     pdl_launch_dependents();
     if (tracing) p.trace[1] = gtime();
-    // the norm's gain is a weight as well: fetch it before the wait when one round covers the row
-    const int nHalf = p.K >> 4;
-    const bool gammaEarly = p.gamma != nullptr && (GPT ? nHalf <= kThreads : nGroups <= 4 * kWarps) &&
-                            (reinterpret_cast<uintptr_t>(p.gamma) & 15) == 0;
-    float gpre[16];
+    // the norm's gain is a weight as well: fetch it before the wait when four groups per warp cover the row
+    const bool gammaEarly = p.gamma != nullptr && nGroups <= 4 * kWarps && (reinterpret_cast<uintptr_t>(p.gamma) & 15) == 0;
     float4 gpre4[4];
 #pragma unroll
-    for (int j = 0; j < 16; j++) gpre[j] = 1.0f;
-#pragma unroll
     for (int j = 0; j < 4; j++) gpre4[j] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-    if (GPT) {
-        if (gammaEarly && tid < nHalf) load16(p.gamma + tid * 16, true, gpre);
-    } else if (gammaEarly) {
+    if (gammaEarly) {
 #pragma unroll
         for (int j = 0; j < 4; j++)
             if (warp + kWarps * j < nGroups) gpre4[j] = gemv_load4(p.gamma + (warp + kWarps * j) * 128 + lane * 4, true);
@@ -136,20 +128,12 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_tma(const __grid_consta
     if (tracing) p.trace[2] = gtime();
 
     // activations → digit columns in the MMA fragment's order; the rest of the ring is queued behind the first loads.
-    // Llama / DeepSeek: every warp converts the groups it consumes and goes on by itself, RMSNorm's 1/rms is applied
-    // in the epilogue.  GPT: LayerNorm needs the row's mean first, so the CTA stages the rows together.
-    if (GPT) {
-        gemv_stage_rows<GPT, true>(p.x, p.ldx, p.gamma, p.beta, p.eps, p.K, p.M, xd, ldxs, xsc, s_red, gpre, gammaEarly, [&]() {
-            for (int d = kPre; d < DEPTH - 1; d++) issue_next();
-        });
-        __syncthreads();
-    } else {
-        gemv_stage_warp_groups(p.x, p.ldx, p.gamma, p.K, p.M, xd, ldxs, xsc, s_ss, gpre4, gammaEarly, [&]() {
-            for (int d = kPre; d < DEPTH - 1; d++) issue_next();
-        });
-        if (warp >= nGroups) {                               // a warp without groups still owes the ring its issue slots
-            for (int d = kPre; d < DEPTH - 1; d++) issue_next();
-        }
+    // Every warp converts the groups it consumes and goes on by itself; RMSNorm's 1/rms is applied in the epilogue.
+    gemv_stage_warp_groups(p.x, p.ldx, p.gamma, p.K, p.M, xd, ldxs, xsc, s_ss, gpre4, gammaEarly, [&]() {
+        for (int d = kPre; d < DEPTH - 1; d++) issue_next();
+    });
+    if (warp >= nGroups) {                               // a warp without groups still owes the ring its issue slots
+        for (int d = kPre; d < DEPTH - 1; d++) issue_next();
     }
     if (tracing) p.trace[3] = gtime();
 
@@ -219,9 +203,9 @@ __global__ void __launch_bounds__(kThreads, 2) k_q8_gemv_tma(const __grid_consta
             cslot = cslot + 1 == DEPTH ? 0 : cslot + 1;
         }
         if (tracing && tile == blockIdx.x) p.trace[4] = gtime();
-        gemv_tile_epilogue<SWIGLU, GPT, NM>(acc, s_part + (size_t)buf * kWarps * NM * 128, tile, p.M, p.N, eo, p.bias != nullptr,
-                                            p.bias2 != nullptr, p.residual != nullptr, p.act, p.out, p.ldo,
-                                            (!GPT && p.gamma) ? s_ss : nullptr, p.eps, p.K);
+        gemv_tile_epilogue<SWIGLU, false, NM>(acc, s_part + (size_t)buf * kWarps * NM * 128, tile, p.M, p.N, eo, p.bias != nullptr,
+                                            p.bias2 != nullptr, p.residual != nullptr, 0, p.out, p.ldo,
+                                            p.gamma ? s_ss : nullptr, p.eps, p.K);
         buf ^= 1;
     }
     if (tracing) p.trace[5] = gtime();
@@ -234,11 +218,11 @@ size_t tma_smem_bytes(int K, int M, int depth) {
 }
 constexpr size_t kSmemBudget = 112 * 1024;       // two CTAs per SM
 
-template <bool SWIGLU, int DEPTH, bool GPT, int NM>
+template <bool SWIGLU, int DEPTH, int NM>
 void launch_tma(const GemvTmaParams& p, cudaStream_t s) {
     static bool attrSet = false;
     if (!attrSet) {
-        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemv_tma<SWIGLU, DEPTH, GPT, NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+        DJ_CUDA_CHECK(cudaFuncSetAttribute(k_q8_gemv_tma<SWIGLU, DEPTH, NM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
         attrSet = true;
     }
     const int rowsPerTile = SWIGLU ? 8 : 16;
@@ -248,7 +232,7 @@ void launch_tma(const GemvTmaParams& p, cudaStream_t s) {
     const int cap = 2 * g_num_sms;
     const int rounds = (nTiles + cap - 1) / cap;
     const int gx = (nTiles + rounds - 1) / rounds;
-    launch_k(k_q8_gemv_tma<SWIGLU, DEPTH, GPT, NM>, dim3(gx), dim3(kThreads), tma_smem_bytes(p.K, p.M, DEPTH), s, true, p);
+    launch_k(k_q8_gemv_tma<SWIGLU, DEPTH, NM>, dim3(gx), dim3(kThreads), tma_smem_bytes(p.K, p.M, DEPTH), s, true, p);
 }
 
 }  // namespace
@@ -300,17 +284,20 @@ bool q8_encode_weight_maps(const Q8View& w, CUtensorMap* codes, CUtensorMap* sca
     return true;
 }
 
-// Returns false when the shape is outside this kernel's domain (K a multiple of 128, rows of at most 12288
-// values when a LayerNorm is fused, a ring of at least three items beside the digits); the caller then takes
-// the cp.async kernel.
+// Returns false when the shape is outside this kernel's domain (K a multiple of 128, no LayerNorm / GELU, the
+// digits of all rows of the call — up to four — beside the ring in shared memory); the caller then takes the cp.async
+// kernel.
 bool launch_q8_gemv_tma(const Q8LinearArgs& a, cudaStream_t s) {
     const int K = a.w.K;
     if (K % kItemK != 0 || a.w.Kp != K || g_dev_error == nullptr) return false;
     const bool swiglu = a.w2.codes != nullptr;
-    const bool gpt = a.beta != nullptr || a.act != 0;
-    if (gpt && (swiglu || (K >> 4) > kGemvStageRounds * kThreads)) return false;
+    // LayerNorm needs the row's mean before any digit, i.e. CTA-wide staging: the cp.async kernel has it (and measured
+    // 1.5 % faster per GPT-2 XL token than this kernel with the same staging)
+    if (a.beta != nullptr || a.act != 0) return false;
     if (swiglu && (a.w2.K != K || a.w2.Kp != K || a.w2.N != a.w.N)) return false;
-    if (tma_smem_bytes(K, 1, kDepth) > kSmemBudget) return false;
+    // all rows (up to four) in one pass, or not at all: where the digits of the rows do not fit beside the ring, the
+    // cp.async kernel with its smaller ring items takes them in fewer passes
+    if (tma_smem_bytes(K, a.M < 4 ? a.M : 4, kDepth) > kSmemBudget) return false;
     GemvTmaParams p;
     if (!q8_encode_weight_maps(a.w, &p.codes, &p.scales)) return false;
     if (swiglu) {
@@ -322,7 +309,6 @@ bool launch_q8_gemv_tma(const Q8LinearArgs& a, cudaStream_t s) {
         int rows = a.M - m0 < 4 ? a.M - m0 : 4;      // 8 MMA columns = 2 activation rows × (3 digits + 1 unused); 3-4 rows take a second MMA
         while (rows > 1 && tma_smem_bytes(K, rows, kDepth) > kSmemBudget) rows--;
         p.x = a.x + (size_t)m0 * a.ldx; p.ldx = a.ldx; p.gamma = a.gamma; p.eps = a.eps;
-        p.beta = a.beta; p.act = a.act;
         p.bias = a.bias; p.bias2 = a.bias2;
         p.residual = a.residual ? a.residual + (size_t)m0 * a.ldr : nullptr; p.ldr = a.ldr;
         p.out = a.out + (size_t)m0 * a.ldo; p.ldo = a.ldo;
@@ -331,13 +317,9 @@ bool launch_q8_gemv_tma(const Q8LinearArgs& a, cudaStream_t s) {
         p.error = g_dev_error;
         p.trace = trace_slot();
         if (rows > 2) {
-            if (swiglu) launch_tma<true, kDepth, false, 2>(p, s);
-            else if (gpt) launch_tma<false, kDepth, true, 2>(p, s);
-            else launch_tma<false, kDepth, false, 2>(p, s);
+            if (swiglu) launch_tma<true, kDepth, 2>(p, s); else launch_tma<false, kDepth, 2>(p, s);
         } else {
-            if (swiglu) launch_tma<true, kDepth, false, 1>(p, s);
-            else if (gpt) launch_tma<false, kDepth, true, 1>(p, s);
-            else launch_tma<false, kDepth, false, 1>(p, s);
+            if (swiglu) launch_tma<true, kDepth, 1>(p, s); else launch_tma<false, kDepth, 1>(p, s);
         }
         m0 += rows;
     }

@@ -1,6 +1,7 @@
-// Activation staging and tile epilogue shared by the two Q8 GEMV kernels (cp.async rings in q8_gemv_i8.cu,
-// TMA rings in q8_gemv_tma.cu): fp32 rows → three int8 digit columns + one power-of-two scale per 32-k block with
-// RMSNorm / LayerNorm fused, and the cross-warp reduction with bias / GELU / residual / SiLU-gate fused.
+// Activation staging and tile epilogue of the two Q8 GEMV kernels (cp.async rings in q8_gemv_i8.cu: CTA-wide
+// staging, RMSNorm / LayerNorm fused; TMA rings in q8_gemv_tma.cu: per-warp staging, RMSNorm split between staging and
+// epilogue): fp32 rows → three int8 digit columns + one power-of-two scale per 32-k block, and the cross-warp reduction
+// with bias / GELU / residual / SiLU-gate fused.
 #pragma once
 #include "q8_common.cuh"
 
@@ -29,8 +30,7 @@ __device__ __forceinline__ float gemv_block_sum(float v, float* s_red, int lane,
 // row costs one load round trip.  `after_first_loads` runs once, behind the first row's loads (the callers queue
 // more weight copies there).  GPT adds LayerNorm1D (norm/LayerNorm1D.java:34-71: mean, biased variance,
 // (x − mean)/√(var + eps)·γ + β); otherwise gamma != nullptr means RMSNorm1D (x / rms · γ).
-// PERM stores every 32-k block in the order the standard int8 MMA fragment reads it (see digits16).
-template <bool GPT, bool PERM, class F>
+template <bool GPT, class F>
 __device__ __forceinline__ void gemv_stage_rows(const float* x, int ldx, const float* gamma, const float* beta, float eps, int K, int M,
                                                 int8_t* xd, int ldxs, float* xsc, float* s_red, const float (&gpre)[16], bool gammaEarly,
                                                 F&& after_first_loads) {
@@ -105,7 +105,7 @@ __device__ __forceinline__ void gemv_stage_rows(const float* x, int ldx, const f
                         for (int j = 0; j < 16; j++) xv[r][j] += gv[j];
                     }
                 }
-                if (r < rounds) digits16<PERM>(xv[r], on, dcol, ldxs, hb, xscRow);
+                if (r < rounds) digits16(xv[r], on, dcol, ldxs, hb, xscRow);
             }
         } else {
             // very wide rows: one pass for the sum of squares, then round by round
@@ -135,7 +135,7 @@ __device__ __forceinline__ void gemv_stage_rows(const float* x, int ldx, const f
 #pragma unroll
                     for (int j = 0; j < 16; j++) xv[j] = (xv[j] * inv) * gv[j];
                 }
-                digits16<PERM>(xv, on, dcol, ldxs, hb, xscRow);
+                digits16(xv, on, dcol, ldxs, hb, xscRow);
             }
         }
     }
@@ -151,7 +151,9 @@ __device__ __forceinline__ float4 gemv_load4(const float* src, bool vec) {
 // block-wide barrier stands between the wait for the previous kernel and the first MMA.  RMSNorm is split: the gain
 // is folded into the digits (x·γ), the warp's part of Σx² goes to ss_part[m][warp], and the tile epilogue multiplies
 // the finished sums by 1/rms (Σ_k w_k·(x_k·γ_k)/rms = Σ_k w_k·(x_k/rms·γ_k)).  A lane converts four consecutive
-// values of a group; eight lanes share a 32-k block.  Digits are stored in the MMA fragment's order (digits16<true>).
+// values of a group; eight lanes share a 32-k block.  Digits are stored in the order of the int8 MMA's B fragment, so that
+// lane t fetches both of its registers (k = 4t … 4t+3 and k = 16+4t … 16+4t+3) with one 8-byte load at offset 8t: value k
+// of a block sits at 8·((k mod 16)/4) + 4·(k/16) + k mod 4.
 constexpr int kGemvWarpGroups = 12;         // groups a warp keeps in registers per load round trip: rows of up to 12288 values in one
 template <class F>
 __device__ __forceinline__ void gemv_stage_warp_groups(const float* x, int ldx, const float* gamma, int K, int M, int8_t* xd, int ldxs,

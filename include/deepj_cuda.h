@@ -83,7 +83,9 @@ int deepj_cuda_trace_read(uint64_t* out, int32_t max_launches, int32_t* n_launch
 
 /* counters[0]=kernel launches issued eagerly, [1]=graph replays, [2]=graphs
  * captured, [3]=kernel nodes in the last replayed graph, [4]=workspace bytes,
- * [5]=device-side error flag of bounded waits (0 = none). */
+ * [5]=device-side error flag of bounded waits (0 = none; 100 + rank: a tensor-parallel peer's data
+ * never arrived; 201-207: a barrier of the tensor-core GEMM; 300-312: the whole-token kernel's grid barrier
+ * or rings; 330 / 331: a bulk-copy item of the GEMV / several-row kernel never arrived). */
 int deepj_cuda_stats(int64_t* counters, int32_t n);
 
 /* Q8 weights.  Format (defined by this library; DeepJ has no quantization): for a
