@@ -95,7 +95,7 @@ bool launch_q8_linear_batch(const Q8LinearArgs& a, int m0, int rows, float* ws, 
 bool launch_q8_linear_batch_tma(const Q8LinearArgs& a, int m0, int rows, float* ws, int* tickets, cudaStream_t s);   // K a multiple of 128; same workspace
 size_t q8_batch_ws_floats(int K, int N, bool swiglu);
 bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s);
-size_t q8_tc_ws_floats(int M, int K);
+size_t q8_tc_ws_floats(int M, int K, int N);     // activation tiles, row scales and, when the reduction is split, the partial outputs
 double q8_tc_estimate_us(int M, int K, int N);
 constexpr int kTcMinRows = 17;            // from this many activation rows on, a Q8 linear runs on the tcgen05 path
 

@@ -359,7 +359,9 @@ void dispatch_q8_linear(const Q8LinearArgs& a, cudaStream_t s) {
     if (batchOk && a.M >= kTcMinRows && a.M <= 256) {
         const bool tmaKernel = g_gemv_mode == 2 && a.w.K % 128 == 0;
         const double perPassUs = tmaKernel ? 3.0 + 0.5e-6 * (double)a.w.K * (double)a.w.N : 0.9e-6 * (double)a.w.K * (double)a.w.N;
-        preferBatch = (double)((a.M + 15) / 16) * perPassUs < q8_tc_estimate_us(a.M, a.w.K, a.w.N);
+        const int rem = a.M % 16;
+        const double passes = (double)(a.M / 16) + (rem == 0 ? 0.0 : rem <= 8 ? 0.75 : 1.0);      // a last pass of up to eight rows issues half the MMAs
+        preferBatch = passes * perPassUs < q8_tc_estimate_us(a.M, a.w.K, a.w.N);
     }
     if (g_gemv_mode >= 1 && !noTc && !preferBatch && a.M >= kTcMinRows && a.ws != nullptr && launch_q8_linear_tc(a, a.ws, s)) return;
     if (batchOk) {

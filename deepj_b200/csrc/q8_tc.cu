@@ -203,6 +203,8 @@ struct TcParams {
     int mTiles;             // 128-row activation tiles
     int pair;               // 1: a CTA takes tiles 2·blockIdx.y and 2·blockIdx.y + 1 (the second may not exist), two accumulators; 0: tile blockIdx.y
     int mode;               // 0: out = acc + bias (+ residual);  1: out = SiLU(out) · (acc + bias)   (SwiGLU's second GEMM)
+    int ktPer;              // k-tiles per K split (blockIdx.z); a multiple of 4.  One split = the whole reduction
+    size_t splitStride;     // floats between the partial outputs of consecutive splits (0 when there is one split)
     int terms;              // correction products on top of x_hi · w_hi: bit 0 adds x_lo · w_hi, bit 1 adds x_hi · w_lo
     int* error;
     unsigned long long* trace;      // optional: thread 0 of CTA (0,0) sums the time it spends waiting / converting / fencing
@@ -220,7 +222,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     const bool has1 = p.pair && tile0 + 1 < p.mTiles;           // a second 128-row tile for the second accumulator
     const int nStA = p.pair ? kStagesA / 2 : kStagesA;          // activation stages in use, and their size
     const uint32_t stABytes = p.pair ? 2 * kAImageBytes : kAImageBytes;
-    const int nK = p.K / kTileK;
+    // K split blockIdx.z covers k-tiles kt0 … kt0 + nK − 1 of the nKfull of the reduction; everything below counts
+    // k-tiles from 0 within the split and only the global addresses know kt0
+    const int nKfull = p.K / kTileK;
+    const int kt0 = (int)blockIdx.z * p.ktPer;
+    const int nK = min(p.ktPer, nKfull - kt0);
+    const int8_t* const codes = p.codes + (size_t)kt0 * kTileK;
+    const float* const scales = p.scales + kt0;
+    float* const outp = p.out + (size_t)blockIdx.z * p.splitStride;
     // the swizzled tiles want 1024-byte alignment: the dynamic segment carries 1 KB of slack for it
     const uint32_t smem_raw = smem_u32(smem);
     const uint32_t smem_s = (smem_raw + 1023u) & ~1023u;
@@ -269,10 +278,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
             for (int i = 0; i < 8; i++) {
                 const int row = (tid >> 3) + 32 * i, c = tid & 7;
                 const int n = min(n0 + row, p.N - 1);
-                cp_async16(raw + row * kRawRow + c * 16, p.codes + (size_t)n * p.Kp + (size_t)G * 128 + c * 16);
+                cp_async16(raw + row * kRawRow + c * 16, codes + (size_t)n * p.Kp + (size_t)G * 128 + c * 16);
             }
             const int n = min(n0 + tid, p.N - 1);
-            cp_async16(raw + tid * kRawRow + 128, p.scales + (size_t)n * p.nb + (size_t)G * 4);
+            cp_async16(raw + tid * kRawRow + 128, scales + (size_t)n * p.nb + (size_t)G * 4);
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar_rawFull) : "memory");
         };
         issue_group(0);
@@ -389,7 +398,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
                 const int m = mbase + i;
                 if (!ok || m >= p.M || nn >= p.N) continue;
                 float val = stg[i * 33 + lane] + bv;
-                float* o = p.out + (size_t)m * p.ldo + nn;
+                float* o = outp + (size_t)m * p.ldo + nn;
                 if (p.mode == 0) {
                     if (p.residual) val += p.residual[(size_t)m * p.ldr + nn];
                     *o = val;
@@ -407,14 +416,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
     } else if (warp == kDqWarps) {
         // ── activation tiles: one bulk copy of 16 KB (hi + lo) per 128-row tile and stage ──
         if (lane == 0) {
-            const unsigned char* src = p.xtiles + (size_t)tile0 * nK * kAImageBytes;
+            const unsigned char* src = p.xtiles + ((size_t)tile0 * nKfull + kt0) * kAImageBytes;
             for (int kt = 0; kt < nK; kt++) {
                 const int s = kt % nStA;
                 if (kt >= nStA && !mbar_wait(bar_emptyA(s), ((kt / nStA) - 1) & 1, &s_abort, p.error, 203)) break;
                 mbar_arrive_expect_tx(bar_fullA(s), has1 ? 2 * kAImageBytes : kAImageBytes);
                 bulk_g2s(smem_s + (uint32_t)s * stABytes, src + (size_t)kt * kAImageBytes, kAImageBytes, bar_fullA(s));
                 if (has1)
-                    bulk_g2s(smem_s + (uint32_t)s * stABytes + kAImageBytes, src + (size_t)(nK + kt) * kAImageBytes, kAImageBytes, bar_fullA(s));
+                    bulk_g2s(smem_s + (uint32_t)s * stABytes + kAImageBytes, src + (size_t)(nKfull + kt) * kAImageBytes, kAImageBytes, bar_fullA(s));
             }
         }
         __syncwarp();
@@ -456,29 +465,81 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_q8_gemm_tc(const TcParams p) 
 
 constexpr size_t kTcSmem = (size_t)kARegionBytes + (size_t)kStagesB * kStageBBytes + (size_t)kTileN * kRawRow + 1024;
 
+// Adds the partial outputs of a K-split launch in split order and runs the epilogue that the GEMM kernel runs itself
+// when the reduction is not split: out = Σ + bias (+ residual), or out = SiLU(out) · (Σ + bias) for SwiGLU's second GEMM.
+__global__ void __launch_bounds__(256) k_q8_tc_split_reduce(const float* __restrict__ part, size_t splitStride, int splits, int M, int N,
+                                                            const float* __restrict__ bias, const float* __restrict__ residual, int ldr,
+                                                            float* __restrict__ out, int ldo, int mode) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t total = (size_t)M * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int m = (int)(i / N), n = (int)(i - (size_t)m * N);
+        float v = 0.0f;
+        for (int z = 0; z < splits; z++) v += __ldcg(part + (size_t)z * splitStride + i);
+        if (bias) v += bias[n];
+        float* o = out + (size_t)m * ldo + n;
+        if (mode == 0) {
+            if (residual) v += residual[(size_t)m * ldr + n];
+            *o = v;
+        } else {
+            const float gte = *o;
+            const float sig = 1.0f / (1.0f + expf(-gte));
+            *o = (gte * sig) * v;
+        }
+    }
+}
+
+// How a launch is laid out: CTAs take one 128-row tile or a pair, and when that leaves most SMs without a tile (a few
+// dozen to a few hundred rows) the reduction is split over up to four CTAs whose partial outputs a small kernel adds.
+struct TcPlan { bool pair; int splits, ktPer; long ctas; };
+TcPlan tc_plan(int M, int K, int N) {
+    const long mTiles = (M + kTileM - 1) / kTileM, nTiles = (N + kTileN - 1) / kTileN;
+    const int nK = K / kTileK;
+    // Two accumulators per CTA halve the conversion work per flop but also the number of CTAs, and a paired CTA
+    // takes 1.55–1.7 × as long as a single one: pair when the rounds of CTAs over the SMs it saves outweigh that.
+    const long single = nTiles * mTiles, paired = nTiles * ((mTiles + 1) / 2);
+    const long roundsSingle = (single + g_num_sms - 1) / g_num_sms, roundsPaired = (paired + g_num_sms - 1) / g_num_sms;
+    TcPlan pl;
+    pl.pair = mTiles >= 2 && 1.7 * (double)roundsPaired < (double)roundsSingle;
+    pl.ctas = pl.pair ? paired : single;
+    pl.splits = 1;
+    if (M <= 256 && 2 * pl.ctas <= g_num_sms) {
+        int sp = (int)(g_num_sms / pl.ctas);
+        if (sp > 4) sp = 4;
+        while (sp > 1 && nK / sp < 16) sp--;              // at least 16 k-tiles (512 k) per split
+        pl.splits = sp;
+    }
+    pl.ktPer = ((nK + pl.splits - 1) / pl.splits + 3) / 4 * 4;      // whole groups of four k-tiles (the raw-code buffer's unit)
+    pl.splits = (nK + pl.ktPer - 1) / pl.ktPer;
+    return pl;
+}
+
 }  // namespace
+
+int g_tc_terms = 3;
 
 // Rough duration of launch_q8_linear_tc in µs, for the choice between this path and passes of the 16-row kernel
 // when M is small: a CTA needs ≈ 0.75 µs per 32-k tile (1.2 µs when it carries two accumulators), CTAs run in
-// rounds over the SMs, and the activation pre-pass costs a few µs.
-int g_tc_terms = 3;
-
+// rounds over the SMs, the activation pre-pass costs a few µs, and a split reduction adds its small second kernel.
 double q8_tc_estimate_us(int M, int K, int N) {
-    const long mTiles = (M + kTileM - 1) / kTileM, nTiles = (N + kTileN - 1) / kTileN;
-    const long single = nTiles * mTiles, paired = nTiles * ((mTiles + 1) / 2);
-    const long roundsSingle = (single + g_num_sms - 1) / g_num_sms, roundsPaired = (paired + g_num_sms - 1) / g_num_sms;
-    const double perTile = 0.75 * (K / kTileK);
-    const double t = mTiles >= 2 && 1.7 * (double)roundsPaired < (double)roundsSingle ? 1.6 * perTile * roundsPaired : perTile * roundsSingle;
-    return t + 5.0;
+    const TcPlan pl = tc_plan(M, K, N);
+    const long rounds = (pl.ctas * pl.splits + g_num_sms - 1) / g_num_sms;
+    // 0.75 µs per k-tile measured with one wave of a few dozen CTAs, 0.95 µs with the ≈ 144 CTAs of a split launch
+    const double perCta = (pl.pair ? 1.2 : pl.splits > 1 ? 0.95 : 0.75) * pl.ktPer;
+    double t = perCta * rounds + 5.0;
+    if (pl.splits > 1) t += 4.0 + (double)pl.splits * M * N * 8.0 / 3.0e6;      // partial outputs written and read back at ≈ 3 TB/s
+    return t;
 }
 
-size_t q8_tc_ws_floats(int M, int K) {
+size_t q8_tc_ws_floats(int M, int K, int N) {
     const size_t mPad = (size_t)(M + kTileM - 1) / kTileM * kTileM;
-    return mPad * K + mPad;          // hi + lo halves = 4 bytes per value, then the row scales
+    const TcPlan pl = tc_plan(M, K, N);
+    return mPad * K + mPad + (pl.splits > 1 ? (size_t)pl.splits * M * N : 0);          // hi + lo halves = 4 bytes per value, the row scales, the splits' partial outputs
 }
 
 // out = x · W (+ fused norm / bias / residual / SiLU-gate) for M ≥ 1 rows on the tensor cores.
-// Returns false when the shape is outside the kernel's domain (K must be a multiple of 64).
+// Returns false when the shape is outside the kernel's domain (K must be a multiple of 128).
 bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s) {
     const int K = a.w.K, N = a.w.N, M = a.M;
     if (K % 128 != 0 || a.w.Kp != K || ws == nullptr || M < 1) return false;      // raw codes travel four k-tiles (and their 4 scales = 16 bytes) at a time
@@ -492,26 +553,33 @@ bool launch_q8_linear_tc(const Q8LinearArgs& a, float* ws, cudaStream_t s) {
     const size_t mPad = (size_t)mTiles * kTileM;
     unsigned char* tiles = reinterpret_cast<unsigned char*>(ws);
     float* rowscale = ws + mPad * K;
+    float* part = rowscale + mPad;
     launch_k(k_x_to_f16_tiles, dim3((unsigned)(mPad / 8)), dim3(256), 0, s, true, a.x, a.ldx, a.gamma, a.eps, M, K, tiles, rowscale);
-    // Two accumulators per CTA halve the conversion work per flop but also the number of CTAs, and a paired CTA
-    // takes 1.55–1.7 × as long as a single one: pair when the rounds of CTAs over the SMs it saves outweigh that.
-    const long single = (long)nTiles * mTiles, paired = (long)nTiles * ((mTiles + 1) / 2);
-    const long roundsSingle = (single + g_num_sms - 1) / g_num_sms, roundsPaired = (paired + g_num_sms - 1) / g_num_sms;
-    bool pair = mTiles >= 2 && 1.7 * (double)roundsPaired < (double)roundsSingle;
-    const dim3 grid(nTiles, pair ? (mTiles + 1) / 2 : mTiles);
+    const TcPlan pl = tc_plan(M, K, N);
+    const bool split = pl.splits > 1;
+    const dim3 grid(nTiles, pl.pair ? (mTiles + 1) / 2 : mTiles, pl.splits);
+    const int redBlocks = (int)(((size_t)M * N + 255) / 256 < (size_t)(4 * g_num_sms) ? ((size_t)M * N + 255) / 256 : (size_t)(4 * g_num_sms));
     TcParams p;
     p.xtiles = tiles; p.rowscale = rowscale;
-    p.codes = a.w.codes; p.scales = a.w.scales; p.bias = a.bias;
-    p.residual = a.residual; p.ldr = a.ldr;
-    p.out = a.out; p.ldo = a.ldo;
-    p.M = M; p.N = N; p.K = K; p.Kp = a.w.Kp; p.nb = a.w.nb; p.mTiles = mTiles; p.pair = pair ? 1 : 0;
-    p.mode = 0; p.terms = g_tc_terms; p.error = g_dev_error; p.trace = trace_slot();
-    launch_k(k_q8_gemm_tc, grid, dim3(kTcThreads), kTcSmem, s, true, p);
-    if (a.w2.codes != nullptr) {
-        // SwiGLU: the gate projection is in `out`; the up projection's epilogue multiplies SiLU(gate) into it
-        p.codes = a.w2.codes; p.scales = a.w2.scales; p.bias = a.bias2; p.residual = nullptr; p.mode = 1;
-        launch_k(k_q8_gemm_tc, grid, dim3(kTcThreads), kTcSmem, s, true, p);
-    }
+    p.M = M; p.N = N; p.K = K; p.Kp = a.w.Kp; p.nb = a.w.nb; p.mTiles = mTiles; p.pair = pl.pair ? 1 : 0;
+    p.ktPer = pl.ktPer; p.splitStride = split ? (size_t)M * N : 0;
+    p.terms = g_tc_terms; p.error = g_dev_error; p.trace = trace_slot();
+    auto run = [&](const Q8View& w, const float* bias, const float* residual, int mode) {
+        p.codes = w.codes; p.scales = w.scales;
+        if (split) {
+            // raw partial sums per split, the epilogue in the reduce kernel
+            p.bias = nullptr; p.residual = nullptr; p.ldr = 0; p.out = part; p.ldo = N; p.mode = 0;
+            launch_k(k_q8_gemm_tc, grid, dim3(kTcThreads), kTcSmem, s, true, p);
+            launch_k(k_q8_tc_split_reduce, dim3(redBlocks), dim3(256), 0, s, true, (const float*)part, p.splitStride, pl.splits, M, N, bias,
+                     residual, a.ldr, a.out, a.ldo, mode);
+        } else {
+            p.bias = bias; p.residual = residual; p.ldr = a.ldr; p.out = a.out; p.ldo = a.ldo; p.mode = mode;
+            launch_k(k_q8_gemm_tc, grid, dim3(kTcThreads), kTcSmem, s, true, p);
+        }
+    };
+    run(a.w, a.bias, a.residual, 0);
+    // SwiGLU: the gate projection is in `out`; the up projection's epilogue multiplies SiLU(gate) into it
+    if (a.w2.codes != nullptr) run(a.w2, a.bias2, nullptr, 1);
     return true;
 }
 

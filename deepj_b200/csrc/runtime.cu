@@ -309,7 +309,7 @@ void do_op(Ctx& ctx, const int32_t* c) {
             size_t need = 0;
             if (M >= 3) {
                 need = q8_batch_ws_floats(wb.K, wb.N, false);
-                if (M >= kTcMinRows) need = std::max(need, q8_tc_ws_floats(M, wb.K));
+                if (M >= kTcMinRows) need = std::max(need, q8_tc_ws_floats(M, wb.K, wb.N));
                 a.ws = R.ws; a.tickets = R.tickets;
             }
             if (ln) {
@@ -345,7 +345,7 @@ void do_op(Ctx& ctx, const int32_t* c) {
             a.M = M;
             if (M >= 3) {
                 size_t need = q8_batch_ws_floats(wg.K, wg.N, true);
-                if (M >= kTcMinRows) need = std::max(need, q8_tc_ws_floats(M, wg.K));
+                if (M >= kTcMinRows) need = std::max(need, q8_tc_ws_floats(M, wg.K, wg.N));
                 if (need > ctx.ws_need) ctx.ws_need = need;
                 a.ws = R.ws; a.tickets = R.tickets;
             }
