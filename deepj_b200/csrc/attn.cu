@@ -403,10 +403,76 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode_regs(
     };
     rotate(q, cs, sn);
 
-    // K and V slices of position p for this lane (zeros when the lane has no position)
-    auto fetch = [&](int p, bool valid, float (&kf)[16], float (&vf)[16]) {
-        if (valid && p == pos && append) {
-            // the new token: k and v come from the projections; rotate k, append both to the cache
+    // K or V slice of a cached position p for this lane (zeros when the lane has no position)
+    auto load_k = [&](int p, bool valid, float (&kx)[16]) {
+        if (valid) KvIo<KT>::ld16_stream(kbase + (size_t)p * HD, kx);
+        else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) kx[j] = 0.0f;
+        }
+    };
+    auto load_v = [&](int p, bool valid, float (&vx)[16]) {
+        if (valid) KvIo<KT>::ld16_stream(vbase + (size_t)p * HD, vx);
+        else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) vx[j] = 0.0f;
+        }
+    };
+
+    float m = -INFINITY, l = 0.0f, acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) acc[j] = 0.0f;
+    auto fold = [&](bool valid, float dot, const float (&vx)[16]) {
+#pragma unroll
+        for (int o = LPP / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (valid) {
+            const float s = dot * scale;
+            const float mn = fmaxf(m, s);
+            const float corr = expf(m - mn);
+            const float pe = expf(s - mn);
+            l = l * corr + pe;
+#pragma unroll
+            for (int j = 0; j < 16; j++) acc[j] = fmaf(pe, vx[j], acc[j] * corr);
+            m = mn;
+        }
+    };
+
+    // The cached rows: two groups of positions travel in two register sets.  A set's K registers are reloaded (two
+    // groups ahead) as soon as the dot product has read them, its V registers as soon as the accumulation has: between
+    // one and two groups of rows are in flight per warp at any time, with no register copies.  The new token's own
+    // position (the last one of the last split) is not in the cache yet and is folded in after the loop.
+    const bool ownsNew = append && pos >= start && pos < end;
+    const int endc = ownsNew ? pos : end;
+    int base = start + warp * PPW;
+    if (base < endc) {
+        const int p0 = base + group;
+        if (T > 1 || pos != specPos) {                                   // a prompt chunk, or a dropped speculation
+            load_k(p0, p0 < endc, kf);
+            load_v(p0, p0 < endc, vf);
+        }
+        if (base + G < endc) {
+            load_k(base + G + group, base + G + group < endc, kn);
+            load_v(base + G + group, base + G + group < endc, vn);
+        }
+    }
+    auto consume = [&](float (&kx)[16], float (&vx)[16], int at, int reload) {
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; j++) dot = fmaf(q[j], kx[j], dot);
+        if (reload < endc) load_k(reload + group, reload + group < endc, kx);
+        fold(at + group < endc, dot, vx);
+        if (reload < endc) load_v(reload + group, reload + group < endc, vx);
+    };
+    for (; base < endc; base += 2 * G) {
+        consume(kf, vf, base, base + 2 * G);
+        if (base + G >= endc) break;
+        consume(kn, vn, base + G, base + 3 * G);
+    }
+    if (ownsNew && warp == 0) {                                          // warp-uniform
+        // the new token: k and v come from the projections; k is rotated, both are appended to the cache, and this step
+        // attends to what later steps will read back (the rounded values of an fp16 cache).  Lane group 0 does it.
+        const bool mine = group == 0;
+        if (mine) {
             const float4* kp = reinterpret_cast<const float4*>(rowp + k_off + h * HD + gl * 16);
             const float4* vp = reinterpret_cast<const float4*>(rowp + v_off + h * HD + gl * 16);
 #pragma unroll
@@ -418,51 +484,15 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) k_attn_decode_regs(
             float ck[8], sk[8];              // fetched again here (a cache hit) rather than kept live through the loop
             load_tables(ck, sk);
             rotate(kf, ck, sk);
-            KvIo<KT>::st16(kbase + (size_t)p * HD, kf);
-            KvIo<KT>::st16(vbase + (size_t)p * HD, vf);
-            // this step attends to what later steps will read back (the rounded values of an fp16 cache)
+            KvIo<KT>::st16(kbase + (size_t)pos * HD, kf);
+            KvIo<KT>::st16(vbase + (size_t)pos * HD, vf);
 #pragma unroll
             for (int j = 0; j < 16; j++) { kf[j] = KvIo<KT>::stored(kf[j]); vf[j] = KvIo<KT>::stored(vf[j]); }
-        } else if (valid) {
-            KvIo<KT>::ld16_stream(kbase + (size_t)p * HD, kf);
-            KvIo<KT>::ld16_stream(vbase + (size_t)p * HD, vf);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; j++) { kf[j] = 0.0f; vf[j] = 0.0f; }
         }
-    };
-
-    float m = -INFINITY, l = 0.0f, acc[16];
-#pragma unroll
-    for (int j = 0; j < 16; j++) acc[j] = 0.0f;
-
-    // the loads of the next group of positions are in flight while this one is folded in
-    int base = start + warp * PPW;
-    if (base < end) {
-        const int p0 = base + group;
-        if (T > 1 || pos != specPos || (p0 == pos && p0 < end)) fetch(p0, p0 < end, kf, vf);      // the new token's lane, a prompt chunk, or a dropped speculation
-    }
-    for (; base < end; base += G) {
-        const bool valid = base + group < end;
-        const int nbase = base + G;
-        if (nbase < end) fetch(nbase + group, nbase + group < end, kn, vn);
         float dot = 0.0f;
 #pragma unroll
         for (int j = 0; j < 16; j++) dot = fmaf(q[j], kf[j], dot);
-#pragma unroll
-        for (int o = LPP / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (valid) {
-            const float s = dot * scale;
-            const float mn = fmaxf(m, s);
-            const float corr = expf(m - mn);
-            const float pe = expf(s - mn);
-            l = l * corr + pe;
-#pragma unroll
-            for (int j = 0; j < 16; j++) acc[j] = fmaf(pe, vf[j], acc[j] * corr);
-            m = mn;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; j++) { kf[j] = kn[j]; vf[j] = vn[j]; }
+        fold(mine, dot, vf);
     }
     const int g = warp * PPW + group;
 #pragma unroll
