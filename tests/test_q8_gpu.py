@@ -133,7 +133,10 @@ def oracle_rmsnorm(x, gamma):
                                    (1, 11008, 64), (1, 100, 33), (1, 512, 2048), (1, 5632, 128), (6, 512, 40), (4, 4096, 24), (1, 1376, 64), (2, 96, 20), (1, 2752, 33),
                                    (5, 1376, 200), (16, 4096, 512), (16, 96, 20), (7, 2752, 33), (40, 512, 300), (9, 11008, 64),
                                    (17, 256, 128), (64, 4096, 512), (130, 512, 300), (512, 2048, 256), (40, 96, 20), (300, 64, 8),
-                                   (257, 256, 128), (300, 512, 300), (640, 128, 520)])
+                                   (257, 256, 128), (300, 512, 300), (640, 128, 520),
+                                   # 17 … 128 rows at K = 4096: passes of the several-row kernel, then the split tensor-core form
+                                   (17, 4096, 768), (24, 4096, 4096), (32, 4096, 768), (48, 4096, 1024), (96, 4096, 768), (128, 4096, 1280),
+                                   (200, 11008, 512)])
 @pytest.mark.parametrize("fused", ["plain", "norm_bias_res"])
 def test_q8_linear_matches_oracle(dev, M, K, N, fused):
     rng = np.random.default_rng(K * 7 + N + M)
