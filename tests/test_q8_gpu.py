@@ -221,3 +221,26 @@ def test_tc_correction_terms_trade_bits_for_products(dev):
     assert errs[3] < 2e-5, errs
     assert all(errs[t] > 8 * errs[3] for t in (1, 2, 0)), errs
     assert errs[0] < 2e-3, errs
+
+
+@pytest.mark.parametrize("M,K,N,x_off", [(1, 256, 37, 101), (2, 1024, 50, 3), (1, 4096, 24, 7), (16, 512, 40, 5), (9, 1024, 21, 1)])
+def test_q8_linear_unaligned_rows_and_ragged_tiles(dev, M, K, N, x_off):
+    """Reduction lengths that take the TMA kernels, with activation rows that start off a 16-byte boundary (the staging
+    falls back to scalar loads), a gain vector, bias and residual, an output window inside a wider row, and a last
+    weight tile that is only partly there (the copy engine fills the missing rows with zeros)."""
+    rng = np.random.default_rng(1000 + M + K + N)
+    ldx, ldo, out_off = K + 2 * x_off + 3, N + 11, 5
+    xw = rng.standard_normal((M, ldx)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.03).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    out0 = rng.standard_normal((M, ldo)).astype(np.float32)
+    q = dev.q8(W)
+    xb, gb, bb, rb, ob = dev.buf(xw.size, xw), dev.buf(K, gamma), dev.buf(N, bias), dev.buf(M * N, res), dev.buf(out0.size, out0)
+    dev.flush([OP_Q8_LINEAR, xb, x_off, ldx, gb, float_bits(1e-6), q, bb, rb, 0, N, ob, out_off, ldo, M])
+    got = dev.get(ob, out0.size).reshape(M, ldo)
+    x = np.ascontiguousarray(xw[:, x_off:x_off + K])
+    expected = (oracle.matmul(oracle_rmsnorm(x, gamma), oracle.q8_dequantize(*oracle.q8_quantize(W))) + bias) + res
+    close(expected, got[:, out_off:out_off + N], floor=MANY_ROW_FLOOR if M >= 5 else 0.0)
+    assert np.array_equal(got[:, :out_off], out0[:, :out_off]) and np.array_equal(got[:, out_off + N:], out0[:, out_off + N:])
