@@ -38,7 +38,7 @@ namespace {
 constexpr int kMaxWorld = 8;
 constexpr int kTpCtas = 32;                   // CTAs of a decode-sized exchange (one pass for one sequence, eight for sixteen)
 constexpr int kTpCtasLarge = 296;             // CTAs of a chunk-sized exchange (a fixed number: the per-CTA counters depend on it)
-constexpr long kTpLargePairs = 1L << 16;      // messages above 2^17 floats take the large grid
+constexpr long kTpLargePairs = 1L << 14;      // messages above 2^15 floats take the large grid (16 sequences of a 4096-wide model: 2.73 → 2.80 k tokens/s at 2 GPUs against a threshold of 2^17)
 constexpr unsigned kTpSpinLimit = 1u << 21;   // polls of one word (≈ a second), then give up
 long g_large_pairs = kTpLargePairs;           // deepj_cuda_tp_configure; the same on every rank
 
@@ -197,7 +197,7 @@ using namespace dj;
 extern "C" {
 
 // The message size (in floats per rank) above which an exchange takes the chunk-sized grid and its own slot
-// region.  Call before tp_create, with the same value on every rank; 0 restores the default (2^17).
+// region.  Call before tp_create, with the same value on every rank; 0 restores the default (2^15).
 int deepj_cuda_tp_configure(int64_t large_message_floats) {
     try {
         if (T.local) throw std::runtime_error("tp_configure: call before tp_create");

@@ -153,7 +153,7 @@ int deepj_cuda_decode_plan(int32_t plan_id, const int32_t* desc, int32_t len);
  * deepj_cuda_clear_device_error() zeroes counter [5] again. */
 int deepj_cuda_tp_create(int32_t rank, int32_t world, int64_t slot_floats, void* handle_out64);
 /* Optional, before tp_create and with the same value on every rank: the message size (floats per rank) above
- * which an exchange takes the chunk-sized grid and its own slot region; 0 = the default of 2^17. */
+ * which an exchange takes the chunk-sized grid and its own slot region; 0 = the default of 2^15. */
 int deepj_cuda_tp_configure(int64_t large_message_floats);
 int deepj_cuda_tp_connect(const void* handles, int32_t world);
 int deepj_cuda_tp_destroy(void);
