@@ -141,6 +141,12 @@ JNIEXPORT void JNICALL CUDA_NATIVE(nativeKvAlloc)(JNIEnv* env, jclass, jint kvId
     if (deepj_cuda_kv_alloc(kvId, layers, batch, heads, maxSeq, headDim) != 0) raise_last(env);
 }
 
+// The same cache with fp16 planes (keys rounded after the rotation, values rounded; fp32 arithmetic in every kernel).
+JNIEXPORT void JNICALL CUDA_NATIVE(nativeKvAllocF16)(JNIEnv* env, jclass, jint kvId, jint layers, jint batch, jint heads,
+                                                     jint maxSeq, jint headDim) {
+    if (deepj_cuda_kv_alloc_f16(kvId, layers, batch, heads, maxSeq, headDim) != 0) raise_last(env);
+}
+
 // Decode plan behind op 76 (the whole-token kernel): desc as deepj_cuda_decode_plan documents it.
 JNIEXPORT void JNICALL CUDA_NATIVE(nativeDecodePlan)(JNIEnv* env, jclass, jint planId, jintArray descArr, jint len) {
     int rc;

@@ -71,6 +71,11 @@ public final class CudaGpuRuntime implements GpuRuntime {
         CudaNative.nativeKvAlloc(kvId, layers, batch, heads, maxSeq, headDim);
     }
 
+    /** A K/V cache that stores fp16 (same op codes, half the cache bytes per step; logits within the Q8 tolerance of the fp32 cache). */
+    public void allocKvCacheF16(int kvId, int layers, int batch, int heads, int maxSeq, int headDim) {
+        CudaNative.nativeKvAllocF16(kvId, layers, batch, heads, maxSeq, headDim);
+    }
+
     /** Everything one batch-1 token step touches, resolved once; afterwards the stream {@code [76, planId, feedBack]} runs the step. */
     public void decodePlan(int planId, int[] desc) {
         CudaNative.nativeDecodePlan(planId, desc, desc.length);

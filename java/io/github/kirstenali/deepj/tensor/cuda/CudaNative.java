@@ -83,6 +83,9 @@ final class CudaNative {
     /** K and V planes of [layers][batch][heads][maxSeq][headDim] floats, zero-filled. */
     static native void nativeKvAlloc(int kvId, int layers, int batch, int heads, int maxSeq, int headDim);
 
+    /** The same cache with fp16 planes: keys rounded after the rotation, values rounded, fp32 arithmetic; half the K/V bytes per step. */
+    static native void nativeKvAllocF16(int kvId, int layers, int batch, int heads, int maxSeq, int headDim);
+
     /** Registers the plan object behind op 76 (one whole token step as one kernel); desc as include/deepj_cuda.h lists it. */
     static native void nativeDecodePlan(int planId, int[] desc, int len);
 

@@ -21,7 +21,7 @@ PREFIX = "Java_io_github_kirstenali_deepj_tensor_cuda_CudaNative_"
 JNI_ABORT = 2
 NATIVES = ["nativeAllocBuffers", "nativeUploadBuffer", "nativeDownloadBuffer", "nativeReleaseBuffers", "nativeFlushOps",
            "nativeFlushOpsAsync", "nativeSynchronize", "nativeInit", "nativeShutdown", "nativeQ8Alloc",
-           "nativeQ8QuantizeInto", "nativeKvAlloc", "nativeDecodePlan", "nativeStats", "nativeTpCreate", "nativeTpConnect", "nativeTpDestroy"]
+           "nativeQ8QuantizeInto", "nativeKvAlloc", "nativeKvAllocF16", "nativeDecodePlan", "nativeStats", "nativeTpCreate", "nativeTpConnect", "nativeTpDestroy"]
 
 
 @pytest.fixture(scope="module")
